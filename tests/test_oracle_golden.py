@@ -1,0 +1,106 @@
+"""The CPU oracle against the fixtures produced by the reference itself
+(tests/golden/make_golden.py).  Pins the oracle; needs no GPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bla_oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def load(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    out = {}
+    for k in z.files:
+        a = z[k]
+        out[k] = torch.from_numpy(a) if a.ndim else a.item()
+    return out
+
+
+def scale_of(g):
+    return None if g["scale"] < 0 else float(g["scale"])
+
+
+# The golden values were produced in fp32 by torch; the oracle runs in fp64.
+TOL = 2e-5
+
+
+def close(got, ref):
+    assert O.rel_l2(got, ref) < TOL, O.rel_l2(got, ref)
+
+
+@pytest.mark.parametrize("name", ["linear_attn_a", "linear_attn_b", "linear_attn_c"])
+def test_linear_attn(name):
+    g = load(name)
+    sc = scale_of(g)
+    close(O.linear_attn_fwd(g["q"], g["k"], g["v"], sc, g["eps"]), g["o"])
+    dq, dk, dv = O.linear_attn_bwd(g["q"], g["k"], g["v"], g["do"], sc, g["eps"])
+    close(dq, g["dq"]), close(dk, g["dk"]), close(dv, g["dv"])
+
+
+@pytest.mark.parametrize("name", ["decoupled_a", "decoupled_b"])
+def test_decoupled(name):
+    g = load(name)
+    sc = scale_of(g)
+    args = (g["q"], g["k"], g["q_rope"], g["k_rope"], g["v"])
+    close(O.decoupled_la_fwd(*args, sc, g["eps"]), g["o"])
+    dq, dk, dqr, dkr, dv = O.decoupled_la_bwd(*args, g["do"], sc, g["eps"])
+    close(dq, g["dq"]), close(dk, g["dk"]), close(dqr, g["dq_rope"])
+    close(dkr, g["dk_rope"]), close(dv, g["dv"])
+
+
+@pytest.mark.parametrize("name", ["simple_la_a", "simple_la_b"])
+def test_simple_la(name):
+    g = load(name)
+    sc = scale_of(g)
+    close(O.simple_la_fwd(g["q"], g["k"], g["v"], sc), g["o"])
+    dq, dk, dv = O.simple_la_bwd(g["q"], g["k"], g["v"], g["do"], sc)
+    close(dq, g["dq"]), close(dk, g["dk"]), close(dv, g["dv"])
+
+
+@pytest.mark.parametrize("name", ["varlen_a", "varlen_b", "varlen_c"])
+def test_varlen(name):
+    g = load(name)
+    sc = scale_of(g)
+    close(O.varlen_linear_attn_fwd(g["q"], g["k"], g["v"], g["cu_seqlens"], sc, g["eps"]), g["o"])
+    dq, dk, dv = O.varlen_linear_attn_bwd(g["q"], g["k"], g["v"], g["do"], g["cu_seqlens"], sc, g["eps"])
+    close(dq, g["dq"]), close(dk, g["dk"]), close(dv, g["dv"])
+
+
+@pytest.mark.parametrize("name", ["pisa_a", "pisa_b"])
+def test_pisa_forward(name):
+    g = load(name)
+    bs = int(g["block_size"])
+    qc, kc, vc, h = O.pisa_block_stats(g["q"], g["k"], g["v"], bs)
+    close(qc, g["qc"]), close(kc, g["kc"]), close(vc, g["vc"])
+    assert O.rel_l2(h, g["h"]) < 1e-4
+    # the selection: same set of blocks per query block
+    idx = O.pisa_select(qc, kc, g["scale"], g["density"])
+    assert torch.equal(idx.sort(-1).values, g["indices"].sort(-1).values)
+    o, _ = O.pisa_fwd(g["q"], g["k"], g["v"], g["density"], bs, g["scale"], indices=g["indices"])
+    assert O.rel_l2(o, g["o"]) < 1e-4
+
+
+def test_pisa_backward_matches_finite_differences():
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 1, 40, 8, dtype=torch.float64) for _ in range(3))
+    do = torch.randn(1, 1, 40, 8, dtype=torch.float64)
+    _, idx = O.pisa_fwd(q, k, v, 0.4, 8)
+    dq, dk, dv = O.pisa_bwd(q, k, v, do, idx, 8)
+
+    def loss(q_, k_, v_):
+        return (O.pisa_fwd(q_, k_, v_, 0.4, 8, indices=idx)[0] * do).sum().item()
+    h = 1e-6
+    for x, gx, name in ((q, dq, "q"), (k, dk, "k"), (v, dv, "v")):
+        for pos in [(0, 0, 3, 2), (0, 0, 39, 7), (0, 0, 17, 0)]:
+            xp, xm = x.clone(), x.clone()
+            xp[pos] += h
+            xm[pos] -= h
+            args_p = {"q": q, "k": k, "v": v}
+            args_m = dict(args_p)
+            args_p[name], args_m[name] = xp, xm
+            fd = (loss(args_p["q"], args_p["k"], args_p["v"]) - loss(args_m["q"], args_m["k"], args_m["v"])) / (2 * h)
+            assert abs(fd - gx[pos].item()) < 1e-5 * max(1.0, abs(fd)), (name, pos, fd, gx[pos].item())
