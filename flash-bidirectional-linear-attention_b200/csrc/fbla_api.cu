@@ -1,0 +1,288 @@
+// The C ABI of flash_bla_sm100: argument validation, kernel-path selection and the
+// per-operator entry points declared in include/flash_bla_sm100.h.  Every entry
+// point only enqueues kernels on the caller's stream.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "fbla_common.cuh"
+#include "tc_kernels.cuh"
+
+namespace fbla {
+static std::atomic<unsigned long long> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+}  // namespace fbla
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(FBLA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+enum OpKind { OP_LINEAR, OP_SIMPLE, OP_DECOUPLED, OP_VARLEN };
+
+// Validates the problem for one operator and resolves the kernel parameters.
+int resolve(const fbla_problem* p, OpKind op, fbla::KParams* kp) {
+    if (p == nullptr) return fail(FBLA_ERR_INVALID, "problem is NULL");
+    if (p->dtype != FBLA_F32 && p->dtype != FBLA_BF16 && p->dtype != FBLA_F16)
+        return fail(FBLA_ERR_INVALID, "dtype %d is not one of FBLA_F32/FBLA_BF16/FBLA_F16", p->dtype);
+    if (p->dk < 1 || p->dk > 128 || p->dv < 1 || p->dv > 128)
+        return fail(FBLA_ERR_UNSUPPORTED, "dk=%d, dv=%d: feature dims must be in [1, 128]", p->dk, p->dv);
+    if (p->heads < 1) return fail(FBLA_ERR_INVALID, "heads=%d must be positive", p->heads);
+    if (p->seq_len < 0) return fail(FBLA_ERR_INVALID, "seq_len=%lld is negative", (long long)p->seq_len);
+    if (p->norm_len < 0) return fail(FBLA_ERR_INVALID, "norm_len=%lld is negative", (long long)p->norm_len);
+    const bool want_norm = (op != OP_SIMPLE);
+    if ((p->normalize != 0) != want_norm)
+        return fail(FBLA_ERR_INVALID, "normalize=%d does not match this operator", p->normalize);
+    kp->heads = p->heads;
+    kp->dk = p->dk;
+    kp->dv = p->dv;
+    kp->seq_len = p->seq_len;
+    kp->scale = p->scale;
+    kp->eps = p->eps;
+    kp->normalize = p->normalize != 0;
+    kp->inv_norm = p->norm_len > 0 ? (float)(1.0 / (double)p->norm_len) : 0.f;
+    kp->state_stride = p->dk * p->dv + (kp->normalize ? p->dk : 0);
+    if (op == OP_VARLEN) {
+        if (p->cu_seqlens == nullptr) return fail(FBLA_ERR_INVALID, "cu_seqlens is NULL");
+        if (p->num_seqs < 1) return fail(FBLA_ERR_INVALID, "num_seqs=%d must be positive", p->num_seqs);
+        if (p->max_seqlen < 1) return fail(FBLA_ERR_INVALID, "max_seqlen=%d must be positive", p->max_seqlen);
+        if ((int64_t)p->num_seqs * p->heads > 0x7fffffffLL || p->seq_len * (int64_t)p->heads > (1LL << 40))
+            return fail(FBLA_ERR_UNSUPPORTED, "problem too large");
+        kp->cu = p->cu_seqlens;
+        kp->units = p->num_seqs * p->heads;
+        kp->max_len = p->max_seqlen;
+        kp->scale_per_seq = p->scale_per_seq != 0;
+    } else {
+        if (p->cu_seqlens != nullptr)
+            return fail(FBLA_ERR_INVALID, "cu_seqlens given to a fixed-length operator");
+        if (p->batch < 1) return fail(FBLA_ERR_INVALID, "batch=%d must be positive", p->batch);
+        if ((int64_t)p->batch * p->heads > 0x7fffffffLL || p->seq_len > 0x7fffffffLL)
+            return fail(FBLA_ERR_UNSUPPORTED, "problem too large");
+        kp->cu = nullptr;
+        kp->units = p->batch * p->heads;
+        kp->max_len = (int)p->seq_len;
+        kp->scale_per_seq = 0;
+    }
+    return FBLA_OK;
+}
+
+OpKind kind_of(const fbla_problem* p) {
+    if (p != nullptr && p->cu_seqlens != nullptr) return OP_VARLEN;
+    if (p != nullptr && !p->normalize) return OP_SIMPLE;
+    return OP_LINEAR;
+}
+
+bool use_tc(const fbla_problem* p, const fbla::KParams& kp) {
+    return !(p->flags & FBLA_FLAG_GENERIC) && fbla::tc_supported(kp, p->dtype);
+}
+
+int64_t workspace_need(const fbla_problem* p, const fbla::KParams& kp) {
+    return use_tc(p, kp) ? fbla::tc_workspace_bytes(kp) : fbla::simt_workspace_bytes(kp);
+}
+
+#define NOT_NULL(x) \
+    if ((x) == nullptr) return fail(FBLA_ERR_INVALID, #x " is NULL")
+
+int check_ws(const fbla_problem* p, const fbla::KParams& kp, void* ws, size_t ws_bytes) {
+    const int64_t need = workspace_need(p, kp);
+    if (need > 0 && (ws == nullptr || (int64_t)ws_bytes < need))
+        return fail(FBLA_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given", (long long)need,
+                    (long long)(ws ? ws_bytes : 0));
+    return FBLA_OK;
+}
+
+// Empty problems (no tokens, or no units) have nothing to launch, but the state must
+// still be defined for the caller.
+bool is_empty(const fbla::KParams& kp) { return kp.units == 0 || kp.seq_len == 0; }
+
+int fwd_state(const fbla_problem* p, OpKind op, const void* k, const void* k_rope, const void* v,
+              float* state, void* ws, size_t ws_bytes, fbla_stream_t stream) {
+    fbla::KParams kp;
+    if (int rc = resolve(p, op, &kp)) return rc;
+    NOT_NULL(state);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (is_empty(kp)) {
+        cudaError_t e = cudaMemsetAsync(state, 0, sizeof(float) * (size_t)kp.units * kp.state_stride, st);
+        return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "memset of the state");
+    }
+    NOT_NULL(k);
+    NOT_NULL(v);
+    if (int rc = check_ws(p, kp, ws, ws_bytes)) return rc;
+    cudaError_t e = use_tc(p, kp) ? fbla::tc_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st)
+                                  : fbla::simt_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st);
+    return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward state pass");
+}
+
+int fwd_out(const fbla_problem* p, OpKind op, const void* q, const void* q_rope, const float* state, void* o,
+            fbla_stream_t stream) {
+    fbla::KParams kp;
+    if (int rc = resolve(p, op, &kp)) return rc;
+    if (is_empty(kp)) return FBLA_OK;
+    NOT_NULL(q);
+    NOT_NULL(state);
+    NOT_NULL(o);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = use_tc(p, kp) ? fbla::tc_fwd_out(kp, p->dtype, q, q_rope, state, o, st)
+                                  : fbla::simt_fwd_out(kp, p->dtype, q, q_rope, state, o, st);
+    return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward output pass");
+}
+
+int bwd_state(const fbla_problem* p, OpKind op, const void* q, const void* q_rope, const void* d_o,
+              const float* state, void* dq, void* dq_rope, float* dstate, void* ws, size_t ws_bytes,
+              fbla_stream_t stream) {
+    fbla::KParams kp;
+    if (int rc = resolve(p, op, &kp)) return rc;
+    NOT_NULL(dstate);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (is_empty(kp)) {
+        cudaError_t e = cudaMemsetAsync(dstate, 0, sizeof(float) * (size_t)kp.units * kp.state_stride, st);
+        return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "memset of the state gradient");
+    }
+    NOT_NULL(q);
+    NOT_NULL(d_o);
+    NOT_NULL(state);
+    NOT_NULL(dq);
+    if (op == OP_DECOUPLED) {
+        NOT_NULL(q_rope);
+        NOT_NULL(dq_rope);
+    }
+    if (int rc = check_ws(p, kp, ws, ws_bytes)) return rc;
+    cudaError_t e = use_tc(p, kp)
+                        ? fbla::tc_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st)
+                        : fbla::simt_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st);
+    return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward state pass");
+}
+
+int bwd_in(const fbla_problem* p, OpKind op, const void* k_rope, const void* v, const float* dstate, void* dk,
+           void* dk_rope, void* dv, fbla_stream_t stream) {
+    fbla::KParams kp;
+    if (int rc = resolve(p, op, &kp)) return rc;
+    if (is_empty(kp)) return FBLA_OK;
+    NOT_NULL(k_rope);
+    NOT_NULL(v);
+    NOT_NULL(dstate);
+    NOT_NULL(dk);
+    NOT_NULL(dv);
+    if (op == OP_DECOUPLED) NOT_NULL(dk_rope);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = use_tc(p, kp) ? fbla::tc_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st)
+                                  : fbla::simt_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st);
+    return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward input pass");
+}
+
+}  // namespace
+
+extern "C" {
+
+int fbla_version(void) { return FBLA_ABI_VERSION; }
+
+const char* fbla_last_error(void) { return g_err; }
+
+uint64_t fbla_launch_count(void) { return fbla::g_launches.load(std::memory_order_relaxed); }
+
+int64_t fbla_state_floats(const fbla_problem* p) {
+    fbla::KParams kp;
+    if (resolve(p, kind_of(p), &kp)) return -1;
+    return (int64_t)kp.units * kp.state_stride;
+}
+
+int64_t fbla_workspace_bytes(const fbla_problem* p) {
+    fbla::KParams kp;
+    if (resolve(p, kind_of(p), &kp)) return -1;
+    if (is_empty(kp)) return 0;
+    return workspace_need(p, kp);
+}
+
+int fbla_kernel_path(const fbla_problem* p) {
+    fbla::KParams kp;
+    if (resolve(p, kind_of(p), &kp)) return -1;
+    return use_tc(p, kp) ? 1 : 0;
+}
+
+// ---- linear_attention ------------------------------------------------------------------
+int fbla_linear_attn_fwd_state(const fbla_problem* p, const void* k, const void* v, float* state, void* ws,
+                               size_t ws_bytes, fbla_stream_t s) {
+    return fwd_state(p, OP_LINEAR, k, nullptr, v, state, ws, ws_bytes, s);
+}
+int fbla_linear_attn_fwd_out(const fbla_problem* p, const void* q, const float* state, void* o,
+                             fbla_stream_t s) {
+    return fwd_out(p, OP_LINEAR, q, nullptr, state, o, s);
+}
+int fbla_linear_attn_bwd_state(const fbla_problem* p, const void* q, const void* d_o, const float* state,
+                               void* dq, float* dstate, void* ws, size_t ws_bytes, fbla_stream_t s) {
+    return bwd_state(p, OP_LINEAR, q, nullptr, d_o, state, dq, nullptr, dstate, ws, ws_bytes, s);
+}
+int fbla_linear_attn_bwd_in(const fbla_problem* p, const void* k, const void* v, const float* dstate, void* dk,
+                            void* dv, fbla_stream_t s) {
+    return bwd_in(p, OP_LINEAR, k, v, dstate, dk, nullptr, dv, s);
+}
+
+// ---- simple_la -------------------------------------------------------------------------
+int fbla_simple_la_fwd_state(const fbla_problem* p, const void* k, const void* v, float* state, void* ws,
+                             size_t ws_bytes, fbla_stream_t s) {
+    return fwd_state(p, OP_SIMPLE, k, nullptr, v, state, ws, ws_bytes, s);
+}
+int fbla_simple_la_fwd_out(const fbla_problem* p, const void* q, const float* state, void* o, fbla_stream_t s) {
+    return fwd_out(p, OP_SIMPLE, q, nullptr, state, o, s);
+}
+int fbla_simple_la_bwd_state(const fbla_problem* p, const void* q, const void* d_o, const float* state,
+                             void* dq, float* dstate, void* ws, size_t ws_bytes, fbla_stream_t s) {
+    return bwd_state(p, OP_SIMPLE, q, nullptr, d_o, state, dq, nullptr, dstate, ws, ws_bytes, s);
+}
+int fbla_simple_la_bwd_in(const fbla_problem* p, const void* k, const void* v, const float* dstate, void* dk,
+                          void* dv, fbla_stream_t s) {
+    return bwd_in(p, OP_SIMPLE, k, v, dstate, dk, nullptr, dv, s);
+}
+
+// ---- decoupled_la ----------------------------------------------------------------------
+int fbla_decoupled_la_fwd_state(const fbla_problem* p, const void* k, const void* k_rope, const void* v,
+                                float* state, void* ws, size_t ws_bytes, fbla_stream_t s) {
+    if (k_rope == nullptr) return fail(FBLA_ERR_INVALID, "k_rope is NULL");
+    return fwd_state(p, OP_DECOUPLED, k, k_rope, v, state, ws, ws_bytes, s);
+}
+int fbla_decoupled_la_fwd_out(const fbla_problem* p, const void* q, const void* q_rope, const float* state,
+                              void* o, fbla_stream_t s) {
+    if (q_rope == nullptr) return fail(FBLA_ERR_INVALID, "q_rope is NULL");
+    return fwd_out(p, OP_DECOUPLED, q, q_rope, state, o, s);
+}
+int fbla_decoupled_la_bwd_state(const fbla_problem* p, const void* q, const void* q_rope, const void* d_o,
+                                const float* state, void* dq, void* dq_rope, float* dstate, void* ws,
+                                size_t ws_bytes, fbla_stream_t s) {
+    return bwd_state(p, OP_DECOUPLED, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, ws_bytes, s);
+}
+int fbla_decoupled_la_bwd_in(const fbla_problem* p, const void* k_rope, const void* v, const float* dstate,
+                             void* dk, void* dk_rope, void* dv, fbla_stream_t s) {
+    return bwd_in(p, OP_DECOUPLED, k_rope, v, dstate, dk, dk_rope, dv, s);
+}
+
+// ---- varlen_linear_attention -----------------------------------------------------------
+int fbla_varlen_linear_attn_fwd_state(const fbla_problem* p, const void* k, const void* v, float* state,
+                                      void* ws, size_t ws_bytes, fbla_stream_t s) {
+    return fwd_state(p, OP_VARLEN, k, nullptr, v, state, ws, ws_bytes, s);
+}
+int fbla_varlen_linear_attn_fwd_out(const fbla_problem* p, const void* q, const float* state, void* o,
+                                    fbla_stream_t s) {
+    return fwd_out(p, OP_VARLEN, q, nullptr, state, o, s);
+}
+int fbla_varlen_linear_attn_bwd_state(const fbla_problem* p, const void* q, const void* d_o, const float* state,
+                                      void* dq, float* dstate, void* ws, size_t ws_bytes, fbla_stream_t s) {
+    return bwd_state(p, OP_VARLEN, q, nullptr, d_o, state, dq, nullptr, dstate, ws, ws_bytes, s);
+}
+int fbla_varlen_linear_attn_bwd_in(const fbla_problem* p, const void* k, const void* v, const float* dstate,
+                                   void* dk, void* dv, fbla_stream_t s) {
+    return bwd_in(p, OP_VARLEN, k, v, dstate, dk, nullptr, dv, s);
+}
+
+}  // extern "C"

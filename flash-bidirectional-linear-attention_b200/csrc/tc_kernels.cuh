@@ -1,0 +1,21 @@
+// Launchers of the tensor-core path (tcgen05 MMA with TMEM accumulators, operands
+// staged by TMA): 16-bit inputs with dk, dv in {64, 128}.
+#pragma once
+
+#include "fbla_common.cuh"
+
+namespace fbla {
+
+bool tc_supported(const KParams& p, int dtype);
+int64_t tc_workspace_bytes(const KParams& p);
+cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
+                         float* state, void* ws, cudaStream_t st);
+cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q, const void* q_rope, const float* state,
+                       void* o, cudaStream_t st);
+cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q, const void* q_rope, const void* d_o,
+                         const float* state, void* dq, void* dq_rope, float* dstate, void* ws,
+                         cudaStream_t st);
+cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const void* v, const float* dstate,
+                      void* dk, void* dk_rope, void* dv, cudaStream_t st);
+
+}  // namespace fbla

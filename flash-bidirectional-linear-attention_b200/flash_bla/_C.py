@@ -1,0 +1,121 @@
+"""ctypes binding of libflash_bla_sm100.so (the C ABI in include/flash_bla_sm100.h).
+
+There is no fallback: if the shared library has not been built, or a call fails,
+an exception is raised.
+"""
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libflash_bla_sm100.so")
+
+F32, BF16, F16 = 0, 1, 2
+FLAG_GENERIC = 1
+
+_DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+
+class Problem(ctypes.Structure):
+    """Mirror of ``struct fbla_problem``."""
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("dk", ctypes.c_int32),
+        ("dv", ctypes.c_int32),
+        ("seq_len", ctypes.c_int64),
+        ("norm_len", ctypes.c_int64),
+        ("cu_seqlens", ctypes.c_void_p),
+        ("num_seqs", ctypes.c_int32),
+        ("max_seqlen", ctypes.c_int32),
+        ("scale", ctypes.c_float),
+        ("scale_per_seq", ctypes.c_int32),
+        ("eps", ctypes.c_float),
+        ("normalize", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
+    ]
+
+
+_P = ctypes.POINTER(Problem)
+_vp = ctypes.c_void_p
+_sz = ctypes.c_size_t
+
+# name -> argument types after the leading ``const fbla_problem*``
+_SIGNATURES = {
+    "fwd_state": [_vp, _vp, _vp, _vp, _sz, _vp],                 # k, v, state, ws, ws_bytes, stream
+    "fwd_out": [_vp, _vp, _vp, _vp],                             # q, state, o, stream
+    "bwd_state": [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp],       # q, d_o, state, dq, dstate, ws, n, stream
+    "bwd_in": [_vp, _vp, _vp, _vp, _vp, _vp],                    # k, v, dstate, dk, dv, stream
+}
+_DECOUPLED_SIGNATURES = {
+    "fwd_state": [_vp, _vp, _vp, _vp, _vp, _sz, _vp],            # k, k_rope, v, state, ws, n, stream
+    "fwd_out": [_vp, _vp, _vp, _vp, _vp],                        # q, q_rope, state, o, stream
+    "bwd_state": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp],
+    "bwd_in": [_vp, _vp, _vp, _vp, _vp, _vp, _vp],               # k_rope, v, dstate, dk, dk_rope, dv, stream
+}
+OPS = ("linear_attn", "simple_la", "decoupled_la", "varlen_linear_attn")
+
+_lib = None
+_lock = threading.Lock()
+
+
+def exported_symbols():
+    """Every symbol include/flash_bla_sm100.h declares."""
+    names = ["fbla_version", "fbla_last_error", "fbla_launch_count", "fbla_state_floats",
+             "fbla_workspace_bytes", "fbla_kernel_path"]
+    for op in OPS:
+        names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
+    return names
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python build.py` in the package root "
+                "(flash_bla has no CPU or Triton fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        L.fbla_version.restype = ctypes.c_int
+        L.fbla_last_error.restype = ctypes.c_char_p
+        L.fbla_launch_count.restype = ctypes.c_uint64
+        for n in ("fbla_state_floats", "fbla_workspace_bytes"):
+            getattr(L, n).restype = ctypes.c_int64
+            getattr(L, n).argtypes = [_P]
+        L.fbla_kernel_path.restype = ctypes.c_int
+        L.fbla_kernel_path.argtypes = [_P]
+        for op in OPS:
+            sigs = _DECOUPLED_SIGNATURES if op == "decoupled_la" else _SIGNATURES
+            for name, args in sigs.items():
+                f = getattr(L, f"fbla_{op}_{name}")
+                f.restype = ctypes.c_int
+                f.argtypes = [_P] + args
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise RuntimeError(f"flash_bla_sm100 error {rc}: {lib().fbla_last_error().decode()}")
+
+
+def dtype_code(dtype):
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise TypeError(f"dtype {dtype} is not supported (float16, bfloat16, float32)") from None
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t):
+    return torch.cuda.current_stream(t.device).cuda_stream

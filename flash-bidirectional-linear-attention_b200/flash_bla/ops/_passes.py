@@ -1,0 +1,143 @@
+"""The four streaming passes every operator is built from, as thin Python calls
+into the C ABI.  Tensors are allocated by torch (caching allocator, current
+stream); the library only enqueues kernels.
+
+    forward :  state = fwd_state(k, v)            [S = K^T V | sum k]   fp32
+               o     = fwd_out(q, state)
+    backward:  dq, dstate = bwd_state(q, dO, state)
+               dk, dv     = bwd_in(k, v, dstate)
+
+A caller that shards the sequence over ranks all-reduces ``state`` / ``dstate``
+between the two passes (see ``flash_bla.ops.sharded``).
+"""
+import ctypes
+
+import torch
+
+from flash_bla import _C
+
+
+def make_problem(like, *, batch, heads, seq_len, dk, dv, normalize, scale=1.0, eps=0.0, norm_len=0,
+                 cu_seqlens=None, num_seqs=0, max_seqlen=0, scale_per_seq=False, flags=0):
+    p = _C.Problem()
+    p.dtype = _C.dtype_code(like.dtype)
+    p.batch, p.heads, p.dk, p.dv = int(batch), int(heads), int(dk), int(dv)
+    p.seq_len, p.norm_len = int(seq_len), int(norm_len)
+    p.cu_seqlens = None if cu_seqlens is None else cu_seqlens.data_ptr()
+    p.num_seqs, p.max_seqlen = int(num_seqs), int(max_seqlen)
+    p.scale = float(scale)
+    p.scale_per_seq = int(bool(scale_per_seq))
+    p.eps = float(eps)
+    p.normalize = int(bool(normalize))
+    p.flags = int(flags)
+    return p
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("flash_bla operators run on CUDA tensors only (there is no CPU path)")
+
+
+def _workspace(prob, like):
+    n = _C.lib().fbla_workspace_bytes(ctypes.byref(prob))
+    if n < 0:
+        _C.check(1)
+    if n == 0:
+        return None, 0
+    return torch.empty(n, dtype=torch.uint8, device=like.device), n
+
+
+def _state_like(prob, like):
+    n = _C.lib().fbla_state_floats(ctypes.byref(prob))
+    if n < 0:
+        _C.check(1)
+    return torch.empty(n, dtype=torch.float32, device=like.device)
+
+
+def fwd_state(op, prob, k, v, k_rope=None):
+    _require_cuda(k, v, k_rope)
+    L = _C.lib()
+    with torch.cuda.device_of(k):
+        state = _state_like(prob, k)
+        ws, n = _workspace(prob, k)
+        f = getattr(L, f"fbla_{op}_fwd_state")
+        if op == "decoupled_la":
+            rc = f(ctypes.byref(prob), _C.ptr(k), _C.ptr(k_rope), _C.ptr(v), _C.ptr(state), _C.ptr(ws), n,
+                   _C.stream_of(k))
+        else:
+            rc = f(ctypes.byref(prob), _C.ptr(k), _C.ptr(v), _C.ptr(state), _C.ptr(ws), n, _C.stream_of(k))
+    _C.check(rc)
+    return state
+
+
+def fwd_out(op, prob, q, state, o, q_rope=None):
+    _require_cuda(q, state, o, q_rope)
+    L = _C.lib()
+    with torch.cuda.device_of(q):
+        f = getattr(L, f"fbla_{op}_fwd_out")
+        if op == "decoupled_la":
+            rc = f(ctypes.byref(prob), _C.ptr(q), _C.ptr(q_rope), _C.ptr(state), _C.ptr(o), _C.stream_of(q))
+        else:
+            rc = f(ctypes.byref(prob), _C.ptr(q), _C.ptr(state), _C.ptr(o), _C.stream_of(q))
+    _C.check(rc)
+    return o
+
+
+def bwd_state(op, prob, q, d_o, state, dq, q_rope=None, dq_rope=None):
+    _require_cuda(q, d_o, state, dq, q_rope, dq_rope)
+    L = _C.lib()
+    with torch.cuda.device_of(q):
+        dstate = _state_like(prob, q)
+        ws, n = _workspace(prob, q)
+        f = getattr(L, f"fbla_{op}_bwd_state")
+        if op == "decoupled_la":
+            rc = f(ctypes.byref(prob), _C.ptr(q), _C.ptr(q_rope), _C.ptr(d_o), _C.ptr(state), _C.ptr(dq),
+                   _C.ptr(dq_rope), _C.ptr(dstate), _C.ptr(ws), n, _C.stream_of(q))
+        else:
+            rc = f(ctypes.byref(prob), _C.ptr(q), _C.ptr(d_o), _C.ptr(state), _C.ptr(dq), _C.ptr(dstate),
+                   _C.ptr(ws), n, _C.stream_of(q))
+    _C.check(rc)
+    return dstate
+
+
+def bwd_in(op, prob, k, v, dstate, dk, dv, dk_rope=None):
+    """``k`` is the key tensor the state was built from (k_rope when decoupled)."""
+    _require_cuda(k, v, dstate, dk, dv, dk_rope)
+    L = _C.lib()
+    with torch.cuda.device_of(k):
+        f = getattr(L, f"fbla_{op}_bwd_in")
+        if op == "decoupled_la":
+            rc = f(ctypes.byref(prob), _C.ptr(k), _C.ptr(v), _C.ptr(dstate), _C.ptr(dk), _C.ptr(dk_rope),
+                   _C.ptr(dv), _C.stream_of(k))
+        else:
+            rc = f(ctypes.byref(prob), _C.ptr(k), _C.ptr(v), _C.ptr(dstate), _C.ptr(dk), _C.ptr(dv),
+                   _C.stream_of(k))
+    _C.check(rc)
+
+
+def kernel_path(prob):
+    """1 when the tensor-core kernels serve ``prob``, 0 for the CUDA-core kernels."""
+    return _C.lib().fbla_kernel_path(ctypes.byref(prob))
+
+
+# Kernel-path override used by tests and benchmarks: inside ``generic_kernels()`` the
+# CUDA-core kernels serve every call, whatever the shape.
+_default_flags = 0
+
+
+class generic_kernels:
+    def __enter__(self):
+        global _default_flags
+        self._saved = _default_flags
+        _default_flags = _C.FLAG_GENERIC
+        return self
+
+    def __exit__(self, *exc):
+        global _default_flags
+        _default_flags = self._saved
+        return False
+
+
+def default_flags():
+    return _default_flags

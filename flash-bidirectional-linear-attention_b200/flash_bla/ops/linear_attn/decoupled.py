@@ -1,0 +1,78 @@
+"""Decoupled bidirectional linear attention: the numerator uses the rotary
+q_rope / k_rope, the normaliser the plain q / k.
+
+    S = K_rope^T (V * scale),  kmean = mean_t K,  O = Q_rope S / (Q . kmean + eps)
+
+Same public surface as the reference module
+``flash_bla/ops/linear_attn/decoupled.py`` (``DecoupledLAFunction`` :411-509,
+``decoupled_la`` :512-542).
+"""
+from typing import Optional
+
+import torch
+
+from flash_bla.ops import _passes as P
+from flash_bla.utils import contiguous
+
+_OP = "decoupled_la"
+
+
+def _problem(q, v, scale, eps, norm_len=0):
+    B, H, L, K = q.shape
+    return P.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
+                          scale=scale, eps=eps, norm_len=norm_len, flags=P.default_flags())
+
+
+def _check(q, k, q_rope, k_rope, v):
+    if q.dim() != 4 or v.dim() != 4 or any(x.shape != q.shape for x in (k, q_rope, k_rope)) \
+            or v.shape[:3] != q.shape[:3]:
+        raise ValueError("expected q, k, q_rope, k_rope of shape (B, H, L, K) and v of shape (B, H, L, V)")
+    if not (q.dtype == k.dtype == q_rope.dtype == k_rope.dtype == v.dtype):
+        raise ValueError("all inputs must have the same dtype")
+
+
+class DecoupledLAFunction(torch.autograd.Function):
+
+    @staticmethod
+    @contiguous
+    def forward(ctx, q, k, q_rope, k_rope, v, scale, eps):
+        _check(q, k, q_rope, k_rope, v)
+        prob = _problem(q, v, scale, eps)
+        state = P.fwd_state(_OP, prob, k, v, k_rope=k_rope)
+        o = P.fwd_out(_OP, prob, q, state, torch.empty_like(v), q_rope=q_rope)
+        ctx.save_for_backward(q, q_rope, k_rope, v, state)
+        ctx.scale, ctx.eps = scale, eps
+        return o
+
+    @staticmethod
+    @contiguous
+    def backward(ctx, do):
+        q, q_rope, k_rope, v, state = ctx.saved_tensors
+        prob = _problem(q, v, ctx.scale, ctx.eps)
+        dq, dq_rope = torch.empty_like(q), torch.empty_like(q_rope)
+        dstate = P.bwd_state(_OP, prob, q, do, state, dq, q_rope=q_rope, dq_rope=dq_rope)
+        dk, dk_rope, dv = torch.empty_like(k_rope), torch.empty_like(k_rope), torch.empty_like(v)
+        P.bwd_in(_OP, prob, k_rope, v, dstate, dk, dv, dk_rope=dk_rope)
+        return dq, dk, dq_rope, dk_rope, dv, None, None
+
+
+def decoupled_la(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    q_rope: torch.Tensor,
+    k_rope: torch.Tensor,
+    v: torch.Tensor,
+    scale: Optional[float] = None,
+    eps: float = 1e-6,
+) -> torch.Tensor:
+    r"""
+    Args:
+        q, k: plain queries / keys `(B, H, L, K)` (normaliser)
+        q_rope, k_rope: rotary queries / keys `(B, H, L, K)` (numerator)
+        v: values `(B, H, L, V)`
+        scale: multiplies the values inside the state; defaults to `1 / L`.
+        eps: added to the normaliser.
+    """
+    if scale is None:
+        scale = k.shape[-2] ** -1.0
+    return DecoupledLAFunction.apply(q, k, q_rope, k_rope, v, scale, eps)

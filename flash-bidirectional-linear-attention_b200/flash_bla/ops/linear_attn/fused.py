@@ -1,0 +1,77 @@
+"""Normalised bidirectional linear attention.
+
+    S = K^T (V * scale),   kmean = mean_t K,   O = Q S / (Q . kmean + eps)
+
+Same public surface as the reference module ``flash_bla/ops/linear_attn/fused.py``
+(``LinearAttnFunction`` :350-453, ``linear_attention`` :456-480); the work is done
+by the sm_100a library through ``flash_bla.ops._passes``.  The feature map is
+applied by the caller: q and k are expected to be positive already.
+"""
+from typing import Optional
+
+import torch
+
+from flash_bla.ops import _passes as P
+from flash_bla.utils import contiguous
+
+_OP = "linear_attn"
+
+
+def _problem(q, v, scale, eps, norm_len=0):
+    B, H, L, K = q.shape
+    return P.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
+                          scale=scale, eps=eps, norm_len=norm_len, flags=P.default_flags())
+
+
+def _check(q, k, v):
+    if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
+        raise ValueError(f"expected q, k of shape (B, H, L, K) and v of shape (B, H, L, V); got "
+                         f"{tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise ValueError("q, k and v must have the same dtype")
+
+
+class LinearAttnFunction(torch.autograd.Function):
+
+    @staticmethod
+    @contiguous
+    def forward(ctx, q, k, v, scale, eps):
+        _check(q, k, v)
+        prob = _problem(q, v, scale, eps)
+        state = P.fwd_state(_OP, prob, k, v)
+        o = P.fwd_out(_OP, prob, q, state, torch.empty_like(v))
+        # The fp32 state is a few KB per head; keeping it avoids pass 1 in backward.
+        ctx.save_for_backward(q, k, v, state)
+        ctx.scale, ctx.eps = scale, eps
+        return o
+
+    @staticmethod
+    @contiguous
+    def backward(ctx, do):
+        q, k, v, state = ctx.saved_tensors
+        prob = _problem(q, v, ctx.scale, ctx.eps)
+        dq = torch.empty_like(q)
+        dstate = P.bwd_state(_OP, prob, q, do, state, dq)
+        dk, dv = torch.empty_like(k), torch.empty_like(v)
+        P.bwd_in(_OP, prob, k, v, dstate, dk, dv)
+        return dq, dk, dv, None, None
+
+
+def linear_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    scale: Optional[float] = None,
+    eps: float = 1e-6,
+) -> torch.Tensor:
+    r"""
+    Args:
+        q: queries of shape `(B, H, L, K)`
+        k: keys of shape `(B, H, L, K)`
+        v: values of shape `(B, H, L, V)`
+        scale: multiplies the values inside the state; defaults to `1 / L`.
+        eps: added to the normaliser `q . mean_t k`.
+    """
+    if scale is None:
+        scale = k.shape[-2] ** -1.0
+    return LinearAttnFunction.apply(q, k, v, scale, eps)

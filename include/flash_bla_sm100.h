@@ -1,0 +1,165 @@
+/*
+ * flash_bla_sm100 -- C ABI of the B200 (sm_100a) bidirectional linear-attention library.
+ *
+ * Every operator of the reference is a pair of streaming passes per direction:
+ *   forward   pass 1 (fwd_state): reduce over tokens into the per-(batch, head) state
+ *                                 [ S = K^T V  |  sum_t k ]            (fp32)
+ *             pass 2 (fwd_out)  : stream over tokens, o = scale * q S / (q . ksum/L + eps)
+ *   backward  pass 1 (bwd_state): stream over tokens, write dq, reduce into
+ *                                 [ dS = (q/z)^T dO  |  sum_t dz q ]    (fp32)
+ *             pass 2 (bwd_in)   : stream over tokens, write dk, dv
+ * The split into *_state / *_out entry points is what lets a caller that shards the
+ * sequence over several GPUs all-reduce the state between the two passes.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; all tensor pointers are DEVICE pointers of the
+ *     element type named by fbla_problem.dtype, contiguous in the layout stated below;
+ *   - state / dstate buffers are fp32, fbla_state_floats() elements, caller-allocated;
+ *   - the workspace is caller-allocated scratch of fbla_workspace_bytes() bytes (may be
+ *     NULL when that returns 0); its contents need not be initialised;
+ *   - every call only enqueues work on `stream` (a cudaStream_t) and returns; no call
+ *     synchronises the device;
+ *   - return value: FBLA_OK or an error code; fbla_last_error() gives the text for the
+ *     calling thread.  No C++ exception crosses this boundary and nothing here exits.
+ *   - there is no CPU fallback: a call on a machine without a CUDA device fails.
+ *
+ * Layouts
+ *   fixed length : q, k, q_rope, k_rope  (batch, heads, seq_len, dk)
+ *                  v, o, d_o             (batch, heads, seq_len, dv)
+ *   varlen       : q, k (total_tokens, heads, dk); v, o, d_o (total_tokens, heads, dv);
+ *                  cu_seqlens int32 [num_seqs + 1] on the device
+ *   state        : per unit u (u = b*heads + h, varlen: u = seq*heads + h):
+ *                  dk*dv floats of S (row-major dk x dv) followed, when normalize != 0,
+ *                  by dk floats of the key sum.  dstate has the same shape.
+ */
+#ifndef FLASH_BLA_SM100_H
+#define FLASH_BLA_SM100_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FBLA_ABI_VERSION 1
+
+enum fbla_dtype { FBLA_F32 = 0, FBLA_BF16 = 1, FBLA_F16 = 2 };
+
+enum fbla_status {
+    FBLA_OK = 0,
+    FBLA_ERR_INVALID = 1,      /* bad argument (null pointer, size out of range, ...) */
+    FBLA_ERR_UNSUPPORTED = 2,  /* valid request this build has no kernel for          */
+    FBLA_ERR_CUDA = 3,         /* a CUDA runtime / driver call failed                 */
+    FBLA_ERR_WORKSPACE = 4,    /* workspace missing or too small                      */
+    FBLA_ERR_DEVICE = 5        /* a kernel reported a device-side error status        */
+};
+
+enum fbla_flags {
+    FBLA_FLAG_GENERIC = 1      /* force the CUDA-core (fp32 FMA) kernels              */
+};
+
+typedef struct fbla_problem {
+    int32_t dtype;          /* enum fbla_dtype                                              */
+    int32_t batch;          /* B; 1 for varlen                                              */
+    int32_t heads;          /* H                                                            */
+    int32_t dk;             /* key / query feature dim                                      */
+    int32_t dv;             /* value feature dim                                            */
+    int64_t seq_len;        /* tokens per (batch, head) held by this call; varlen: total    */
+    int64_t norm_len;       /* length the key sum is divided by; 0 means seq_len (varlen:   */
+                            /* each sequence's own length).  A caller that shards the       */
+                            /* sequence passes the global length here.                      */
+    const int32_t *cu_seqlens; /* device int32 [num_seqs+1]; NULL selects fixed length      */
+    int32_t num_seqs;       /* varlen only                                                  */
+    int32_t max_seqlen;     /* varlen only: an upper bound on the sequence lengths          */
+    float scale;            /* multiplies V inside the state                                */
+    int32_t scale_per_seq;  /* varlen only: use 1/length of each sequence, ignore `scale`   */
+    float eps;              /* added to the normaliser                                      */
+    int32_t normalize;      /* 1: o = q S / (q.kmean + eps);  0: o = q S  (simple_la)       */
+    int32_t flags;          /* enum fbla_flags                                              */
+} fbla_problem;
+
+typedef void *fbla_stream_t; /* a cudaStream_t */
+
+/* ---- library ------------------------------------------------------------------------ */
+int fbla_version(void);
+const char *fbla_last_error(void);
+/* Kernels this library has launched in this process so far (all threads, all devices): a
+ * measurement aid, no counterpart in the reference.                                      */
+uint64_t fbla_launch_count(void);
+/* Number of fp32 elements of one state (or dstate) buffer for this problem; <0 on error. */
+int64_t fbla_state_floats(const fbla_problem *p);
+/* Bytes of scratch the *_state passes need for this problem; <0 on error.                */
+int64_t fbla_workspace_bytes(const fbla_problem *p);
+/* 1 when the tensor-core (tcgen05 + TMA) kernels serve this problem, 0 when the CUDA-core
+ * kernels do, <0 on error.                                                               */
+int fbla_kernel_path(const fbla_problem *p);
+
+/* ---- linear_attention (normalised) ---------------------------------------------------
+ * Replaces the kernels launched by LinearAttnFunction.forward / .backward,
+ * flash_bla/ops/linear_attn/fused.py:350-398 and :400-453 (kernels :27-88, :103-165,
+ * :169-266, :270-347).  p->normalize must be 1.                                          */
+int fbla_linear_attn_fwd_state(const fbla_problem *p, const void *k, const void *v,
+                               float *state, void *workspace, size_t workspace_bytes,
+                               fbla_stream_t stream);
+int fbla_linear_attn_fwd_out(const fbla_problem *p, const void *q, const float *state,
+                             void *o, fbla_stream_t stream);
+int fbla_linear_attn_bwd_state(const fbla_problem *p, const void *q, const void *d_o,
+                               const float *state, void *dq, float *dstate,
+                               void *workspace, size_t workspace_bytes, fbla_stream_t stream);
+int fbla_linear_attn_bwd_in(const fbla_problem *p, const void *k, const void *v,
+                            const float *dstate, void *dk, void *dv, fbla_stream_t stream);
+
+/* ---- simple_la (no normaliser) -------------------------------------------------------
+ * Replaces SimpleLinearAttnFunction.forward / .backward,
+ * flash_bla/ops/simple_la/fused.py:495-535 and :539-626 (kernels :26-79, :94-145,
+ * :160-211, :324-426).  p->normalize must be 0.                                          */
+int fbla_simple_la_fwd_state(const fbla_problem *p, const void *k, const void *v,
+                             float *state, void *workspace, size_t workspace_bytes,
+                             fbla_stream_t stream);
+int fbla_simple_la_fwd_out(const fbla_problem *p, const void *q, const float *state,
+                           void *o, fbla_stream_t stream);
+int fbla_simple_la_bwd_state(const fbla_problem *p, const void *q, const void *d_o,
+                             const float *state, void *dq, float *dstate,
+                             void *workspace, size_t workspace_bytes, fbla_stream_t stream);
+int fbla_simple_la_bwd_in(const fbla_problem *p, const void *k, const void *v,
+                          const float *dstate, void *dk, void *dv, fbla_stream_t stream);
+
+/* ---- decoupled_la (rotary numerator, plain normaliser) -------------------------------
+ * Replaces DecoupledLAFunction.forward / .backward,
+ * flash_bla/ops/linear_attn/decoupled.py:411-509 (kernels :27-100, :115-190, :194-316,
+ * :320-408).  State = [ k_rope^T v | sum_t k ].  p->normalize must be 1.                  */
+int fbla_decoupled_la_fwd_state(const fbla_problem *p, const void *k, const void *k_rope,
+                                const void *v, float *state, void *workspace,
+                                size_t workspace_bytes, fbla_stream_t stream);
+int fbla_decoupled_la_fwd_out(const fbla_problem *p, const void *q, const void *q_rope,
+                              const float *state, void *o, fbla_stream_t stream);
+int fbla_decoupled_la_bwd_state(const fbla_problem *p, const void *q, const void *q_rope,
+                                const void *d_o, const float *state, void *dq, void *dq_rope,
+                                float *dstate, void *workspace, size_t workspace_bytes,
+                                fbla_stream_t stream);
+int fbla_decoupled_la_bwd_in(const fbla_problem *p, const void *k_rope, const void *v,
+                             const float *dstate, void *dk, void *dk_rope, void *dv,
+                             fbla_stream_t stream);
+
+/* ---- varlen_linear_attention (packed sequences, cu_seqlens) --------------------------
+ * Replaces VarlenLinearAttnFunction.forward / .backward,
+ * flash_bla/ops/linear_attn/varlen.py:335-422 and :426-505 (kernels :30-88, :96-149,
+ * :157-224, :232-332).  p->cu_seqlens must be set; p->normalize must be 1.               */
+int fbla_varlen_linear_attn_fwd_state(const fbla_problem *p, const void *k, const void *v,
+                                      float *state, void *workspace, size_t workspace_bytes,
+                                      fbla_stream_t stream);
+int fbla_varlen_linear_attn_fwd_out(const fbla_problem *p, const void *q, const float *state,
+                                    void *o, fbla_stream_t stream);
+int fbla_varlen_linear_attn_bwd_state(const fbla_problem *p, const void *q, const void *d_o,
+                                      const float *state, void *dq, float *dstate,
+                                      void *workspace, size_t workspace_bytes,
+                                      fbla_stream_t stream);
+int fbla_varlen_linear_attn_bwd_in(const fbla_problem *p, const void *k, const void *v,
+                                   const float *dstate, void *dk, void *dv,
+                                   fbla_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_BLA_SM100_H */

@@ -1,0 +1,71 @@
+"""Shared helpers of the parity tests: seeded inputs with the distributions of the
+benchmark configurations, and the two acceptance metrics."""
+import os
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from oracle import bla_oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# acceptance bars: fp32 within 1e-5 relative; 16-bit inputs within 2e-2 of the output
+# RMS (max-abs) against an fp32/fp64 reference evaluated on the same rounded inputs.
+FP32_REL = 1e-5
+LOWP_MAXABS_OVER_RMS = 2e-2
+
+
+def load_golden(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    out = {}
+    for k in z.files:
+        a = z[k]
+        out[k] = torch.from_numpy(a) if a.ndim else a.item()
+    return out
+
+
+def golden_scale(g):
+    return None if g["scale"] < 0 else float(g["scale"])
+
+
+def make_inputs(seed, shape_qk, shape_v, dtype, positive=True, n_qk=2):
+    """q, k (and further q/k-shaped tensors), v, dO on the CPU, rounded to ``dtype``."""
+    g = torch.Generator().manual_seed(seed)
+    qk = [torch.randn(shape_qk, generator=g) for _ in range(n_qk)]
+    v = torch.randn(shape_v, generator=g)
+    do = torch.randn(shape_v, generator=g)
+    if positive:
+        qk[:2] = [F.elu(x) + 1 for x in qk[:2]]
+    return [x.to(dtype) for x in qk] + [v.to(dtype), do.to(dtype)]
+
+
+def check(got, ref, dtype, what="", magnitude=None):
+    """``magnitude``: a tensor whose RMS sets the error scale instead of ``ref``'s; for
+    results that are a difference of two much larger terms (dq when L = 1, where
+    o is almost independent of q) the achievable accuracy is relative to those terms."""
+    got = got.detach().cpu()
+    assert torch.isfinite(got.float()).all(), f"{what}: non-finite values"
+    if magnitude is not None:
+        rms = magnitude.double().square().mean().sqrt().item()
+        err = (got.double() - ref.double()).abs().max().item() / rms
+        bar = 20 * FP32_REL if dtype == torch.float32 else LOWP_MAXABS_OVER_RMS
+        assert err <= bar, f"{what}: max-abs over term rms {err:.3e} > {bar}"
+        return
+    if dtype == torch.float32:
+        err = O.rel_l2(got, ref)
+        assert err <= FP32_REL, f"{what}: relative L2 error {err:.3e} > {FP32_REL}"
+        # elementwise as well, scaled by the tensor's RMS
+        err2 = O.max_abs_over_rms(got, ref)
+        assert err2 <= 20 * FP32_REL, f"{what}: max-abs/rms {err2:.3e}"
+    else:
+        err = O.max_abs_over_rms(got, ref)
+        assert err <= LOWP_MAXABS_OVER_RMS, f"{what}: max-abs/rms {err:.3e} > {LOWP_MAXABS_OVER_RMS}"
+
+
+def run_op(fn, inputs, do):
+    """Runs ``fn(*inputs)`` on cuda:0 with autograd; returns (o, grads...) on the device."""
+    xs = [x.cuda().requires_grad_() for x in inputs]
+    o = fn(*xs)
+    o.backward(do.cuda())
+    return [o] + [x.grad for x in xs]

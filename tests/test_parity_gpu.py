@@ -1,0 +1,244 @@
+"""Parity of the CUDA library (called through its C ABI by the flash_bla operators)
+against the CPU oracle and the golden fixtures.  All tests here need a GPU."""
+import pytest
+import torch
+
+from oracle import bla_oracle as O
+from helpers import check, golden_scale, load_golden, make_inputs, run_op
+
+pytestmark = pytest.mark.gpu
+
+from flash_bla.ops import _passes as P
+from flash_bla.ops.linear_attn.decoupled import decoupled_la
+from flash_bla.ops.linear_attn.fused import linear_attention
+from flash_bla.ops.linear_attn.varlen import varlen_linear_attention
+from flash_bla.ops.simple_la.fused import simple_la
+
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+# ---------------------------------------------------------------------------------------
+# golden fixtures (values computed by the reference itself), fp32
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["linear_attn_a", "linear_attn_b", "linear_attn_c"])
+def test_golden_linear_attn(name):
+    g = load_golden(name)
+    o, dq, dk, dv = run_op(lambda q, k, v: linear_attention(q, k, v, golden_scale(g), g["eps"]),
+                           [g["q"], g["k"], g["v"]], g["do"])
+    for got, key in ((o, "o"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        check(got, g[key], torch.float32, f"{name}.{key}")
+
+
+@pytest.mark.parametrize("name", ["decoupled_a", "decoupled_b"])
+def test_golden_decoupled(name):
+    g = load_golden(name)
+    outs = run_op(lambda *a: decoupled_la(*a, golden_scale(g), g["eps"]),
+                  [g["q"], g["k"], g["q_rope"], g["k_rope"], g["v"]], g["do"])
+    for got, key in zip(outs, ("o", "dq", "dk", "dq_rope", "dk_rope", "dv")):
+        check(got, g[key], torch.float32, f"{name}.{key}")
+
+
+@pytest.mark.parametrize("name", ["simple_la_a", "simple_la_b"])
+def test_golden_simple_la(name):
+    g = load_golden(name)
+    outs = run_op(lambda q, k, v: simple_la(q, k, v, golden_scale(g)), [g["q"], g["k"], g["v"]], g["do"])
+    for got, key in zip(outs, ("o", "dq", "dk", "dv")):
+        check(got, g[key], torch.float32, f"{name}.{key}")
+
+
+@pytest.mark.parametrize("name", ["varlen_a", "varlen_b", "varlen_c"])
+def test_golden_varlen(name):
+    g = load_golden(name)
+    cu = g["cu_seqlens"].cuda()
+    max_len = int((g["cu_seqlens"][1:] - g["cu_seqlens"][:-1]).max())
+    outs = run_op(lambda q, k, v: varlen_linear_attention(q, k, v, cu, max_len, golden_scale(g), g["eps"]),
+                  [g["q"], g["k"], g["v"]], g["do"])
+    for got, key in zip(outs, ("o", "dq", "dk", "dv")):
+        check(got, g[key], torch.float32, f"{name}.{key}")
+
+
+# ---------------------------------------------------------------------------------------
+# oracle parity on seeded inputs: dtypes, ragged lengths, DK != DV, both kernel paths
+# ---------------------------------------------------------------------------------------
+LINEAR_SHAPES = [
+    (2, 4, 1024, 64, 64),     # the fp32 acceptance configuration
+    (1, 2, 1, 64, 64),
+    (1, 2, 31, 16, 16),
+    (1, 3, 129, 64, 64),
+    (2, 2, 383, 128, 128),
+    (1, 2, 640, 128, 32),     # DK = 2*d, DV = d/2 as PolaFormer calls it
+    (1, 1, 200, 40, 40),
+    (1, 2, 2048, 64, 64),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", LINEAR_SHAPES)
+@pytest.mark.parametrize("generic", [False, True])
+def test_linear_attn(shape, dtype, generic):
+    B, H, T, DK, DV = shape
+    q, k, v, do = make_inputs(0, (B, H, T, DK), (B, H, T, DV), dtype)
+    if generic:
+        with P.generic_kernels():
+            outs = run_op(lambda *a: linear_attention(*a), [q, k, v], do)
+    else:
+        outs = run_op(lambda *a: linear_attention(*a), [q, k, v], do)
+    ref = [O.linear_attn_fwd(q, k, v)] + list(O.linear_attn_bwd(q, k, v, do))
+    # with a single token o barely depends on q: dq is the difference of two terms that
+    # cancel to ~1e-9 of their size, so its error is measured against one of the terms
+    # (the same holds for dk: with one token o depends on k only through eps)
+    terms = {}
+    if T == 1:
+        parts = O.decoupled_la_bwd(q, k, q, k, v, do)
+        terms = {"dq": parts[2], "dk": parts[3]}
+    for got, r, key in zip(outs, ref, ("o", "dq", "dk", "dv")):
+        assert got.dtype == dtype and got.is_contiguous()
+        check(got, r, dtype, f"linear_attn{shape}.{key}", magnitude=terms.get(key))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 2, 300, 64, 64), (2, 2, 257, 128, 128), (1, 2, 100, 24, 8)])
+@pytest.mark.parametrize("scale,eps", [(None, 1e-6), (0.02, 1e-4)])
+def test_linear_attn_scale_eps(shape, dtype, scale, eps):
+    B, H, T, DK, DV = shape
+    q, k, v, do = make_inputs(3, (B, H, T, DK), (B, H, T, DV), dtype)
+    outs = run_op(lambda *a: linear_attention(*a, scale=scale, eps=eps), [q, k, v], do)
+    ref = [O.linear_attn_fwd(q, k, v, scale, eps)] + list(O.linear_attn_bwd(q, k, v, do, scale, eps))
+    for got, r, key in zip(outs, ref, ("o", "dq", "dk", "dv")):
+        check(got, r, dtype, f"linear_attn{shape}.{key}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(2, 2, 515, 64, 64), (1, 2, 256, 128, 128), (1, 2, 77, 32, 48)])
+def test_decoupled(shape, dtype):
+    B, H, T, DK, DV = shape
+    q, k, qr, kr, v, do = make_inputs(1, (B, H, T, DK), (B, H, T, DV), dtype, n_qk=4)
+    outs = run_op(lambda *a: decoupled_la(*a), [q, k, qr, kr, v], do)
+    ref = [O.decoupled_la_fwd(q, k, qr, kr, v)] + list(O.decoupled_la_bwd(q, k, qr, kr, v, do))
+    for got, r, key in zip(outs, ref, ("o", "dq", "dk", "dq_rope", "dk_rope", "dv")):
+        check(got, r, dtype, f"decoupled{shape}.{key}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(2, 2, 1000, 128, 128), (1, 2, 333, 64, 64), (1, 1, 50, 20, 36)])
+def test_simple_la(shape, dtype):
+    B, H, T, DK, DV = shape
+    q, k, v, do = make_inputs(2, (B, H, T, DK), (B, H, T, DV), dtype, positive=False)
+    outs = run_op(lambda *a: simple_la(*a), [q, k, v], do)
+    ref = [O.simple_la_fwd(q, k, v)] + list(O.simple_la_bwd(q, k, v, do))
+    for got, r, key in zip(outs, ref, ("o", "dq", "dk", "dv")):
+        check(got, r, dtype, f"simple_la{shape}.{key}")
+
+
+VARLEN_CASES = [
+    ([8, 17, 32], 1, 8, 8), ([8, 17, 32], 8, 17, 13), ([8, 17, 32], 8, 64, 48), ([8, 17, 32], 1, 128, 128),
+    ([300, 1, 129, 640], 4, 64, 64), ([1000, 24], 2, 128, 128),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", VARLEN_CASES)
+@pytest.mark.parametrize("scale", [None, 0.02])
+def test_varlen(case, dtype, scale):
+    lengths, H, DK, DV = case
+    tot = sum(lengths)
+    q, k, v, do = make_inputs(42, (tot, H, DK), (tot, H, DV), dtype)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    cud = cu.cuda()
+    outs = run_op(lambda *a: varlen_linear_attention(*a, cud, max(lengths), scale=scale), [q, k, v], do)
+    ref = [O.varlen_linear_attn_fwd(q, k, v, cu, scale)] + list(O.varlen_linear_attn_bwd(q, k, v, do, cu, scale))
+    # sequences of different lengths have outputs of different magnitude (scale 1/len):
+    # each sequence is judged against its own RMS
+    for got, r, key in zip(outs, ref, ("o", "dq", "dk", "dv")):
+        for lo, hi in zip(cu[:-1].tolist(), cu[1:].tolist()):
+            check(got[lo:hi], r[lo:hi], dtype, f"varlen{case}.{key}[{lo}:{hi}]")
+
+
+def test_varlen_oversized_max_seqlen_and_no_leakage():
+    lengths = [7, 11, 140]
+    tot = sum(lengths)
+    q, k, v, do = make_inputs(7, (tot, 2, 16), (tot, 2, 16), torch.float32)
+    cu = torch.tensor([0, 7, 18, tot], dtype=torch.int32).cuda()
+    exact = varlen_linear_attention(q.cuda(), k.cuda(), v.cuda(), cu, max(lengths))
+    over = varlen_linear_attention(q.cuda(), k.cuda(), v.cuda(), cu, tot)
+    assert torch.equal(exact, over)
+    # changing one sequence leaves the outputs of the others bit-identical
+    k2, v2 = k.clone(), v.clone()
+    k2[7:18] += 1.0
+    v2[7:18] -= 3.0
+    other = varlen_linear_attention(q.cuda(), k2.cuda(), v2.cuda(), cu, max(lengths))
+    assert torch.equal(other[:7], exact[:7]) and torch.equal(other[18:], exact[18:])
+    assert not torch.equal(other[7:18], exact[7:18])
+
+
+def test_varlen_argument_contract():
+    q = torch.rand(10, 2, 16, device="cuda")
+    cu = torch.tensor([0, 4, 10], dtype=torch.int32, device="cuda")
+    ok = dict(q=q, k=q.clone(), v=q.clone(), cu_seqlens=cu, max_seqlen=6)
+    varlen_linear_attention(**ok)
+    bad = [
+        (dict(ok, q=q[0]), ValueError), (dict(ok, k=q[:, :1]), ValueError),
+        (dict(ok, v=torch.rand(9, 2, 16, device="cuda")), ValueError),
+        (dict(ok, v=q.double()), ValueError), (dict(ok, q=q.cpu(), k=q.cpu(), v=q.cpu()), ValueError),
+        (dict(ok, q=q.double(), k=q.double(), v=q.double()), TypeError),
+        (dict(ok, q=torch.rand(10, 2, 129, device="cuda"), k=torch.rand(10, 2, 129, device="cuda")), ValueError),
+        (dict(ok, cu_seqlens=cu.long()), ValueError), (dict(ok, cu_seqlens=cu.cpu()), ValueError),
+        (dict(ok, cu_seqlens=cu[:1]), ValueError), (dict(ok, max_seqlen=0), ValueError),
+        (dict(ok, max_seqlen=6.0), ValueError),
+    ]
+    for kwargs, exc in bad:
+        with pytest.raises(exc):
+            varlen_linear_attention(**kwargs)
+
+
+# ---------------------------------------------------------------------------------------
+# size-independent properties at the benchmark's full size
+# ---------------------------------------------------------------------------------------
+def test_full_size_properties_bf16():
+    B, H, T, D = 8, 16, 32768, 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.nn.functional.elu(torch.randn(B, H, T, D, device="cuda", generator=g)).add_(1).bfloat16()
+    k = torch.nn.functional.elu(torch.randn(B, H, T, D, device="cuda", generator=g)).add_(1).bfloat16()
+    v = torch.randn(B, H, T, D, device="cuda", generator=g).bfloat16()
+    do = torch.randn(B, H, T, D, device="cuda", generator=g).bfloat16()
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = linear_attention(q, k, v)
+    o.backward(do)
+    # (1) spot-check two (b, h) slices against the CPU oracle
+    for b, h in ((0, 0), (7, 15)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        qq, kk, vv, dd = (x[sl].detach().cpu() for x in (q, k, v, do))
+        check(o[sl], O.linear_attn_fwd(qq, kk, vv), torch.bfloat16, "o")
+        for got, r, key in zip((q.grad[sl], k.grad[sl], v.grad[sl]), O.linear_attn_bwd(qq, kk, vv, dd),
+                               ("dq", "dk", "dv")):
+            check(got, r, torch.bfloat16, key)
+    # (2) (b, h) units are independent: permuting the batch permutes the output, bit for bit
+    perm = torch.arange(B - 1, -1, -1, device="cuda")
+    o_perm = linear_attention(q.detach()[perm].contiguous(), k.detach()[perm].contiguous(),
+                              v.detach()[perm].contiguous())
+    assert torch.equal(o_perm, o.detach()[perm])
+    # (3) the operator is linear in v: doubling v doubles o exactly (power-of-two scaling)
+    o2 = linear_attention(q.detach(), k.detach(), (v.detach() * 2))
+    assert torch.equal(o2, o.detach() * 2)
+    # (4) run-to-run determinism of forward and backward
+    q2, k2, v2 = (x.detach().clone().requires_grad_() for x in (q, k, v))
+    o_again = linear_attention(q2, k2, v2)
+    o_again.backward(do)
+    assert torch.equal(o_again, o) and torch.equal(q2.grad, q.grad)
+    assert torch.equal(k2.grad, k.grad) and torch.equal(v2.grad, v.grad)
+
+
+def test_empty_and_errors():
+    # no tokens: nothing to compute (the default scale 1/L is undefined, as in the reference)
+    q = torch.rand(1, 2, 0, 16, device="cuda", requires_grad=True)
+    o = linear_attention(q, q, q, scale=1.0)
+    assert o.shape == q.shape
+    o.sum().backward()
+    assert q.grad.shape == q.shape
+    with pytest.raises(ZeroDivisionError):
+        linear_attention(q, q, q)
+    with pytest.raises(RuntimeError):
+        linear_attention(torch.rand(1, 1, 4, 300, device="cuda"), torch.rand(1, 1, 4, 300, device="cuda"),
+                         torch.rand(1, 1, 4, 8, device="cuda"))
+    with pytest.raises(RuntimeError):
+        linear_attention(torch.rand(1, 1, 4, 8), torch.rand(1, 1, 4, 8), torch.rand(1, 1, 4, 8))
