@@ -324,3 +324,23 @@ def rel_l2(got: torch.Tensor, ref: torch.Tensor) -> float:
     the same ratio as flash_bla/utils.py:49-52."""
     ref64 = ref.detach().double()
     return ((got.detach().double() - ref64).norm() / (ref64.norm() + 1e-30)).item()
+
+
+# ---------------------------------------------------------------------------
+# The reference's CPU execution model, for timing: the dense torch forward in
+# the tensors' own dtype and torch autograd for the backward, exactly how
+# benchmarks/ops/benchmark_linear_attn.py:49-58 drives naive_linear_attn.
+# ---------------------------------------------------------------------------
+
+def linear_attn_torch_fwd_bwd(q, k, v, do, scale: Optional[float] = None, eps: float = 1e-6):
+    """One forward + autograd backward of the dense torch statement
+    (flash_bla/ops/linear_attn/naive.py:6-14) in the dtype of the inputs.
+    Returns (o, dq, dk, dv)."""
+    q_, k_, v_ = (x.detach().clone().requires_grad_() for x in (q, k, v))
+    if scale is None:
+        scale = 1.0 / k_.shape[-2]
+    z = q_ @ k_.mean(dim=-2, keepdim=True).transpose(-2, -1)
+    s = k_.transpose(-2, -1) @ (v_ * scale)
+    o = q_ @ s / (z + eps)
+    o.backward(do)
+    return o.detach(), q_.grad, k_.grad, v_.grad

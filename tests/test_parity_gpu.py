@@ -149,9 +149,17 @@ def test_varlen(case, dtype, scale):
     ref = [O.varlen_linear_attn_fwd(q, k, v, cu, scale)] + list(O.varlen_linear_attn_bwd(q, k, v, do, cu, scale))
     # sequences of different lengths have outputs of different magnitude (scale 1/len):
     # each sequence is judged against its own RMS
+    # a one-token sequence has dq, dk that are differences of two cancelling terms (see
+    # test_linear_attn): those are judged against the size of one term
     for got, r, key in zip(outs, ref, ("o", "dq", "dk", "dv")):
         for lo, hi in zip(cu[:-1].tolist(), cu[1:].tolist()):
-            check(got[lo:hi], r[lo:hi], dtype, f"varlen{case}.{key}[{lo}:{hi}]")
+            mag = None
+            if hi - lo == 1 and key in ("dq", "dk"):
+                qs, ks, vs, ds = (x[lo:hi].transpose(0, 1) for x in (q, k, v, do))
+                sc = 1.0 if scale is None else scale
+                parts = O.decoupled_la_bwd(qs, ks, qs, ks, vs, ds, scale=sc)
+                mag = (parts[2] if key == "dq" else parts[3]).transpose(0, 1)
+            check(got[lo:hi], r[lo:hi], dtype, f"varlen{case}.{key}[{lo}:{hi}]", magnitude=mag)
 
 
 def test_varlen_oversized_max_seqlen_and_no_leakage():
