@@ -88,8 +88,27 @@ bool use_tc(const fbla_problem* p, const fbla::KParams& kp) {
     return !(p->flags & FBLA_FLAG_GENERIC) && fbla::tc_supported(kp, p->dtype);
 }
 
+// TMA needs 16-byte aligned tensors; anything else takes the CUDA-core kernels.
+bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr, const void* d = nullptr,
+               const void* e = nullptr, const void* f = nullptr) {
+    const void* ps[6] = {a, b, c, d, e, f};
+    for (const void* x : ps)
+        if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
+    return true;
+}
+
+// The workspace must serve whichever kernel path the pass ends up taking.
 int64_t workspace_need(const fbla_problem* p, const fbla::KParams& kp) {
-    return use_tc(p, kp) ? fbla::tc_workspace_bytes(kp) : fbla::simt_workspace_bytes(kp);
+    const int64_t simt = fbla::simt_workspace_bytes(kp);
+    if (!use_tc(p, kp)) return simt;
+    const int64_t tc = fbla::tc_workspace_bytes(kp);
+    return tc > simt ? tc : simt;
+}
+
+int check_device_status() {
+    const int s = fbla::tc_device_status();
+    if (s != 0) return fail(FBLA_ERR_DEVICE, "a kernel gave up a bounded wait (site %d); results are invalid", s);
+    return FBLA_OK;
 }
 
 #define NOT_NULL(x) \
@@ -120,8 +139,10 @@ int fwd_state(const fbla_problem* p, OpKind op, const void* k, const void* k_rop
     NOT_NULL(k);
     NOT_NULL(v);
     if (int rc = check_ws(p, kp, ws, ws_bytes)) return rc;
-    cudaError_t e = use_tc(p, kp) ? fbla::tc_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st)
-                                  : fbla::simt_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st);
+    if (int rc = check_device_status()) return rc;
+    const bool tc = use_tc(p, kp) && aligned16(k, k_rope, v, ws) && (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    cudaError_t e = tc ? fbla::tc_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st)
+                       : fbla::simt_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward state pass");
 }
 
@@ -134,8 +155,10 @@ int fwd_out(const fbla_problem* p, OpKind op, const void* q, const void* q_rope,
     NOT_NULL(state);
     NOT_NULL(o);
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = use_tc(p, kp) ? fbla::tc_fwd_out(kp, p->dtype, q, q_rope, state, o, st)
-                                  : fbla::simt_fwd_out(kp, p->dtype, q, q_rope, state, o, st);
+    if (int rc = check_device_status()) return rc;
+    const bool tc = use_tc(p, kp) && aligned16(q, q_rope, o) && (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    cudaError_t e = tc ? fbla::tc_fwd_out(kp, p->dtype, q, q_rope, state, o, st)
+                       : fbla::simt_fwd_out(kp, p->dtype, q, q_rope, state, o, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward output pass");
 }
 
@@ -159,9 +182,11 @@ int bwd_state(const fbla_problem* p, OpKind op, const void* q, const void* q_rop
         NOT_NULL(dq_rope);
     }
     if (int rc = check_ws(p, kp, ws, ws_bytes)) return rc;
-    cudaError_t e = use_tc(p, kp)
-                        ? fbla::tc_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st)
-                        : fbla::simt_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st);
+    if (int rc = check_device_status()) return rc;
+    const bool tc = use_tc(p, kp) && aligned16(q, q_rope, d_o, dq, dq_rope, ws) &&
+                    (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    cudaError_t e = tc ? fbla::tc_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st)
+                       : fbla::simt_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward state pass");
 }
 
@@ -177,8 +202,11 @@ int bwd_in(const fbla_problem* p, OpKind op, const void* k_rope, const void* v, 
     NOT_NULL(dv);
     if (op == OP_DECOUPLED) NOT_NULL(dk_rope);
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = use_tc(p, kp) ? fbla::tc_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st)
-                                  : fbla::simt_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st);
+    if (int rc = check_device_status()) return rc;
+    const bool tc = use_tc(p, kp) && aligned16(k_rope, v, dk, dk_rope, dv) &&
+                    (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    cudaError_t e = tc ? fbla::tc_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st)
+                       : fbla::simt_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward input pass");
 }
 

@@ -1,0 +1,653 @@
+// Tensor-core kernels of the backward direction.
+//
+//   tc_bwd_state_kernel : per 128-token tile
+//         t  = dO . (scale*S)^T                    (MMA 1, K-major operands, accumulator in TMEM)
+//         z  = q . kmean + eps,  dz = -(qr . t) / z^2
+//         dq = t / z + dz * kmean                  (written through a TMA store)
+//         qs = qr / z                              (written back over the qr tile in shared memory)
+//         [ dS | dkm ] += qs^T . [ dO | dz*z ]     (MMA 2, MN-major operands: contraction over tokens)
+//     and one fp32 partial [ dS | sum_t dz q ] per segment.  The saved output o is not read:
+//     sum_v o*dO = (qr . t) / z.  HBM traffic: q, dO once; dq once.
+//   tc_bwd_in_kernel    : dk = v . (scale*dS)^T + dkm/L,  dv = kr . (scale*dS)  per tile, both from
+//     one copy of the bf16 dS in shared memory (read K-major by the first MMA, MN-major by the
+//     second).  HBM traffic: k, v once; dk, dv once.
+#pragma once
+
+#include "tc_common.cuh"
+
+namespace fbla {
+namespace tc {
+
+// Writes the [DK x DV] fp32 matrix `src` (row-major), multiplied by `scale`, into shared memory as
+// 16-bit DV/64 blocks of [DK rows][64 columns] in the 128-byte-swizzled layout.  Read K-major it is
+// the operand B[n = row][k = column]; read MN-major it is B[k = row][n = column].
+template <int DK, int DV>
+__device__ __forceinline__ void stage_matrix_sw128(uint8_t* dst, const float* __restrict__ src, float scale,
+                                                   int is_bf16, int et) {
+    for (int i = et; i < DK * DV / 2; i += kEpiThreads) {
+        const int k = (2 * i) / DV, v = (2 * i) - k * DV;
+        const float2 x = *reinterpret_cast<const float2*>(src + 2 * i);
+        const uint32_t h = pack2(x.x * scale, x.y * scale, is_bf16);
+        *reinterpret_cast<uint32_t*>(dst + (v >> 6) * (DK * 128) + ptx::sw128_offset(k, v & 63)) = h;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+template <int DK, int DV, int MODE>
+struct BwdInCfg {
+    static constexpr int kKB = DK / 64, kVB = DV / 64;
+    static constexpr int kBopBytes = kVB * DK * 128;                        // 16-bit scale*dS
+    static constexpr int kVecBytes = 1024;                                  // fp32 dkm / L
+    static constexpr int kStageBytes = (kKB + kVB) * kBlockBytes;           // v tile, kr tile
+    static constexpr int kOutBytes = (kKB + kVB) * kBlockBytes;             // staged dk (dkr) and dv tile
+    static constexpr int kConstBytes = MODE == kDecoupled ? kKB * kBlockBytes : 0;  // dk tile of the decoupled op
+    static constexpr int kBig = (DK == 128 && DV == 128);
+    static constexpr int kOutBufs = kBig ? 1 : 2;
+    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kOutBufs * kOutBytes + kConstBytes + 512;
+    static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
+    static constexpr int kAccCols = DK + DV;
+    static constexpr int kTmemCols = 2 * kAccCols <= 256 ? 256 : 512;
+    static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
+};
+
+template <int DK, int DV, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_v,
+                 const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dkr,
+                 const __grid_constant__ CUtensorMap tm_dv, const Params p) {
+    using Cfg = BwdInCfg<DK, DV, MODE>;
+    constexpr int NS = Cfg::kStages;
+    constexpr int NO = Cfg::kOutBufs;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_1024(smem_raw);
+    uint8_t* bop = smem;
+    float* vec = reinterpret_cast<float*>(bop + Cfg::kBopBytes);
+    uint8_t* stages = reinterpret_cast<uint8_t*>(vec) + Cfg::kVecBytes;
+    uint8_t* outbuf = stages + NS * Cfg::kStageBytes;
+    uint8_t* constbuf = outbuf + NO * Cfg::kOutBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(constbuf + Cfg::kConstBytes);
+    uint64_t* full = bars;                  // [NS]
+    uint64_t* empty = bars + NS;            // [NS]
+    uint64_t* tfull = bars + 2 * NS;        // [2]
+    uint64_t* tempty = tfull + 2;           // [2]
+    uint64_t* bop_ready = tempty + 2;
+    uint64_t* out_free = bop_ready + 1;     // [NO]
+    uint64_t* out_written = out_free + NO;  // [NO]
+    uint64_t* const_free = out_written + NO; // constant dk tile no longer read by a store
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_free + 1);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Schedule& sch = p.sch;
+    const int g0 = blockIdx.x * sch.tiles_per_cta;
+    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    const ptx::Abort ab{cta_abort, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; ++i) {
+            ptx::mbar_init(&full[i], 1);
+            ptx::mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&tfull[i], 1);
+            ptx::mbar_init(&tempty[i], kEpiThreads);
+        }
+        for (int i = 0; i < NO; ++i) {
+            ptx::mbar_init(&out_free[i], 1);
+            ptx::mbar_init(&out_written[i], kEpiThreads);
+        }
+        ptx::mbar_init(bop_ready, kEpiThreads);
+        ptx::mbar_init(const_free, 1);
+        *cta_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tm_kr);
+        ptx::prefetch_tensormap(&tm_v);
+        ptx::prefetch_tensormap(&tm_dk);
+        ptx::prefetch_tensormap(&tm_dv);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer: v tile then kr tile ----------------
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 401)) break;
+            ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+            const int unit = g / sch.tiles_per_unit;
+            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            uint8_t* st = stages + s * Cfg::kStageBytes;
+#pragma unroll
+            for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_v, &full[s], b * 64, t0, unit);
+#pragma unroll
+            for (int b = 0; b < Cfg::kKB; ++b)
+                ptx::tma_load_3d(st + (Cfg::kVB + b) * kBlockBytes, &tm_kr, &full[s], b * 64, t0, unit);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc_dk = ptx::instr_desc(128, DK, p.is_bf16, false, false);
+        const uint32_t idesc_dv = ptx::instr_desc(128, DV, p.is_bf16, false, true);
+        const uint32_t bop_base = ptx::smem_u32(bop);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int a = it & 1;
+            const int tile = g % sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            if (first) {
+                if (!ptx::mbar_wait(bop_ready, (uint32_t)seg & 1u, ab, 411)) break;
+                ++seg;
+            }
+            if (!ptx::mbar_wait(&full[s], ph, ab, 412)) break;
+            if (!ptx::mbar_wait(&tempty[a], ((uint32_t)(it >> 1) & 1u) ^ 1u, ab, 413)) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t v_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t kr_base = v_base + Cfg::kVB * kBlockBytes;
+            const uint32_t acc = tmem + a * Cfg::kAccCols;
+            // dk[tok][k] = sum_v V[tok][v] * dS[k][v]   (B K-major: rows k, 128 bytes along v)
+#pragma unroll
+            for (int vb = 0; vb < Cfg::kVB; ++vb) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t da = ptx::smem_desc(v_base + vb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t db = ptx::smem_desc(bop_base + vb * (DK * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(acc, da, db, idesc_dk, !(vb == 0 && kk == 0));
+                }
+            }
+            // dv[tok][v] = sum_k KR[tok][k] * dS[k][v]  (B MN-major: rows k, 128 bytes along v)
+#pragma unroll
+            for (int kb = 0; kb < Cfg::kKB; ++kb) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t da = ptx::smem_desc(kr_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t db = ptx::smem_desc(bop_base + (kb * 64 + kk * 16) * 128, DK * 128, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(acc + DK, da, db, idesc_dv, !(kb == 0 && kk == 0));
+                }
+            }
+            ptx::mma_commit(&empty[s]);
+            ptx::mma_commit(&tfull[a]);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;
+        const int et = threadIdx.x - 64;
+        const int row = quarter * 32 + lane;
+        const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool issuer = (et == 0);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int unit = g / sch.tiles_per_unit;
+            const int tile = g - unit * sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            const int a = it & 1;
+            const int ob_i = it % NO;
+            const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
+            const uint32_t pho = (uint32_t)(it / NO) & 1u;
+            if (first) {
+                const float* st = p.state + (size_t)unit * p.state_stride;
+                // `vec` (and the constant tile) of the previous unit are read by every epilogue thread
+                // until it has arrived on out_written of the previous tile
+                if (it > 0 && !ptx::mbar_wait(&out_written[(it - 1) % NO], (uint32_t)((it - 1) / NO) & 1u, ab, 424)) break;
+                if (MODE == kDecoupled) {
+                    if (issuer) {
+                        ptx::tma_store_wait_read<0>();
+                        ptx::mbar_arrive(const_free);
+                    }
+                    if (!ptx::mbar_wait(const_free, (uint32_t)seg & 1u, ab, 425)) break;
+                }
+                ++seg;
+                stage_matrix_sw128<DK, DV>(bop, st, p.scale, p.is_bf16, et);
+                if (MODE != kSimple)
+                    for (int i = et; i < DK; i += kEpiThreads) vec[i] = st[DK * DV + i] * p.inv_norm;
+                if (MODE == kDecoupled) {
+                    // every token's dk is dkm / L: one constant tile, stored once per tile
+                    for (int i = et; i < kTileTokens * DK / 2; i += kEpiThreads) {
+                        const int r = (2 * i) / DK, k = (2 * i) - r * DK;
+                        const float x0 = st[DK * DV + k] * p.inv_norm, x1 = st[DK * DV + k + 1] * p.inv_norm;
+                        *reinterpret_cast<uint32_t*>(constbuf + (k >> 6) * kBlockBytes + ptx::sw128_offset(r, k & 63)) =
+                            pack2(x0, x1, p.is_bf16);
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(bop_ready);
+            }
+            if (!ptx::mbar_wait(&tfull[a], ph2, ab, 421)) break;
+            ptx::tc_fence_after_sync();
+            if (issuer) {
+                ptx::tma_store_wait_read<NO - 1>();
+                ptx::mbar_arrive(&out_free[ob_i]);
+            }
+            if (!ptx::mbar_wait(&out_free[ob_i], pho, ab, 422)) break;
+            uint8_t* ob = outbuf + ob_i * Cfg::kOutBytes;
+            // dk (or dk_rope) tile
+#pragma unroll
+            for (int c0 = 0; c0 < DK; c0 += 32) {
+                float v[32];
+                ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + c0, v);
+                ptx::tmem_ld_wait();
+                if (MODE == kLinear) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += vec[c0 + j];
+                }
+                uint8_t* blk = ob + (c0 >> 6) * kBlockBytes + row * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 w;
+                    w.x = pack2(v[8 * j], v[8 * j + 1], p.is_bf16);
+                    w.y = pack2(v[8 * j + 2], v[8 * j + 3], p.is_bf16);
+                    w.z = pack2(v[8 * j + 4], v[8 * j + 5], p.is_bf16);
+                    w.w = pack2(v[8 * j + 6], v[8 * j + 7], p.is_bf16);
+                    const int chunk = ((c0 & 63) >> 3) + j;
+                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                }
+            }
+            // dv tile
+#pragma unroll
+            for (int c0 = 0; c0 < DV; c0 += 32) {
+                float v[32];
+                ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + DK + c0, v);
+                ptx::tmem_ld_wait();
+                uint8_t* blk = ob + (Cfg::kKB + (c0 >> 6)) * kBlockBytes + row * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 w;
+                    w.x = pack2(v[8 * j], v[8 * j + 1], p.is_bf16);
+                    w.y = pack2(v[8 * j + 2], v[8 * j + 3], p.is_bf16);
+                    w.z = pack2(v[8 * j + 4], v[8 * j + 5], p.is_bf16);
+                    w.w = pack2(v[8 * j + 6], v[8 * j + 7], p.is_bf16);
+                    const int chunk = ((c0 & 63) >> 3) + j;
+                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                }
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&tempty[a]);
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&out_written[ob_i]);
+            if (issuer) {
+                if (!ptx::mbar_wait(&out_written[ob_i], pho, ab, 423)) break;
+                const int t0 = tile * kTileTokens;
+#pragma unroll
+                for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_store_3d(&tm_dkr, ob + b * kBlockBytes, b * 64, t0, unit);
+#pragma unroll
+                for (int b = 0; b < Cfg::kVB; ++b)
+                    ptx::tma_store_3d(&tm_dv, ob + (Cfg::kKB + b) * kBlockBytes, b * 64, t0, unit);
+                if (MODE == kDecoupled) {
+#pragma unroll
+                    for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_store_3d(&tm_dk, constbuf + b * kBlockBytes, b * 64, t0, unit);
+                }
+                ptx::tma_store_commit();
+            }
+        }
+        if (issuer) ptx::tma_store_wait_all<0>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+template <int DK, int DV, int MODE>
+struct BwdStateCfg {
+    static constexpr int kKB = DK / 64, kVB = DV / 64;
+    static constexpr int kBopBytes = kVB * DK * 128;                        // 16-bit scale*S
+    static constexpr int kVecBytes = 1024;                                  // fp32 kmean
+    static constexpr int kDzBytes = MODE != kSimple ? 4096 : 0;             // [2 token blocks][16 rows][128 B]
+    static constexpr int kQBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
+    static constexpr int kTmaBytes = (kQBlocks + kVB) * kBlockBytes;        // qr (, q), dO tiles
+    static constexpr int kStageBytes = kTmaBytes + kDzBytes;
+    static constexpr int kOutBytes = kQBlocks * kBlockBytes;                // staged dq (dq_rope, dq) tile
+    static constexpr int kBig = (DK == 128) || MODE == kDecoupled;
+    static constexpr int kOutBufs = kBig ? 1 : 2;
+    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kOutBufs * kOutBytes + 512;
+    static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
+    static constexpr int kColT = 0;                 // two t accumulators of DK columns
+    static constexpr int kColS = 2 * DK;            // dS accumulator, DV columns
+    static constexpr int kColM = 2 * DK + DV;       // dkm accumulator, 16 columns
+    static constexpr int kTmemCols = (kColM + 16) <= 256 ? 256 : 512;
+    static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
+};
+
+template <int DK, int DV, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
+                    const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
+                    const __grid_constant__ CUtensorMap tm_dqr, const Params p) {
+    using Cfg = BwdStateCfg<DK, DV, MODE>;
+    constexpr int NS = Cfg::kStages;
+    constexpr int NO = Cfg::kOutBufs;
+    constexpr int KB = Cfg::kKB, VB = Cfg::kVB;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_1024(smem_raw);
+    uint8_t* bop = smem;
+    float* km = reinterpret_cast<float*>(bop + Cfg::kBopBytes);
+    uint8_t* stages = reinterpret_cast<uint8_t*>(km) + Cfg::kVecBytes;
+    uint8_t* outbuf = stages + NS * Cfg::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(outbuf + NO * Cfg::kOutBytes);
+    uint64_t* full = bars;                  // [NS] TMA landed
+    uint64_t* empty = bars + NS;            // [NS] MMA 2 done with the stage
+    uint64_t* qs_ready = bars + 2 * NS;     // [NS] epilogue wrote qr/z and the dz columns
+    uint64_t* tfull = bars + 3 * NS;        // [2] t accumulator ready
+    uint64_t* tempty = tfull + 2;           // [2] t accumulator drained
+    uint64_t* bop_ready = tempty + 2;
+    uint64_t* acc_full = bop_ready + 1;     // dS / dkm of a segment complete
+    uint64_t* acc_empty = acc_full + 1;
+    uint64_t* out_free = acc_empty + 1;     // [NO]
+    uint64_t* out_written = out_free + NO;  // [NO]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_written + NO);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Schedule& sch = p.sch;
+    const int g0 = blockIdx.x * sch.tiles_per_cta;
+    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    const ptx::Abort ab{cta_abort, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; ++i) {
+            ptx::mbar_init(&full[i], 1);
+            ptx::mbar_init(&empty[i], 1);
+            ptx::mbar_init(&qs_ready[i], kEpiThreads);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&tfull[i], 1);
+            ptx::mbar_init(&tempty[i], kEpiThreads);
+        }
+        for (int i = 0; i < NO; ++i) {
+            ptx::mbar_init(&out_free[i], 1);
+            ptx::mbar_init(&out_written[i], kEpiThreads);
+        }
+        ptx::mbar_init(bop_ready, kEpiThreads);
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, kEpiThreads);
+        *cta_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tm_qr);
+        ptx::prefetch_tensormap(&tm_do);
+        ptx::prefetch_tensormap(&tm_dq);
+    }
+    if (MODE != kSimple) {
+        // rows 2..15 of every dz tile stay zero for the whole kernel
+        for (int s = 0; s < NS; ++s) {
+            uint32_t* dzt = reinterpret_cast<uint32_t*>(stages + s * Cfg::kStageBytes + Cfg::kTmaBytes);
+            for (int i = threadIdx.x; i < Cfg::kDzBytes / 4; i += kThreads) dzt[i] = 0u;
+        }
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer: qr tile, (q tile,) dO tile ----------------
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 301)) break;
+            ptx::mbar_arrive_expect_tx(&full[s], Cfg::kTmaBytes);
+            const int unit = g / sch.tiles_per_unit;
+            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            uint8_t* st = stages + s * Cfg::kStageBytes;
+#pragma unroll
+            for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_qr, &full[s], b * 64, t0, unit);
+            if (MODE == kDecoupled) {
+#pragma unroll
+                for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + (KB + b) * kBlockBytes, &tm_q, &full[s], b * 64, t0, unit);
+            }
+#pragma unroll
+            for (int b = 0; b < VB; ++b)
+                ptx::tma_load_3d(st + (Cfg::kQBlocks + b) * kBlockBytes, &tm_do, &full[s], b * 64, t0, unit);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc_t = ptx::instr_desc(128, DK, p.is_bf16, false, false);
+        const uint32_t idesc_s = ptx::instr_desc(DK, DV, p.is_bf16, true, true);
+        const uint32_t idesc_m = ptx::instr_desc(DK, 16, p.is_bf16, true, false);
+        const uint32_t bop_base = ptx::smem_u32(bop);
+        int seg_bop = 0, seg_acc = 0;
+        bool ok = true;
+        // second MMA of iteration j (tile gj): [dS | dkm] += qs^T [dO | dz]
+        auto mma2 = [&](int j, int gj) -> bool {
+            const int s = j % NS;
+            const uint32_t ph = (uint32_t)(j / NS) & 1u;
+            const int tile = gj % sch.tiles_per_unit;
+            const bool first = (gj == g0) || tile == 0;
+            const bool last = (gj == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            if (!ptx::mbar_wait(&qs_ready[s], ph, ab, 314)) return false;
+            if (first && !ptx::mbar_wait(acc_empty, ((uint32_t)seg_acc & 1u) ^ 1u, ab, 315)) return false;
+            ptx::tc_fence_after_sync();
+            const uint32_t qr_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t q_base = MODE == kDecoupled ? qr_base + KB * kBlockBytes : qr_base;
+            const uint32_t do_base = qr_base + Cfg::kQBlocks * kBlockBytes;
+            const uint32_t dz_base = qr_base + Cfg::kTmaBytes;
+#pragma unroll
+            for (int ks = 0; ks < kTileTokens / 16; ++ks) {
+                const bool acc = !(first && ks == 0);
+                const uint64_t da = ptx::smem_desc(qr_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                const uint64_t db = ptx::smem_desc(do_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                ptx::mma_ss(tmem + Cfg::kColS, da, db, idesc_s, acc);
+                if (MODE != kSimple) {
+                    const uint64_t dq_ = ptx::smem_desc(q_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                    const uint64_t dz_ = ptx::smem_desc(dz_base + (ks >> 2) * 2048 + (ks & 3) * 32, 16, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + Cfg::kColM, dq_, dz_, idesc_m, acc);
+                }
+            }
+            ptx::mma_commit(&empty[s]);
+            if (last) {
+                ptx::mma_commit(acc_full);
+                ++seg_acc;
+            }
+            return true;
+        };
+        int it = 0;
+        for (int g = g0; g < g1 && ok; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int a = it & 1;
+            const int tile = g % sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            if (first) {
+                // finish the previous segment before its B operand is replaced
+                if (it > 0 && !mma2(it - 1, g - 1)) { ok = false; break; }
+                if (!ptx::mbar_wait(bop_ready, (uint32_t)seg_bop & 1u, ab, 311)) { ok = false; break; }
+                ++seg_bop;
+            }
+            if (!ptx::mbar_wait(&full[s], ph, ab, 312)) { ok = false; break; }
+            if (!ptx::mbar_wait(&tempty[a], ((uint32_t)(it >> 1) & 1u) ^ 1u, ab, 313)) { ok = false; break; }
+            ptx::tc_fence_after_sync();
+            const uint32_t do_base = ptx::smem_u32(stages + s * Cfg::kStageBytes) + Cfg::kQBlocks * kBlockBytes;
+            // t[tok][k] = sum_v dO[tok][v] * S[k][v]
+#pragma unroll
+            for (int vb = 0; vb < VB; ++vb) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t da = ptx::smem_desc(do_base + vb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t db = ptx::smem_desc(bop_base + vb * (DK * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + Cfg::kColT + a * DK, da, db, idesc_t, !(vb == 0 && kk == 0));
+                }
+            }
+            ptx::mma_commit(&tfull[a]);
+            if (!first && it > 0 && !mma2(it - 1, g - 1)) { ok = false; break; }
+        }
+        if (ok && it > 0) mma2(it - 1, g1 - 1);
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;
+        const int et = threadIdx.x - 64;
+        const int row = quarter * 32 + lane;
+        const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool issuer = (et == 0);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int unit = g / sch.tiles_per_unit;
+            const int tile = g - unit * sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int a = it & 1;
+            const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
+            const int ob_i = it % NO;
+            const uint32_t pho = (uint32_t)(it / NO) & 1u;
+            if (first) {
+                const float* st = p.state + (size_t)unit * p.state_stride;
+                // km of the previous unit is read by every epilogue thread until it has arrived on
+                // out_written of the previous tile
+                if (it > 0 && !ptx::mbar_wait(&out_written[(it - 1) % NO], (uint32_t)((it - 1) / NO) & 1u, ab, 326)) break;
+                stage_matrix_sw128<DK, DV>(bop, st, p.scale, p.is_bf16, et);
+                if (MODE != kSimple)
+                    for (int i = et; i < DK; i += kEpiThreads) km[i] = st[DK * DV + i] * p.inv_norm;
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(bop_ready);
+            }
+            if (!ptx::mbar_wait(&full[s], ph, ab, 321)) break;       // the q tile is read below
+            if (!ptx::mbar_wait(&tfull[a], ph2, ab, 322)) break;
+            ptx::tc_fence_after_sync();
+            uint8_t* stg = stages + s * Cfg::kStageBytes;
+            uint8_t* qr_row = stg + row * 128;                        // + block * kBlockBytes
+            uint8_t* q_row = MODE == kDecoupled ? qr_row + KB * kBlockBytes : qr_row;
+            const uint32_t t_acc = t_lane + Cfg::kColT + a * DK;
+            float rz = 1.f, dz = 0.f, z = 1.f;
+            if (MODE != kSimple) {
+                // pass A: z = q . km + eps, w = qr . t
+                float zs = 0.f, w = 0.f;
+#pragma unroll
+                for (int c0 = 0; c0 < DK; c0 += 32) {
+                    float t[32];
+                    ptx::tmem_ld32(t_acc + c0, t);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int chunk = ((c0 & 63) >> 3) + j;
+                        const uint32_t off = (uint32_t)(c0 >> 6) * kBlockBytes + (((chunk ^ row) & 7) << 4);
+                        const uint4 qr4 = *reinterpret_cast<const uint4*>(qr_row + off);
+                        uint4 q4 = qr4;
+                        if (MODE == kDecoupled) q4 = *reinterpret_cast<const uint4*>(q_row + off);
+                        const uint32_t qw[4] = {q4.x, q4.y, q4.z, q4.w};
+                        const uint32_t rw[4] = {qr4.x, qr4.y, qr4.z, qr4.w};
+                        if (j == 0) ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 qf = unpack2(qw[e], p.is_bf16);
+                            const float2 rf = unpack2(rw[e], p.is_bf16);
+                            const int c = c0 + 8 * j + 2 * e;
+                            zs = fmaf(qf.x, km[c], zs);
+                            zs = fmaf(qf.y, km[c + 1], zs);
+                            w = fmaf(rf.x, t[8 * j + 2 * e], w);
+                            w = fmaf(rf.y, t[8 * j + 2 * e + 1], w);
+                        }
+                    }
+                }
+                z = zs + p.eps;
+                rz = 1.f / z;
+                dz = -w * rz * rz;
+            }
+            if (issuer) {
+                ptx::tma_store_wait_read<NO - 1>();
+                ptx::mbar_arrive(&out_free[ob_i]);
+            }
+            if (!ptx::mbar_wait(&out_free[ob_i], pho, ab, 323)) break;
+            uint8_t* ob = outbuf + ob_i * Cfg::kOutBytes;
+            // pass B: dq, and qr/z written back over the qr tile
+#pragma unroll
+            for (int c0 = 0; c0 < DK; c0 += 32) {
+                float t[32];
+                ptx::tmem_ld32(t_acc + c0, t);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int chunk = ((c0 & 63) >> 3) + j;
+                    const uint32_t off = (uint32_t)(c0 >> 6) * kBlockBytes + (((chunk ^ row) & 7) << 4);
+                    uint32_t o1[4], o2[4], qs[4];
+                    uint4 qr4 = make_uint4(0, 0, 0, 0);
+                    if (MODE != kSimple) qr4 = *reinterpret_cast<const uint4*>(qr_row + off);
+                    const uint32_t rw[4] = {qr4.x, qr4.y, qr4.z, qr4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = c0 + 8 * j + 2 * e;
+                        const float t0 = t[8 * j + 2 * e] * rz, t1 = t[8 * j + 2 * e + 1] * rz;
+                        if (MODE == kSimple) {
+                            o1[e] = pack2(t0, t1, p.is_bf16);
+                        } else {
+                            const float g0_ = dz * km[c], g1_ = dz * km[c + 1];
+                            if (MODE == kLinear) {
+                                o1[e] = pack2(t0 + g0_, t1 + g1_, p.is_bf16);
+                            } else {
+                                o1[e] = pack2(t0, t1, p.is_bf16);       // dq_rope
+                                o2[e] = pack2(g0_, g1_, p.is_bf16);     // dq
+                            }
+                            const float2 rf = unpack2(rw[e], p.is_bf16);
+                            qs[e] = pack2(rf.x * rz, rf.y * rz, p.is_bf16);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(ob + row * 128 + off) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                    if (MODE == kDecoupled)
+                        *reinterpret_cast<uint4*>(ob + KB * kBlockBytes + row * 128 + off) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+                    if (MODE != kSimple) *reinterpret_cast<uint4*>(qr_row + off) = make_uint4(qs[0], qs[1], qs[2], qs[3]);
+                }
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&tempty[a]);
+            if (MODE != kSimple) {
+                // two 16-bit columns whose sum is dz*z (paired with qr/z) or dz (decoupled: paired with q)
+                const float x = MODE == kLinear ? dz * z : dz;
+                const uint16_t hi = pack1(x, p.is_bf16);
+                const uint16_t lo = pack1(x - unpack1(hi, p.is_bf16), p.is_bf16);
+                uint8_t* dzt = stg + Cfg::kTmaBytes + (row >> 6) * 2048;
+                const int tc = row & 63;
+                *reinterpret_cast<uint16_t*>(dzt + ptx::sw128_offset(0, tc)) = hi;
+                *reinterpret_cast<uint16_t*>(dzt + ptx::sw128_offset(1, tc)) = lo;
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&qs_ready[s]);
+            ptx::mbar_arrive(&out_written[ob_i]);
+            if (issuer) {
+                if (!ptx::mbar_wait(&out_written[ob_i], pho, ab, 324)) break;
+                const int t0 = tile * kTileTokens;
+#pragma unroll
+                for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t0, unit);
+                if (MODE == kDecoupled) {
+#pragma unroll
+                    for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dq, ob + (KB + b) * kBlockBytes, b * 64, t0, unit);
+                }
+                ptx::tma_store_commit();
+            }
+            if (last) {
+                if (!ptx::mbar_wait(acc_full, (uint32_t)seg & 1u, ab, 325)) break;
+                ptx::tc_fence_after_sync();
+                const int slot = unit * sch.slots_per_unit + ((int)blockIdx.x - first_cta_of_unit(sch, unit));
+                float* out = p.part + (size_t)slot * p.state_stride;
+                drain_state_acc<DK, DV, (MODE != kSimple ? 2 : 0)>(tmem + Cfg::kColS, DV, out, warp, lane);
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(acc_empty);
+                ++seg;
+            }
+        }
+        if (issuer) ptx::tma_store_wait_all<0>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace tc
+}  // namespace fbla

@@ -1,0 +1,401 @@
+// Tensor-core kernels of the forward direction.
+//
+//   tc_fwd_state_kernel : [ S = Kr^T V | sum_t k ] per segment.  TMA streams 128-token tiles of
+//       k (kr) and v through a ring of shared-memory stages; one thread issues, per 16 tokens,
+//       tcgen05.mma with BOTH operands MN-major (the tiles are token-major, the contraction
+//       runs over tokens) accumulating fp32 in TMEM; the key sum is a second MMA of the key
+//       tile against a tile of ones.  HBM traffic: k and v once.
+//   tc_fwd_out_kernel   : o = (qr . scale*S) / (q . kmean + eps).  The bf16 state (and the key
+//       mean split in a high and a low 16-bit part, as two extra columns) sits in shared
+//       memory as the K-major B operand; per tile one MMA gives numerator and normaliser, the
+//       epilogue divides, converts and hands the tile to a TMA store.  HBM traffic: q once, o once.
+#pragma once
+
+#include "tc_common.cuh"
+
+namespace fbla {
+namespace tc {
+
+// ------------------------------------------------------------------------------------------
+template <int DK, int DV, int MODE>
+struct FwdStateCfg {
+    static constexpr int kKB = DK / 64, kVB = DV / 64;
+    static constexpr int kStageBlocks = kKB + kVB + (MODE == kDecoupled ? kKB : 0);
+    static constexpr int kStageBytes = kStageBlocks * kBlockBytes;
+    static constexpr int kStages = (192 * 1024) / kStageBytes < 8 ? (192 * 1024) / kStageBytes : 8;
+    static constexpr int kOnesBytes = 1024;
+    static constexpr int kTmemCols = (DV + 16) <= 128 ? 128 : 256;
+    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kOnesBytes + 256;
+};
+
+template <int DK, int DV, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const Params p) {
+    using Cfg = FwdStateCfg<DK, DV, MODE>;
+    constexpr int NS = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_1024(smem_raw);
+    uint8_t* stages = smem;
+    uint8_t* ones = stages + NS * Cfg::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ones + Cfg::kOnesBytes);
+    uint64_t* full = bars;              // [NS] TMA -> MMA
+    uint64_t* empty = bars + NS;        // [NS] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * NS; // MMA -> epilogue (segment finished)
+    uint64_t* acc_empty = acc_full + 1; // epilogue -> MMA (accumulator drained)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Schedule& sch = p.sch;
+    const int g0 = blockIdx.x * sch.tiles_per_cta;
+    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    const ptx::Abort ab{cta_abort, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; ++i) {
+            ptx::mbar_init(&full[i], 1);
+            ptx::mbar_init(&empty[i], 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, kEpiThreads);
+        *cta_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tm_kr);
+        ptx::prefetch_tensormap(&tm_v);
+    }
+    // a tile of ones (any layout of ones is ones): B operand of the key-sum MMA
+    for (int i = threadIdx.x; i < Cfg::kOnesBytes / 2; i += kThreads)
+        reinterpret_cast<uint16_t*>(ones)[i] = p.is_bf16 ? (uint16_t)0x3F80 : (uint16_t)0x3C00;
+    ptx::fence_proxy_async_smem();
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 101)) break;
+            ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+            const int unit = g / sch.tiles_per_unit;
+            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            uint8_t* st = stages + s * Cfg::kStageBytes;
+#pragma unroll
+            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_kr, &full[s], b * 64, t0, unit);
+#pragma unroll
+            for (int b = 0; b < Cfg::kVB; ++b)
+                ptx::tma_load_3d(st + (Cfg::kKB + b) * kBlockBytes, &tm_v, &full[s], b * 64, t0, unit);
+            if (MODE == kDecoupled) {
+#pragma unroll
+                for (int b = 0; b < Cfg::kKB; ++b)
+                    ptx::tma_load_3d(st + (Cfg::kKB + Cfg::kVB + b) * kBlockBytes, &tm_k, &full[s], b * 64, t0, unit);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc_s = ptx::instr_desc(DK, DV, p.is_bf16, true, true);
+        const uint32_t idesc_k = ptx::instr_desc(DK, 16, p.is_bf16, true, false);
+        const uint64_t d_ones = ptx::smem_desc(ptx::smem_u32(ones), 128, 256, ptx::kLayoutNone);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int tile = g % sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            if (first && !ptx::mbar_wait(acc_empty, ((uint32_t)seg & 1u) ^ 1u, ab, 111)) break;
+            if (!ptx::mbar_wait(&full[s], ph, ab, 112)) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t a_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t b_base = a_base + Cfg::kKB * kBlockBytes;
+            const uint32_t k_base = MODE == kDecoupled ? b_base + Cfg::kVB * kBlockBytes : a_base;
+#pragma unroll
+            for (int ks = 0; ks < kTileTokens / 16; ++ks) {
+                const bool acc = !(first && ks == 0);
+                const uint64_t da = ptx::smem_desc(a_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                const uint64_t db = ptx::smem_desc(b_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                ptx::mma_ss(tmem, da, db, idesc_s, acc);
+                if (MODE != kSimple) {
+                    const uint64_t dk = ptx::smem_desc(k_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + DV, dk, d_ones, idesc_k, acc);
+                }
+            }
+            ptx::mma_commit(&empty[s]);
+            if (last) {
+                ptx::mma_commit(acc_full);
+                ++seg;
+            }
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue: drain the accumulator of each finished segment ----------------
+        int seg = 0;
+        for (int g = g0; g < g1; ++g) {
+            const int unit = g / sch.tiles_per_unit;
+            const int tile = g - unit * sch.tiles_per_unit;
+            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            if (!last) continue;
+            if (!ptx::mbar_wait(acc_full, (uint32_t)seg & 1u, ab, 121)) break;
+            ptx::tc_fence_after_sync();
+            const int slot = unit * sch.slots_per_unit + ((int)blockIdx.x - first_cta_of_unit(sch, unit));
+            float* out = p.part + (size_t)slot * p.state_stride;
+            drain_state_acc<DK, DV, (MODE != kSimple ? 1 : 0)>(tmem, DV, out, warp, lane);
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(acc_empty);
+            ++seg;
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+// Adds the per-segment partials of every unit, in CTA order (deterministic).
+__global__ void __launch_bounds__(256)
+tc_reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ state, Schedule sch, int stride) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long long)sch.units * stride) return;
+    const int unit = (int)(i / stride);
+    const int e = (int)(i - (long long)unit * stride);
+    const int n = last_cta_of_unit(sch, unit) - first_cta_of_unit(sch, unit) + 1;
+    const float* src = part + (size_t)unit * sch.slots_per_unit * stride + e;
+    float s = 0.f;
+    for (int j = 0; j < n; ++j) s += src[(size_t)j * stride];
+    state[i] = s;
+}
+
+// ------------------------------------------------------------------------------------------
+template <int DK, int DV, int MODE>
+struct FwdOutCfg {
+    static constexpr int kKB = DK / 64, kVB = DV / 64;
+    static constexpr int kBopRows = DV + (MODE != kSimple ? 16 : 0);     // N of the B operand
+    static constexpr int kBopBlock = kBopRows * 128;                      // bytes per 64-wide K block
+    static constexpr int kBopBytes = ((kKB * kBopBlock + 1023) / 1024) * 1024;
+    static constexpr int kStageBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
+    static constexpr int kStageBytes = kStageBlocks * kBlockBytes;
+    static constexpr int kOutBytes = kVB * kBlockBytes;                   // one staged output tile
+    static constexpr int kAvail = 200 * 1024 - kBopBytes - 2 * kOutBytes;
+    static constexpr int kStages = kAvail / kStageBytes < 8 ? kAvail / kStageBytes : 8;
+    static constexpr int kAccCols = DV + 16;
+    static constexpr int kTmemCols = 2 * kAccCols <= 256 ? 256 : 512;
+    static constexpr int kSmemBytes = 1024 + kBopBytes + kStages * kStageBytes + 2 * kOutBytes + 512;
+};
+
+template <int DK, int DV, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
+                  const __grid_constant__ CUtensorMap tm_o, const Params p) {
+    using Cfg = FwdOutCfg<DK, DV, MODE>;
+    constexpr int NS = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_1024(smem_raw);
+    uint8_t* bop = smem;
+    uint8_t* stages = bop + Cfg::kBopBytes;
+    uint8_t* outbuf = stages + NS * Cfg::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(outbuf + 2 * Cfg::kOutBytes);
+    uint64_t* full = bars;                 // [NS]
+    uint64_t* empty = bars + NS;           // [NS]
+    uint64_t* tfull = bars + 2 * NS;       // [2] accumulator ready
+    uint64_t* tempty = tfull + 2;          // [2] accumulator drained
+    uint64_t* bop_ready = tempty + 2;      // state of the segment is in shared memory
+    uint64_t* out_free = bop_ready + 1;    // [2] staged tile no longer read by its TMA store
+    uint64_t* out_written = out_free + 2;  // [2] staged tile written by all epilogue threads
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_written + 2);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Schedule& sch = p.sch;
+    const int g0 = blockIdx.x * sch.tiles_per_cta;
+    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    const ptx::Abort ab{cta_abort, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; ++i) {
+            ptx::mbar_init(&full[i], 1);
+            ptx::mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&tfull[i], 1);
+            ptx::mbar_init(&tempty[i], kEpiThreads);
+            ptx::mbar_init(&out_free[i], 1);
+            ptx::mbar_init(&out_written[i], kEpiThreads);
+        }
+        ptx::mbar_init(bop_ready, kEpiThreads);
+        *cta_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tm_qr);
+        ptx::prefetch_tensormap(&tm_o);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 201)) break;
+            ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+            const int unit = g / sch.tiles_per_unit;
+            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            uint8_t* st = stages + s * Cfg::kStageBytes;
+#pragma unroll
+            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_qr, &full[s], b * 64, t0, unit);
+            if (MODE == kDecoupled) {
+#pragma unroll
+                for (int b = 0; b < Cfg::kKB; ++b)
+                    ptx::tma_load_3d(st + (Cfg::kKB + b) * kBlockBytes, &tm_q, &full[s], b * 64, t0, unit);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc_n = ptx::instr_desc(128, DV, p.is_bf16, false, false);
+        const uint32_t idesc_z = ptx::instr_desc(128, 16, p.is_bf16, false, false);
+        const uint32_t bop_base = ptx::smem_u32(bop);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int a = it & 1;
+            const int tile = g % sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            if (first) {
+                if (!ptx::mbar_wait(bop_ready, (uint32_t)seg & 1u, ab, 211)) break;
+                ++seg;
+            }
+            if (!ptx::mbar_wait(&full[s], ph, ab, 212)) break;
+            if (!ptx::mbar_wait(&tempty[a], ((uint32_t)(it >> 1) & 1u) ^ 1u, ab, 213)) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t qr_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t q_base = MODE == kDecoupled ? qr_base + Cfg::kKB * kBlockBytes : qr_base;
+            const uint32_t acc = tmem + a * Cfg::kAccCols;
+#pragma unroll
+            for (int kb = 0; kb < Cfg::kKB; ++kb) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const bool accum = !(kb == 0 && kk == 0);
+                    const uint64_t da = ptx::smem_desc(qr_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t db = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(acc, da, db, idesc_n, accum);
+                    if (MODE != kSimple) {
+                        const uint64_t dq = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t dz = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + DV * 128 + kk * 32, 16, 1024,
+                                                           ptx::kLayoutSw128);
+                        ptx::mma_ss(acc + DV, dq, dz, idesc_z, accum);
+                    }
+                }
+            }
+            ptx::mma_commit(&empty[s]);
+            ptx::mma_commit(&tfull[a]);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;
+        const int et = threadIdx.x - 64;                 // 0..127
+        const int row = quarter * 32 + lane;             // token row of this thread inside a tile
+        const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool issuer = (et == 0);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int unit = g / sch.tiles_per_unit;
+            const int tile = g - unit * sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            const int a = it & 1;
+            const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
+            if (first) {
+                // Every MMA of the previous segment has completed (its accumulators were drained
+                // below), so the B operand can be rewritten for this unit.
+                const float* st = p.state + (size_t)unit * p.state_stride;
+                for (int i = et; i < DK * DV; i += kEpiThreads) {
+                    const int k = i / DV, v = i - k * DV;
+                    const uint16_t h = pack1(st[i] * p.scale, p.is_bf16);
+                    *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(v, k & 63)) = h;
+                }
+                if (MODE != kSimple) {
+                    for (int i = et; i < 16 * DK; i += kEpiThreads) {
+                        const int r = i / DK, k = i - r * DK;
+                        uint16_t h = 0;
+                        if (r < 2) {
+                            const float km = st[DK * DV + k] * p.inv_norm;
+                            const uint16_t hi = pack1(km, p.is_bf16);
+                            h = r == 0 ? hi : pack1(km - unpack1(hi, p.is_bf16), p.is_bf16);
+                        }
+                        *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(DV + r, k & 63)) = h;
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(bop_ready);
+                ++seg;
+            }
+            if (!ptx::mbar_wait(&tfull[a], ph2, ab, 221)) break;
+            ptx::tc_fence_after_sync();
+            float rz = 1.f;
+            if (MODE != kSimple) {
+                float zc[16];
+                ptx::tmem_ld16(t_lane + a * Cfg::kAccCols + DV, zc);
+                ptx::tmem_ld_wait();
+                rz = 1.f / (zc[0] + zc[1] + p.eps);
+            }
+            // the staged tile of two tiles ago must have been read by its store
+            if (issuer) {
+                ptx::tma_store_wait_read<1>();
+                ptx::mbar_arrive(&out_free[a]);
+            }
+            if (!ptx::mbar_wait(&out_free[a], ph2, ab, 222)) break;
+            uint8_t* ob = outbuf + a * Cfg::kOutBytes;
+#pragma unroll
+            for (int c0 = 0; c0 < DV; c0 += 32) {
+                float v[32];
+                ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + c0, v);
+                ptx::tmem_ld_wait();
+                uint8_t* blk = ob + (c0 >> 6) * kBlockBytes + row * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 w;
+                    w.x = pack2(v[8 * j] * rz, v[8 * j + 1] * rz, p.is_bf16);
+                    w.y = pack2(v[8 * j + 2] * rz, v[8 * j + 3] * rz, p.is_bf16);
+                    w.z = pack2(v[8 * j + 4] * rz, v[8 * j + 5] * rz, p.is_bf16);
+                    w.w = pack2(v[8 * j + 6] * rz, v[8 * j + 7] * rz, p.is_bf16);
+                    const int chunk = ((c0 & 63) >> 3) + j;
+                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                }
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&tempty[a]);
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&out_written[a]);
+            if (issuer) {
+                if (!ptx::mbar_wait(&out_written[a], ph2, ab, 223)) break;
+#pragma unroll
+                for (int b = 0; b < Cfg::kVB; ++b)
+                    ptx::tma_store_3d(&tm_o, ob + b * kBlockBytes, b * 64, tile * kTileTokens, unit);
+                ptx::tma_store_commit();
+            }
+        }
+        if (issuer) ptx::tma_store_wait_all<0>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace tc
+}  // namespace fbla

@@ -1,17 +1,296 @@
+// Host side of the tensor-core path: TMA tensor maps, the static tile schedule, shared
+// memory opt-in and the launches of the kernels in tc_fwd.cuh / tc_bwd.cuh.
 #include "tc_kernels.cuh"
 
-namespace fbla {
+#include <cuda.h>
 
-bool tc_supported(const KParams&, int) { return false; }
-int64_t tc_workspace_bytes(const KParams&) { return 0; }
-cudaError_t tc_fwd_state(const KParams&, int, const void*, const void*, const void*, float*, void*,
-                         cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t tc_fwd_out(const KParams&, int, const void*, const void*, const float*, void*, cudaStream_t) {
-    return cudaErrorNotSupported;
+#include <mutex>
+
+#include "tc_bwd.cuh"
+#include "tc_fwd.cuh"
+
+namespace fbla {
+namespace {
+
+using namespace tc;
+
+// ---- driver entry point for tensor-map encoding (no link-time dependency on libcuda) ------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
 }
-cudaError_t tc_bwd_state(const KParams&, int, const void*, const void*, const void*, const float*, void*,
-                         void*, float*, void*, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t tc_bwd_in(const KParams&, int, const void*, const void*, const float*, void*, void*, void*,
-                      cudaStream_t) { return cudaErrorNotSupported; }
+
+// (units, T, D) 16-bit tensor viewed as a 3-D map {D, T, units}; one box = 64 features x 128
+// tokens of one unit, written to shared memory in the 128-byte-swizzled layout.  Tokens past T
+// read as zero and are dropped on stores.
+cudaError_t make_map(CUtensorMap* m, const void* base, int dtype, int D, int64_t T, int units) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)units};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)T * D * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)kTileTokens, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = dtype == FBLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+Schedule make_schedule(const KParams& p, int sms) {
+    Schedule s;
+    s.units = p.units;
+    s.tiles_per_unit = (int)((p.seq_len + kTileTokens - 1) / kTileTokens);
+    s.total_tiles = s.units * s.tiles_per_unit;
+    const int ctas = s.total_tiles < sms ? s.total_tiles : sms;
+    s.tiles_per_cta = (s.total_tiles + ctas - 1) / ctas;
+    s.ctas = (s.total_tiles + s.tiles_per_cta - 1) / s.tiles_per_cta;
+    s.slots_per_unit = (s.tiles_per_unit + s.tiles_per_cta - 1) / s.tiles_per_cta + 1;
+    return s;
+}
+
+// Host-visible status word the kernels write when a bounded wait gives up.
+int* g_status_host = nullptr;
+int* g_status_dev = nullptr;
+std::once_flag g_status_once;
+
+int* status_word() {
+    std::call_once(g_status_once, [] {
+        void* h = nullptr;
+        if (cudaHostAlloc(&h, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+            *static_cast<int*>(h) = 0;
+            void* d = nullptr;
+            if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) {
+                g_status_host = static_cast<int*>(h);
+                g_status_dev = static_cast<int*>(d);
+            }
+        }
+    });
+    return g_status_dev;
+}
+
+Params make_params(const KParams& p, int dtype, const Schedule& s) {
+    Params q;
+    q.sch = s;
+    q.seq_len = (int)p.seq_len;
+    q.scale = p.scale;
+    q.inv_norm = p.inv_norm > 0.f ? p.inv_norm : 1.f / (float)p.seq_len;
+    q.eps = p.eps;
+    q.is_bf16 = dtype == FBLA_BF16;
+    q.status = status_word();
+    q.part = nullptr;
+    q.state = nullptr;
+    q.state_stride = p.state_stride;
+    return q;
+}
+
+template <typename K>
+cudaError_t set_smem(K kernel, int bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int mode_of(const KParams& p, bool decoupled) { return !p.normalize ? kSimple : (decoupled ? kDecoupled : kLinear); }
+
+cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
+    const long long total = (long long)q.sch.units * q.state_stride;
+    tc_reduce_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(q.part, state, q.sch, q.state_stride);
+    note_launches(1);
+    return cudaGetLastError();
+}
+
+// ---- per-shape launch helpers ----------------------------------------------------------------
+template <int DK, int DV, int MODE>
+cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tk, const CUtensorMap& tv,
+                             cudaStream_t st) {
+    using Cfg = FwdStateCfg<DK, DV, MODE>;
+    static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
+    auto kernel = tc_fwd_state_kernel<DK, DV, MODE>;
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tkr, tk, tv, q);
+    note_launches(1);
+    return cudaGetLastError();
+}
+
+template <int DK, int DV, int MODE>
+cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& to,
+                           cudaStream_t st) {
+    using Cfg = FwdOutCfg<DK, DV, MODE>;
+    static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
+    static_assert(Cfg::kStages >= 2, "pipeline depth");
+    auto kernel = tc_fwd_out_kernel<DK, DV, MODE>;
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tqr, tq, to, q);
+    note_launches(1);
+    return cudaGetLastError();
+}
+
+template <int DK, int DV, int MODE>
+cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
+                             const CUtensorMap& tdq, const CUtensorMap& tdqr, cudaStream_t st) {
+    using Cfg = BwdStateCfg<DK, DV, MODE>;
+    static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
+    static_assert(Cfg::kStages >= 2, "pipeline depth");
+    auto kernel = tc_bwd_state_kernel<DK, DV, MODE>;
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tqr, tq, tdo, tdq, tdqr, q);
+    note_launches(1);
+    return cudaGetLastError();
+}
+
+template <int DK, int DV, int MODE>
+cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tv, const CUtensorMap& tdk,
+                          const CUtensorMap& tdkr, const CUtensorMap& tdv, cudaStream_t st) {
+    using Cfg = BwdInCfg<DK, DV, MODE>;
+    static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
+    static_assert(Cfg::kStages >= 2, "pipeline depth");
+    auto kernel = tc_bwd_in_kernel<DK, DV, MODE>;
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tkr, tv, tdk, tdkr, tdv, q);
+    note_launches(1);
+    return cudaGetLastError();
+}
+
+// Expands to a switch over (dk, dv, mode); `CALL` names one of the launch_* templates.
+#define FBLA_TC_DISPATCH(CALL, ...)                                                                     \
+    do {                                                                                                \
+        const int key = (p.dk == 128 ? 2 : 0) + (p.dv == 128 ? 1 : 0);                                  \
+        switch (mode * 4 + key) {                                                                       \
+            case 0: return CALL<64, 64, kSimple>(__VA_ARGS__);                                          \
+            case 1: return CALL<64, 128, kSimple>(__VA_ARGS__);                                         \
+            case 2: return CALL<128, 64, kSimple>(__VA_ARGS__);                                         \
+            case 3: return CALL<128, 128, kSimple>(__VA_ARGS__);                                        \
+            case 4: return CALL<64, 64, kLinear>(__VA_ARGS__);                                          \
+            case 5: return CALL<64, 128, kLinear>(__VA_ARGS__);                                         \
+            case 6: return CALL<128, 64, kLinear>(__VA_ARGS__);                                         \
+            case 7: return CALL<128, 128, kLinear>(__VA_ARGS__);                                        \
+            case 8: return CALL<64, 64, kDecoupled>(__VA_ARGS__);                                       \
+            default: return cudaErrorNotSupported;                                                      \
+        }                                                                                               \
+    } while (0)
+
+}  // namespace
+
+// The tensor-core kernels serve 16-bit inputs in the fixed-length layout with dk, dv in
+// {64, 128}; the decoupled operator at 64 x 64 only (its extra tiles do not fit the shared
+// memory budget at 128).
+bool tc_supported(const KParams& p, int dtype) {
+    if (dtype != FBLA_BF16 && dtype != FBLA_F16) return false;
+    if (p.cu != nullptr) return false;
+    if ((p.dk != 64 && p.dk != 128) || (p.dv != 64 && p.dv != 128)) return false;
+    if (p.seq_len < 1 || p.units < 1) return false;
+    if (encode_fn() == nullptr) return false;
+    return true;
+}
+
+bool tc_supported_decoupled(const KParams& p) { return p.dk == 64 && p.dv == 64; }
+
+int64_t tc_workspace_bytes(const KParams& p) {
+    const Schedule s = make_schedule(p, sm_count());
+    return (int64_t)s.units * s.slots_per_unit * p.state_stride * (int64_t)sizeof(float);
+}
+
+int tc_device_status() { return g_status_host != nullptr ? *g_status_host : 0; }
+
+cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v, float* state,
+                         void* ws, cudaStream_t st) {
+    const bool dec = k_rope != nullptr && k_rope != k;
+    const int mode = mode_of(p, dec);
+    const Schedule s = make_schedule(p, sm_count());
+    Params q = make_params(p, dtype, s);
+    if (q.status == nullptr) return cudaErrorMemoryAllocation;
+    q.part = static_cast<float*>(ws);
+    CUtensorMap tkr, tk, tv;
+    cudaError_t e;
+    if ((e = make_map(&tkr, dec ? k_rope : k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tk, k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, tkr, tk, tv, st); };
+    if ((e = launch()) != cudaSuccess) return e;
+    return reduce_partials(q, state, st);
+}
+
+cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* q_rope, const float* state, void* o,
+                       cudaStream_t st) {
+    const bool dec = q_rope != nullptr && q_rope != q_;
+    const int mode = mode_of(p, dec);
+    const Schedule s = make_schedule(p, sm_count());
+    Params q = make_params(p, dtype, s);
+    if (q.status == nullptr) return cudaErrorMemoryAllocation;
+    q.state = state;
+    CUtensorMap tqr, tq, to;
+    cudaError_t e;
+    if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tq, q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&to, o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    FBLA_TC_DISPATCH(launch_fwd_out, q, tqr, tq, to, st);
+}
+
+cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void* q_rope, const void* d_o,
+                         const float* state, void* dq, void* dq_rope, float* dstate, void* ws, cudaStream_t st) {
+    const bool dec = dq_rope != nullptr;
+    const int mode = mode_of(p, dec);
+    const Schedule s = make_schedule(p, sm_count());
+    Params q = make_params(p, dtype, s);
+    if (q.status == nullptr) return cudaErrorMemoryAllocation;
+    q.state = state;
+    q.part = static_cast<float*>(ws);
+    CUtensorMap tqr, tq, tdo, tdq, tdqr;
+    cudaError_t e;
+    if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tq, q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdo, d_o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdq, dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdqr, dec ? dq_rope : dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, tqr, tq, tdo, tdq, tdqr, st); };
+    if ((e = launch()) != cudaSuccess) return e;
+    return reduce_partials(q, dstate, st);
+}
+
+cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const void* v, const float* dstate, void* dk,
+                      void* dk_rope, void* dv, cudaStream_t st) {
+    const bool dec = dk_rope != nullptr;
+    const int mode = mode_of(p, dec);
+    const Schedule s = make_schedule(p, sm_count());
+    Params q = make_params(p, dtype, s);
+    if (q.status == nullptr) return cudaErrorMemoryAllocation;
+    q.state = dstate;
+    CUtensorMap tkr, tv, tdk, tdkr, tdv;
+    cudaError_t e;
+    if ((e = make_map(&tkr, k_rope, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdk, dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdkr, dec ? dk_rope : dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdv, dv, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    FBLA_TC_DISPATCH(launch_bwd_in, q, tkr, tv, tdk, tdkr, tdv, st);
+}
 
 }  // namespace fbla

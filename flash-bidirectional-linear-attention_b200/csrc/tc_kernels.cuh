@@ -7,6 +7,10 @@
 namespace fbla {
 
 bool tc_supported(const KParams& p, int dtype);
+// The decoupled operator has tensor-core kernels at dk = dv = 64 only.
+bool tc_supported_decoupled(const KParams& p);
+// Status word written by a kernel whose bounded wait gave up (0 = none did).
+int tc_device_status();
 int64_t tc_workspace_bytes(const KParams& p);
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
                          float* state, void* ws, cudaStream_t st);
