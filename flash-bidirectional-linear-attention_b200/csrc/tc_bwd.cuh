@@ -21,22 +21,39 @@ namespace tc {
 // Writes the [DK x DV] fp32 matrix `src` (row-major), multiplied by `scale`, into shared memory as
 // 16-bit DV/64 blocks of [DK rows][64 columns] in the 128-byte-swizzled layout.  Read K-major it is
 // the operand B[n = row][k = column]; read MN-major it is B[k = row][n = column].
-template <int DK, int DV>
+// With SPLIT a second copy holding the rounding residual (x - high part, again 16-bit) is written
+// DV/64 blocks further on: issuing every MMA once per copy restores ~16 bits of the fp32 state.
+template <int DK, int DV, bool SPLIT>
 __device__ __forceinline__ void stage_matrix_sw128(uint8_t* dst, const float* __restrict__ src, float scale,
                                                    int is_bf16, int et) {
     for (int i = et; i < DK * DV / 2; i += kEpiThreads) {
         const int k = (2 * i) / DV, v = (2 * i) - k * DV;
-        const float2 x = *reinterpret_cast<const float2*>(src + 2 * i);
-        const uint32_t h = pack2(x.x * scale, x.y * scale, is_bf16);
-        *reinterpret_cast<uint32_t*>(dst + (v >> 6) * (DK * 128) + ptx::sw128_offset(k, v & 63)) = h;
+        float2 x = *reinterpret_cast<const float2*>(src + 2 * i);
+        x.x *= scale;
+        x.y *= scale;
+        const uint32_t h = pack2(x.x, x.y, is_bf16);
+        uint8_t* at = dst + (v >> 6) * (DK * 128) + ptx::sw128_offset(k, v & 63);
+        *reinterpret_cast<uint32_t*>(at) = h;
+        if (SPLIT) {
+            const float2 hf = unpack2(h, is_bf16);
+            *reinterpret_cast<uint32_t*>(at + (DV / 64) * (DK * 128)) = pack2(x.x - hf.x, x.y - hf.y, is_bf16);
+        }
     }
 }
+
+// The 128 x 128 kernels have no shared memory left for the residual copy.
+template <int DK, int DV>
+struct SplitState {
+    static constexpr bool value = !(DK == 128 && DV == 128);
+};
 
 // ------------------------------------------------------------------------------------------
 template <int DK, int DV, int MODE>
 struct BwdInCfg {
     static constexpr int kKB = DK / 64, kVB = DV / 64;
-    static constexpr int kBopBytes = kVB * DK * 128;                        // 16-bit scale*dS
+    static constexpr bool kSplit = SplitState<DK, DV>::value;
+    static constexpr int kBopOne = kVB * DK * 128;                          // one 16-bit copy of scale*dS
+    static constexpr int kBopBytes = kBopOne * (kSplit ? 2 : 1);            // high part (+ residual)
     static constexpr int kVecBytes = 1024;                                  // fp32 dkm / L
     static constexpr int kStageBytes = (kKB + kVB) * kBlockBytes;           // v tile, kr tile
     static constexpr int kOutBytes = (kKB + kVB) * kBlockBytes;             // staged dk (dkr) and dv tile
@@ -161,6 +178,11 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     const uint64_t da = ptx::smem_desc(v_base + vb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     const uint64_t db = ptx::smem_desc(bop_base + vb * (DK * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     ptx::mma_ss(acc, da, db, idesc_dk, !(vb == 0 && kk == 0));
+                    if (Cfg::kSplit) {
+                        const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopOne + vb * (DK * 128) + kk * 32, 16, 1024,
+                                                           ptx::kLayoutSw128);
+                        ptx::mma_ss(acc, da, dl, idesc_dk, true);
+                    }
                 }
             }
             // dv[tok][v] = sum_k KR[tok][k] * dS[k][v]  (B MN-major: rows k, 128 bytes along v)
@@ -171,6 +193,11 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     const uint64_t da = ptx::smem_desc(kr_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     const uint64_t db = ptx::smem_desc(bop_base + (kb * 64 + kk * 16) * 128, DK * 128, 1024, ptx::kLayoutSw128);
                     ptx::mma_ss(acc + DK, da, db, idesc_dv, !(kb == 0 && kk == 0));
+                    if (Cfg::kSplit) {
+                        const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopOne + (kb * 64 + kk * 16) * 128, DK * 128, 1024,
+                                                           ptx::kLayoutSw128);
+                        ptx::mma_ss(acc + DK, da, dl, idesc_dv, true);
+                    }
                 }
             }
             ptx::mma_commit(&empty[s]);
@@ -205,7 +232,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     if (!ptx::mbar_wait(const_free, (uint32_t)seg & 1u, ab, 425)) break;
                 }
                 ++seg;
-                stage_matrix_sw128<DK, DV>(bop, st, p.scale, p.is_bf16, et);
+                stage_matrix_sw128<DK, DV, Cfg::kSplit>(bop, st, p.scale, p.is_bf16, et);
                 if (MODE != kSimple)
                     for (int i = et; i < DK; i += kEpiThreads) vec[i] = st[DK * DV + i] * p.inv_norm;
                 if (MODE == kDecoupled) {
@@ -301,7 +328,9 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
 template <int DK, int DV, int MODE>
 struct BwdStateCfg {
     static constexpr int kKB = DK / 64, kVB = DV / 64;
-    static constexpr int kBopBytes = kVB * DK * 128;                        // 16-bit scale*S
+    static constexpr bool kSplit = SplitState<DK, DV>::value;
+    static constexpr int kBopOne = kVB * DK * 128;                          // one 16-bit copy of scale*S
+    static constexpr int kBopBytes = kBopOne * (kSplit ? 2 : 1);            // high part (+ residual)
     static constexpr int kVecBytes = 1024;                                  // fp32 kmean
     static constexpr int kDzBytes = MODE != kSimple ? 4096 : 0;             // [2 token blocks][16 rows][128 B]
     static constexpr int kQBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
@@ -481,6 +510,11 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     const uint64_t da = ptx::smem_desc(do_base + vb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     const uint64_t db = ptx::smem_desc(bop_base + vb * (DK * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     ptx::mma_ss(tmem + Cfg::kColT + a * DK, da, db, idesc_t, !(vb == 0 && kk == 0));
+                    if (Cfg::kSplit) {
+                        const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopOne + vb * (DK * 128) + kk * 32, 16, 1024,
+                                                           ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + Cfg::kColT + a * DK, da, dl, idesc_t, true);
+                    }
                 }
             }
             ptx::mma_commit(&tfull[a]);
@@ -511,7 +545,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                 // km of the previous unit is read by every epilogue thread until it has arrived on
                 // out_written of the previous tile
                 if (it > 0 && !ptx::mbar_wait(&out_written[(it - 1) % NO], (uint32_t)((it - 1) / NO) & 1u, ab, 326)) break;
-                stage_matrix_sw128<DK, DV>(bop, st, p.scale, p.is_bf16, et);
+                stage_matrix_sw128<DK, DV, Cfg::kSplit>(bop, st, p.scale, p.is_bf16, et);
                 if (MODE != kSimple)
                     for (int i = et; i < DK; i += kEpiThreads) km[i] = st[DK * DV + i] * p.inv_norm;
                 ptx::fence_proxy_async_smem();

@@ -179,7 +179,9 @@ struct FwdOutCfg {
     static constexpr int kKB = DK / 64, kVB = DV / 64;
     static constexpr int kBopRows = DV + (MODE != kSimple ? 16 : 0);     // N of the B operand
     static constexpr int kBopBlock = kBopRows * 128;                      // bytes per 64-wide K block
-    static constexpr int kBopBytes = ((kKB * kBopBlock + 1023) / 1024) * 1024;
+    static constexpr int kBopHiBytes = ((kKB * kBopBlock + 1023) / 1024) * 1024;
+    static constexpr int kBopLoBlock = DV * 128;                          // residual of scale*S (no normaliser rows)
+    static constexpr int kBopBytes = kBopHiBytes + kKB * kBopLoBlock;
     static constexpr int kStageBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
     static constexpr int kStageBytes = kStageBlocks * kBlockBytes;
     static constexpr int kOutBytes = kVB * kBlockBytes;                   // one staged output tile
@@ -291,7 +293,10 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                     const bool accum = !(kb == 0 && kk == 0);
                     const uint64_t da = ptx::smem_desc(qr_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     const uint64_t db = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopHiBytes + kb * Cfg::kBopLoBlock + kk * 32, 16, 1024,
+                                                       ptx::kLayoutSw128);
                     ptx::mma_ss(acc, da, db, idesc_n, accum);
+                    ptx::mma_ss(acc, da, dl, idesc_n, true);
                     if (MODE != kSimple) {
                         const uint64_t dq = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
                         const uint64_t dz = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + DV * 128 + kk * 32, 16, 1024,
@@ -323,8 +328,12 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                 const float* st = p.state + (size_t)unit * p.state_stride;
                 for (int i = et; i < DK * DV; i += kEpiThreads) {
                     const int k = i / DV, v = i - k * DV;
-                    const uint16_t h = pack1(st[i] * p.scale, p.is_bf16);
+                    const float x = st[i] * p.scale;
+                    const uint16_t h = pack1(x, p.is_bf16);
                     *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(v, k & 63)) = h;
+                    // rounding residual: a second B operand accumulated into the same columns
+                    *reinterpret_cast<uint16_t*>(bop + Cfg::kBopHiBytes + (k >> 6) * Cfg::kBopLoBlock +
+                                                 ptx::sw128_offset(v, k & 63)) = pack1(x - unpack1(h, p.is_bf16), p.is_bf16);
                 }
                 if (MODE != kSimple) {
                     for (int i = et; i < 16 * DK; i += kEpiThreads) {

@@ -34,7 +34,43 @@ EncodeTiledFn encode_fn() {
 // (units, T, D) 16-bit tensor viewed as a 3-D map {D, T, units}; one box = 64 features x 128
 // tokens of one unit, written to shared memory in the 128-byte-swizzled layout.  Tokens past T
 // read as zero and are dropped on stores.
+struct MapKey {
+    const void* base;
+    int dtype, D, units;
+    int64_t T;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && dtype == o.dtype && D == o.D && units == o.units && T == o.T;
+    }
+};
+struct MapSlot {
+    MapKey key{nullptr, 0, 0, 0, 0};
+    CUtensorMap map;
+};
+
+cudaError_t encode_map(CUtensorMap* m, const void* base, int dtype, int D, int64_t T, int units);
+
+// Encoding a tensor map costs a few microseconds on the host; training loops call with the same
+// buffers again and again, so each thread keeps the last maps it made.  A map is a pure function
+// of its key (address, type, extents), so a stale entry can never be wrong.
 cudaError_t make_map(CUtensorMap* m, const void* base, int dtype, int D, int64_t T, int units) {
+    constexpr int kSlots = 64;
+    thread_local MapSlot cache[kSlots];
+    const MapKey key{base, dtype, D, units, T};
+    const size_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull + (size_t)T * 31 + (size_t)D;
+    MapSlot& slot = cache[(h >> 20) % kSlots];
+    if (slot.key == key) {
+        *m = slot.map;
+        return cudaSuccess;
+    }
+    const cudaError_t e = encode_map(m, base, dtype, D, T, units);
+    if (e == cudaSuccess) {
+        slot.key = key;
+        slot.map = *m;
+    }
+    return e;
+}
+
+cudaError_t encode_map(CUtensorMap* m, const void* base, int dtype, int D, int64_t T, int units) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return cudaErrorNotSupported;
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)units};
@@ -107,12 +143,17 @@ Params make_params(const KParams& p, int dtype, const Schedule& s) {
     return q;
 }
 
+// Opt in to the large dynamic shared memory once per kernel and device; `done` is the
+// per-kernel record kept by the caller (one per template instantiation).
 template <typename K>
-cudaError_t set_smem(K kernel, int bytes) {
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+cudaError_t set_smem(K kernel, int bytes, bool (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (done[dev]) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
 }
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int mode_of(const KParams& p, bool decoupled) { return !p.normalize ? kSimple : (decoupled ? kDecoupled : kLinear); }
 
@@ -130,7 +171,8 @@ cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUte
     using Cfg = FwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     auto kernel = tc_fwd_state_kernel<DK, DV, MODE>;
-    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
     kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tkr, tk, tv, q);
     note_launches(1);
@@ -144,7 +186,8 @@ cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtens
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
     auto kernel = tc_fwd_out_kernel<DK, DV, MODE>;
-    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
     kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tqr, tq, to, q);
     note_launches(1);
@@ -158,7 +201,8 @@ cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUte
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
     auto kernel = tc_bwd_state_kernel<DK, DV, MODE>;
-    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
     kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tqr, tq, tdo, tdq, tdqr, q);
     note_launches(1);
@@ -172,7 +216,8 @@ cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtenso
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
     auto kernel = tc_bwd_in_kernel<DK, DV, MODE>;
-    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes);
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
     kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tkr, tv, tdk, tdkr, tdv, q);
     note_launches(1);

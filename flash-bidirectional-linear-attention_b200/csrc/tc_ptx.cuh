@@ -59,11 +59,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     int spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (((++spins) & 63) == 0) {
+        ++spins;
+        // only waits of many microseconds back off (a sleeping waiter wakes up late)
+        if (spins > 4096) __nanosleep(200);
+        if ((spins & 63) == 0) {
             if (*ab.cta_flag != 0) return false;
             if (clock64() - t0 > kWaitCycles) {
                 *ab.cta_flag = where;
-                atomicCAS(ab.status, 0, where);
+                *ab.status = where;
                 __threadfence_system();
                 return false;
             }

@@ -59,8 +59,13 @@ def check(got, ref, dtype, what="", magnitude=None):
         err2 = O.max_abs_over_rms(got, ref)
         assert err2 <= 20 * FP32_REL, f"{what}: max-abs/rms {err2:.3e}"
     else:
+        # The bar is 2e-2 of the output RMS.  Merely rounding the exact result to the 16-bit
+        # output type already costs up to 2^-8 of the largest element (0.4 % of 5 x RMS = 2e-2),
+        # so for heavy-tailed outputs the bar is lifted to 1.25 x that unavoidable floor.
         err = O.max_abs_over_rms(got, ref)
-        assert err <= LOWP_MAXABS_OVER_RMS, f"{what}: max-abs/rms {err:.3e} > {LOWP_MAXABS_OVER_RMS}"
+        floor = O.max_abs_over_rms(ref.to(dtype), ref)
+        bar = max(LOWP_MAXABS_OVER_RMS, 1.25 * floor)
+        assert err <= bar, f"{what}: max-abs/rms {err:.3e} > {bar:.3e} (rounding floor {floor:.3e})"
 
 
 def run_op(fn, inputs, do):
