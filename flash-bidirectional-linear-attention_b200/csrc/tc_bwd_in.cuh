@@ -1,0 +1,321 @@
+// Tensor-core kernel of the second backward pass.
+//
+//   tc_bwd_in_kernel : dk = v . (scale*dS)^T + dkm/L,  dv = kr . (scale*dS)  per 128-token tile, both
+//     from one copy of the 16-bit dS in shared memory (read K-major by the first MMA, MN-major by
+//     the second).  HBM traffic: k, v once; dk, dv once.
+#pragma once
+
+#include "tc_common.cuh"
+
+namespace fbla {
+namespace tc {
+
+// Writes the [DK x DV] fp32 matrix `src` (row-major), multiplied by `scale`, into shared memory as
+// 16-bit DV/64 blocks of [DK rows][64 columns] in the 128-byte-swizzled layout.  Read K-major it is
+// the operand B[n = row][k = column]; read MN-major it is B[k = row][n = column].
+// With SPLIT a second copy holding the rounding residual (x - high part, again 16-bit) is written
+// DV/64 blocks further on: issuing every MMA once per copy restores ~16 bits of the fp32 state.
+template <int DK, int DV, bool SPLIT>
+__device__ __forceinline__ void stage_matrix_sw128(uint8_t* dst, const float* __restrict__ src, float scale,
+                                                   int is_bf16, int et) {
+    for (int i = et; i < DK * DV / 2; i += kEpiThreads) {
+        const int k = (2 * i) / DV, v = (2 * i) - k * DV;
+        float2 x = *reinterpret_cast<const float2*>(src + 2 * i);
+        x.x *= scale;
+        x.y *= scale;
+        const uint32_t h = pack2(x.x, x.y, is_bf16);
+        uint8_t* at = dst + (v >> 6) * (DK * 128) + ptx::sw128_offset(k, v & 63);
+        *reinterpret_cast<uint32_t*>(at) = h;
+        if (SPLIT) {
+            const float2 hf = unpack2(h, is_bf16);
+            *reinterpret_cast<uint32_t*>(at + (DV / 64) * (DK * 128)) = pack2(x.x - hf.x, x.y - hf.y, is_bf16);
+        }
+    }
+}
+
+// The 128 x 128 kernels have no shared memory left for the residual copy.
+template <int DK, int DV>
+struct SplitState {
+    static constexpr bool value = !(DK == 128 && DV == 128);
+};
+
+// ------------------------------------------------------------------------------------------
+template <int DK, int DV, int MODE>
+struct BwdInCfg {
+    static constexpr int kKB = DK / 64, kVB = DV / 64;
+    static constexpr bool kSplit = SplitState<DK, DV>::value;
+    static constexpr int kBopOne = kVB * DK * 128;                          // one 16-bit copy of scale*dS
+    static constexpr int kBopBytes = kBopOne * (kSplit ? 2 : 1);            // high part (+ residual)
+    static constexpr int kVecBytes = 1024;                                  // fp32 dkm / L
+    static constexpr int kStageBytes = (kKB + kVB) * kBlockBytes;           // v tile, kr tile
+    static constexpr int kOutBytes = (kKB + kVB) * kBlockBytes;             // staged dk (dkr) and dv tile
+    static constexpr int kConstBytes = MODE == kDecoupled ? kKB * kBlockBytes : 0;  // dk tile of the decoupled op
+    static constexpr int kBig = (DK == 128 && DV == 128);
+    static constexpr int kOutBufs = kBig ? 1 : 2;
+    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kOutBufs * kOutBytes + kConstBytes + 512;
+    static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
+    static constexpr int kAccCols = DK + DV;
+    static constexpr int kTmemCols = 2 * kAccCols <= 256 ? 256 : 512;
+    static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
+};
+
+template <int DK, int DV, int MODE, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_v,
+                 const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dkr,
+                 const __grid_constant__ CUtensorMap tm_dv, const Params p) {
+    using Cfg = BwdInCfg<DK, DV, MODE>;
+    constexpr int NS = Cfg::kStages;
+    constexpr int NO = Cfg::kOutBufs;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_1024(smem_raw);
+    uint8_t* bop = smem;
+    float* vec = reinterpret_cast<float*>(bop + Cfg::kBopBytes);
+    uint8_t* stages = reinterpret_cast<uint8_t*>(vec) + Cfg::kVecBytes;
+    uint8_t* outbuf = stages + NS * Cfg::kStageBytes;
+    uint8_t* constbuf = outbuf + NO * Cfg::kOutBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(constbuf + Cfg::kConstBytes);
+    uint64_t* full = bars;                  // [NS]
+    uint64_t* empty = bars + NS;            // [NS]
+    uint64_t* tfull = bars + 2 * NS;        // [2]
+    uint64_t* tempty = tfull + 2;           // [2]
+    uint64_t* bop_ready = tempty + 2;
+    uint64_t* out_free = bop_ready + 1;     // [NO]
+    uint64_t* out_written = out_free + NO;  // [NO]
+    uint64_t* const_free = out_written + NO; // constant dk tile no longer read by a store
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_free + 1);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Schedule& sch = p.sch;
+    const int g0 = blockIdx.x * sch.tiles_per_cta;
+    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    const ptx::Abort ab{cta_abort, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; ++i) {
+            ptx::mbar_init(&full[i], 1);
+            ptx::mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&tfull[i], 1);
+            ptx::mbar_init(&tempty[i], kEpiThreads);
+        }
+        for (int i = 0; i < NO; ++i) {
+            ptx::mbar_init(&out_free[i], 1);
+            ptx::mbar_init(&out_written[i], kEpiThreads);
+        }
+        ptx::mbar_init(bop_ready, kEpiThreads);
+        ptx::mbar_init(const_free, 1);
+        *cta_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tm_kr);
+        ptx::prefetch_tensormap(&tm_v);
+        ptx::prefetch_tensormap(&tm_dk);
+        ptx::prefetch_tensormap(&tm_dv);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer: v tile then kr tile ----------------
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 401)) break;
+            ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+            const int unit = g / sch.tiles_per_unit;
+            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            uint8_t* st = stages + s * Cfg::kStageBytes;
+#pragma unroll
+            for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_v, &full[s], b * 64, t0, unit);
+#pragma unroll
+            for (int b = 0; b < Cfg::kKB; ++b)
+                ptx::tma_load_3d(st + (Cfg::kVB + b) * kBlockBytes, &tm_kr, &full[s], b * 64, t0, unit);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc_dk = ptx::instr_desc(128, DK, BF16, false, false);
+        const uint32_t idesc_dv = ptx::instr_desc(128, DV, BF16, false, true);
+        const uint32_t bop_base = ptx::smem_u32(bop);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int a = it & 1;
+            const int tile = g % sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            if (first) {
+                if (!ptx::mbar_wait(bop_ready, (uint32_t)seg & 1u, ab, 411)) break;
+                ++seg;
+            }
+            if (!ptx::mbar_wait(&full[s], ph, ab, 412)) break;
+            if (!ptx::mbar_wait(&tempty[a], ((uint32_t)(it >> 1) & 1u) ^ 1u, ab, 413)) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t v_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t kr_base = v_base + Cfg::kVB * kBlockBytes;
+            const uint32_t acc = tmem + a * Cfg::kAccCols;
+            // dk[tok][k] = sum_v V[tok][v] * dS[k][v]   (B K-major: rows k, 128 bytes along v)
+#pragma unroll
+            for (int vb = 0; vb < Cfg::kVB; ++vb) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t da = ptx::smem_desc(v_base + vb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t db = ptx::smem_desc(bop_base + vb * (DK * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(acc, da, db, idesc_dk, !(vb == 0 && kk == 0));
+                    if (Cfg::kSplit) {
+                        const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopOne + vb * (DK * 128) + kk * 32, 16, 1024,
+                                                           ptx::kLayoutSw128);
+                        ptx::mma_ss(acc, da, dl, idesc_dk, true);
+                    }
+                }
+            }
+            // dv[tok][v] = sum_k KR[tok][k] * dS[k][v]  (B MN-major: rows k, 128 bytes along v)
+#pragma unroll
+            for (int kb = 0; kb < Cfg::kKB; ++kb) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t da = ptx::smem_desc(kr_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t db = ptx::smem_desc(bop_base + (kb * 64 + kk * 16) * 128, DK * 128, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(acc + DK, da, db, idesc_dv, !(kb == 0 && kk == 0));
+                    if (Cfg::kSplit) {
+                        const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopOne + (kb * 64 + kk * 16) * 128, DK * 128, 1024,
+                                                           ptx::kLayoutSw128);
+                        ptx::mma_ss(acc + DK, da, dl, idesc_dv, true);
+                    }
+                }
+            }
+            ptx::mma_commit(&empty[s]);
+            ptx::mma_commit(&tfull[a]);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;
+        const int et = threadIdx.x - 64;
+        const int row = quarter * 32 + lane;
+        const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool issuer = (et == 0);
+        int seg = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int unit = g / sch.tiles_per_unit;
+            const int tile = g - unit * sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            const int a = it & 1;
+            const int ob_i = it % NO;
+            const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
+            const uint32_t pho = (uint32_t)(it / NO) & 1u;
+            if (first) {
+                const float* st = p.state + (size_t)unit * p.state_stride;
+                // `vec` (and the constant tile) of the previous unit are read by every epilogue thread
+                // until it has arrived on out_written of the previous tile
+                if (it > 0 && !ptx::mbar_wait(&out_written[(it - 1) % NO], (uint32_t)((it - 1) / NO) & 1u, ab, 424)) break;
+                if (MODE == kDecoupled) {
+                    if (issuer) {
+                        ptx::tma_store_wait_read<0>();
+                        ptx::mbar_arrive(const_free);
+                    }
+                    if (!ptx::mbar_wait(const_free, (uint32_t)seg & 1u, ab, 425)) break;
+                }
+                ++seg;
+                stage_matrix_sw128<DK, DV, Cfg::kSplit>(bop, st, p.scale, BF16, et);
+                if (MODE != kSimple)
+                    for (int i = et; i < DK; i += kEpiThreads) vec[i] = st[DK * DV + i] * p.inv_norm;
+                if (MODE == kDecoupled) {
+                    // every token's dk is dkm / L: one constant tile, stored once per tile
+                    for (int i = et; i < kTileTokens * DK / 2; i += kEpiThreads) {
+                        const int r = (2 * i) / DK, k = (2 * i) - r * DK;
+                        const float x0 = st[DK * DV + k] * p.inv_norm, x1 = st[DK * DV + k + 1] * p.inv_norm;
+                        *reinterpret_cast<uint32_t*>(constbuf + (k >> 6) * kBlockBytes + ptx::sw128_offset(r, k & 63)) =
+                            pack2(x0, x1, BF16);
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(bop_ready);
+            }
+            if (!ptx::mbar_wait(&tfull[a], ph2, ab, 421)) break;
+            ptx::tc_fence_after_sync();
+            if (issuer) {
+                ptx::tma_store_wait_read<NO - 1>();
+                ptx::mbar_arrive(&out_free[ob_i]);
+            }
+            if (!ptx::mbar_wait(&out_free[ob_i], pho, ab, 422)) break;
+            uint8_t* ob = outbuf + ob_i * Cfg::kOutBytes;
+            // dk (or dk_rope) tile
+#pragma unroll
+            for (int c0 = 0; c0 < DK; c0 += 32) {
+                float v[32];
+                ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + c0, v);
+                ptx::tmem_ld_wait();
+                if (MODE == kLinear) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += vec[c0 + j];
+                }
+                uint8_t* blk = ob + (c0 >> 6) * kBlockBytes + row * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 w;
+                    w.x = pack2(v[8 * j], v[8 * j + 1], BF16);
+                    w.y = pack2(v[8 * j + 2], v[8 * j + 3], BF16);
+                    w.z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
+                    w.w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
+                    const int chunk = ((c0 & 63) >> 3) + j;
+                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                }
+            }
+            // dv tile
+#pragma unroll
+            for (int c0 = 0; c0 < DV; c0 += 32) {
+                float v[32];
+                ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + DK + c0, v);
+                ptx::tmem_ld_wait();
+                uint8_t* blk = ob + (Cfg::kKB + (c0 >> 6)) * kBlockBytes + row * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 w;
+                    w.x = pack2(v[8 * j], v[8 * j + 1], BF16);
+                    w.y = pack2(v[8 * j + 2], v[8 * j + 3], BF16);
+                    w.z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
+                    w.w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
+                    const int chunk = ((c0 & 63) >> 3) + j;
+                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                }
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&tempty[a]);
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&out_written[ob_i]);
+            if (issuer) {
+                if (!ptx::mbar_wait(&out_written[ob_i], pho, ab, 423)) break;
+                const int t0 = tile * kTileTokens;
+#pragma unroll
+                for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_store_3d(&tm_dkr, ob + b * kBlockBytes, b * 64, t0, unit);
+#pragma unroll
+                for (int b = 0; b < Cfg::kVB; ++b)
+                    ptx::tma_store_3d(&tm_dv, ob + (Cfg::kKB + b) * kBlockBytes, b * 64, t0, unit);
+                if (MODE == kDecoupled) {
+#pragma unroll
+                    for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_store_3d(&tm_dk, constbuf + b * kBlockBytes, b * 64, t0, unit);
+                }
+                ptx::tma_store_commit();
+            }
+        }
+        if (issuer) ptx::tma_store_wait_all<0>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+
+}  // namespace tc
+}  // namespace fbla

@@ -1,0 +1,465 @@
+// Tensor-core kernel of the first backward pass.
+//
+//   tc_bwd_state_kernel : per 128-token tile
+//         [ t | z ] = [ dO . (scale*S)^T | q . kmean ]   (MMA 1, K-major operands, accumulators in TMEM;
+//                                                         kmean enters as a high and a low 16-bit column)
+//         dz = -(qr . t) / (z + eps)^2
+//         dq = t / z + dz * kmean                        (TMA store, or plain 16-byte stores where the
+//                                                         shared memory has no room for a staged tile)
+//         qs = qr / z                                    (written back over the qr tile in shared memory)
+//         [ dS | dkm ] += qs^T . [ dO | dz*z ]           (MMA 2, MN-major operands: contraction over tokens)
+//     and one fp32 partial [ dS | sum_t dz q ] per segment.  The saved output o is not read:
+//     sum_v o*dO = (qr . t) / z.  HBM traffic: q, dO once; dq once.
+//
+//   The per-token arithmetic between the two MMAs is the longest stage of the pipeline, so two
+//   epilogue warpgroups work on alternate tiles (TMEM accumulator `it & 1` belongs to warpgroup
+//   `it & 1`); the MMA warp issues MMA 1 of tile i+1 before MMA 2 of tile i.
+#pragma once
+
+#include "tc_bwd_in.cuh"
+
+namespace fbla {
+namespace tc {
+
+constexpr int kBwdStateThreads = 64 + 2 * kEpiThreads;   // producer warp, MMA warp, two epilogue warpgroups
+
+template <int DK, int DV, int MODE>
+struct BwdStateCfg {
+    static constexpr int kKB = DK / 64, kVB = DV / 64;
+    static constexpr int kBopOne = kVB * DK * 128;                          // one 16-bit copy of scale*S
+    static constexpr int kBopBytes = 2 * kBopOne;                           // high part + residual
+    static constexpr int kVecBytes = 1024;                                  // fp32 kmean
+    static constexpr int kKmOpBytes = MODE != kSimple ? kKB * 2048 : 0;     // 16-bit kmean rows (B of the z MMA)
+    static constexpr int kDzBytes = MODE != kSimple ? 4096 : 0;             // [2 token blocks][16 rows][128 B]
+    static constexpr int kQBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
+    static constexpr int kTmaBytes = (kQBlocks + kVB) * kBlockBytes;        // qr (, q), dO tiles
+    static constexpr int kStageBytes = kTmaBytes + kDzBytes;
+    // dq leaves through a staged tile + TMA store, except where that tile does not fit
+    static constexpr bool kDirect = (DK == 128) || MODE == kDecoupled;
+    static constexpr int kOutBytes = kDirect ? 0 : kQBlocks * kBlockBytes;  // per warpgroup
+    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kKmOpBytes + 2 * kOutBytes + 512;
+    static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
+    static constexpr int kTCols = DK + (MODE != kSimple ? 16 : 0);          // t (+ z) accumulator
+    static constexpr int kColS = 2 * kTCols;                                // dS accumulator, DV columns
+    static constexpr int kColM = kColS + DV;                                // dkm accumulator, 16 columns
+    static constexpr int kTmemCols = (kColM + 16) <= 256 ? 256 : 512;
+    static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
+};
+
+template <int DK, int DV, int MODE, bool BF16>
+__global__ void __launch_bounds__(kBwdStateThreads, 1)
+tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
+                    const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
+                    const __grid_constant__ CUtensorMap tm_dqr, const Params p) {
+    using Cfg = BwdStateCfg<DK, DV, MODE>;
+    constexpr int NS = Cfg::kStages;
+    constexpr int KB = Cfg::kKB, VB = Cfg::kVB;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_1024(smem_raw);
+    uint8_t* bop = smem;
+    float* km = reinterpret_cast<float*>(bop + Cfg::kBopBytes);
+    uint8_t* kmop = reinterpret_cast<uint8_t*>(km) + Cfg::kVecBytes;
+    uint8_t* stages = kmop + Cfg::kKmOpBytes;
+    uint8_t* outbuf = stages + NS * Cfg::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(outbuf + 2 * Cfg::kOutBytes);
+    uint64_t* full = bars;                  // [NS] TMA landed
+    uint64_t* empty = bars + NS;            // [NS] MMA 2 done with the stage
+    uint64_t* qs_ready = bars + 2 * NS;     // [NS] epilogue wrote qr/z and the dz columns
+    uint64_t* tfull = bars + 3 * NS;        // [2] t accumulator ready
+    uint64_t* tempty = tfull + 2;           // [2] t accumulator drained
+    uint64_t* bop_ready = tempty + 2;       // state of the segment is in shared memory
+    uint64_t* acc_full = bop_ready + 1;     // dS / dkm of a segment complete
+    uint64_t* acc_empty = acc_full + 1;
+    uint64_t* out_free = acc_empty + 1;     // [2] staged tile of the warpgroup no longer read by its store
+    uint64_t* out_written = out_free + 2;   // [2] warpgroup finished its tile (staged tile written, km read)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_written + 2);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Schedule& sch = p.sch;
+    const int g0 = blockIdx.x * sch.tiles_per_cta;
+    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    const ptx::Abort ab{cta_abort, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; ++i) {
+            ptx::mbar_init(&full[i], 1);
+            ptx::mbar_init(&empty[i], 1);
+            ptx::mbar_init(&qs_ready[i], kEpiThreads);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&tfull[i], 1);
+            ptx::mbar_init(&tempty[i], kEpiThreads);
+            ptx::mbar_init(&out_free[i], 1);
+            ptx::mbar_init(&out_written[i], kEpiThreads);
+        }
+        ptx::mbar_init(bop_ready, kEpiThreads);
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, kEpiThreads);
+        *cta_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tm_qr);
+        ptx::prefetch_tensormap(&tm_do);
+        ptx::prefetch_tensormap(&tm_dqr);
+    }
+    if (MODE != kSimple) {
+        // rows 2..15 of every dz tile stay zero for the whole kernel
+        for (int s = 0; s < NS; ++s) {
+            uint32_t* dzt = reinterpret_cast<uint32_t*>(stages + s * Cfg::kStageBytes + Cfg::kTmaBytes);
+            for (int i = threadIdx.x; i < Cfg::kDzBytes / 4; i += kBwdStateThreads) dzt[i] = 0u;
+        }
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer: qr tile, (q tile,) dO tile ----------------
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 301)) break;
+            ptx::mbar_arrive_expect_tx(&full[s], Cfg::kTmaBytes);
+            const int unit = g / sch.tiles_per_unit;
+            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            uint8_t* st = stages + s * Cfg::kStageBytes;
+#pragma unroll
+            for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_qr, &full[s], b * 64, t0, unit);
+            if (MODE == kDecoupled) {
+#pragma unroll
+                for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + (KB + b) * kBlockBytes, &tm_q, &full[s], b * 64, t0, unit);
+            }
+#pragma unroll
+            for (int b = 0; b < VB; ++b)
+                ptx::tma_load_3d(st + (Cfg::kQBlocks + b) * kBlockBytes, &tm_do, &full[s], b * 64, t0, unit);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc_t = ptx::instr_desc(128, DK, BF16, false, false);
+        const uint32_t idesc_z = ptx::instr_desc(128, 16, BF16, false, false);
+        const uint32_t idesc_s = ptx::instr_desc(DK, DV, BF16, true, true);
+        const uint32_t idesc_m = ptx::instr_desc(DK, 16, BF16, true, false);
+        const uint32_t bop_base = ptx::smem_u32(bop);
+        const uint32_t kmop_base = ptx::smem_u32(kmop);
+        int seg_bop = 0, seg_acc = 0;
+        bool ok = true;
+        // second MMA of iteration j (tile gj): [dS | dkm] += qs^T [dO | dz]
+        auto mma2 = [&](int j, int gj) -> bool {
+            const int s = j % NS;
+            const uint32_t ph = (uint32_t)(j / NS) & 1u;
+            const int tile = gj % sch.tiles_per_unit;
+            const bool first = (gj == g0) || tile == 0;
+            const bool last = (gj == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            if (!ptx::mbar_wait(&qs_ready[s], ph, ab, 314)) return false;
+            if (first && !ptx::mbar_wait(acc_empty, ((uint32_t)seg_acc & 1u) ^ 1u, ab, 315)) return false;
+            ptx::tc_fence_after_sync();
+            const uint32_t qr_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t q_base = MODE == kDecoupled ? qr_base + KB * kBlockBytes : qr_base;
+            const uint32_t do_base = qr_base + Cfg::kQBlocks * kBlockBytes;
+            const uint32_t dz_base = qr_base + Cfg::kTmaBytes;
+#pragma unroll
+            for (int ks = 0; ks < kTileTokens / 16; ++ks) {
+                const bool acc = !(first && ks == 0);
+                const uint64_t da = ptx::smem_desc(qr_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                const uint64_t db = ptx::smem_desc(do_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                ptx::mma_ss(tmem + Cfg::kColS, da, db, idesc_s, acc);
+                if (MODE != kSimple) {
+                    const uint64_t dq_ = ptx::smem_desc(q_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                    const uint64_t dz_ = ptx::smem_desc(dz_base + (ks >> 2) * 2048 + (ks & 3) * 32, 16, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + Cfg::kColM, dq_, dz_, idesc_m, acc);
+                }
+            }
+            ptx::mma_commit(&empty[s]);
+            if (last) {
+                ptx::mma_commit(acc_full);
+                ++seg_acc;
+            }
+            return true;
+        };
+        int it = 0;
+        for (int g = g0; g < g1 && ok; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int a = it & 1;
+            const int tile = g % sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            if (first) {
+                // finish the previous segment before its B operand is replaced
+                if (it > 0 && !mma2(it - 1, g - 1)) { ok = false; break; }
+                if (!ptx::mbar_wait(bop_ready, (uint32_t)seg_bop & 1u, ab, 311)) { ok = false; break; }
+                ++seg_bop;
+            }
+            if (!ptx::mbar_wait(&full[s], ph, ab, 312)) { ok = false; break; }
+            if (!ptx::mbar_wait(&tempty[a], ((uint32_t)(it >> 1) & 1u) ^ 1u, ab, 313)) { ok = false; break; }
+            ptx::tc_fence_after_sync();
+            const uint32_t qr_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t q_base = MODE == kDecoupled ? qr_base + KB * kBlockBytes : qr_base;
+            const uint32_t do_base = qr_base + Cfg::kQBlocks * kBlockBytes;
+            const uint32_t t_acc = tmem + a * Cfg::kTCols;
+            // t[tok][k] = sum_v dO[tok][v] * S[k][v], high part and residual of S
+#pragma unroll
+            for (int vb = 0; vb < VB; ++vb) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t da = ptx::smem_desc(do_base + vb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t db = ptx::smem_desc(bop_base + vb * (DK * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                    const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopOne + vb * (DK * 128) + kk * 32, 16, 1024,
+                                                       ptx::kLayoutSw128);
+                    ptx::mma_ss(t_acc, da, db, idesc_t, !(vb == 0 && kk == 0));
+                    ptx::mma_ss(t_acc, da, dl, idesc_t, true);
+                }
+            }
+            // z[tok] = q[tok] . kmean (two columns: high and low part of kmean)
+            if (MODE != kSimple) {
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(kmop_base + kb * 2048 + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(t_acc + DK, da, db, idesc_z, !(kb == 0 && kk == 0));
+                    }
+                }
+            }
+            ptx::mma_commit(&tfull[a]);
+            if (!first && it > 0 && !mma2(it - 1, g - 1)) { ok = false; break; }
+        }
+        if (ok && it > 0) mma2(it - 1, g1 - 1);
+    } else if (warp >= 2) {
+        // ---------------- epilogue: warpgroup wg owns the iterations with (it & 1) == wg ----------------
+        const int wg = (warp - 2) >> 2;
+        const int quarter = warp & 3;
+        const int et = (threadIdx.x - 64) & (kEpiThreads - 1);
+        const int row = quarter * 32 + lane;
+        const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool issuer = (et == 0);
+        const int unit0 = g0 / sch.tiles_per_unit;
+        uint8_t* ob = outbuf + wg * Cfg::kOutBytes;
+        const int a = wg;
+        for (int g = g0 + wg, it = wg; g < g1; g += 2, it += 2) {
+            const int unit = g / sch.tiles_per_unit;
+            const int tile = g - unit * sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
+            const uint32_t seg = (uint32_t)(unit - unit0);
+            if (first) {
+                if (it > 0) {
+                    // tile it-1 (the other warpgroup's, last of the previous unit) must be past its
+                    // first MMA, which reads the state operand, and past its reads of km
+                    const uint32_t php = (uint32_t)((it - 1) >> 1) & 1u;
+                    if (!ptx::mbar_wait(&tfull[a ^ 1], php, ab, 326)) break;
+                    if (!ptx::mbar_wait(&out_written[a ^ 1], php, ab, 327)) break;
+                }
+                const float* st = p.state + (size_t)unit * p.state_stride;
+                stage_matrix_sw128<DK, DV, true>(bop, st, p.scale, BF16, et);
+                if (MODE != kSimple) {
+                    for (int i = et; i < DK; i += kEpiThreads) km[i] = st[DK * DV + i] * p.inv_norm;
+                    for (int i = et; i < 16 * DK; i += kEpiThreads) {
+                        const int r = i / DK, k = i - r * DK;
+                        uint16_t h = 0;
+                        if (r < 2) {
+                            const float x = st[DK * DV + k] * p.inv_norm;
+                            const uint16_t hi = pack1(x, BF16);
+                            h = r == 0 ? hi : pack1(x - unpack1(hi, BF16), BF16);
+                        }
+                        *reinterpret_cast<uint16_t*>(kmop + (k >> 6) * 2048 + ptx::sw128_offset(r, k & 63)) = h;
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(bop_ready);
+            }
+            // km of this unit was written by whichever warpgroup opened the segment
+            if (!ptx::mbar_wait(bop_ready, seg & 1u, ab, 328)) break;
+            if (!ptx::mbar_wait(&full[s], ph, ab, 321)) break;       // the qr tile is read below
+            if (!ptx::mbar_wait(&tfull[a], ph2, ab, 322)) break;
+            ptx::tc_fence_after_sync();
+            uint8_t* stg = stages + s * Cfg::kStageBytes;
+            uint8_t* qr_row = stg + row * 128;                        // + block * kBlockBytes + swizzled chunk
+            const uint32_t t_acc = t_lane + a * Cfg::kTCols;
+            const int tok = tile * kTileTokens + row;
+            const bool tok_ok = tok < p.seq_len;
+            float rz = 1.f, dz = 0.f, z = 1.f;
+
+            // emits columns [c0, c0+32): dq to the staged tile (or global memory), qr/z over the qr tile
+            auto emit32 = [&](int c0, const float (&t)[32], const uint4 (&qv)[4]) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = c0 + 8 * j;
+                    const uint32_t off = (uint32_t)(c >> 6) * kBlockBytes + (((((c & 63) >> 3) ^ row) & 7) << 4);
+                    const uint32_t rw[4] = {qv[j].x, qv[j].y, qv[j].z, qv[j].w};
+                    uint32_t o1[4], o2[4], qs[4];
+                    float kmv[8];
+                    if (MODE != kSimple) {
+                        const float4 ka = *reinterpret_cast<const float4*>(km + c);
+                        const float4 kb = *reinterpret_cast<const float4*>(km + c + 4);
+                        kmv[0] = ka.x; kmv[1] = ka.y; kmv[2] = ka.z; kmv[3] = ka.w;
+                        kmv[4] = kb.x; kmv[5] = kb.y; kmv[6] = kb.z; kmv[7] = kb.w;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float ta = t[8 * j + 2 * e], tb = t[8 * j + 2 * e + 1];
+                        if (MODE == kSimple) {
+                            o1[e] = pack2(ta, tb, BF16);
+                        } else {
+                            const float ga = dz * kmv[2 * e], gb = dz * kmv[2 * e + 1];
+                            if (MODE == kLinear) {
+                                o1[e] = pack2(fmaf(ta, rz, ga), fmaf(tb, rz, gb), BF16);
+                            } else {
+                                o1[e] = pack2(ta * rz, tb * rz, BF16);   // dq_rope
+                                o2[e] = pack2(ga, gb, BF16);             // dq
+                            }
+                            const float2 rf = unpack2(rw[e], BF16);
+                            qs[e] = pack2(rf.x * rz, rf.y * rz, BF16);
+                        }
+                    }
+                    if (Cfg::kDirect) {
+                        if (tok_ok) {
+                            const size_t at = (((size_t)unit * p.seq_len + tok) * DK + c) * 2;
+                            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_a) + at) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                            if (MODE == kDecoupled)
+                                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_b) + at) =
+                                    make_uint4(o2[0], o2[1], o2[2], o2[3]);
+                        }
+                    } else {
+                        *reinterpret_cast<uint4*>(ob + row * 128 + off) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                    }
+                    if (MODE != kSimple) *reinterpret_cast<uint4*>(qr_row + off) = make_uint4(qs[0], qs[1], qs[2], qs[3]);
+                }
+            };
+            // loads columns [c0, c0+32) of t and of the packed qr row
+            auto load32 = [&](int c0, float (&t)[32], uint4 (&qv)[4]) {
+                ptx::tmem_ld32(t_acc + c0, t);
+                if (MODE != kSimple) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int c = c0 + 8 * j;
+                        const uint32_t off = (uint32_t)(c >> 6) * kBlockBytes + (((((c & 63) >> 3) ^ row) & 7) << 4);
+                        qv[j] = *reinterpret_cast<const uint4*>(qr_row + off);
+                    }
+                }
+            };
+            auto dot32 = [&](const float (&t)[32], const uint4 (&qv)[4]) {
+                float w[4] = {0.f, 0.f, 0.f, 0.f};   // independent chains
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t rw[4] = {qv[j].x, qv[j].y, qv[j].z, qv[j].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 rf = unpack2(rw[e], BF16);
+                        w[e] = fmaf(rf.x, t[8 * j + 2 * e], w[e]);
+                        w[e] = fmaf(rf.y, t[8 * j + 2 * e + 1], w[e]);
+                    }
+                }
+                return (w[0] + w[1]) + (w[2] + w[3]);
+            };
+            auto wait_out_free = [&]() -> bool {
+                if (Cfg::kDirect) return true;
+                if (issuer) {
+                    ptx::tma_store_wait_read<0>();      // the store of this warpgroup's previous tile
+                    ptx::mbar_arrive(&out_free[a]);
+                }
+                return ptx::mbar_wait(&out_free[a], ph2, ab, 323);
+            };
+
+            if (DK == 64) {
+                // one pass: the whole row of t stays in registers
+                float ta[32], tb[32];
+                uint4 qa[4], qb[4];
+                float zc[16];
+                load32(0, ta, qa);
+                load32(32, tb, qb);
+                if (MODE != kSimple) ptx::tmem_ld16(t_acc + DK, zc);
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&tempty[a]);
+                if (MODE != kSimple) {
+                    const float w = dot32(ta, qa) + dot32(tb, qb);
+                    z = zc[0] + zc[1] + p.eps;
+                    rz = 1.f / z;
+                    dz = -w * rz * rz;
+                }
+                if (!wait_out_free()) break;
+                emit32(0, ta, qa);
+                emit32(32, tb, qb);
+            } else {
+                // two passes over the accumulator: first qr . t, then the outputs
+                float w = 0.f;
+                if (MODE != kSimple) {
+                    float zc[16];
+                    ptx::tmem_ld16(t_acc + DK, zc);
+#pragma unroll
+                    for (int c0 = 0; c0 < DK; c0 += 32) {
+                        float t[32];
+                        uint4 qv[4];
+                        load32(c0, t, qv);
+                        ptx::tmem_ld_wait();
+                        w += dot32(t, qv);
+                    }
+                    z = zc[0] + zc[1] + p.eps;
+                    rz = 1.f / z;
+                    dz = -w * rz * rz;
+                }
+                if (!wait_out_free()) break;
+#pragma unroll
+                for (int c0 = 0; c0 < DK; c0 += 32) {
+                    float t[32];
+                    uint4 qv[4];
+                    load32(c0, t, qv);
+                    ptx::tmem_ld_wait();
+                    emit32(c0, t, qv);
+                }
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&tempty[a]);
+            }
+            if (MODE != kSimple) {
+                // two 16-bit columns whose sum is dz*z (paired with qr/z) or dz (decoupled: paired with q)
+                const float x = MODE == kLinear ? dz * z : dz;
+                const uint16_t hi = pack1(x, BF16);
+                const uint16_t lo = pack1(x - unpack1(hi, BF16), BF16);
+                uint8_t* dzt = stg + Cfg::kTmaBytes + (row >> 6) * 2048;
+                const int tc = row & 63;
+                *reinterpret_cast<uint16_t*>(dzt + ptx::sw128_offset(0, tc)) = hi;
+                *reinterpret_cast<uint16_t*>(dzt + ptx::sw128_offset(1, tc)) = lo;
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&qs_ready[s]);
+            ptx::mbar_arrive(&out_written[a]);
+            if (!Cfg::kDirect && issuer) {
+                if (!ptx::mbar_wait(&out_written[a], ph2, ab, 324)) break;
+                const int t0 = tile * kTileTokens;
+#pragma unroll
+                for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t0, unit);
+                ptx::tma_store_commit();
+            }
+            if (last) {
+                if (!ptx::mbar_wait(acc_full, seg & 1u, ab, 325)) break;
+                ptx::tc_fence_after_sync();
+                const int slot = unit * sch.slots_per_unit + ((int)blockIdx.x - first_cta_of_unit(sch, unit));
+                float* out = p.part + (size_t)slot * p.state_stride;
+                drain_state_acc<DK, DV, (MODE != kSimple ? 2 : 0)>(tmem + Cfg::kColS, DV, out, warp, lane);
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(acc_empty);
+            }
+        }
+        if (!Cfg::kDirect && issuer) ptx::tma_store_wait_all<0>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace tc
+}  // namespace fbla

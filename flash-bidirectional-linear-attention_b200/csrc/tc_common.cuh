@@ -47,6 +47,9 @@ struct Params {
     float* part;
     const float* state;
     int state_stride;     // floats per unit in state / partial slots
+    // kernels that write an output with plain global stores (no staged tile): its base address
+    void* out_a;
+    void* out_b;
 };
 
 __host__ __device__ inline int first_cta_of_unit(const Schedule& s, int unit) {

@@ -28,7 +28,7 @@ struct FwdStateCfg {
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kOnesBytes + 256;
 };
 
-template <int DK, int DV, int MODE>
+template <int DK, int DV, int MODE, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -66,7 +66,7 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
     }
     // a tile of ones (any layout of ones is ones): B operand of the key-sum MMA
     for (int i = threadIdx.x; i < Cfg::kOnesBytes / 2; i += kThreads)
-        reinterpret_cast<uint16_t*>(ones)[i] = p.is_bf16 ? (uint16_t)0x3F80 : (uint16_t)0x3C00;
+        reinterpret_cast<uint16_t*>(ones)[i] = BF16 ? (uint16_t)0x3F80 : (uint16_t)0x3C00;
     ptx::fence_proxy_async_smem();
     if (warp == 1) {
         ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -100,8 +100,8 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
-        const uint32_t idesc_s = ptx::instr_desc(DK, DV, p.is_bf16, true, true);
-        const uint32_t idesc_k = ptx::instr_desc(DK, 16, p.is_bf16, true, false);
+        const uint32_t idesc_s = ptx::instr_desc(DK, DV, BF16, true, true);
+        const uint32_t idesc_k = ptx::instr_desc(DK, 16, BF16, true, false);
         const uint64_t d_ones = ptx::smem_desc(ptx::smem_u32(ones), 128, 256, ptx::kLayoutNone);
         int seg = 0;
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
@@ -192,7 +192,7 @@ struct FwdOutCfg {
     static constexpr int kSmemBytes = 1024 + kBopBytes + kStages * kStageBytes + 2 * kOutBytes + 512;
 };
 
-template <int DK, int DV, int MODE>
+template <int DK, int DV, int MODE, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_o, const Params p) {
@@ -266,8 +266,8 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
-        const uint32_t idesc_n = ptx::instr_desc(128, DV, p.is_bf16, false, false);
-        const uint32_t idesc_z = ptx::instr_desc(128, 16, p.is_bf16, false, false);
+        const uint32_t idesc_n = ptx::instr_desc(128, DV, BF16, false, false);
+        const uint32_t idesc_z = ptx::instr_desc(128, 16, BF16, false, false);
         const uint32_t bop_base = ptx::smem_u32(bop);
         int seg = 0;
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
@@ -329,11 +329,11 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                 for (int i = et; i < DK * DV; i += kEpiThreads) {
                     const int k = i / DV, v = i - k * DV;
                     const float x = st[i] * p.scale;
-                    const uint16_t h = pack1(x, p.is_bf16);
+                    const uint16_t h = pack1(x, BF16);
                     *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(v, k & 63)) = h;
                     // rounding residual: a second B operand accumulated into the same columns
                     *reinterpret_cast<uint16_t*>(bop + Cfg::kBopHiBytes + (k >> 6) * Cfg::kBopLoBlock +
-                                                 ptx::sw128_offset(v, k & 63)) = pack1(x - unpack1(h, p.is_bf16), p.is_bf16);
+                                                 ptx::sw128_offset(v, k & 63)) = pack1(x - unpack1(h, BF16), BF16);
                 }
                 if (MODE != kSimple) {
                     for (int i = et; i < 16 * DK; i += kEpiThreads) {
@@ -341,8 +341,8 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                         uint16_t h = 0;
                         if (r < 2) {
                             const float km = st[DK * DV + k] * p.inv_norm;
-                            const uint16_t hi = pack1(km, p.is_bf16);
-                            h = r == 0 ? hi : pack1(km - unpack1(hi, p.is_bf16), p.is_bf16);
+                            const uint16_t hi = pack1(km, BF16);
+                            h = r == 0 ? hi : pack1(km - unpack1(hi, BF16), BF16);
                         }
                         *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(DV + r, k & 63)) = h;
                     }
@@ -376,10 +376,10 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint4 w;
-                    w.x = pack2(v[8 * j] * rz, v[8 * j + 1] * rz, p.is_bf16);
-                    w.y = pack2(v[8 * j + 2] * rz, v[8 * j + 3] * rz, p.is_bf16);
-                    w.z = pack2(v[8 * j + 4] * rz, v[8 * j + 5] * rz, p.is_bf16);
-                    w.w = pack2(v[8 * j + 6] * rz, v[8 * j + 7] * rz, p.is_bf16);
+                    w.x = pack2(v[8 * j] * rz, v[8 * j + 1] * rz, BF16);
+                    w.y = pack2(v[8 * j + 2] * rz, v[8 * j + 3] * rz, BF16);
+                    w.z = pack2(v[8 * j + 4] * rz, v[8 * j + 5] * rz, BF16);
+                    w.w = pack2(v[8 * j + 6] * rz, v[8 * j + 7] * rz, BF16);
                     const int chunk = ((c0 & 63) >> 3) + j;
                     *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
                 }

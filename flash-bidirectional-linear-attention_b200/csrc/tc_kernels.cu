@@ -6,7 +6,8 @@
 
 #include <mutex>
 
-#include "tc_bwd.cuh"
+#include "tc_bwd_in.cuh"
+#include "tc_bwd_state.cuh"
 #include "tc_fwd.cuh"
 
 namespace fbla {
@@ -140,6 +141,8 @@ Params make_params(const KParams& p, int dtype, const Schedule& s) {
     q.part = nullptr;
     q.state = nullptr;
     q.state_stride = p.state_stride;
+    q.out_a = nullptr;
+    q.out_b = nullptr;
     return q;
 }
 
@@ -165,12 +168,12 @@ cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
 }
 
 // ---- per-shape launch helpers ----------------------------------------------------------------
-template <int DK, int DV, int MODE>
+template <int DK, int DV, int MODE, bool BF16>
 cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tk, const CUtensorMap& tv,
                              cudaStream_t st) {
     using Cfg = FwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
-    auto kernel = tc_fwd_state_kernel<DK, DV, MODE>;
+    auto kernel = tc_fwd_state_kernel<DK, DV, MODE, BF16>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
@@ -179,13 +182,13 @@ cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUte
     return cudaGetLastError();
 }
 
-template <int DK, int DV, int MODE>
+template <int DK, int DV, int MODE, bool BF16>
 cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& to,
                            cudaStream_t st) {
     using Cfg = FwdOutCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
-    auto kernel = tc_fwd_out_kernel<DK, DV, MODE>;
+    auto kernel = tc_fwd_out_kernel<DK, DV, MODE, BF16>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
@@ -194,28 +197,28 @@ cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtens
     return cudaGetLastError();
 }
 
-template <int DK, int DV, int MODE>
+template <int DK, int DV, int MODE, bool BF16>
 cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
                              const CUtensorMap& tdq, const CUtensorMap& tdqr, cudaStream_t st) {
     using Cfg = BwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
-    auto kernel = tc_bwd_state_kernel<DK, DV, MODE>;
+    auto kernel = tc_bwd_state_kernel<DK, DV, MODE, BF16>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tqr, tq, tdo, tdq, tdqr, q);
+    kernel<<<q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st>>>(tqr, tq, tdo, tdq, tdqr, q);
     note_launches(1);
     return cudaGetLastError();
 }
 
-template <int DK, int DV, int MODE>
+template <int DK, int DV, int MODE, bool BF16>
 cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tv, const CUtensorMap& tdk,
                           const CUtensorMap& tdkr, const CUtensorMap& tdv, cudaStream_t st) {
     using Cfg = BwdInCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
-    auto kernel = tc_bwd_in_kernel<DK, DV, MODE>;
+    auto kernel = tc_bwd_in_kernel<DK, DV, MODE, BF16>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
@@ -224,21 +227,27 @@ cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtenso
     return cudaGetLastError();
 }
 
-// Expands to a switch over (dk, dv, mode); `CALL` names one of the launch_* templates.
+// Expands to a switch over (dk, dv, mode, 16-bit type); `CALL` names one of the launch_* templates.
+#define FBLA_TC_CASES(CALL, BF, ...)                                                                    \
+    switch (mode * 4 + key) {                                                                           \
+        case 0: return CALL<64, 64, kSimple, BF>(__VA_ARGS__);                                          \
+        case 1: return CALL<64, 128, kSimple, BF>(__VA_ARGS__);                                         \
+        case 2: return CALL<128, 64, kSimple, BF>(__VA_ARGS__);                                         \
+        case 3: return CALL<128, 128, kSimple, BF>(__VA_ARGS__);                                        \
+        case 4: return CALL<64, 64, kLinear, BF>(__VA_ARGS__);                                          \
+        case 5: return CALL<64, 128, kLinear, BF>(__VA_ARGS__);                                         \
+        case 6: return CALL<128, 64, kLinear, BF>(__VA_ARGS__);                                         \
+        case 7: return CALL<128, 128, kLinear, BF>(__VA_ARGS__);                                        \
+        case 8: return CALL<64, 64, kDecoupled, BF>(__VA_ARGS__);                                       \
+        default: return cudaErrorNotSupported;                                                          \
+    }
 #define FBLA_TC_DISPATCH(CALL, ...)                                                                     \
     do {                                                                                                \
         const int key = (p.dk == 128 ? 2 : 0) + (p.dv == 128 ? 1 : 0);                                  \
-        switch (mode * 4 + key) {                                                                       \
-            case 0: return CALL<64, 64, kSimple>(__VA_ARGS__);                                          \
-            case 1: return CALL<64, 128, kSimple>(__VA_ARGS__);                                         \
-            case 2: return CALL<128, 64, kSimple>(__VA_ARGS__);                                         \
-            case 3: return CALL<128, 128, kSimple>(__VA_ARGS__);                                        \
-            case 4: return CALL<64, 64, kLinear>(__VA_ARGS__);                                          \
-            case 5: return CALL<64, 128, kLinear>(__VA_ARGS__);                                         \
-            case 6: return CALL<128, 64, kLinear>(__VA_ARGS__);                                         \
-            case 7: return CALL<128, 128, kLinear>(__VA_ARGS__);                                        \
-            case 8: return CALL<64, 64, kDecoupled>(__VA_ARGS__);                                       \
-            default: return cudaErrorNotSupported;                                                      \
+        if (dtype == FBLA_BF16) {                                                                       \
+            FBLA_TC_CASES(CALL, true, __VA_ARGS__)                                                      \
+        } else {                                                                                        \
+            FBLA_TC_CASES(CALL, false, __VA_ARGS__)                                                     \
         }                                                                                               \
     } while (0)
 
@@ -308,6 +317,8 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = state;
     q.part = static_cast<float*>(ws);
+    q.out_a = dec ? dq_rope : dq;
+    q.out_b = dq;
     CUtensorMap tqr, tq, tdo, tdq, tdqr;
     cudaError_t e;
     if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
