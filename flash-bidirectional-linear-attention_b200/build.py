@@ -12,8 +12,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "flash_bla", "lib")
-LIB = os.path.join(LIB_DIR, "libflash_bla_sm100.so")
-OBJ_DIR = os.path.join(HERE, "build")
+LIB = os.path.join(LIB_DIR, os.environ.get("FBLA_LIB_NAME", "libflash_bla_sm100.so"))
+OBJ_DIR = os.path.join(HERE, os.environ.get("FBLA_OBJ_DIR", "build"))
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -50,7 +50,8 @@ def build(force=False, verbose=False):
         o = os.path.join(OBJ_DIR, src[:-3] + ".o")
         objs.append(o)
         if force or not _newer(o, [s] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            extra = os.environ.get("FBLA_NVCC_EXTRA", "").split()
+            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:

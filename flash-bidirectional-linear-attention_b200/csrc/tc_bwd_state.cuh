@@ -12,8 +12,8 @@
 //     sum_v o*dO = (qr . t) / z.  HBM traffic: q, dO once; dq once.
 //
 //   The per-token arithmetic between the two MMAs is the longest stage of the pipeline, so two
-//   epilogue warpgroups work on alternate tiles (TMEM accumulator `it & 1` belongs to warpgroup
-//   `it & 1`); the MMA warp issues MMA 1 of tile i+1 before MMA 2 of tile i.
+//   epilogue warpgroups work on alternate tiles, and the two MMAs have an issuing thread each: the
+//   thread of MMA 1 runs ahead (up to three t accumulators), the thread of MMA 2 follows the epilogue.
 #pragma once
 
 #include "tc_bwd_in.cuh"
@@ -21,7 +21,23 @@
 namespace fbla {
 namespace tc {
 
-constexpr int kBwdStateThreads = 64 + 2 * kEpiThreads;   // producer warp, MMA warp, two epilogue warpgroups
+// producer warp, MMA-1 warp, two epilogue warpgroups, MMA-2 warp
+constexpr int kBwdStateThreads = 64 + 2 * kEpiThreads + 32;
+
+#ifdef FBLA_PROFILE
+// Debug builds only: cycle counts of the epilogue phases of one thread (CTA 1, warpgroup 0).
+__device__ long long g_prof_bwd_state[16];
+#define FBLA_PROF_MARK(i)                                              \
+    do {                                                               \
+        if (prof_on) {                                                 \
+            const long long now_ = clock64();                          \
+            g_prof_bwd_state[i] += now_ - prof_t;                      \
+            prof_t = now_;                                             \
+        }                                                              \
+    } while (0)
+#else
+#define FBLA_PROF_MARK(i) do { } while (0)
+#endif
 
 template <int DK, int DV, int MODE>
 struct BwdStateCfg {
@@ -41,7 +57,10 @@ struct BwdStateCfg {
     static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
     static constexpr int kTCols = DK + (MODE != kSimple ? 16 : 0);          // t (+ z) accumulator
-    static constexpr int kColS = 2 * kTCols;                                // dS accumulator, DV columns
+    // t accumulators: with three, MMA 1 runs ahead of the epilogue, so a warpgroup finds its next
+    // accumulator complete when it finishes a tile
+    static constexpr int kTBufs = (3 * kTCols + DV + 16 <= 512) ? 3 : 2;
+    static constexpr int kColS = kTBufs * kTCols;                           // dS accumulator, DV columns
     static constexpr int kColM = kColS + DV;                                // dkm accumulator, 16 columns
     static constexpr int kTmemCols = (kColM + 16) <= 256 ? 256 : 512;
     static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
@@ -54,6 +73,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     const __grid_constant__ CUtensorMap tm_dqr, const Params p) {
     using Cfg = BwdStateCfg<DK, DV, MODE>;
     constexpr int NS = Cfg::kStages;
+    constexpr int NB = Cfg::kTBufs;
     constexpr int KB = Cfg::kKB, VB = Cfg::kVB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_1024(smem_raw);
@@ -66,9 +86,9 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
     uint64_t* full = bars;                  // [NS] TMA landed
     uint64_t* empty = bars + NS;            // [NS] MMA 2 done with the stage
     uint64_t* qs_ready = bars + 2 * NS;     // [NS] epilogue wrote qr/z and the dz columns
-    uint64_t* tfull = bars + 3 * NS;        // [2] t accumulator ready
-    uint64_t* tempty = tfull + 2;           // [2] t accumulator drained
-    uint64_t* bop_ready = tempty + 2;       // state of the segment is in shared memory
+    uint64_t* tfull = bars + 3 * NS;        // [NB] t accumulator ready
+    uint64_t* tempty = tfull + NB;          // [NB] t accumulator drained
+    uint64_t* bop_ready = tempty + NB;      // state of the segment is in shared memory
     uint64_t* acc_full = bop_ready + 1;     // dS / dkm of a segment complete
     uint64_t* acc_empty = acc_full + 1;
     uint64_t* out_free = acc_empty + 1;     // [2] staged tile of the warpgroup no longer read by its store
@@ -88,9 +108,11 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             ptx::mbar_init(&empty[i], 1);
             ptx::mbar_init(&qs_ready[i], kEpiThreads);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NB; ++i) {
             ptx::mbar_init(&tfull[i], 1);
             ptx::mbar_init(&tempty[i], kEpiThreads);
+        }
+        for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(&out_free[i], 1);
             ptx::mbar_init(&out_written[i], kEpiThreads);
         }
@@ -141,68 +163,31 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                 ptx::tma_load_3d(st + (Cfg::kQBlocks + b) * kBlockBytes, &tm_do, &full[s], b * 64, t0, unit);
         }
     } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- issuer of MMA 1: [t | z] = [dO . S^T | q . kmean] ----------------
         const uint32_t idesc_t = ptx::instr_desc(128, DK, BF16, false, false);
         const uint32_t idesc_z = ptx::instr_desc(128, 16, BF16, false, false);
-        const uint32_t idesc_s = ptx::instr_desc(DK, DV, BF16, true, true);
-        const uint32_t idesc_m = ptx::instr_desc(DK, 16, BF16, true, false);
         const uint32_t bop_base = ptx::smem_u32(bop);
         const uint32_t kmop_base = ptx::smem_u32(kmop);
-        int seg_bop = 0, seg_acc = 0;
-        bool ok = true;
-        // second MMA of iteration j (tile gj): [dS | dkm] += qs^T [dO | dz]
-        auto mma2 = [&](int j, int gj) -> bool {
-            const int s = j % NS;
-            const uint32_t ph = (uint32_t)(j / NS) & 1u;
-            const int tile = gj % sch.tiles_per_unit;
-            const bool first = (gj == g0) || tile == 0;
-            const bool last = (gj == g1 - 1) || tile == sch.tiles_per_unit - 1;
-            if (!ptx::mbar_wait(&qs_ready[s], ph, ab, 314)) return false;
-            if (first && !ptx::mbar_wait(acc_empty, ((uint32_t)seg_acc & 1u) ^ 1u, ab, 315)) return false;
-            ptx::tc_fence_after_sync();
-            const uint32_t qr_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
-            const uint32_t q_base = MODE == kDecoupled ? qr_base + KB * kBlockBytes : qr_base;
-            const uint32_t do_base = qr_base + Cfg::kQBlocks * kBlockBytes;
-            const uint32_t dz_base = qr_base + Cfg::kTmaBytes;
-#pragma unroll
-            for (int ks = 0; ks < kTileTokens / 16; ++ks) {
-                const bool acc = !(first && ks == 0);
-                const uint64_t da = ptx::smem_desc(qr_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                const uint64_t db = ptx::smem_desc(do_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                ptx::mma_ss(tmem + Cfg::kColS, da, db, idesc_s, acc);
-                if (MODE != kSimple) {
-                    const uint64_t dq_ = ptx::smem_desc(q_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                    const uint64_t dz_ = ptx::smem_desc(dz_base + (ks >> 2) * 2048 + (ks & 3) * 32, 16, 1024, ptx::kLayoutSw128);
-                    ptx::mma_ss(tmem + Cfg::kColM, dq_, dz_, idesc_m, acc);
-                }
-            }
-            ptx::mma_commit(&empty[s]);
-            if (last) {
-                ptx::mma_commit(acc_full);
-                ++seg_acc;
-            }
-            return true;
-        };
-        int it = 0;
-        for (int g = g0; g < g1 && ok; ++g, ++it) {
+        int seg_bop = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
-            const int a = it & 1;
+            const int tb = it % NB;
             const int tile = g % sch.tiles_per_unit;
             const bool first = (g == g0) || tile == 0;
             if (first) {
-                // finish the previous segment before its B operand is replaced
-                if (it > 0 && !mma2(it - 1, g - 1)) { ok = false; break; }
-                if (!ptx::mbar_wait(bop_ready, (uint32_t)seg_bop & 1u, ab, 311)) { ok = false; break; }
+                // the epilogue rewrites the state operand only after the first MMA of the previous
+                // unit's last tile has completed, then arrives here
+                if (!ptx::mbar_wait(bop_ready, (uint32_t)seg_bop & 1u, ab, 311)) break;
                 ++seg_bop;
             }
-            if (!ptx::mbar_wait(&full[s], ph, ab, 312)) { ok = false; break; }
-            if (!ptx::mbar_wait(&tempty[a], ((uint32_t)(it >> 1) & 1u) ^ 1u, ab, 313)) { ok = false; break; }
+            if (!ptx::mbar_wait(&full[s], ph, ab, 312)) break;
+            if (!ptx::mbar_wait(&tempty[tb], ((uint32_t)(it / NB) & 1u) ^ 1u, ab, 313)) break;
             ptx::tc_fence_after_sync();
             const uint32_t qr_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
             const uint32_t q_base = MODE == kDecoupled ? qr_base + KB * kBlockBytes : qr_base;
             const uint32_t do_base = qr_base + Cfg::kQBlocks * kBlockBytes;
-            const uint32_t t_acc = tmem + a * Cfg::kTCols;
+            const uint32_t t_acc = tmem + tb * Cfg::kTCols;
             // t[tok][k] = sum_v dO[tok][v] * S[k][v], high part and residual of S
 #pragma unroll
             for (int vb = 0; vb < VB; ++vb) {
@@ -228,11 +213,47 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     }
                 }
             }
-            ptx::mma_commit(&tfull[a]);
-            if (!first && it > 0 && !mma2(it - 1, g - 1)) { ok = false; break; }
+            ptx::mma_commit(&tfull[tb]);
         }
-        if (ok && it > 0) mma2(it - 1, g1 - 1);
-    } else if (warp >= 2) {
+    } else if (warp == kBwdStateThreads / 32 - 1 && lane == 0) {
+        // ---------------- issuer of MMA 2: [dS | dkm] += qs^T . [dO | dz] ----------------
+        // A thread of its own: it follows the epilogue (qs_ready) while the issuer of MMA 1 runs
+        // ahead of it by as many tiles as there are t accumulators and stages.
+        const uint32_t idesc_s = ptx::instr_desc(DK, DV, BF16, true, true);
+        const uint32_t idesc_m = ptx::instr_desc(DK, 16, BF16, true, false);
+        int seg_acc = 0;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            const int tile = g % sch.tiles_per_unit;
+            const bool first = (g == g0) || tile == 0;
+            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            if (!ptx::mbar_wait(&qs_ready[s], ph, ab, 314)) break;
+            if (first && !ptx::mbar_wait(acc_empty, ((uint32_t)seg_acc & 1u) ^ 1u, ab, 315)) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t qr_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
+            const uint32_t q_base = MODE == kDecoupled ? qr_base + KB * kBlockBytes : qr_base;
+            const uint32_t do_base = qr_base + Cfg::kQBlocks * kBlockBytes;
+            const uint32_t dz_base = qr_base + Cfg::kTmaBytes;
+#pragma unroll
+            for (int ks = 0; ks < kTileTokens / 16; ++ks) {
+                const bool acc = !(first && ks == 0);
+                const uint64_t da = ptx::smem_desc(qr_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                const uint64_t db = ptx::smem_desc(do_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                ptx::mma_ss(tmem + Cfg::kColS, da, db, idesc_s, acc);
+                if (MODE != kSimple) {
+                    const uint64_t dq_ = ptx::smem_desc(q_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                    const uint64_t dz_ = ptx::smem_desc(dz_base + (ks >> 2) * 2048 + (ks & 3) * 32, 16, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + Cfg::kColM, dq_, dz_, idesc_m, acc);
+                }
+            }
+            ptx::mma_commit(&empty[s]);
+            if (last) {
+                ptx::mma_commit(acc_full);
+                ++seg_acc;
+            }
+        }
+    } else if (warp >= 2 && warp < 2 + 2 * (kEpiThreads / 32)) {
         // ---------------- epilogue: warpgroup wg owns the iterations with (it & 1) == wg ----------------
         const int wg = (warp - 2) >> 2;
         const int quarter = warp & 3;
@@ -242,23 +263,29 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
         const bool issuer = (et == 0);
         const int unit0 = g0 / sch.tiles_per_unit;
         uint8_t* ob = outbuf + wg * Cfg::kOutBytes;
-        const int a = wg;
+        const int a = wg;                                   // staged tile / out_* barriers of this warpgroup
+#ifdef FBLA_PROFILE
+        const bool prof_on = (blockIdx.x == 1 && wg == 0 && et == 0);
+        long long prof_t = clock64();
+#endif
         for (int g = g0 + wg, it = wg; g < g1; g += 2, it += 2) {
+            FBLA_PROF_MARK(7);
             const int unit = g / sch.tiles_per_unit;
             const int tile = g - unit * sch.tiles_per_unit;
             const bool first = (g == g0) || tile == 0;
             const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
-            const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
+            const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;   // phase of this warpgroup's out_* barriers
+            const int tb = it % NB;                          // t accumulator of this tile
+            const uint32_t pht = (uint32_t)(it / NB) & 1u;
             const uint32_t seg = (uint32_t)(unit - unit0);
             if (first) {
                 if (it > 0) {
                     // tile it-1 (the other warpgroup's, last of the previous unit) must be past its
                     // first MMA, which reads the state operand, and past its reads of km
-                    const uint32_t php = (uint32_t)((it - 1) >> 1) & 1u;
-                    if (!ptx::mbar_wait(&tfull[a ^ 1], php, ab, 326)) break;
-                    if (!ptx::mbar_wait(&out_written[a ^ 1], php, ab, 327)) break;
+                    if (!ptx::mbar_wait(&tfull[(it - 1) % NB], (uint32_t)((it - 1) / NB) & 1u, ab, 326)) break;
+                    if (!ptx::mbar_wait(&out_written[a ^ 1], (uint32_t)((it - 1) >> 1) & 1u, ab, 327)) break;
                 }
                 const float* st = p.state + (size_t)unit * p.state_stride;
                 stage_matrix_sw128<DK, DV, true>(bop, st, p.scale, BF16, et);
@@ -280,12 +307,15 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             }
             // km of this unit was written by whichever warpgroup opened the segment
             if (!ptx::mbar_wait(bop_ready, seg & 1u, ab, 328)) break;
+            FBLA_PROF_MARK(6);
             if (!ptx::mbar_wait(&full[s], ph, ab, 321)) break;       // the qr tile is read below
-            if (!ptx::mbar_wait(&tfull[a], ph2, ab, 322)) break;
+            FBLA_PROF_MARK(9);
+            if (!ptx::mbar_wait(&tfull[tb], pht, ab, 322)) break;
             ptx::tc_fence_after_sync();
+            FBLA_PROF_MARK(0);
             uint8_t* stg = stages + s * Cfg::kStageBytes;
             uint8_t* qr_row = stg + row * 128;                        // + block * kBlockBytes + swizzled chunk
-            const uint32_t t_acc = t_lane + a * Cfg::kTCols;
+            const uint32_t t_acc = t_lane + tb * Cfg::kTCols;
             const int tok = tile * kTileTokens + row;
             const bool tok_ok = tok < p.seq_len;
             float rz = 1.f, dz = 0.f, z = 1.f;
@@ -373,24 +403,27 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
 
             if (DK == 64) {
                 // one pass: the whole row of t stays in registers
-                float ta[32], tb[32];
+                float t_lo[32], t_hi[32];
                 uint4 qa[4], qb[4];
                 float zc[16];
-                load32(0, ta, qa);
-                load32(32, tb, qb);
+                load32(0, t_lo, qa);
+                load32(32, t_hi, qb);
                 if (MODE != kSimple) ptx::tmem_ld16(t_acc + DK, zc);
                 ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&tempty[a]);
+                ptx::mbar_arrive(&tempty[tb]);
                 if (MODE != kSimple) {
-                    const float w = dot32(ta, qa) + dot32(tb, qb);
+                    const float w = dot32(t_lo, qa) + dot32(t_hi, qb);
                     z = zc[0] + zc[1] + p.eps;
                     rz = 1.f / z;
                     dz = -w * rz * rz;
                 }
+                FBLA_PROF_MARK(1);
                 if (!wait_out_free()) break;
-                emit32(0, ta, qa);
-                emit32(32, tb, qb);
+                FBLA_PROF_MARK(2);
+                emit32(0, t_lo, qa);
+                emit32(32, t_hi, qb);
+                FBLA_PROF_MARK(3);
             } else {
                 // two passes over the accumulator: first qr . t, then the outputs
                 float w = 0.f;
@@ -419,7 +452,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     emit32(c0, t, qv);
                 }
                 ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&tempty[a]);
+                ptx::mbar_arrive(&tempty[tb]);
             }
             if (MODE != kSimple) {
                 // two 16-bit columns whose sum is dz*z (paired with qr/z) or dz (decoupled: paired with q)
@@ -434,6 +467,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             ptx::fence_proxy_async_smem();
             ptx::mbar_arrive(&qs_ready[s]);
             ptx::mbar_arrive(&out_written[a]);
+            FBLA_PROF_MARK(4);
             if (!Cfg::kDirect && issuer) {
                 if (!ptx::mbar_wait(&out_written[a], ph2, ab, 324)) break;
                 const int t0 = tile * kTileTokens;
@@ -441,6 +475,10 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                 for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t0, unit);
                 ptx::tma_store_commit();
             }
+            FBLA_PROF_MARK(5);
+#ifdef FBLA_PROFILE
+            if (prof_on) g_prof_bwd_state[8] += 1;
+#endif
             if (last) {
                 if (!ptx::mbar_wait(acc_full, seg & 1u, ab, 325)) break;
                 ptx::tc_fence_after_sync();

@@ -11,6 +11,9 @@
 namespace fbla {
 namespace tc {
 
+#ifndef FBLA_PREFETCH_TILES
+#define FBLA_PREFETCH_TILES 0
+#endif
 constexpr int kTileTokens = 128;      // tokens per tile = rows of one MMA
 constexpr int kBlockBytes = 16384;    // one [128 tokens][64 features] 16-bit block in shared memory
 constexpr int kThreads = 192;         // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue

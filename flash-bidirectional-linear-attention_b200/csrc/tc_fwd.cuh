@@ -13,6 +13,10 @@
 
 #include "tc_common.cuh"
 
+#ifndef FBLA_FWD_STATE_SMEM_KB
+#define FBLA_FWD_STATE_SMEM_KB 128
+#endif
+
 namespace fbla {
 namespace tc {
 
@@ -22,8 +26,13 @@ struct FwdStateCfg {
     static constexpr int kKB = DK / 64, kVB = DV / 64;
     static constexpr int kStageBlocks = kKB + kVB + (MODE == kDecoupled ? kKB : 0);
     static constexpr int kStageBytes = kStageBlocks * kBlockBytes;
-    static constexpr int kStages = (192 * 1024) / kStageBytes < 8 ? (192 * 1024) / kStageBytes : 8;
-    static constexpr int kOnesBytes = 1024;
+    static constexpr int kStages = (FBLA_FWD_STATE_SMEM_KB * 1024) / kStageBytes < 8 ? (FBLA_FWD_STATE_SMEM_KB * 1024) / kStageBytes : 8;
+    // The key sum is K^T . ones.  With dv = 64 (and k the same tensor as kr) the ones are a full
+    // 128-token block that the B descriptor reaches as the N-block after the v tile, so state and
+    // key sum come from ONE MMA per 16 tokens (N = dv + 16) and the key tile is read once.
+    // Otherwise a small ones tile feeds a second MMA (N = 16).
+    static constexpr bool kMergedSum = (MODE == kLinear && DV == 64);
+    static constexpr int kOnesBytes = kMergedSum ? kBlockBytes : 1024;
     static constexpr int kTmemCols = (DV + 16) <= 128 ? 128 : 256;
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kOnesBytes + 256;
 };
@@ -79,9 +88,27 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
+        constexpr int kAhead = FBLA_PREFETCH_TILES;   // L2 prefetch distance, in tiles
+        for (int g = g0; g < min(g1, g0 + kAhead); ++g) {
+            const int unit = g / sch.tiles_per_unit;
+            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+#pragma unroll
+            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_prefetch_3d(&tm_kr, b * 64, t0, unit);
+#pragma unroll
+            for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_prefetch_3d(&tm_v, b * 64, t0, unit);
+        }
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
+            if (kAhead > 0 && g + kAhead < g1) {
+                const int gp = g + kAhead;
+                const int unit = gp / sch.tiles_per_unit;
+                const int t0 = (gp - unit * sch.tiles_per_unit) * kTileTokens;
+#pragma unroll
+                for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_prefetch_3d(&tm_kr, b * 64, t0, unit);
+#pragma unroll
+                for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_prefetch_3d(&tm_v, b * 64, t0, unit);
+            }
             if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 101)) break;
             ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
             const int unit = g / sch.tiles_per_unit;
@@ -100,8 +127,9 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
-        const uint32_t idesc_s = ptx::instr_desc(DK, DV, BF16, true, true);
+        const uint32_t idesc_s = ptx::instr_desc(DK, Cfg::kMergedSum ? DV + 16 : DV, BF16, true, true);
         const uint32_t idesc_k = ptx::instr_desc(DK, 16, BF16, true, false);
+        const uint32_t ones_base = ptx::smem_u32(ones);
         const uint64_t d_ones = ptx::smem_desc(ptx::smem_u32(ones), 128, 256, ptx::kLayoutNone);
         int seg = 0;
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
@@ -120,9 +148,11 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
             for (int ks = 0; ks < kTileTokens / 16; ++ks) {
                 const bool acc = !(first && ks == 0);
                 const uint64_t da = ptx::smem_desc(a_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                const uint64_t db = ptx::smem_desc(b_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                // merged: the N-block after the v tile (leading byte offset) is the block of ones
+                const uint64_t db = ptx::smem_desc(b_base + ks * 2048, Cfg::kMergedSum ? ones_base - b_base : kBlockBytes,
+                                                   1024, ptx::kLayoutSw128);
                 ptx::mma_ss(tmem, da, db, idesc_s, acc);
-                if (MODE != kSimple) {
+                if (MODE != kSimple && !Cfg::kMergedSum) {
                     const uint64_t dk = ptx::smem_desc(k_base + ks * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
                     ptx::mma_ss(tmem + DV, dk, d_ones, idesc_k, acc);
                 }
@@ -177,17 +207,21 @@ tc_reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ st
 template <int DK, int DV, int MODE>
 struct FwdOutCfg {
     static constexpr int kKB = DK / 64, kVB = DV / 64;
-    static constexpr int kBopRows = DV + (MODE != kSimple ? 16 : 0);     // N of the B operand
-    static constexpr int kBopBlock = kBopRows * 128;                      // bytes per 64-wide K block
-    static constexpr int kBopHiBytes = ((kKB * kBopBlock + 1023) / 1024) * 1024;
-    static constexpr int kBopLoBlock = DV * 128;                          // residual of scale*S (no normaliser rows)
-    static constexpr int kBopBytes = kBopHiBytes + kKB * kBopLoBlock;
+    // B operand, per 64-wide K block: [dv rows: high part of scale*S^T][dv rows: rounding residual]
+    // [16 rows: kmean high, kmean low, zeros].  With dv = 64 the three groups are the N range of ONE
+    // MMA (N = 144): the accumulator holds [num_hi | num_lo | z] and the epilogue adds the halves.
+    // With dv = 128 that would exceed N = 256, so high and residual accumulate into the same columns.
+    static constexpr bool kWide = (DV == 64);
+    static constexpr int kZRows = MODE != kSimple ? 16 : 0;
+    static constexpr int kBopBlock = (2 * DV + kZRows) * 128;            // bytes per 64-wide K block
+    static constexpr int kBopBytes = ((kKB * kBopBlock + 1023) / 1024) * 1024;
+    static constexpr int kZCol = kWide ? 2 * DV : DV;                     // accumulator column of z
     static constexpr int kStageBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
     static constexpr int kStageBytes = kStageBlocks * kBlockBytes;
     static constexpr int kOutBytes = kVB * kBlockBytes;                   // one staged output tile
     static constexpr int kAvail = 200 * 1024 - kBopBytes - 2 * kOutBytes;
     static constexpr int kStages = kAvail / kStageBytes < 8 ? kAvail / kStageBytes : 8;
-    static constexpr int kAccCols = DV + 16;
+    static constexpr int kAccCols = kZCol + 16;
     static constexpr int kTmemCols = 2 * kAccCols <= 256 ? 256 : 512;
     static constexpr int kSmemBytes = 1024 + kBopBytes + kStages * kStageBytes + 2 * kOutBytes + 512;
 };
@@ -266,7 +300,9 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
-        const uint32_t idesc_n = ptx::instr_desc(128, DV, BF16, false, false);
+        constexpr bool kOneMma = Cfg::kWide && MODE != kDecoupled;   // numerator halves and z in one instruction
+        const uint32_t idesc_n =
+            ptx::instr_desc(128, kOneMma ? 2 * DV + Cfg::kZRows : (Cfg::kWide ? 2 * DV : DV), BF16, false, false);
         const uint32_t idesc_z = ptx::instr_desc(128, 16, BF16, false, false);
         const uint32_t bop_base = ptx::smem_u32(bop);
         int seg = 0;
@@ -293,15 +329,17 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                     const bool accum = !(kb == 0 && kk == 0);
                     const uint64_t da = ptx::smem_desc(qr_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     const uint64_t db = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                    const uint64_t dl = ptx::smem_desc(bop_base + Cfg::kBopHiBytes + kb * Cfg::kBopLoBlock + kk * 32, 16, 1024,
-                                                       ptx::kLayoutSw128);
                     ptx::mma_ss(acc, da, db, idesc_n, accum);
-                    ptx::mma_ss(acc, da, dl, idesc_n, true);
-                    if (MODE != kSimple) {
-                        const uint64_t dq = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t dz = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + DV * 128 + kk * 32, 16, 1024,
+                    if (!Cfg::kWide) {
+                        const uint64_t dl = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + DV * 128 + kk * 32, 16, 1024,
                                                            ptx::kLayoutSw128);
-                        ptx::mma_ss(acc + DV, dq, dz, idesc_z, accum);
+                        ptx::mma_ss(acc, da, dl, idesc_n, true);
+                    }
+                    if (MODE != kSimple && !kOneMma) {
+                        const uint64_t dq = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t dz = ptx::smem_desc(bop_base + kb * Cfg::kBopBlock + 2 * DV * 128 + kk * 32, 16, 1024,
+                                                           ptx::kLayoutSw128);
+                        ptx::mma_ss(acc + Cfg::kZCol, dq, dz, idesc_z, accum);
                     }
                 }
             }
@@ -332,8 +370,8 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                     const uint16_t h = pack1(x, BF16);
                     *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(v, k & 63)) = h;
                     // rounding residual: a second B operand accumulated into the same columns
-                    *reinterpret_cast<uint16_t*>(bop + Cfg::kBopHiBytes + (k >> 6) * Cfg::kBopLoBlock +
-                                                 ptx::sw128_offset(v, k & 63)) = pack1(x - unpack1(h, BF16), BF16);
+                    *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(DV + v, k & 63)) =
+                        pack1(x - unpack1(h, BF16), BF16);
                 }
                 if (MODE != kSimple) {
                     for (int i = et; i < 16 * DK; i += kEpiThreads) {
@@ -344,7 +382,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                             const uint16_t hi = pack1(km, BF16);
                             h = r == 0 ? hi : pack1(km - unpack1(hi, BF16), BF16);
                         }
-                        *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(DV + r, k & 63)) = h;
+                        *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(2 * DV + r, k & 63)) = h;
                     }
                 }
                 ptx::fence_proxy_async_smem();
@@ -356,7 +394,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
             float rz = 1.f;
             if (MODE != kSimple) {
                 float zc[16];
-                ptx::tmem_ld16(t_lane + a * Cfg::kAccCols + DV, zc);
+                ptx::tmem_ld16(t_lane + a * Cfg::kAccCols + Cfg::kZCol, zc);
                 ptx::tmem_ld_wait();
                 rz = 1.f / (zc[0] + zc[1] + p.eps);
             }
@@ -371,7 +409,15 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
             for (int c0 = 0; c0 < DV; c0 += 32) {
                 float v[32];
                 ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + c0, v);
-                ptx::tmem_ld_wait();
+                if (Cfg::kWide) {
+                    float lo[32];
+                    ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + DV + c0, lo);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += lo[j];
+                } else {
+                    ptx::tmem_ld_wait();
+                }
                 uint8_t* blk = ob + (c0 >> 6) * kBlockBytes + row * 128;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {

@@ -15,6 +15,10 @@ namespace {
 
 using namespace tc;
 
+#ifndef FBLA_L2_PROMOTION
+#define FBLA_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
+
 // ---- driver entry point for tensor-map encoding (no link-time dependency on libcuda) ------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -80,7 +84,7 @@ cudaError_t encode_map(CUtensorMap* m, const void* base, int dtype, int D, int64
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = dtype == FBLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_SWIZZLE_128B, FBLA_L2_PROMOTION,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
@@ -271,6 +275,20 @@ int64_t tc_workspace_bytes(const KParams& p) {
     const Schedule s = make_schedule(p, sm_count());
     return (int64_t)s.units * s.slots_per_unit * p.state_stride * (int64_t)sizeof(float);
 }
+
+#ifdef FBLA_PROFILE
+}  // namespace fbla
+extern "C" int fbla_debug_read_profile(long long* out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, fbla::tc::g_prof_bwd_state, sizeof(long long) * 16);
+    if (reset) {
+        long long z[16] = {0};
+        cudaMemcpyToSymbol(fbla::tc::g_prof_bwd_state, z, sizeof(z));
+    }
+    return 0;
+}
+namespace fbla {
+#endif
 
 int tc_device_status() { return g_status_host != nullptr ? *g_status_host : 0; }
 

@@ -10,7 +10,7 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libflash_bla_sm100.so")
+LIB_PATH = os.environ.get("FLASH_BLA_LIB") or os.path.join(_HERE, "lib", "libflash_bla_sm100.so")
 
 F32, BF16, F16 = 0, 1, 2
 FLAG_GENERIC = 1
