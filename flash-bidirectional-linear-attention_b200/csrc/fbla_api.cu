@@ -212,6 +212,17 @@ int bwd_in(const fbla_problem* p, OpKind op, const void* k_rope, const void* v, 
 
 }  // namespace
 
+namespace fbla {
+int api_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int api_resolve_linear(const fbla_problem* p, KParams* kp) { return resolve(p, OP_LINEAR, kp); }
+}  // namespace fbla
+
 extern "C" {
 
 int fbla_version(void) { return FBLA_ABI_VERSION; }

@@ -69,6 +69,11 @@ template <> __device__ __forceinline__ float from_f<float>(float x) { return x; 
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
 
+// Used by entry points that live outside fbla_api.cu: record an error text for the calling thread
+// (returns `code`), and validate a fixed-length linear_attention problem.
+int api_fail(int code, const char* fmt, ...);
+int api_resolve_linear(const fbla_problem* p, KParams* kp);
+
 // Kernel-launch counter behind fbla_launch_count(): every launcher reports what it enqueued.
 void note_launches(int n);
 

@@ -133,7 +133,11 @@ int* status_word() {
     return g_status_dev;
 }
 
-Params make_params(const KParams& p, int dtype, const Schedule& s) {
+Params make_params(const KParams& p, int dtype, const Schedule& s, int* status);
+
+Params make_params(const KParams& p, int dtype, const Schedule& s) { return make_params(p, dtype, s, status_word()); }
+
+Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) {
     Params q;
     q.sch = s;
     q.seq_len = (int)p.seq_len;
@@ -141,7 +145,7 @@ Params make_params(const KParams& p, int dtype, const Schedule& s) {
     q.inv_norm = p.inv_norm > 0.f ? p.inv_norm : 1.f / (float)p.seq_len;
     q.eps = p.eps;
     q.is_bf16 = dtype == FBLA_BF16;
-    q.status = status_word();
+    q.status = status;
     q.part = nullptr;
     q.state = nullptr;
     q.state_stride = p.state_stride;
@@ -294,11 +298,16 @@ int tc_device_status() { return g_status_host != nullptr ? *g_status_host : 0; }
 
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v, float* state,
                          void* ws, cudaStream_t st) {
+    return tc_fwd_state_status(p, dtype, k, k_rope, v, state, ws, status_word(), st);
+}
+
+cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
+                                float* state, void* ws, int* status, cudaStream_t st) {
     const bool dec = k_rope != nullptr && k_rope != k;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
-    Params q = make_params(p, dtype, s);
-    if (q.status == nullptr) return cudaErrorMemoryAllocation;
+    if (status == nullptr) return cudaErrorMemoryAllocation;
+    Params q = make_params(p, dtype, s, status);
     q.part = static_cast<float*>(ws);
     CUtensorMap tkr, tk, tv;
     cudaError_t e;

@@ -14,6 +14,9 @@ int tc_device_status();
 int64_t tc_workspace_bytes(const KParams& p);
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
                          float* state, void* ws, cudaStream_t st);
+// Same pass with the kernels' status word supplied by the caller (device-accessible memory).
+cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
+                                float* state, void* ws, int* status, cudaStream_t st);
 cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q, const void* q_rope, const float* state,
                        void* o, cudaStream_t st);
 cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q, const void* q_rope, const void* d_o,

@@ -68,6 +68,7 @@ def exported_symbols():
              "fbla_workspace_bytes", "fbla_kernel_path"]
     for op in OPS:
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
+    names.append("fbla_linear_attn_fwd_state_noalloc")
     return names
 
 
@@ -97,6 +98,8 @@ def lib():
                 f = getattr(L, f"fbla_{op}_{name}")
                 f.restype = ctypes.c_int
                 f.argtypes = [_P] + args
+        L.fbla_linear_attn_fwd_state_noalloc.restype = ctypes.c_int
+        L.fbla_linear_attn_fwd_state_noalloc.argtypes = [_P, _vp, _vp, _vp, _vp]   # k, v, state, stream
         _lib = L
     return _lib
 

@@ -110,6 +110,15 @@ int fbla_linear_attn_bwd_state(const fbla_problem *p, const void *q, const void 
 int fbla_linear_attn_bwd_in(const fbla_problem *p, const void *k, const void *v,
                             const float *dstate, void *dk, void *dv, fbla_stream_t stream);
 
+/* Forward state pass for callers that cannot hand over a workspace and must not allocate: same
+ * result as fbla_linear_attn_fwd_state, with the scratch in an 8 MiB device array inside the
+ * library (held by every GPU that loads it).  No counterpart in the reference.  Refuses problems
+ * whose fbla_workspace_bytes() exceeds 8 MiB or that the tensor-core kernels do not serve.  The
+ * first call on a device resolves the array's address and should precede any stream capture;
+ * calls that overlap on the GPU race on the shared array.                                   */
+int fbla_linear_attn_fwd_state_noalloc(const fbla_problem *p, const void *k, const void *v,
+                                       float *state, fbla_stream_t stream);
+
 /* ---- simple_la (no normaliser) -------------------------------------------------------
  * Replaces SimpleLinearAttnFunction.forward / .backward,
  * flash_bla/ops/simple_la/fused.py:495-535 and :539-626 (kernels :26-79, :94-145,
