@@ -1,0 +1,71 @@
+"""Sequence sharding on real GPUs: two NCCL ranks each hold half of the tokens; outputs and
+gradients must match the single-GPU operator on the whole sequence.  Needs two GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from flash_bla.ops.linear_attn.fused import linear_attention
+        from flash_bla.ops.simple_la.fused import simple_la
+        from flash_bla.ops.sharded import seq_sharded_linear_attention, seq_sharded_simple_la
+        errs = {}
+        for name, D, dtype in (("linear", 64, torch.bfloat16), ("simple", 128, torch.bfloat16),
+                               ("linear_f32", 32, torch.float32)):
+            g = torch.Generator(device="cuda").manual_seed(7)
+            B, H, T = 2, 4, 2048
+            q = torch.rand(B, H, T, D, device="cuda", generator=g).add_(0.1).to(dtype)
+            k = torch.rand(B, H, T, D, device="cuda", generator=g).add_(0.1).to(dtype)
+            v = torch.randn(B, H, T, D, device="cuda", generator=g).to(dtype)
+            do = torch.randn(B, H, T, D, device="cuda", generator=g).to(dtype)
+            sl = slice(rank * T // world, (rank + 1) * T // world)
+            xs = [x[:, :, sl].contiguous().requires_grad_() for x in (q, k, v)]
+            full = [x.clone().requires_grad_() for x in (q, k, v)]
+            if name.startswith("linear"):
+                o = seq_sharded_linear_attention(*xs)
+                o_ref = linear_attention(*full)
+            else:
+                o = seq_sharded_simple_la(*xs)
+                o_ref = simple_la(*full)
+            o.backward(do[:, :, sl].contiguous())
+            o_ref.backward(do)
+            # The sharded and the single-GPU run add the fp32 state in a different order, so 16-bit
+            # outputs may land on neighbouring representable values: allow one unit in the last
+            # place of the output type plus 0.2 % of the RMS (fp32: 1e-4 of the RMS).
+            ulp = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10, torch.float32: 0.0}[dtype]
+            worst = 0.0
+            for a, b in [(o, o_ref[:, :, sl])] + [(x.grad, f.grad[:, :, sl]) for x, f in zip(xs, full)]:
+                a, b = a.float(), b.float()
+                rms = b.pow(2).mean().sqrt().item()
+                slack = ulp * b.abs() + (2e-3 if ulp else 1e-4) * rms
+                worst = max(worst, ((a - b).abs() / slack).max().item())
+            errs[name] = worst
+        ret[rank] = errs
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_sequence_sharding_matches_one_gpu():
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for errs in ret.values():
+        assert all(e <= 1.0 for e in errs.values()), dict(ret)
