@@ -39,6 +39,21 @@ class Problem(ctypes.Structure):
     ]
 
 
+class PisaProblem(ctypes.Structure):
+    """Mirror of ``struct fbla_pisa_problem``."""
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("dk", ctypes.c_int32),
+        ("dv", ctypes.c_int32),
+        ("block_size", ctypes.c_int32),
+        ("num_selected", ctypes.c_int32),
+        ("seq_len", ctypes.c_int64),
+        ("scale", ctypes.c_float),
+    ]
+
+
 _P = ctypes.POINTER(Problem)
 _vp = ctypes.c_void_p
 _sz = ctypes.c_size_t
@@ -69,6 +84,7 @@ def exported_symbols():
     for op in OPS:
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
     names.append("fbla_linear_attn_fwd_state_noalloc")
+    names += ["fbla_pisa_block_stats", "fbla_pisa_first_order_state", "fbla_pisa_fwd"]
     return names
 
 
@@ -100,6 +116,11 @@ def lib():
                 f.argtypes = [_P] + args
         L.fbla_linear_attn_fwd_state_noalloc.restype = ctypes.c_int
         L.fbla_linear_attn_fwd_state_noalloc.argtypes = [_P, _vp, _vp, _vp, _vp]   # k, v, state, stream
+        _PP = ctypes.POINTER(PisaProblem)
+        for name, n_ptr in (("fbla_pisa_block_stats", 7), ("fbla_pisa_first_order_state", 5), ("fbla_pisa_fwd", 10)):
+            f = getattr(L, name)
+            f.restype = ctypes.c_int
+            f.argtypes = [_PP] + [_vp] * n_ptr          # tensor pointers, then the stream
         _lib = L
     return _lib
 

@@ -1,0 +1,131 @@
+"""Piecewise sparse attention (PISA): softmax attention that is exact on the top-scoring key
+blocks of every query block and approximated on the rest by the blocks' mean key / summed
+value (zeroth order) plus one global first-order term.
+
+Same public surface as the reference module ``flash_bla/ops/piecewise_attn/kernel.py``
+(``chunk_reduce`` :131-149, ``fused_chunk_reduce`` :152-176, ``piecewise_sparse_attention``
+:295-333).  As there, the block scores and the top-k selection are a few torch calls between
+the two CUDA stages; everything that touches q, k, v runs in the sm_100a library.
+"""
+import ctypes
+
+import torch
+
+from flash_bla import _C
+from flash_bla.ops import _passes as P
+
+
+def _problem(q, v, block_size, num_selected, scale):
+    B, H, T, K = q.shape
+    p = _C.PisaProblem()
+    p.dtype = _C.dtype_code(q.dtype)
+    p.batch, p.heads, p.dk, p.dv = B, H, K, v.shape[-1]
+    p.block_size, p.num_selected, p.seq_len = int(block_size), int(num_selected), T
+    p.scale = float(scale)
+    return p
+
+
+def _check(q, k, v):
+    if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
+        raise ValueError("expected q, k of shape (B, H, T, K) and v of shape (B, H, T, V)")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise ValueError("q, k and v must have the same dtype")
+    if not q.is_cuda:
+        raise RuntimeError("flash_bla operators run on CUDA tensors only (there is no CPU path)")
+
+
+def block_statistics(q, k, v, block_size):
+    """fp32 block statistics: qc, kc ``(B,H,NT,K)`` block means (true length of a ragged last
+    block), vc ``(B,H,NT,V)`` block sums."""
+    _check(q, k, v)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, H, T, K = q.shape
+    V = v.shape[-1]
+    nt = -(-T // block_size)
+    prob = _problem(q, v, block_size, 1, 1.0)
+    qc = torch.empty(B, H, nt, K, dtype=torch.float32, device=q.device)
+    kc = torch.empty_like(qc)
+    vc = torch.empty(B, H, nt, V, dtype=torch.float32, device=q.device)
+    with torch.cuda.device_of(q):
+        _C.check(_C.lib().fbla_pisa_block_stats(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), _C.stream_of(q)))
+    return qc, kc, vc
+
+
+def first_order_state(k, v, kc, vc, block_size):
+    """h = sum over blocks of (K_c - kc_c)^T V_c = K^T V - sum_c kc_c (x) vc_c, fp32 ``(B,H,K,V)``.
+    K^T V is the state pass of ``simple_la`` (tensor cores for 16-bit inputs with K, V in {64, 128})."""
+    B, H, T, K = k.shape
+    V = v.shape[-1]
+    sp = P.make_problem(k, batch=B, heads=H, seq_len=T, dk=K, dv=V, normalize=False, scale=1.0,
+                        flags=P.default_flags())
+    kv = P.fwd_state("simple_la", sp, k, v)
+    prob = _problem(k, v, block_size, 1, 1.0)
+    h = torch.empty(B, H, K, V, dtype=torch.float32, device=k.device)
+    with torch.cuda.device_of(k):
+        _C.check(_C.lib().fbla_pisa_first_order_state(ctypes.byref(prob), kv.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                      h.data_ptr(), _C.stream_of(k)))
+    return h
+
+
+def chunk_reduce(q, k, v, chunk_size):
+    """Block means of q and k and block sums of v, in the dtype of the inputs."""
+    qc, kc, vc = block_statistics(q, k, v, chunk_size)
+    return qc.to(q.dtype), kc.to(k.dtype), vc.to(v.dtype)
+
+
+def fused_chunk_reduce(q, k, v, chunk_size, use_bias=False, p=2):
+    """``(qc, kc, vc, h, bias)`` in the dtype of the inputs; ``bias`` is ``None`` unless ``use_bias``."""
+    if use_bias:
+        raise NotImplementedError("use_bias=True (per-block norm of the first-order state) is not built yet")
+    qc, kc, vc = block_statistics(q, k, v, chunk_size)
+    h = first_order_state(k.contiguous(), v.contiguous(), kc, vc, chunk_size)
+    return qc.to(q.dtype), kc.to(k.dtype), vc.to(v.dtype), h.to(v.dtype), None
+
+
+def select_blocks(qc, kc, scale, density, dtype):
+    """Indices ``(B,H,NT,NS)`` of the key blocks each query block attends exactly: top-k of the
+    block-mean scores computed in the dtype of the inputs, ``NS = max(1, int(density * NT))``."""
+    nt = kc.shape[-2]
+    score = torch.einsum('bhid,bhjd->bhij', qc.to(dtype), (kc * scale).to(dtype))
+    top_k = max(1, int(density * nt))
+    return torch.topk(score, k=top_k, dim=-1).indices
+
+
+def attention_forward(q, k, v, kc, vc, h, indices, block_size, scale, want_stats=False):
+    """The attention stage with statistics and selection given (all fp32 statistics)."""
+    _check(q, k, v)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, H, T, K = q.shape
+    idx = indices.to(torch.int32).contiguous()
+    prob = _problem(q, v, block_size, idx.shape[-1], scale)
+    o = torch.empty_like(v)
+    stats = torch.empty(B, H, T, 4, dtype=torch.float32, device=q.device) if want_stats else None
+    with torch.cuda.device_of(q):
+        _C.check(_C.lib().fbla_pisa_fwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                        kc.contiguous().data_ptr(), vc.contiguous().data_ptr(),
+                                        h.contiguous().data_ptr(), idx.data_ptr(), o.data_ptr(),
+                                        _C.ptr(stats), _C.stream_of(q)))
+    return (o, stats) if want_stats else o
+
+
+def piecewise_sparse_attention(q, k, v, density=0.1, block_size=64, scale=None, use_bias=False):
+    r"""
+    Args:
+        q, k: queries / keys `(B, H, T, K)`; v: values `(B, H, T, V)`.
+        density: fraction of key blocks attended exactly per query block (at least one).
+        block_size: tokens per block.
+        scale: logit scale, `K ** -0.5` by default.
+        use_bias: add the log of the blocks' first-order norm to the selection scores.
+    Returns the attention output `(B, H, T, V)`.
+    """
+    if use_bias:
+        raise NotImplementedError("use_bias=True (per-block norm of the first-order state) is not built yet")
+    _check(q, k, v)
+    K = k.shape[-1]
+    scale = K ** -0.5 if scale is None else scale
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    qc, kc, vc = block_statistics(q, k, v, block_size)
+    h = first_order_state(k, v, kc, vc, block_size)
+    indices = select_blocks(qc, kc, scale, density, q.dtype)
+    return attention_forward(q, k, v, kc, vc, h, indices, block_size, scale)

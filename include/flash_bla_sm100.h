@@ -168,6 +168,38 @@ int fbla_varlen_linear_attn_bwd_in(const fbla_problem *p, const void *k, const v
                                    const float *dstate, void *dk, void *dv,
                                    fbla_stream_t stream);
 
+/* ---- piecewise_sparse_attention (PISA) ------------------------------------------------
+ * Softmax attention approximated piecewise: exact on the `num_selected` key blocks chosen per
+ * query block, zeroth order (block means / sums) plus a global first-order term on the rest.
+ * Replaces fused_chunk_reduce + fused_chunk_reduce_kernel
+ * (flash_bla/ops/piecewise_attn/kernel.py:152-176, :89-128) and
+ * piecewise_sparse_attention_fwd_kernel (:189-292).  The block scores and the top-k selection
+ * between the two calls stay with the caller, as in the reference (:313-318).
+ *   q, k (batch, heads, seq_len, dk), v, o (batch, heads, seq_len, dv); block statistics fp32:
+ *   qc, kc (batch, heads, NT, dk) block means; vc (batch, heads, NT, dv) block sums;
+ *   kv (batch, heads, dk, dv) = K^T V (the state of fbla_simple_la_fwd_state);
+ *   h (batch, heads, dk, dv) = kv - sum_c kc_c (x) vc_c = sum_c (K_c - kc_c)^T V_c;
+ *   indices int32 (batch, heads, NT, num_selected); NT = ceil(seq_len / block_size).
+ *   row_stats fp32 (batch, heads, seq_len, 4): running max (log2 domain), denominator, g, unused;
+ *   may be NULL when no backward follows.                                                   */
+typedef struct fbla_pisa_problem {
+    int32_t dtype;          /* enum fbla_dtype of q, k, v, o                        */
+    int32_t batch, heads;
+    int32_t dk, dv;         /* 1..128                                               */
+    int32_t block_size;     /* tokens per block, 1..128                             */
+    int32_t num_selected;   /* key blocks attended exactly per query block          */
+    int64_t seq_len;
+    float scale;            /* logit scale (reference default dk^-0.5)              */
+} fbla_pisa_problem;
+
+int fbla_pisa_block_stats(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,
+                          float *qc, float *kc, float *vc, fbla_stream_t stream);
+int fbla_pisa_first_order_state(const fbla_pisa_problem *p, const float *kv, const float *kc,
+                                const float *vc, float *h, fbla_stream_t stream);
+int fbla_pisa_fwd(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,
+                  const float *kc, const float *vc, const float *h, const int32_t *indices,
+                  void *o, float *row_stats, fbla_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,73 @@
+"""piecewise_sparse_attention on the GPU against the golden fixtures (produced by the
+reference's own Triton kernels) and the CPU oracle."""
+import pytest
+import torch
+
+from oracle import bla_oracle as O
+from helpers import check, load_golden
+
+pytestmark = pytest.mark.gpu
+
+from flash_bla.ops.piecewise_attn.kernel import (attention_forward, block_statistics, first_order_state,
+                                                 fused_chunk_reduce, piecewise_sparse_attention, select_blocks)
+
+
+@pytest.mark.parametrize("name", ["pisa_a", "pisa_b"])
+def test_golden(name):
+    g = load_golden(name)
+    bs = int(g["block_size"])
+    q, k, v = (g[x].cuda() for x in ("q", "k", "v"))
+    qc, kc, vc = block_statistics(q, k, v, bs)
+    h = first_order_state(k, v, kc, vc, bs)
+    for got, key in ((qc, "qc"), (kc, "kc"), (vc, "vc")):
+        check(got, g[key], torch.float32, f"{name}.{key}")
+    assert O.rel_l2(h.cpu(), g["h"]) < 1e-4
+    idx = select_blocks(qc, kc, g["scale"], g["density"], torch.float32)
+    assert torch.equal(idx.sort(-1).values.cpu(), g["indices"].sort(-1).values)
+    o = attention_forward(q, k, v, kc, vc, h, g["indices"].cuda(), bs, g["scale"])
+    assert O.rel_l2(o.cpu(), g["o"]) < 1e-4
+    # the whole operator picks the same blocks here, so it must give the same output
+    o2 = piecewise_sparse_attention(q, k, v, density=g["density"], block_size=bs, scale=g["scale"])
+    assert O.rel_l2(o2.cpu(), g["o"]) < 1e-4
+
+
+CASES = [
+    (1, 2, 300, 64, 64, 64, 0.2),
+    (2, 2, 1000, 128, 128, 64, 0.1),
+    (1, 3, 257, 32, 48, 32, 0.3),
+    (1, 1, 130, 16, 16, 128, 0.5),
+    (1, 2, 4608, 128, 128, 64, 0.1),     # one (b, h) pair of the DiT-layer configuration
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", CASES)
+def test_forward_matches_oracle(case, dtype):
+    B, H, T, K, V, bs, density = case
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(B, H, T, d, generator=g).to(dtype) for d in (K, K, V))
+    scale = K ** -0.5
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    qc, kc, vc = block_statistics(qd, kd, vd, bs)
+    h = first_order_state(kd, vd, kc, vc, bs)
+    idx = select_blocks(qc, kc, scale, density, dtype)
+    o, stats = attention_forward(qd, kd, vd, kc, vc, h, idx, bs, scale, want_stats=True)
+    rqc, rkc, rvc, rh = O.pisa_block_stats(q, k, v, bs)
+    assert O.rel_l2(qc.cpu(), rqc) < 1e-5 and O.rel_l2(kc.cpu(), rkc) < 1e-5 and O.rel_l2(vc.cpu(), rvc) < 1e-5
+    assert O.rel_l2(h.cpu(), rh) < (1e-4 if dtype == torch.float32 else 2e-3)
+    ref, _ = O.pisa_fwd(q, k, v, density, bs, scale, indices=idx.cpu())
+    if dtype == torch.float32:
+        assert O.rel_l2(o.cpu(), ref) < 2e-5
+    else:
+        check(o, ref, dtype, f"pisa{case}.o")
+    assert torch.isfinite(stats).all() and (stats[..., 1] > 0).all()
+
+
+def test_reference_surface():
+    q = torch.randn(1, 2, 128, 32, device="cuda")
+    qc, kc, vc, h, bias = fused_chunk_reduce(q, q, q, 32)
+    assert qc.shape == (1, 2, 4, 32) and h.shape == (1, 2, 32, 32) and bias is None and qc.dtype == q.dtype
+    with pytest.raises(NotImplementedError):
+        piecewise_sparse_attention(q, q, q, use_bias=True)
+    with pytest.raises(RuntimeError):
+        piecewise_sparse_attention(q.cpu(), q.cpu(), q.cpu())
