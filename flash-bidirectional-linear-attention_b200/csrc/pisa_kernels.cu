@@ -329,3 +329,421 @@ int fbla_pisa_fwd(const fbla_pisa_problem* p, const void* q, const void* k, cons
 }
 
 }  // extern "C"
+
+// =========================================================================================
+// Backward.  The reference has no backward for this operator; these kernels differentiate the
+// forward above with the block selection held constant (gradients flow through the block
+// statistics kc, vc, h as well).  Per query row, with dnum = dO / D, dD = -(o . dO) / D,
+// r = q h, w = scale / T:
+//   dg = dD + (dnum . r) w            dr = dnum g w
+//   exact keys j : dp_j = dnum . v_j + dD      ds_j = p_j dp_j
+//   blocks c     : dpi_c = dnum . vc_c + dg len_c   da_c = pi_c dpi_c
+//   dq  = scale (sum_j ds_j k_j + sum_c da_c kc_c) + h dr
+//   dk_j += scale ds_j q      dv_j += p_j dnum
+//   dkc_c += scale da_c q     dvc_c += pi_c dnum     dh += q (x) dr
+// and through the statistics:  dk_t += dkc_c / len_c + dh (v_t - vc_c / len_c),
+//                              dv_t += dvc_c + dh^T (k_t - kc_c).
+// Kernel 1 (one CTA per query block) writes dq and the per-row dD, and adds dkc, dvc, dh into
+// fp32 buffers with atomics; kernel 2 (one CTA per key block) gathers the exact-attention part
+// of dk, dv from the query blocks that selected it and adds the statistics terms.
+// =========================================================================================
+namespace fbla {
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(kPisaThreads)
+pisa_bwd_q_kernel(PisaParams p, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                  const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ kc,
+                  const float* __restrict__ vc, const float* __restrict__ h, const int32_t* __restrict__ indices,
+                  const float* __restrict__ row_stats, T* __restrict__ dq, float* __restrict__ dkc,
+                  float* __restrict__ dvc, float* __restrict__ dh, float* __restrict__ drow) {
+    extern __shared__ float smem[];
+    const int K = p.dk, V = p.dv, KP = K + 1, VP = V + 1;
+    const int rows_buf = max(p.bs, kChunkRows);
+    float* qs = smem;                          // [bs][K]
+    float* dos = qs + p.bs * K;                // [bs][V]   dO rows
+    float* drs = dos + p.bs * V;               // [bs][V]   dr rows
+    float* kb = drs + p.bs * V;                // [rows_buf][K+1]
+    float* vb = kb + rows_buf * KP;            // [rows_buf][V+1]
+    float* das = vb + rows_buf * VP;           // [bs][64]  scale * da   (one chunk of blocks)
+    float* pis = das + p.bs * kChunkRows;      // [bs][64]  pi / D
+    unsigned char* sel = reinterpret_cast<unsigned char*>(pis + p.bs * kChunkRows);
+
+    const int i_blk = blockIdx.x, bh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = i_blk * p.bs;
+    const int nrows = min(p.bs, p.T - t0);
+    const size_t base_row = (size_t)bh * p.T;
+    const float sm = p.scale * 1.44269504f;
+    const float w = p.scale / (float)p.T;
+    const int32_t* idx = indices + ((size_t)bh * p.nt + i_blk) * p.ns;
+
+    for (int i = threadIdx.x; i < p.bs * K; i += kPisaThreads) {
+        const int r = i / K, d = i - r * K;
+        qs[i] = r < nrows ? to_f<T>(q[(base_row + t0 + r) * K + d]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < p.bs * V; i += kPisaThreads) {
+        const int r = i / V, d = i - r * V;
+        dos[i] = r < nrows ? to_f<T>(d_o[(base_row + t0 + r) * V + d]) : 0.f;
+        drs[i] = 0.f;
+    }
+    for (int i = threadIdx.x; i < p.nt; i += kPisaThreads) sel[i] = 0;
+    // h, padded rows: hs[d * (V+1) + col]
+    float* hs = kb;
+    const float* hb = h + (size_t)bh * K * V;
+    for (int i = threadIdx.x; i < K * V; i += kPisaThreads) {
+        const int d = i / V, c = i - d * V;
+        hs[d * VP + c] = hb[i];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.ns; i += kPisaThreads) {
+        const int c = idx[i];
+        if (c >= 0 && c < p.nt) sel[c] = 1;
+    }
+
+    float mrow[kMaxRowsPerWarp], rD[kMaxRowsPerWarp], dD[kMaxRowsPerWarp], dg[kMaxRowsPerWarp];
+    float dqa[kMaxRowsPerWarp][4];
+    // ---- per row: dD, r = q h, dg, dr, and the first-order part of dq ----
+    for (int r = warp, ri = 0; r < p.bs; r += kPisaWarps, ++ri) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dqa[ri][c] = 0.f;
+        mrow[ri] = 0.f; rD[ri] = 0.f; dD[ri] = 0.f; dg[ri] = 0.f;
+        if (r >= nrows) continue;
+        const size_t row = base_row + t0 + r;
+        const float4 st = *reinterpret_cast<const float4*>(row_stats + row * 4);
+        mrow[ri] = st.x;
+        rD[ri] = 1.f / st.y;
+        const float g = st.z;
+        float od = 0.f, nr = 0.f, rr[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            rr[c] = 0.f;
+            if (col < V) {
+                od = fmaf(to_f<T>(o[row * V + col]), dos[r * V + col], od);
+                float a = 0.f;
+                for (int d = 0; d < K; ++d) a = fmaf(qs[r * K + d], hs[d * VP + col], a);
+                rr[c] = a;
+                nr = fmaf(dos[r * V + col], a, nr);
+            }
+        }
+        dD[ri] = -wsum(od) * rD[ri];
+        dg[ri] = dD[ri] + wsum(nr) * rD[ri] * w;
+        const float gw = g * w * rD[ri];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            if (col < V) drs[r * V + col] = dos[r * V + col] * gw;
+        }
+        __syncwarp();
+        // dq += h dr  (lanes over the key-feature columns)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            if (col < K) {
+                float a = 0.f;
+                for (int vv = 0; vv < V; ++vv) a = fmaf(hs[col * VP + vv], drs[r * V + vv], a);
+                dqa[ri][c] = a;
+            }
+        }
+        if (lane == 0) drow[row] = dD[ri];
+    }
+    __syncthreads();
+    // dh += q^T dr over the rows of this block
+    {
+        float* dhb = dh + (size_t)bh * K * V;
+        for (int i = threadIdx.x; i < K * V; i += kPisaThreads) {
+            const int d = i / V, c = i - d * V;
+            float a = 0.f;
+            for (int r = 0; r < nrows; ++r) a = fmaf(qs[r * K + d], drs[r * V + c], a);
+            atomicAdd(dhb + i, a);
+        }
+    }
+
+    // one group of up to 32 keys / blocks against one query row
+    auto group = [&](int ri, int r, int j0, int nvalid, bool approx, int c0) {
+        const int j = j0 + lane;
+        bool ok = j < nvalid;
+        if (approx && ok) ok = !sel[c0 + j];
+        float pj = 0.f, dsj = 0.f;
+        if (ok) {
+            float a = 0.f, b = 0.f;
+            const float* qrow = qs + r * K;
+            const float* krow = kb + j * KP;
+            for (int d = 0; d < K; ++d) a = fmaf(qrow[d], krow[d], a);
+            const float* dorow = dos + r * V;
+            const float* vrow = vb + j * VP;
+            for (int d = 0; d < V; ++d) b = fmaf(dorow[d], vrow[d], b);
+            pj = exp2f(a * sm - mrow[ri]);
+            float dp = b * rD[ri];
+            if (approx) {
+                const int cblk = c0 + j;
+                const float len = (cblk == p.nt - 1) ? (float)(p.T - (p.nt - 1) * p.bs) : (float)p.bs;
+                dp += dg[ri] * len;
+            } else {
+                dp += dD[ri];
+            }
+            dsj = pj * dp * p.scale;
+        }
+        if (approx) {
+            das[r * kChunkRows + j0 + lane] = dsj;
+            pis[r * kChunkRows + j0 + lane] = pj * rD[ri];
+        }
+        const int jn = min(32, nvalid - j0);
+        for (int jj = 0; jj < jn; ++jj) {
+            const float sb = __shfl_sync(0xffffffffu, dsj, jj);
+            const float* krow = kb + (j0 + jj) * KP;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int col = lane + 32 * c;
+                if (col < K) dqa[ri][c] = fmaf(sb, krow[col], dqa[ri][c]);
+            }
+        }
+    };
+
+    // ---- exact part ----
+    for (int n = 0; n < p.ns; ++n) {
+        __syncthreads();
+        const int cb = idx[n];
+        const int bos = cb * p.bs;
+        const int nvalid = max(0, min(p.bs, p.T - bos));
+        for (int i = threadIdx.x; i < p.bs * K; i += kPisaThreads) {
+            const int r = i / K, d = i - r * K;
+            kb[r * KP + d] = r < nvalid ? to_f<T>(k[(base_row + bos + r) * K + d]) : 0.f;
+        }
+        for (int i = threadIdx.x; i < p.bs * V; i += kPisaThreads) {
+            const int r = i / V, d = i - r * V;
+            vb[r * VP + d] = r < nvalid ? to_f<T>(v[(base_row + bos + r) * V + d]) : 0.f;
+        }
+        __syncthreads();
+        for (int r = warp, ri = 0; r < nrows; r += kPisaWarps, ++ri)
+            for (int j0 = 0; j0 < nvalid; j0 += 32) group(ri, r, j0, nvalid, false, 0);
+    }
+    // ---- zeroth-order part, 64 blocks at a time ----
+    for (int c0 = 0; c0 < p.nt; c0 += kChunkRows) {
+        __syncthreads();
+        const int nvalid = min(kChunkRows, p.nt - c0);
+        const float* kcb = kc + ((size_t)bh * p.nt + c0) * K;
+        const float* vcb = vc + ((size_t)bh * p.nt + c0) * V;
+        for (int i = threadIdx.x; i < nvalid * K; i += kPisaThreads) {
+            const int r = i / K, d = i - r * K;
+            kb[r * KP + d] = kcb[i];
+        }
+        for (int i = threadIdx.x; i < nvalid * V; i += kPisaThreads) {
+            const int r = i / V, d = i - r * V;
+            vb[r * VP + d] = vcb[i];
+        }
+        for (int i = threadIdx.x; i < p.bs * kChunkRows; i += kPisaThreads) {
+            das[i] = 0.f;
+            pis[i] = 0.f;
+        }
+        __syncthreads();
+        for (int r = warp, ri = 0; r < nrows; r += kPisaWarps, ++ri)
+            for (int j0 = 0; j0 < nvalid; j0 += 32) group(ri, r, j0, nvalid, true, c0);
+        __syncthreads();
+        // dkc_c += sum_rows (scale da_c) q,  dvc_c += sum_rows (pi_c / D) dO
+        float* dkcb = dkc + ((size_t)bh * p.nt + c0) * K;
+        float* dvcb = dvc + ((size_t)bh * p.nt + c0) * V;
+        for (int i = threadIdx.x; i < nvalid * K; i += kPisaThreads) {
+            const int cc = i / K, d = i - cc * K;
+            float a = 0.f;
+            for (int r = 0; r < nrows; ++r) a = fmaf(das[r * kChunkRows + cc], qs[r * K + d], a);
+            if (a != 0.f) atomicAdd(dkcb + i, a);
+        }
+        for (int i = threadIdx.x; i < nvalid * V; i += kPisaThreads) {
+            const int cc = i / V, d = i - cc * V;
+            float a = 0.f;
+            for (int r = 0; r < nrows; ++r) a = fmaf(pis[r * kChunkRows + cc], dos[r * V + d], a);
+            if (a != 0.f) atomicAdd(dvcb + i, a);
+        }
+    }
+    for (int r = warp, ri = 0; r < nrows; r += kPisaWarps, ++ri) {
+        const size_t row = base_row + t0 + r;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            if (col < K) dq[row * K + col] = from_f<T>(dqa[ri][c]);
+        }
+    }
+}
+
+// One CTA per key block c.  Warp w owns the keys w, w+8, ... of the block; the lanes split the
+// feature columns.
+template <typename T>
+__global__ void __launch_bounds__(kPisaThreads)
+pisa_bwd_kv_kernel(PisaParams p, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                   const T* __restrict__ d_o, const float* __restrict__ kc, const float* __restrict__ vc,
+                   const int32_t* __restrict__ indices, const float* __restrict__ row_stats,
+                   const float* __restrict__ drow, const float* __restrict__ dkc, const float* __restrict__ dvc,
+                   const float* __restrict__ dh, T* __restrict__ dk, T* __restrict__ dv) {
+    extern __shared__ float smem[];
+    const int K = p.dk, V = p.dv, VP = V + 1;
+    float* qs = smem;                  // [bs][K]   q rows of one query block; later the k rows of this block
+    float* dos = qs + p.bs * K;        // [bs][V]   dO rows;                   later the v rows of this block
+    float* rst = dos + p.bs * V;       // [bs][4]   m, 1/D, dD per query row
+    float* dhs = rst + p.bs * 4;       // [K][V+1]
+
+    const int c_blk = blockIdx.x, bh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bos = c_blk * p.bs;
+    const int nkeys = min(p.bs, p.T - bos);
+    const size_t base_row = (size_t)bh * p.T;
+    const float sm = p.scale * 1.44269504f;
+    constexpr int KPW = kMaxRowsPerWarp;   // keys per warp (block_size <= 128)
+
+    float kr[KPW][4], vr[KPW][4], dka[KPW][4], dva[KPW][4];
+#pragma unroll
+    for (int i = 0; i < KPW; ++i) {
+        const int key = warp + kPisaWarps * i;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            kr[i][c] = (key < nkeys && col < K) ? to_f<T>(k[(base_row + bos + key) * K + col]) : 0.f;
+            vr[i][c] = (key < nkeys && col < V) ? to_f<T>(v[(base_row + bos + key) * V + col]) : 0.f;
+            dka[i][c] = 0.f;
+            dva[i][c] = 0.f;
+        }
+    }
+    const int nkw = (nkeys - warp + kPisaWarps - 1) / kPisaWarps;   // keys this warp owns (may be <= 0)
+
+    for (int i_blk = 0; i_blk < p.nt; ++i_blk) {
+        const int32_t* idx = indices + ((size_t)bh * p.nt + i_blk) * p.ns;
+        bool hit = false;
+        for (int n = 0; n < p.ns; ++n) hit |= (idx[n] == c_blk);
+        if (!hit) continue;                                        // uniform over the CTA
+        const int t0 = i_blk * p.bs;
+        const int nrows = min(p.bs, p.T - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nrows * K; i += kPisaThreads) qs[i] = to_f<T>(q[(base_row + t0) * K + i]);
+        for (int i = threadIdx.x; i < nrows * V; i += kPisaThreads) dos[i] = to_f<T>(d_o[(base_row + t0) * V + i]);
+        for (int r = threadIdx.x; r < nrows; r += kPisaThreads) {
+            const float4 st = *reinterpret_cast<const float4*>(row_stats + (base_row + t0 + r) * 4);
+            rst[r * 4 + 0] = st.x;
+            rst[r * 4 + 1] = 1.f / st.y;
+            rst[r * 4 + 2] = drow[base_row + t0 + r];
+        }
+        __syncthreads();
+        for (int r = 0; r < nrows; ++r) {
+            float qv[4], dv_[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int col = lane + 32 * c;
+                qv[c] = col < K ? qs[r * K + col] : 0.f;
+                dv_[c] = col < V ? dos[r * V + col] : 0.f;
+            }
+            const float m = rst[r * 4], rD = rst[r * 4 + 1], dDr = rst[r * 4 + 2];
+#pragma unroll
+            for (int i = 0; i < KPW; ++i) {
+                if (i >= nkw) break;
+                float a = 0.f, b = 0.f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    a = fmaf(qv[c], kr[i][c], a);
+                    b = fmaf(dv_[c], vr[i][c], b);
+                }
+                a = wsum(a);
+                b = wsum(b);
+                const float pj = exp2f(a * sm - m);
+                const float ds = pj * (b * rD + dDr) * p.scale;
+                const float pd = pj * rD;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    dka[i][c] = fmaf(ds, qv[c], dka[i][c]);
+                    dva[i][c] = fmaf(pd, dv_[c], dva[i][c]);
+                }
+            }
+        }
+    }
+    // ---- statistics terms: dkc / len, dvc, and the first-order state ----
+    __syncthreads();
+    const float* dhb = dh + (size_t)bh * K * V;
+    for (int i = threadIdx.x; i < K * V; i += kPisaThreads) {
+        const int d = i / V, c = i - d * V;
+        dhs[d * VP + c] = dhb[i];
+    }
+    for (int i = threadIdx.x; i < nkeys * K; i += kPisaThreads) qs[i] = to_f<T>(k[(base_row + bos) * K + i]);
+    for (int i = threadIdx.x; i < nkeys * V; i += kPisaThreads) dos[i] = to_f<T>(v[(base_row + bos) * V + i]);
+    __syncthreads();
+    const float inv_len = 1.f / (float)nkeys;
+    const float* kcb = kc + ((size_t)bh * p.nt + c_blk) * K;
+    const float* vcb = vc + ((size_t)bh * p.nt + c_blk) * V;
+    const float* dkcb = dkc + ((size_t)bh * p.nt + c_blk) * K;
+    const float* dvcb = dvc + ((size_t)bh * p.nt + c_blk) * V;
+#pragma unroll
+    for (int i = 0; i < KPW; ++i) {
+        const int key = warp + kPisaWarps * i;
+        if (key >= nkeys) break;
+        const size_t row = base_row + bos + key;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            if (col < K) {
+                float a = 0.f;   // dh (v_t - mean v)
+                for (int vv = 0; vv < V; ++vv) a = fmaf(dhs[col * VP + vv], dos[key * V + vv] - vcb[vv] * inv_len, a);
+                dk[row * K + col] = from_f<T>(dka[i][c] + dkcb[col] * inv_len + a);
+            }
+            if (col < V) {
+                float a = 0.f;   // dh^T (k_t - kc)
+                for (int d = 0; d < K; ++d) a = fmaf(dhs[d * VP + col], qs[key * K + d] - kcb[d], a);
+                dv[row * V + col] = from_f<T>(dva[i][c] + dvcb[col] + a);
+            }
+        }
+    }
+}
+
+size_t bwd_q_smem_bytes(const PisaParams& p) {
+    const int rows_buf = p.bs > kChunkRows ? p.bs : kChunkRows;
+    return sizeof(float) * ((size_t)p.bs * p.dk + 2 * (size_t)p.bs * p.dv + (size_t)rows_buf * (p.dk + 1 + p.dv + 1) +
+                            2 * (size_t)p.bs * kChunkRows) + (size_t)p.nt + 16;
+}
+size_t bwd_kv_smem_bytes(const PisaParams& p) {
+    return sizeof(float) * ((size_t)p.bs * p.dk + (size_t)p.bs * p.dv + (size_t)p.bs * 4 + (size_t)p.dk * (p.dv + 1));
+}
+
+}  // namespace
+}  // namespace fbla
+
+extern "C" int fbla_pisa_bwd(const fbla_pisa_problem* p, const void* q, const void* k, const void* v, const void* o,
+                             const void* d_o, const float* kc, const float* vc, const float* h, const int32_t* indices,
+                             const float* row_stats, void* dq, void* dk, void* dv, float* scratch,
+                             size_t scratch_floats, fbla_stream_t stream) {
+    fbla::PisaArgs a;
+    if (int rc = fbla::resolve_pisa(p, &a)) return rc;
+    if (!q || !k || !v || !o || !d_o || !kc || !vc || !h || !indices || !row_stats || !dq || !dk || !dv || !scratch)
+        return fbla::api_fail(FBLA_ERR_INVALID, "a tensor pointer is NULL");
+    const fbla::PisaParams& kp = a.kp;
+    // scratch: dkc [BH,NT,K] | dvc [BH,NT,V] | dh [BH,K,V] (zeroed here, filled with atomics) | drow [BH,T]
+    const size_t n_dkc = (size_t)a.bh * kp.nt * kp.dk, n_dvc = (size_t)a.bh * kp.nt * kp.dv;
+    const size_t n_dh = (size_t)a.bh * kp.dk * kp.dv, n_row = (size_t)a.bh * kp.T;
+    if (scratch_floats < n_dkc + n_dvc + n_dh + n_row)
+        return fbla::api_fail(FBLA_ERR_WORKSPACE, "scratch of %lld floats needed, %lld given",
+                              (long long)(n_dkc + n_dvc + n_dh + n_row), (long long)scratch_floats);
+    float* dkc = scratch;
+    float* dvc = dkc + n_dkc;
+    float* dh = dvc + n_dvc;
+    float* drow = dh + n_dh;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * (n_dkc + n_dvc + n_dh), st);
+    if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "memset: %s", cudaGetErrorString(e));
+    const size_t smem1 = fbla::bwd_q_smem_bytes(kp), smem2 = fbla::bwd_kv_smem_bytes(kp);
+    if (smem1 > 227 * 1024 || smem2 > 227 * 1024)
+        return fbla::api_fail(FBLA_ERR_UNSUPPORTED, "block_size, dk, dv too large for the backward kernels");
+    dim3 grid(kp.nt, a.bh);
+    PISA_BY_DTYPE(a.dtype, {
+        auto k1 = fbla::pisa_bwd_q_kernel<T>;
+        auto k2 = fbla::pisa_bwd_kv_kernel<T>;
+        if (smem1 > 48 * 1024) e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+        if (e == cudaSuccess && smem2 > 48 * 1024)
+            e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+        if (e == cudaSuccess) {
+            k1<<<grid, fbla::kPisaThreads, smem1, st>>>(kp, (const T*)q, (const T*)k, (const T*)v, (const T*)o,
+                                                        (const T*)d_o, kc, vc, h, indices, row_stats, (T*)dq, dkc, dvc,
+                                                        dh, drow);
+            k2<<<grid, fbla::kPisaThreads, smem2, st>>>(kp, (const T*)q, (const T*)k, (const T*)v, (const T*)d_o, kc, vc,
+                                                        indices, row_stats, drow, dkc, dvc, dh, (T*)dk, (T*)dv);
+        }
+    });
+    fbla::note_launches(2);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "backward kernels: %s", cudaGetErrorString(e));
+}

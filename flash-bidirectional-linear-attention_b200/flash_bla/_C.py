@@ -84,7 +84,7 @@ def exported_symbols():
     for op in OPS:
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
     names.append("fbla_linear_attn_fwd_state_noalloc")
-    names += ["fbla_pisa_block_stats", "fbla_pisa_first_order_state", "fbla_pisa_fwd"]
+    names += ["fbla_pisa_block_stats", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd"]
     return names
 
 
@@ -121,6 +121,8 @@ def lib():
             f = getattr(L, name)
             f.restype = ctypes.c_int
             f.argtypes = [_PP] + [_vp] * n_ptr          # tensor pointers, then the stream
+        L.fbla_pisa_bwd.restype = ctypes.c_int
+        L.fbla_pisa_bwd.argtypes = [_PP] + [_vp] * 14 + [_sz, _vp]   # 14 tensors, scratch size, stream
         _lib = L
     return _lib
 

@@ -109,6 +109,48 @@ def attention_forward(q, k, v, kc, vc, h, indices, block_size, scale, want_stats
     return (o, stats) if want_stats else o
 
 
+def attention_backward(q, k, v, o, do, kc, vc, h, indices, stats, block_size, scale):
+    """Gradients (dq, dk, dv) of ``attention_forward`` composed with the block statistics, the
+    selection ``indices`` held constant."""
+    q, k, v, o, do = (x.contiguous() for x in (q, k, v, o, do))
+    B, H, T, K = q.shape
+    V = v.shape[-1]
+    idx = indices.to(torch.int32).contiguous()
+    nt = idx.shape[-2]
+    prob = _problem(q, v, block_size, idx.shape[-1], scale)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    n = B * H * (nt * K + nt * V + K * V + T)
+    scratch = torch.empty(n, dtype=torch.float32, device=q.device)
+    with torch.cuda.device_of(q):
+        _C.check(_C.lib().fbla_pisa_bwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                        do.data_ptr(), kc.contiguous().data_ptr(), vc.contiguous().data_ptr(),
+                                        h.contiguous().data_ptr(), idx.data_ptr(), stats.data_ptr(), dq.data_ptr(),
+                                        dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(), n, _C.stream_of(q)))
+    return dq, dk, dv
+
+
+class PiecewiseSparseAttnFunction(torch.autograd.Function):
+    """Forward as the reference; the backward (which the reference lacks) treats the selected
+    block indices as constants."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, density, block_size, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        qc, kc, vc = block_statistics(q, k, v, block_size)
+        h = first_order_state(k, v, kc, vc, block_size)
+        indices = select_blocks(qc, kc, scale, density, q.dtype)
+        o, stats = attention_forward(q, k, v, kc, vc, h, indices, block_size, scale, want_stats=True)
+        ctx.save_for_backward(q, k, v, o, kc, vc, h, indices, stats)
+        ctx.block_size, ctx.scale = block_size, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, kc, vc, h, indices, stats = ctx.saved_tensors
+        dq, dk, dv = attention_backward(q, k, v, o, do, kc, vc, h, indices, stats, ctx.block_size, ctx.scale)
+        return dq, dk, dv, None, None, None
+
+
 def piecewise_sparse_attention(q, k, v, density=0.1, block_size=64, scale=None, use_bias=False):
     r"""
     Args:
@@ -124,8 +166,4 @@ def piecewise_sparse_attention(q, k, v, density=0.1, block_size=64, scale=None, 
     _check(q, k, v)
     K = k.shape[-1]
     scale = K ** -0.5 if scale is None else scale
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    qc, kc, vc = block_statistics(q, k, v, block_size)
-    h = first_order_state(k, v, kc, vc, block_size)
-    indices = select_blocks(qc, kc, scale, density, q.dtype)
-    return attention_forward(q, k, v, kc, vc, h, indices, block_size, scale)
+    return PiecewiseSparseAttnFunction.apply(q, k, v, density, block_size, scale)

@@ -200,6 +200,15 @@ int fbla_pisa_fwd(const fbla_pisa_problem *p, const void *q, const void *k, cons
                   const float *kc, const float *vc, const float *h, const int32_t *indices,
                   void *o, float *row_stats, fbla_stream_t stream);
 
+/* Backward of fbla_pisa_fwd with the block selection held constant; gradients flow through the
+ * block statistics as well.  The reference has no backward for this operator (no counterpart).
+ * o, d_o: forward output and its gradient; row_stats: as written by fbla_pisa_fwd.
+ * scratch: fp32, at least batch*heads*(NT*dk + NT*dv + dk*dv + seq_len) elements.            */
+int fbla_pisa_bwd(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,
+                  const void *o, const void *d_o, const float *kc, const float *vc, const float *h,
+                  const int32_t *indices, const float *row_stats, void *dq, void *dk, void *dv,
+                  float *scratch, size_t scratch_floats, fbla_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
