@@ -33,10 +33,11 @@ __device__ __forceinline__ void stage_matrix_sw128(uint8_t* dst, const float* __
     }
 }
 
-// The 128 x 128 kernels have no shared memory left for the residual copy.
+// Every shape keeps the residual copy; the 128 x 128 kernel pays for it by writing its outputs
+// with plain 16-byte global stores instead of a staged tile.
 template <int DK, int DV>
 struct SplitState {
-    static constexpr bool value = !(DK == 128 && DV == 128);
+    static constexpr bool value = true;
 };
 
 // ------------------------------------------------------------------------------------------
@@ -48,10 +49,10 @@ struct BwdInCfg {
     static constexpr int kBopBytes = kBopOne * (kSplit ? 2 : 1);            // high part (+ residual)
     static constexpr int kVecBytes = 1024;                                  // fp32 dkm / L
     static constexpr int kStageBytes = (kKB + kVB) * kBlockBytes;           // v tile, kr tile
-    static constexpr int kOutBytes = (kKB + kVB) * kBlockBytes;             // staged dk (dkr) and dv tile
+    static constexpr bool kDirect = (DK == 128 && DV == 128);               // no room for a staged output tile
+    static constexpr int kOutBytes = kDirect ? 0 : (kKB + kVB) * kBlockBytes;   // staged dk (dkr) and dv tile
     static constexpr int kConstBytes = MODE == kDecoupled ? kKB * kBlockBytes : 0;  // dk tile of the decoupled op
-    static constexpr int kBig = (DK == 128 && DV == 128);
-    static constexpr int kOutBufs = kBig ? 1 : 2;
+    static constexpr int kOutBufs = kDirect ? 1 : 2;
     static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kOutBufs * kOutBytes + kConstBytes + 512;
     static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
@@ -241,12 +242,17 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             }
             if (!ptx::mbar_wait(&tfull[a], ph2, ab, 421)) break;
             ptx::tc_fence_after_sync();
-            if (issuer) {
-                ptx::tma_store_wait_read<NO - 1>();
-                ptx::mbar_arrive(&out_free[ob_i]);
+            if (!Cfg::kDirect) {
+                if (issuer) {
+                    ptx::tma_store_wait_read<NO - 1>();
+                    ptx::mbar_arrive(&out_free[ob_i]);
+                }
+                if (!ptx::mbar_wait(&out_free[ob_i], pho, ab, 422)) break;
             }
-            if (!ptx::mbar_wait(&out_free[ob_i], pho, ab, 422)) break;
             uint8_t* ob = outbuf + ob_i * Cfg::kOutBytes;
+            const int tok = tile * kTileTokens + row;
+            const bool tok_ok = tok < p.seq_len;
+            const size_t grow = (size_t)unit * p.seq_len + tok;       // row of this thread in the (units*T, D) view
             // dk (or dk_rope) tile
 #pragma unroll
             for (int c0 = 0; c0 < DK; c0 += 32) {
@@ -258,15 +264,26 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     for (int j = 0; j < 32; ++j) v[j] += vec[c0 + j];
                 }
                 uint8_t* blk = ob + (c0 >> 6) * kBlockBytes + row * 128;
+                uint4 w4[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    uint4 w;
-                    w.x = pack2(v[8 * j], v[8 * j + 1], BF16);
-                    w.y = pack2(v[8 * j + 2], v[8 * j + 3], BF16);
-                    w.z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
-                    w.w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
-                    const int chunk = ((c0 & 63) >> 3) + j;
-                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                    w4[j].x = pack2(v[8 * j], v[8 * j + 1], BF16);
+                    w4[j].y = pack2(v[8 * j + 2], v[8 * j + 3], BF16);
+                    w4[j].z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
+                    w4[j].w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
+                }
+                if (Cfg::kDirect) {
+                    if (tok_ok) {
+                        uint8_t* dst = static_cast<uint8_t*>(p.out_a) + (grow * DK + c0) * 2;
+                        ptx::st_global_32B(dst, w4[0], w4[1]);
+                        ptx::st_global_32B(dst + 32, w4[2], w4[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int chunk = ((c0 & 63) >> 3) + j;
+                        *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w4[j];
+                    }
                 }
             }
             // dv tile
@@ -276,22 +293,33 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                 ptx::tmem_ld32(t_lane + a * Cfg::kAccCols + DK + c0, v);
                 ptx::tmem_ld_wait();
                 uint8_t* blk = ob + (Cfg::kKB + (c0 >> 6)) * kBlockBytes + row * 128;
+                uint4 w4[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    uint4 w;
-                    w.x = pack2(v[8 * j], v[8 * j + 1], BF16);
-                    w.y = pack2(v[8 * j + 2], v[8 * j + 3], BF16);
-                    w.z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
-                    w.w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
-                    const int chunk = ((c0 & 63) >> 3) + j;
-                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                    w4[j].x = pack2(v[8 * j], v[8 * j + 1], BF16);
+                    w4[j].y = pack2(v[8 * j + 2], v[8 * j + 3], BF16);
+                    w4[j].z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
+                    w4[j].w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
+                }
+                if (Cfg::kDirect) {
+                    if (tok_ok) {
+                        uint8_t* dst = static_cast<uint8_t*>(p.out_b) + (grow * DV + c0) * 2;
+                        ptx::st_global_32B(dst, w4[0], w4[1]);
+                        ptx::st_global_32B(dst + 32, w4[2], w4[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int chunk = ((c0 & 63) >> 3) + j;
+                        *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w4[j];
+                    }
                 }
             }
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&tempty[a]);
             ptx::fence_proxy_async_smem();
             ptx::mbar_arrive(&out_written[ob_i]);
-            if (issuer) {
+            if (!Cfg::kDirect && issuer) {
                 if (!ptx::mbar_wait(&out_written[ob_i], pho, ab, 423)) break;
                 const int t0 = tile * kTileTokens;
 #pragma unroll
@@ -306,7 +334,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                 ptx::tma_store_commit();
             }
         }
-        if (issuer) ptx::tma_store_wait_all<0>();
+        if (!Cfg::kDirect && issuer) ptx::tma_store_wait_all<0>();
     }
     ptx::tc_fence_before_sync();
     __syncthreads();

@@ -50,12 +50,14 @@ struct BwdStateCfg {
     static constexpr int kQBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
     static constexpr int kTmaBytes = (kQBlocks + kVB) * kBlockBytes;        // qr (, q), dO tiles
     static constexpr int kStageBytes = kTmaBytes + kDzBytes;
-    // dq leaves through a staged tile + TMA store, except where that tile does not fit
-    static constexpr bool kDirect = (DK == 128) || MODE == kDecoupled;
+    // dq leaves in 32-byte global stores straight from registers (one full sector per thread and
+    // store): measured as fast as a staged tile + TMA store, and the 16-32 KB per warpgroup it saves
+    // buy a deeper load pipeline.  (The staged path is kept behind kDirect = false.)
+    static constexpr bool kDirect = true;
     static constexpr int kOutBytes = kDirect ? 0 : kQBlocks * kBlockBytes;  // per warpgroup
     static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kKmOpBytes + 2 * kOutBytes + 512;
     static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
-    static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
+    static constexpr int kStages = kStagesRaw > 5 ? 5 : kStagesRaw;
     static constexpr int kTCols = DK + (MODE != kSimple ? 16 : 0);          // t (+ z) accumulator
     // t accumulators: with three, MMA 1 runs ahead of the epilogue, so a warpgroup finds its next
     // accumulator complete when it finishes a tile
@@ -322,6 +324,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
 
             // emits columns [c0, c0+32): dq to the staged tile (or global memory), qr/z over the qr tile
             auto emit32 = [&](int c0, const float (&t)[32], const uint4 (&qv)[4]) {
+                uint4 keep1[4], keep2[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int c = c0 + 8 * j;
@@ -353,12 +356,13 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                         }
                     }
                     if (Cfg::kDirect) {
-                        if (tok_ok) {
-                            const size_t at = (((size_t)unit * p.seq_len + tok) * DK + c) * 2;
-                            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_a) + at) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                        keep1[j] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                        if (MODE == kDecoupled) keep2[j] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+                        if ((j & 1) && tok_ok) {       // two 16-byte chunks = one 32-byte sector per store
+                            const size_t at = (((size_t)unit * p.seq_len + tok) * DK + c - 8) * 2;
+                            ptx::st_global_32B(static_cast<uint8_t*>(p.out_a) + at, keep1[j - 1], keep1[j]);
                             if (MODE == kDecoupled)
-                                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_b) + at) =
-                                    make_uint4(o2[0], o2[1], o2[2], o2[3]);
+                                ptx::st_global_32B(static_cast<uint8_t*>(p.out_b) + at, keep2[j - 1], keep2[j]);
                         }
                     } else {
                         *reinterpret_cast<uint4*>(ob + row * 128 + off) = make_uint4(o1[0], o1[1], o1[2], o1[3]);

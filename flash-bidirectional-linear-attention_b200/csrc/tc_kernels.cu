@@ -366,6 +366,8 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
     Params q = make_params(p, dtype, s);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = dstate;
+    q.out_a = dec ? dk_rope : dk;      // kernels without a staged output tile store through these
+    q.out_b = dv;
     CUtensorMap tkr, tv, tdk, tdkr, tdv;
     cudaError_t e;
     if ((e = make_map(&tkr, k_rope, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;

@@ -216,6 +216,13 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                  : "memory");
 }
 
+// 32-byte global store (one full sector per thread).
+__device__ __forceinline__ void st_global_32B(void* ptr, const uint4& a, const uint4& b) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a.x), "r"(a.y), "r"(a.z),
+                 "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 // Byte offset of element (row, col) of a [rows][64] 16-bit tile in the 128-byte-swizzled
 // layout (tile base 1024-byte aligned): what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B and
 // what the descriptors above read.
