@@ -52,8 +52,8 @@ struct BwdInCfg {
     static constexpr bool kDirect = (DK == 128 && DV == 128);               // no room for a staged output tile
     static constexpr int kOutBytes = kDirect ? 0 : (kKB + kVB) * kBlockBytes;   // staged dk (dkr) and dv tile
     static constexpr int kConstBytes = MODE == kDecoupled ? kKB * kBlockBytes : 0;  // dk tile of the decoupled op
-    static constexpr int kOutBufs = kDirect ? 1 : 2;
-    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kOutBufs * kOutBytes + kConstBytes + 512;
+    static constexpr int kOutBufs = (DK == 64 && DV == 64) ? 2 : 1;         // staged output tiles
+    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kOutBufs * kOutBytes + kConstBytes + 512 + kPlanBytes;
     static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
     static constexpr int kAccCols = DK + DV;
@@ -61,12 +61,15 @@ struct BwdInCfg {
     static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
 };
 
-template <int DK, int DV, int MODE, bool BF16>
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_v,
                  const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dkr,
-                 const __grid_constant__ CUtensorMap tm_dv, const Params p) {
+                 const __grid_constant__ CUtensorMap tm_dv, const Params p_in) {
     using Cfg = BwdInCfg<DK, DV, MODE>;
+    using Map = TileMap<VARLEN>;
+    // packed layout: rows are strided and tiles may end inside the next sequence -> guarded stores
+    constexpr bool kDirectOut = Cfg::kDirect || VARLEN;
     constexpr int NS = Cfg::kStages;
     constexpr int NO = Cfg::kOutBufs;
     extern __shared__ uint8_t smem_raw[];
@@ -89,9 +92,15 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const Schedule& sch = p.sch;
-    const int g0 = blockIdx.x * sch.tiles_per_cta;
-    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    Params pv = p_in;
+    if (VARLEN) {
+        int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
+        build_plan(plan, p_in.cu, p_in.num_seqs, p_in.heads);
+        pv.plan = plan;
+    }
+    const Params& p = pv;
+    int g0, g1;
+    Map::range(p, g0, g1);
     const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
@@ -132,14 +141,13 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 401)) break;
             ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
-            const int unit = g / sch.tiles_per_unit;
-            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            const Tile t = Map::get(p, g, g0, g1);
             uint8_t* st = stages + s * Cfg::kStageBytes;
 #pragma unroll
-            for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_v, &full[s], b * 64, t0, unit);
+            for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_v, &full[s], b * 64, t.c1, t.c2);
 #pragma unroll
             for (int b = 0; b < Cfg::kKB; ++b)
-                ptx::tma_load_3d(st + (Cfg::kVB + b) * kBlockBytes, &tm_kr, &full[s], b * 64, t0, unit);
+                ptx::tma_load_3d(st + (Cfg::kVB + b) * kBlockBytes, &tm_kr, &full[s], b * 64, t.c1, t.c2);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
@@ -151,8 +159,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             const int a = it & 1;
-            const int tile = g % sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
+            const bool first = Map::get(p, g, g0, g1).first;
             if (first) {
                 if (!ptx::mbar_wait(bop_ready, (uint32_t)seg & 1u, ab, 411)) break;
                 ++seg;
@@ -205,9 +212,9 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
         const bool issuer = (et == 0);
         int seg = 0;
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
-            const int unit = g / sch.tiles_per_unit;
-            const int tile = g - unit * sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
+            const Tile t = Map::get(p, g, g0, g1);
+            const int unit = t.unit, tile = t.tile;
+            const bool first = t.first;
             const int a = it & 1;
             const int ob_i = it % NO;
             const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
@@ -225,14 +232,14 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     if (!ptx::mbar_wait(const_free, (uint32_t)seg & 1u, ab, 425)) break;
                 }
                 ++seg;
-                stage_matrix_sw128<DK, DV, Cfg::kSplit>(bop, st, p.scale, BF16, et);
+                stage_matrix_sw128<DK, DV, Cfg::kSplit>(bop, st, t.scale, BF16, et);
                 if (MODE != kSimple)
-                    for (int i = et; i < DK; i += kEpiThreads) vec[i] = st[DK * DV + i] * p.inv_norm;
+                    for (int i = et; i < DK; i += kEpiThreads) vec[i] = st[DK * DV + i] * t.inv_norm;
                 if (MODE == kDecoupled) {
                     // every token's dk is dkm / L: one constant tile, stored once per tile
                     for (int i = et; i < kTileTokens * DK / 2; i += kEpiThreads) {
                         const int r = (2 * i) / DK, k = (2 * i) - r * DK;
-                        const float x0 = st[DK * DV + k] * p.inv_norm, x1 = st[DK * DV + k + 1] * p.inv_norm;
+                        const float x0 = st[DK * DV + k] * t.inv_norm, x1 = st[DK * DV + k + 1] * t.inv_norm;
                         *reinterpret_cast<uint32_t*>(constbuf + (k >> 6) * kBlockBytes + ptx::sw128_offset(r, k & 63)) =
                             pack2(x0, x1, BF16);
                     }
@@ -242,7 +249,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             }
             if (!ptx::mbar_wait(&tfull[a], ph2, ab, 421)) break;
             ptx::tc_fence_after_sync();
-            if (!Cfg::kDirect) {
+            if (!kDirectOut) {
                 if (issuer) {
                     ptx::tma_store_wait_read<NO - 1>();
                     ptx::mbar_arrive(&out_free[ob_i]);
@@ -250,9 +257,8 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                 if (!ptx::mbar_wait(&out_free[ob_i], pho, ab, 422)) break;
             }
             uint8_t* ob = outbuf + ob_i * Cfg::kOutBytes;
-            const int tok = tile * kTileTokens + row;
-            const bool tok_ok = tok < p.seq_len;
-            const size_t grow = (size_t)unit * p.seq_len + tok;       // row of this thread in the (units*T, D) view
+            const bool tok_ok = row < t.valid;
+            const size_t grow = (size_t)(t.row0 + (long long)row * t.row_stride);   // this thread's row in the (rows, D) view
             // dk (or dk_rope) tile
 #pragma unroll
             for (int c0 = 0; c0 < DK; c0 += 32) {
@@ -272,7 +278,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     w4[j].z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
                     w4[j].w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
                 }
-                if (Cfg::kDirect) {
+                if (kDirectOut) {
                     if (tok_ok) {
                         uint8_t* dst = static_cast<uint8_t*>(p.out_a) + (grow * DK + c0) * 2;
                         ptx::st_global_32B(dst, w4[0], w4[1]);
@@ -301,7 +307,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     w4[j].z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
                     w4[j].w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
                 }
-                if (Cfg::kDirect) {
+                if (kDirectOut) {
                     if (tok_ok) {
                         uint8_t* dst = static_cast<uint8_t*>(p.out_b) + (grow * DV + c0) * 2;
                         ptx::st_global_32B(dst, w4[0], w4[1]);
@@ -319,7 +325,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             ptx::mbar_arrive(&tempty[a]);
             ptx::fence_proxy_async_smem();
             ptx::mbar_arrive(&out_written[ob_i]);
-            if (!Cfg::kDirect && issuer) {
+            if (!kDirectOut && issuer) {
                 if (!ptx::mbar_wait(&out_written[ob_i], pho, ab, 423)) break;
                 const int t0 = tile * kTileTokens;
 #pragma unroll
@@ -334,7 +340,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                 ptx::tma_store_commit();
             }
         }
-        if (!Cfg::kDirect && issuer) ptx::tma_store_wait_all<0>();
+        if (!kDirectOut && issuer) ptx::tma_store_wait_all<0>();
     }
     ptx::tc_fence_before_sync();
     __syncthreads();

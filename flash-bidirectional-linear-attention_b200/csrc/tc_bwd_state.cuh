@@ -55,7 +55,7 @@ struct BwdStateCfg {
     // buy a deeper load pipeline.  (The staged path is kept behind kDirect = false.)
     static constexpr bool kDirect = true;
     static constexpr int kOutBytes = kDirect ? 0 : kQBlocks * kBlockBytes;  // per warpgroup
-    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kKmOpBytes + 2 * kOutBytes + 512;
+    static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kKmOpBytes + 2 * kOutBytes + 512 + kPlanBytes;
     static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 5 ? 5 : kStagesRaw;
     static constexpr int kTCols = DK + (MODE != kSimple ? 16 : 0);          // t (+ z) accumulator
@@ -68,12 +68,13 @@ struct BwdStateCfg {
     static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
 };
 
-template <int DK, int DV, int MODE, bool BF16>
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kBwdStateThreads, 1)
 tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
                     const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
-                    const __grid_constant__ CUtensorMap tm_dqr, const Params p) {
+                    const __grid_constant__ CUtensorMap tm_dqr, const Params p_in) {
     using Cfg = BwdStateCfg<DK, DV, MODE>;
+    using Map = TileMap<VARLEN>;
     constexpr int NS = Cfg::kStages;
     constexpr int NB = Cfg::kTBufs;
     constexpr int KB = Cfg::kKB, VB = Cfg::kVB;
@@ -99,9 +100,15 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const Schedule& sch = p.sch;
-    const int g0 = blockIdx.x * sch.tiles_per_cta;
-    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    Params pv = p_in;
+    if (VARLEN) {
+        int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
+        build_plan(plan, p_in.cu, p_in.num_seqs, p_in.heads);
+        pv.plan = plan;
+    }
+    const Params& p = pv;
+    int g0, g1;
+    Map::range(p, g0, g1);
     const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
@@ -151,18 +158,17 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 301)) break;
             ptx::mbar_arrive_expect_tx(&full[s], Cfg::kTmaBytes);
-            const int unit = g / sch.tiles_per_unit;
-            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            const Tile t = Map::get(p, g, g0, g1);
             uint8_t* st = stages + s * Cfg::kStageBytes;
 #pragma unroll
-            for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_qr, &full[s], b * 64, t0, unit);
+            for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_qr, &full[s], b * 64, t.c1, t.c2);
             if (MODE == kDecoupled) {
 #pragma unroll
-                for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + (KB + b) * kBlockBytes, &tm_q, &full[s], b * 64, t0, unit);
+                for (int b = 0; b < KB; ++b) ptx::tma_load_3d(st + (KB + b) * kBlockBytes, &tm_q, &full[s], b * 64, t.c1, t.c2);
             }
 #pragma unroll
             for (int b = 0; b < VB; ++b)
-                ptx::tma_load_3d(st + (Cfg::kQBlocks + b) * kBlockBytes, &tm_do, &full[s], b * 64, t0, unit);
+                ptx::tma_load_3d(st + (Cfg::kQBlocks + b) * kBlockBytes, &tm_do, &full[s], b * 64, t.c1, t.c2);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- issuer of MMA 1: [t | z] = [dO . S^T | q . kmean] ----------------
@@ -175,8 +181,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             const int tb = it % NB;
-            const int tile = g % sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
+            const bool first = Map::get(p, g, g0, g1).first;
             if (first) {
                 // the epilogue rewrites the state operand only after the first MMA of the previous
                 // unit's last tile has completed, then arrives here
@@ -227,9 +232,8 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
-            const int tile = g % sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
-            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            const Tile t = Map::get(p, g, g0, g1);
+            const bool first = t.first, last = t.last;
             if (!ptx::mbar_wait(&qs_ready[s], ph, ab, 314)) break;
             if (first && !ptx::mbar_wait(acc_empty, ((uint32_t)seg_acc & 1u) ^ 1u, ab, 315)) break;
             ptx::tc_fence_after_sync();
@@ -263,25 +267,26 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
         const int row = quarter * 32 + lane;
         const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool issuer = (et == 0);
-        const int unit0 = g0 / sch.tiles_per_unit;
         uint8_t* ob = outbuf + wg * Cfg::kOutBytes;
         const int a = wg;                                   // staged tile / out_* barriers of this warpgroup
 #ifdef FBLA_PROFILE
         const bool prof_on = (blockIdx.x == 1 && wg == 0 && et == 0);
         long long prof_t = clock64();
 #endif
-        for (int g = g0 + wg, it = wg; g < g1; g += 2, it += 2) {
+        int nseg = 0;                                       // segments opened so far in this CTA's range
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const Tile t = Map::get(p, g, g0, g1);
+            if (t.first) ++nseg;
+            if ((it & 1) != wg) continue;
             FBLA_PROF_MARK(7);
-            const int unit = g / sch.tiles_per_unit;
-            const int tile = g - unit * sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
-            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            const int unit = t.unit;
+            const bool first = t.first, last = t.last;
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;   // phase of this warpgroup's out_* barriers
             const int tb = it % NB;                          // t accumulator of this tile
             const uint32_t pht = (uint32_t)(it / NB) & 1u;
-            const uint32_t seg = (uint32_t)(unit - unit0);
+            const uint32_t seg = (uint32_t)(nseg - 1);
             if (first) {
                 if (it > 0) {
                     // tile it-1 (the other warpgroup's, last of the previous unit) must be past its
@@ -290,14 +295,14 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     if (!ptx::mbar_wait(&out_written[a ^ 1], (uint32_t)((it - 1) >> 1) & 1u, ab, 327)) break;
                 }
                 const float* st = p.state + (size_t)unit * p.state_stride;
-                stage_matrix_sw128<DK, DV, true>(bop, st, p.scale, BF16, et);
+                stage_matrix_sw128<DK, DV, true>(bop, st, t.scale, BF16, et);
                 if (MODE != kSimple) {
-                    for (int i = et; i < DK; i += kEpiThreads) km[i] = st[DK * DV + i] * p.inv_norm;
+                    for (int i = et; i < DK; i += kEpiThreads) km[i] = st[DK * DV + i] * t.inv_norm;
                     for (int i = et; i < 16 * DK; i += kEpiThreads) {
                         const int r = i / DK, k = i - r * DK;
                         uint16_t h = 0;
                         if (r < 2) {
-                            const float x = st[DK * DV + k] * p.inv_norm;
+                            const float x = st[DK * DV + k] * t.inv_norm;
                             const uint16_t hi = pack1(x, BF16);
                             h = r == 0 ? hi : pack1(x - unpack1(hi, BF16), BF16);
                         }
@@ -318,8 +323,8 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             uint8_t* stg = stages + s * Cfg::kStageBytes;
             uint8_t* qr_row = stg + row * 128;                        // + block * kBlockBytes + swizzled chunk
             const uint32_t t_acc = t_lane + tb * Cfg::kTCols;
-            const int tok = tile * kTileTokens + row;
-            const bool tok_ok = tok < p.seq_len;
+            const bool tok_ok = row < t.valid;
+            const size_t grow = (size_t)(t.row0 + (long long)row * t.row_stride);   // this thread's row in the (rows, D) view
             float rz = 1.f, dz = 0.f, z = 1.f;
 
             // emits columns [c0, c0+32): dq to the staged tile (or global memory), qr/z over the qr tile
@@ -352,14 +357,14 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                                 o2[e] = pack2(ga, gb, BF16);             // dq
                             }
                             const float2 rf = unpack2(rw[e], BF16);
-                            qs[e] = pack2(rf.x * rz, rf.y * rz, BF16);
+                            qs[e] = (VARLEN && !tok_ok) ? 0u : pack2(rf.x * rz, rf.y * rz, BF16);
                         }
                     }
                     if (Cfg::kDirect) {
                         keep1[j] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
                         if (MODE == kDecoupled) keep2[j] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
                         if ((j & 1) && tok_ok) {       // two 16-byte chunks = one 32-byte sector per store
-                            const size_t at = (((size_t)unit * p.seq_len + tok) * DK + c - 8) * 2;
+                            const size_t at = (grow * DK + c - 8) * 2;
                             ptx::st_global_32B(static_cast<uint8_t*>(p.out_a) + at, keep1[j - 1], keep1[j]);
                             if (MODE == kDecoupled)
                                 ptx::st_global_32B(static_cast<uint8_t*>(p.out_b) + at, keep2[j - 1], keep2[j]);
@@ -460,7 +465,18 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             }
             if (MODE != kSimple) {
                 // two 16-bit columns whose sum is dz*z (paired with qr/z) or dz (decoupled: paired with q)
-                const float x = MODE == kLinear ? dz * z : dz;
+                float x = MODE == kLinear ? dz * z : dz;
+                if (VARLEN && !tok_ok) {
+                    // rows past the end of a packed sequence belong to the next one: they must not
+                    // reach the token contraction (qs is zero already; clear dO and dz as well)
+                    x = 0.f;
+                    uint8_t* do_row = stg + Cfg::kQBlocks * kBlockBytes + row * 128;
+#pragma unroll
+                    for (int b = 0; b < VB; ++b)
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4*>(do_row + b * kBlockBytes + c * 16) = make_uint4(0, 0, 0, 0);
+                }
                 const uint16_t hi = pack1(x, BF16);
                 const uint16_t lo = pack1(x - unpack1(hi, BF16), BF16);
                 uint8_t* dzt = stg + Cfg::kTmaBytes + (row >> 6) * 2048;
@@ -474,9 +490,8 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             FBLA_PROF_MARK(4);
             if (!Cfg::kDirect && issuer) {
                 if (!ptx::mbar_wait(&out_written[a], ph2, ab, 324)) break;
-                const int t0 = tile * kTileTokens;
 #pragma unroll
-                for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t0, unit);
+                for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t.c1, t.c2);
                 ptx::tma_store_commit();
             }
             FBLA_PROF_MARK(5);
@@ -486,8 +501,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             if (last) {
                 if (!ptx::mbar_wait(acc_full, seg & 1u, ab, 325)) break;
                 ptx::tc_fence_after_sync();
-                const int slot = unit * sch.slots_per_unit + ((int)blockIdx.x - first_cta_of_unit(sch, unit));
-                float* out = p.part + (size_t)slot * p.state_stride;
+                float* out = segment_destination<VARLEN>(p, t, p.state_out);
                 drain_state_acc<DK, DV, (MODE != kSimple ? 2 : 0)>(tmem + Cfg::kColS, DV, out, warp, lane);
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(acc_empty);

@@ -19,6 +19,10 @@ constexpr int kBlockBytes = 16384;    // one [128 tokens][64 features] 16-bit bl
 constexpr int kThreads = 192;         // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
 constexpr int kEpiThreads = 128;
 constexpr int kSmemLimit = 227 * 1024;
+// Packed layout: every kernel keeps the tile plan (one int per sequence + 1) at the end of its
+// dynamic shared memory, so at most kMaxPackedSeqs sequences per call take the tensor-core path.
+constexpr int kPlanBytes = 8192;
+constexpr int kMaxPackedSeqs = kPlanBytes / 4 - 1;
 
 // Operator variant a kernel is instantiated for.
 constexpr int kSimple = 0;      // no normaliser
@@ -38,6 +42,13 @@ struct Schedule {
     int ctas;
 };
 
+__host__ __device__ inline int first_cta_of_unit(const Schedule& s, int unit) {
+    return (int)(((long long)unit * s.tiles_per_unit) / s.tiles_per_cta);
+}
+__host__ __device__ inline int last_cta_of_unit(const Schedule& s, int unit) {
+    return (int)((((long long)unit + 1) * s.tiles_per_unit - 1) / s.tiles_per_cta);
+}
+
 struct Params {
     Schedule sch;
     int seq_len;          // tokens per unit
@@ -48,19 +59,139 @@ struct Params {
     int* status;          // host-visible status word (0 = ok)
     // forward state / backward state: per-segment partials; others: the reduced state
     float* part;
+    float* state_out;     // packed layout: reducing kernels write whole-unit states here directly
     const float* state;
     int state_stride;     // floats per unit in state / partial slots
     // kernels that write an output with plain global stores (no staged tile): its base address
     void* out_a;
     void* out_b;
+    // packed variable-length layout (total_tokens, heads, D); all null / zero for fixed length
+    const int32_t* cu;    // cu_seqlens, device
+    const int32_t* plan;  // plan[s] = heads * (tiles of sequences before s), plan[num_seqs] = all tiles
+    int num_seqs;
+    int heads;
+    int scale_per_seq;    // scale = 1 / length of the sequence
+    float inv_norm_fixed; // > 0: divide the key sum by this length for every sequence; 0: by its own
 };
 
-__host__ __device__ inline int first_cta_of_unit(const Schedule& s, int unit) {
-    return (int)(((long long)unit * s.tiles_per_unit) / s.tiles_per_cta);
+// One 128-token tile of the work list, as every role of a kernel sees it.
+struct Tile {
+    int unit;          // state index
+    int tile;          // index of the tile inside its unit
+    int c1, c2;        // TMA coordinates after the feature coordinate
+    int valid;         // tokens of the tile that belong to the unit (1..128)
+    long long row0;    // row of the tile's first token in the (rows, D) view of the tensor
+    int row_stride;    // rows between consecutive tokens (1, or heads when packed)
+    bool first, last;  // first / last tile of a segment (run of one unit inside this CTA's range)
+    bool starts_here, ends_here;   // the unit's first / last tile lies inside this CTA's range
+    float scale, inv_norm;
+};
+
+// plan[s] = heads * (128-token tiles of the sequences before s), plan[num_seqs] = all tiles; built by
+// every CTA for itself from cu_seqlens (all threads of the block must call this).
+__device__ __forceinline__ void build_plan(int32_t* plan, const int32_t* __restrict__ cu, int num_seqs, int heads) {
+    for (int i = threadIdx.x; i <= num_seqs; i += blockDim.x) plan[i] = cu[i];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0, prev = plan[0];
+        for (int s = 0; s < num_seqs; ++s) {
+            const int next = plan[s + 1];
+            plan[s] = acc;
+            acc += heads * ((next - prev + kTileTokens - 1) / kTileTokens);
+            prev = next;
+        }
+        plan[num_seqs] = acc;
+    }
+    __syncthreads();
 }
-__host__ __device__ inline int last_cta_of_unit(const Schedule& s, int unit) {
-    return (int)((((long long)unit + 1) * s.tiles_per_unit - 1) / s.tiles_per_cta);
+
+template <bool VARLEN>
+struct TileMap;
+
+template <>
+struct TileMap<false> {
+    __device__ static __forceinline__ void range(const Params& p, int& g0, int& g1) {
+        g0 = blockIdx.x * p.sch.tiles_per_cta;
+        g1 = min(p.sch.total_tiles, g0 + p.sch.tiles_per_cta);
+    }
+    __device__ static __forceinline__ Tile get(const Params& p, int g, int g0, int g1) {
+        Tile t;
+        const int tpu = p.sch.tiles_per_unit;
+        t.unit = g / tpu;
+        t.tile = g - t.unit * tpu;
+        t.c1 = t.tile * kTileTokens;
+        t.c2 = t.unit;
+        t.valid = min(kTileTokens, p.seq_len - t.c1);
+        t.row0 = (long long)t.unit * p.seq_len + t.c1;
+        t.row_stride = 1;
+        t.first = (g == g0) || t.tile == 0;
+        t.last = (g == g1 - 1) || t.tile == tpu - 1;
+        t.starts_here = (g - t.tile) >= g0;
+        t.ends_here = (g - t.tile + tpu) <= g1;
+        t.scale = p.scale;
+        t.inv_norm = p.inv_norm;
+        return t;
+    }
+};
+
+template <>
+struct TileMap<true> {
+    __device__ static __forceinline__ void range(const Params& p, int& g0, int& g1) {
+        const int total = p.plan[p.num_seqs];
+        const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+        g0 = min(total, (int)blockIdx.x * per);
+        g1 = min(total, g0 + per);
+    }
+    __device__ static __forceinline__ Tile get(const Params& p, int g, int g0, int g1) {
+        // sequence s with plan[s] <= g < plan[s+1]
+        int lo = 0, hi = p.num_seqs;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (p.plan[mid] <= g) lo = mid; else hi = mid;
+        }
+        const int s = lo;
+        const int a0 = p.plan[s];
+        const int nt = (p.plan[s + 1] - a0) / p.heads;
+        const int r = g - a0;
+        const int h = r / nt;
+        Tile t;
+        t.tile = r - h * nt;
+        t.unit = s * p.heads + h;
+        const int bos = p.cu[s];
+        const int len = p.cu[s + 1] - bos;
+        t.c1 = h;
+        t.c2 = bos + t.tile * kTileTokens;
+        t.valid = min(kTileTokens, len - t.tile * kTileTokens);
+        t.row0 = (long long)t.c2 * p.heads + h;
+        t.row_stride = p.heads;
+        t.first = (g == g0) || t.tile == 0;
+        t.last = (g == g1 - 1) || t.tile == nt - 1;
+        t.starts_here = (g - t.tile) >= g0;
+        t.ends_here = (g - t.tile + nt) <= g1;
+        const float inv_len = 1.f / (float)len;
+        t.scale = p.scale_per_seq ? inv_len : p.scale;
+        t.inv_norm = p.inv_norm_fixed > 0.f ? p.inv_norm_fixed : inv_len;
+        return t;
+    }
+};
+
+// Where a reducing kernel puts the state of a finished segment.
+//   fixed length : slot (unit, cta - first_cta(unit)) of the partial buffer, added by
+//                  tc_reduce_partials_kernel.
+//   packed       : a unit that lies wholly inside this CTA's range goes straight to the state; a
+//                  piece of a unit that started in an earlier CTA goes to partial slot (cta, 0), a
+//                  unit that starts here but continues in the next CTA to slot (cta, 1);
+//                  tc_reduce_varlen_kernel adds the pieces in CTA order.
+template <bool VARLEN>
+__device__ __forceinline__ float* segment_destination(const Params& p, const Tile& t, float* state_out) {
+    if (!VARLEN) {
+        const int slot = t.unit * p.sch.slots_per_unit + ((int)blockIdx.x - first_cta_of_unit(p.sch, t.unit));
+        return p.part + (size_t)slot * p.state_stride;
+    }
+    if (t.starts_here && t.ends_here) return state_out + (size_t)t.unit * p.state_stride;
+    return p.part + ((size_t)blockIdx.x * 2 + (t.starts_here ? 1 : 0)) * p.state_stride;
 }
+
 
 __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16) {
     if (is_bf16) {

@@ -34,14 +34,25 @@ struct FwdStateCfg {
     static constexpr bool kMergedSum = (MODE == kLinear && DV == 64);
     static constexpr int kOnesBytes = kMergedSum ? kBlockBytes : 1024;
     static constexpr int kTmemCols = (DV + 16) <= 128 ? 128 : 256;
-    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kOnesBytes + 256;
+    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kOnesBytes + 256 + kPlanBytes;
 };
 
-template <int DK, int DV, int MODE, bool BF16>
+// Zeroes the rows [valid, 128) of `nblocks` swizzled [128][64] blocks (a tile whose tail belongs to
+// the next packed sequence); executed by the 128 epilogue threads.
+__device__ __forceinline__ void zero_tail_rows(uint8_t* blocks, int nblocks, int valid, int et) {
+    const int rows = kTileTokens - valid;
+    for (int i = et; i < nblocks * rows * 8; i += kEpiThreads) {
+        const int b = i / (rows * 8), r = (i / 8) % rows, c = i & 7;
+        *reinterpret_cast<uint4*>(blocks + b * kBlockBytes + (valid + r) * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+}
+
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const Params p) {
+                    const __grid_constant__ CUtensorMap tm_v, const Params p_in) {
     using Cfg = FwdStateCfg<DK, DV, MODE>;
+    using Map = TileMap<VARLEN>;
     constexpr int NS = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_1024(smem_raw);
@@ -50,21 +61,29 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
     uint64_t* bars = reinterpret_cast<uint64_t*>(ones + Cfg::kOnesBytes);
     uint64_t* full = bars;              // [NS] TMA -> MMA
     uint64_t* empty = bars + NS;        // [NS] MMA -> TMA
-    uint64_t* acc_full = bars + 2 * NS; // MMA -> epilogue (segment finished)
+    uint64_t* fixed = bars + 2 * NS;    // [NS] packed layout: tail rows of the stage zeroed
+    uint64_t* acc_full = bars + 3 * NS; // MMA -> epilogue (segment finished)
     uint64_t* acc_empty = acc_full + 1; // epilogue -> MMA (accumulator drained)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const Schedule& sch = p.sch;
-    const int g0 = blockIdx.x * sch.tiles_per_cta;
-    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    Params pv = p_in;
+    if (VARLEN) {
+        int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
+        build_plan(plan, p_in.cu, p_in.num_seqs, p_in.heads);
+        pv.plan = plan;
+    }
+    const Params& p = pv;
+    int g0, g1;
+    Map::range(p, g0, g1);
     const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
             ptx::mbar_init(&full[i], 1);
             ptx::mbar_init(&empty[i], 1);
+            ptx::mbar_init(&fixed[i], kEpiThreads);
         }
         ptx::mbar_init(acc_full, 1);
         ptx::mbar_init(acc_empty, kEpiThreads);
@@ -88,41 +107,22 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
-        constexpr int kAhead = FBLA_PREFETCH_TILES;   // L2 prefetch distance, in tiles
-        for (int g = g0; g < min(g1, g0 + kAhead); ++g) {
-            const int unit = g / sch.tiles_per_unit;
-            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
-#pragma unroll
-            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_prefetch_3d(&tm_kr, b * 64, t0, unit);
-#pragma unroll
-            for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_prefetch_3d(&tm_v, b * 64, t0, unit);
-        }
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
-            if (kAhead > 0 && g + kAhead < g1) {
-                const int gp = g + kAhead;
-                const int unit = gp / sch.tiles_per_unit;
-                const int t0 = (gp - unit * sch.tiles_per_unit) * kTileTokens;
-#pragma unroll
-                for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_prefetch_3d(&tm_kr, b * 64, t0, unit);
-#pragma unroll
-                for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_prefetch_3d(&tm_v, b * 64, t0, unit);
-            }
             if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 101)) break;
             ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
-            const int unit = g / sch.tiles_per_unit;
-            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            const Tile t = Map::get(p, g, g0, g1);
             uint8_t* st = stages + s * Cfg::kStageBytes;
 #pragma unroll
-            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_kr, &full[s], b * 64, t0, unit);
+            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_kr, &full[s], b * 64, t.c1, t.c2);
 #pragma unroll
             for (int b = 0; b < Cfg::kVB; ++b)
-                ptx::tma_load_3d(st + (Cfg::kKB + b) * kBlockBytes, &tm_v, &full[s], b * 64, t0, unit);
+                ptx::tma_load_3d(st + (Cfg::kKB + b) * kBlockBytes, &tm_v, &full[s], b * 64, t.c1, t.c2);
             if (MODE == kDecoupled) {
 #pragma unroll
                 for (int b = 0; b < Cfg::kKB; ++b)
-                    ptx::tma_load_3d(st + (Cfg::kKB + Cfg::kVB + b) * kBlockBytes, &tm_k, &full[s], b * 64, t0, unit);
+                    ptx::tma_load_3d(st + (Cfg::kKB + Cfg::kVB + b) * kBlockBytes, &tm_k, &full[s], b * 64, t.c1, t.c2);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -135,11 +135,11 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
-            const int tile = g % sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
-            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
+            const Tile t = Map::get(p, g, g0, g1);
+            const bool first = t.first, last = t.last;
             if (first && !ptx::mbar_wait(acc_empty, ((uint32_t)seg & 1u) ^ 1u, ab, 111)) break;
-            if (!ptx::mbar_wait(&full[s], ph, ab, 112)) break;
+            // packed layout: the epilogue warps hand the stage over once its tail rows are zero
+            if (!ptx::mbar_wait(VARLEN ? &fixed[s] : &full[s], ph, ab, 112)) break;
             ptx::tc_fence_after_sync();
             const uint32_t a_base = ptx::smem_u32(stages + s * Cfg::kStageBytes);
             const uint32_t b_base = a_base + Cfg::kKB * kBlockBytes;
@@ -165,16 +165,23 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
         }
     } else if (warp >= 2) {
         // ---------------- epilogue: drain the accumulator of each finished segment ----------------
+        const int et = threadIdx.x - 64;
         int seg = 0;
-        for (int g = g0; g < g1; ++g) {
-            const int unit = g / sch.tiles_per_unit;
-            const int tile = g - unit * sch.tiles_per_unit;
-            const bool last = (g == g1 - 1) || tile == sch.tiles_per_unit - 1;
-            if (!last) continue;
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+            const Tile t = Map::get(p, g, g0, g1);
+            if (VARLEN) {
+                const int s = it % NS;
+                if (!ptx::mbar_wait(&full[s], (uint32_t)(it / NS) & 1u, ab, 122)) break;
+                if (t.valid < kTileTokens) {
+                    zero_tail_rows(stages + s * Cfg::kStageBytes, Cfg::kStageBlocks, t.valid, et);
+                    ptx::fence_proxy_async_smem();
+                }
+                ptx::mbar_arrive(&fixed[s]);
+            }
+            if (!t.last) continue;
             if (!ptx::mbar_wait(acc_full, (uint32_t)seg & 1u, ab, 121)) break;
             ptx::tc_fence_after_sync();
-            const int slot = unit * sch.slots_per_unit + ((int)blockIdx.x - first_cta_of_unit(sch, unit));
-            float* out = p.part + (size_t)slot * p.state_stride;
+            float* out = segment_destination<VARLEN>(p, t, p.state_out);
             drain_state_acc<DK, DV, (MODE != kSimple ? 1 : 0)>(tmem, DV, out, warp, lane);
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(acc_empty);
@@ -186,6 +193,42 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+// Packed layout: block b adds the pieces of the unit that starts inside CTA b's tile range and
+// continues into later CTAs (slot (b, 1), then slot (c, 0) of every later CTA the unit reaches),
+// in CTA order, and writes the unit's state.  `ctas` = grid size of the producing kernel.
+__global__ void __launch_bounds__(256)
+tc_reduce_varlen_kernel(const Params p_in, float* __restrict__ state, int ctas) {
+    __shared__ int32_t plan_s[kMaxPackedSeqs + 1];
+    build_plan(plan_s, p_in.cu, p_in.num_seqs, p_in.heads);
+    Params p = p_in;
+    p.plan = plan_s;
+    const int total = p.plan[p.num_seqs];
+    if (total == 0) return;
+    const int per = (total + ctas - 1) / ctas;
+    const int b = blockIdx.x;
+    const int g0 = min(total, b * per), g1 = min(total, g0 + per);
+    if (g1 <= g0) return;
+    // the unit of this CTA's last tile
+    const int g = g1 - 1;
+    int lo = 0, hi = p.num_seqs;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (p.plan[mid] <= g) lo = mid; else hi = mid;
+    }
+    const int a0 = p.plan[lo];
+    const int nt = (p.plan[lo + 1] - a0) / p.heads;
+    const int h = (g - a0) / nt;
+    const int us = a0 + h * nt, ue = us + nt;          // global tile range of the unit
+    if (ue <= g1 || us < g0) return;                   // complete here, or owned by an earlier block
+    const int unit = lo * p.heads + h;
+    const int stride = p.state_stride;
+    for (int e = threadIdx.x; e < stride; e += 256) {
+        float s = p.part[((size_t)b * 2 + 1) * stride + e];
+        for (int c = b + 1; c < ctas && c * per < ue; ++c) s += p.part[((size_t)c * 2) * stride + e];
+        state[(size_t)unit * stride + e] = s;
     }
 }
 
@@ -223,14 +266,15 @@ struct FwdOutCfg {
     static constexpr int kStages = kAvail / kStageBytes < 8 ? kAvail / kStageBytes : 8;
     static constexpr int kAccCols = kZCol + 16;
     static constexpr int kTmemCols = 2 * kAccCols <= 256 ? 256 : 512;
-    static constexpr int kSmemBytes = 1024 + kBopBytes + kStages * kStageBytes + 2 * kOutBytes + 512;
+    static constexpr int kSmemBytes = 1024 + kBopBytes + kStages * kStageBytes + 2 * kOutBytes + 512 + kPlanBytes;
 };
 
-template <int DK, int DV, int MODE, bool BF16>
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
-                  const __grid_constant__ CUtensorMap tm_o, const Params p) {
+                  const __grid_constant__ CUtensorMap tm_o, const Params p_in) {
     using Cfg = FwdOutCfg<DK, DV, MODE>;
+    using Map = TileMap<VARLEN>;
     constexpr int NS = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_1024(smem_raw);
@@ -249,9 +293,15 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const Schedule& sch = p.sch;
-    const int g0 = blockIdx.x * sch.tiles_per_cta;
-    const int g1 = min(sch.total_tiles, g0 + sch.tiles_per_cta);
+    Params pv = p_in;
+    if (VARLEN) {
+        int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
+        build_plan(plan, p_in.cu, p_in.num_seqs, p_in.heads);
+        pv.plan = plan;
+    }
+    const Params& p = pv;
+    int g0, g1;
+    Map::range(p, g0, g1);
     const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
@@ -287,15 +337,14 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             if (!ptx::mbar_wait(&empty[s], ph ^ 1u, ab, 201)) break;
             ptx::mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
-            const int unit = g / sch.tiles_per_unit;
-            const int t0 = (g - unit * sch.tiles_per_unit) * kTileTokens;
+            const Tile t = Map::get(p, g, g0, g1);
             uint8_t* st = stages + s * Cfg::kStageBytes;
 #pragma unroll
-            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_qr, &full[s], b * 64, t0, unit);
+            for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_load_3d(st + b * kBlockBytes, &tm_qr, &full[s], b * 64, t.c1, t.c2);
             if (MODE == kDecoupled) {
 #pragma unroll
                 for (int b = 0; b < Cfg::kKB; ++b)
-                    ptx::tma_load_3d(st + (Cfg::kKB + b) * kBlockBytes, &tm_q, &full[s], b * 64, t0, unit);
+                    ptx::tma_load_3d(st + (Cfg::kKB + b) * kBlockBytes, &tm_q, &full[s], b * 64, t.c1, t.c2);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -310,8 +359,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
             const int s = it % NS;
             const uint32_t ph = (uint32_t)(it / NS) & 1u;
             const int a = it & 1;
-            const int tile = g % sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
+            const bool first = Map::get(p, g, g0, g1).first;
             if (first) {
                 if (!ptx::mbar_wait(bop_ready, (uint32_t)seg & 1u, ab, 211)) break;
                 ++seg;
@@ -355,9 +403,9 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
         const bool issuer = (et == 0);
         int seg = 0;
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
-            const int unit = g / sch.tiles_per_unit;
-            const int tile = g - unit * sch.tiles_per_unit;
-            const bool first = (g == g0) || tile == 0;
+            const Tile t = Map::get(p, g, g0, g1);
+            const int unit = t.unit, tile = t.tile;
+            const bool first = t.first;
             const int a = it & 1;
             const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
             if (first) {
@@ -366,7 +414,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                 const float* st = p.state + (size_t)unit * p.state_stride;
                 for (int i = et; i < DK * DV; i += kEpiThreads) {
                     const int k = i / DV, v = i - k * DV;
-                    const float x = st[i] * p.scale;
+                    const float x = st[i] * t.scale;
                     const uint16_t h = pack1(x, BF16);
                     *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(v, k & 63)) = h;
                     // rounding residual: a second B operand accumulated into the same columns
@@ -378,7 +426,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                         const int r = i / DK, k = i - r * DK;
                         uint16_t h = 0;
                         if (r < 2) {
-                            const float km = st[DK * DV + k] * p.inv_norm;
+                            const float km = st[DK * DV + k] * t.inv_norm;
                             const uint16_t hi = pack1(km, BF16);
                             h = r == 0 ? hi : pack1(km - unpack1(hi, BF16), BF16);
                         }
@@ -399,11 +447,17 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                 rz = 1.f / (zc[0] + zc[1] + p.eps);
             }
             // the staged tile of two tiles ago must have been read by its store
-            if (issuer) {
-                ptx::tma_store_wait_read<1>();
-                ptx::mbar_arrive(&out_free[a]);
+            if (!VARLEN) {
+                if (issuer) {
+                    ptx::tma_store_wait_read<1>();
+                    ptx::mbar_arrive(&out_free[a]);
+                }
+                if (!ptx::mbar_wait(&out_free[a], ph2, ab, 222)) break;
             }
-            if (!ptx::mbar_wait(&out_free[a], ph2, ab, 222)) break;
+            // packed layout: rows are heads*dv apart and a tile may end inside the next sequence, so
+            // the output leaves in guarded 32-byte stores instead of a staged tile
+            uint8_t* orow = static_cast<uint8_t*>(p.out_a) + (size_t)(t.row0 + (long long)row * t.row_stride) * DV * 2;
+            const bool row_ok = row < t.valid;
             uint8_t* ob = outbuf + a * Cfg::kOutBytes;
 #pragma unroll
             for (int c0 = 0; c0 < DV; c0 += 32) {
@@ -419,6 +473,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                     ptx::tmem_ld_wait();
                 }
                 uint8_t* blk = ob + (c0 >> 6) * kBlockBytes + row * 128;
+                uint4 keep[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint4 w;
@@ -427,14 +482,19 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                     w.z = pack2(v[8 * j + 4] * rz, v[8 * j + 5] * rz, BF16);
                     w.w = pack2(v[8 * j + 6] * rz, v[8 * j + 7] * rz, BF16);
                     const int chunk = ((c0 & 63) >> 3) + j;
-                    *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                    if (!VARLEN) *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                    keep[j] = w;
+                }
+                if (VARLEN && row_ok) {
+                    ptx::st_global_32B(orow + c0 * 2, keep[0], keep[1]);
+                    ptx::st_global_32B(orow + c0 * 2 + 32, keep[2], keep[3]);
                 }
             }
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&tempty[a]);
             ptx::fence_proxy_async_smem();
             ptx::mbar_arrive(&out_written[a]);
-            if (issuer) {
+            if (!VARLEN && issuer) {
                 if (!ptx::mbar_wait(&out_written[a], ph2, ab, 223)) break;
 #pragma unroll
                 for (int b = 0; b < Cfg::kVB; ++b)
@@ -442,7 +502,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                 ptx::tma_store_commit();
             }
         }
-        if (issuer) ptx::tma_store_wait_all<0>();
+        if (!VARLEN && issuer) ptx::tma_store_wait_all<0>();
     }
     ptx::tc_fence_before_sync();
     __syncthreads();

@@ -151,6 +151,13 @@ Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) 
     q.state_stride = p.state_stride;
     q.out_a = nullptr;
     q.out_b = nullptr;
+    q.state_out = nullptr;
+    q.cu = nullptr;
+    q.plan = nullptr;
+    q.num_seqs = 0;
+    q.heads = p.heads;
+    q.scale_per_seq = 0;
+    q.inv_norm_fixed = 0.f;
     return q;
 }
 
@@ -176,12 +183,12 @@ cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
 }
 
 // ---- per-shape launch helpers ----------------------------------------------------------------
-template <int DK, int DV, int MODE, bool BF16>
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
 cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tk, const CUtensorMap& tv,
                              cudaStream_t st) {
     using Cfg = FwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
-    auto kernel = tc_fwd_state_kernel<DK, DV, MODE, BF16>;
+    auto kernel = tc_fwd_state_kernel<DK, DV, MODE, BF16, VARLEN>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
@@ -190,13 +197,13 @@ cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUte
     return cudaGetLastError();
 }
 
-template <int DK, int DV, int MODE, bool BF16>
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
 cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& to,
                            cudaStream_t st) {
     using Cfg = FwdOutCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
-    auto kernel = tc_fwd_out_kernel<DK, DV, MODE, BF16>;
+    auto kernel = tc_fwd_out_kernel<DK, DV, MODE, BF16, VARLEN>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
@@ -205,13 +212,13 @@ cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtens
     return cudaGetLastError();
 }
 
-template <int DK, int DV, int MODE, bool BF16>
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
 cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
                              const CUtensorMap& tdq, const CUtensorMap& tdqr, cudaStream_t st) {
     using Cfg = BwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
-    auto kernel = tc_bwd_state_kernel<DK, DV, MODE, BF16>;
+    auto kernel = tc_bwd_state_kernel<DK, DV, MODE, BF16, VARLEN>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
@@ -220,13 +227,13 @@ cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUte
     return cudaGetLastError();
 }
 
-template <int DK, int DV, int MODE, bool BF16>
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
 cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tv, const CUtensorMap& tdk,
                           const CUtensorMap& tdkr, const CUtensorMap& tdv, cudaStream_t st) {
     using Cfg = BwdInCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
-    auto kernel = tc_bwd_in_kernel<DK, DV, MODE, BF16>;
+    auto kernel = tc_bwd_in_kernel<DK, DV, MODE, BF16, VARLEN>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
@@ -259,6 +266,53 @@ cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtenso
         }                                                                                               \
     } while (0)
 
+// Packed (varlen) layout: normalised operator only.
+#define FBLA_TC_VARLEN_DISPATCH(CALL, ...)                                                              \
+    do {                                                                                                \
+        const int key = (p.dk == 128 ? 2 : 0) + (p.dv == 128 ? 1 : 0) + (dtype == FBLA_BF16 ? 4 : 0);   \
+        switch (key) {                                                                                  \
+            case 0: return CALL<64, 64, kLinear, false, true>(__VA_ARGS__);                             \
+            case 1: return CALL<64, 128, kLinear, false, true>(__VA_ARGS__);                            \
+            case 2: return CALL<128, 64, kLinear, false, true>(__VA_ARGS__);                            \
+            case 3: return CALL<128, 128, kLinear, false, true>(__VA_ARGS__);                           \
+            case 4: return CALL<64, 64, kLinear, true, true>(__VA_ARGS__);                              \
+            case 5: return CALL<64, 128, kLinear, true, true>(__VA_ARGS__);                             \
+            case 6: return CALL<128, 64, kLinear, true, true>(__VA_ARGS__);                             \
+            default: return CALL<128, 128, kLinear, true, true>(__VA_ARGS__);                           \
+        }                                                                                               \
+    } while (0)
+
+// ---- packed layout: tensor maps, tile plan, workspace split ---------------------------------------
+// (total_tokens, heads, D) 16-bit tensor as a 3-D map {D, heads, total_tokens}; one box = 64 features
+// of one head over 128 consecutive tokens, same shared-memory tile as the fixed-length box.
+cudaError_t make_map_packed(CUtensorMap* m, const void* base, int dtype, int D, int heads, int64_t tokens) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)heads * D * 2};
+    const cuuint32_t box[3] = {64, 1, (cuuint32_t)kTileTokens};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = dtype == FBLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, FBLA_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// Fills the packed-layout fields of the kernel parameters (each kernel builds its tile plan itself).
+Params make_params_packed(const KParams& p, int dtype) {
+    Schedule s{};
+    s.units = p.units;
+    s.ctas = sm_count();
+    Params q = make_params(p, dtype, s);
+    q.cu = p.cu;
+    q.plan = nullptr;
+    q.num_seqs = p.units / p.heads;
+    q.heads = p.heads;
+    q.scale_per_seq = p.scale_per_seq;
+    q.inv_norm_fixed = p.inv_norm > 0.f ? p.inv_norm : 0.f;
+    return q;
+}
+
 }  // namespace
 
 // The tensor-core kernels serve 16-bit inputs in the fixed-length layout with dk, dv in
@@ -266,7 +320,9 @@ cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtenso
 // memory budget at 128).
 bool tc_supported(const KParams& p, int dtype) {
     if (dtype != FBLA_BF16 && dtype != FBLA_F16) return false;
-    if (p.cu != nullptr) return false;
+    if (p.cu != nullptr &&
+        (!p.normalize || p.seq_len >= (1LL << 31) - 256 || p.units / p.heads > kMaxPackedSeqs))
+        return false;
     if ((p.dk != 64 && p.dk != 128) || (p.dv != 64 && p.dv != 128)) return false;
     if (p.seq_len < 1 || p.units < 1) return false;
     if (encode_fn() == nullptr) return false;
@@ -276,6 +332,8 @@ bool tc_supported(const KParams& p, int dtype) {
 bool tc_supported_decoupled(const KParams& p) { return p.dk == 64 && p.dv == 64; }
 
 int64_t tc_workspace_bytes(const KParams& p) {
+    if (p.cu != nullptr)   // two partial slots per CTA
+        return (int64_t)sm_count() * 2 * p.state_stride * (int64_t)sizeof(float);
     const Schedule s = make_schedule(p, sm_count());
     return (int64_t)s.units * s.slots_per_unit * p.state_stride * (int64_t)sizeof(float);
 }
@@ -303,6 +361,23 @@ cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void*
 
 cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
                                 float* state, void* ws, int* status, cudaStream_t st) {
+    if (p.cu != nullptr) {
+        // packed layout: zeroed state (units without tokens stay zero), state kernel, reduce
+        cudaError_t e;
+        if ((e = cudaMemsetAsync(state, 0, sizeof(float) * (size_t)p.units * p.state_stride, st)) != cudaSuccess) return e;
+        Params q = make_params_packed(p, dtype);
+        q.status = status;
+        q.state_out = state;
+        q.part = static_cast<float*>(ws);
+        CUtensorMap tk, tv;
+        if ((e = make_map_packed(&tk, k, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_fwd_state, q, tk, tk, tv, st); };
+        if ((e = launch()) != cudaSuccess) return e;
+        tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, state, q.sch.ctas);
+        note_launches(1);
+        return cudaGetLastError();
+    }
     const bool dec = k_rope != nullptr && k_rope != k;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
@@ -321,12 +396,24 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
 
 cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* q_rope, const float* state, void* o,
                        cudaStream_t st) {
+    if (p.cu != nullptr) {
+        Params q = make_params_packed(p, dtype);
+        if (q.status == nullptr) return cudaErrorMemoryAllocation;
+        q.state = state;
+        q.out_a = o;
+        CUtensorMap tq, to;
+        cudaError_t e;
+        if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&to, o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        FBLA_TC_VARLEN_DISPATCH(launch_fwd_out, q, tq, tq, to, st);
+    }
     const bool dec = q_rope != nullptr && q_rope != q_;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = state;
+    q.out_a = o;
     CUtensorMap tqr, tq, to;
     cudaError_t e;
     if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
@@ -337,6 +424,26 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
 
 cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void* q_rope, const void* d_o,
                          const float* state, void* dq, void* dq_rope, float* dstate, void* ws, cudaStream_t st) {
+    if (p.cu != nullptr) {
+        cudaError_t e;
+        if ((e = cudaMemsetAsync(dstate, 0, sizeof(float) * (size_t)p.units * p.state_stride, st)) != cudaSuccess) return e;
+        Params q = make_params_packed(p, dtype);
+        if (q.status == nullptr) return cudaErrorMemoryAllocation;
+        q.state = state;
+        q.state_out = dstate;
+        q.part = static_cast<float*>(ws);
+        q.out_a = dq;
+        q.out_b = dq;
+        CUtensorMap tq, tdo, tdq;
+        if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdo, d_o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdq, dq, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_bwd_state, q, tq, tq, tdo, tdq, tdq, st); };
+        if ((e = launch()) != cudaSuccess) return e;
+        tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, dstate, q.sch.ctas);
+        note_launches(1);
+        return cudaGetLastError();
+    }
     const bool dec = dq_rope != nullptr;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
@@ -360,6 +467,20 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
 
 cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const void* v, const float* dstate, void* dk,
                       void* dk_rope, void* dv, cudaStream_t st) {
+    if (p.cu != nullptr) {
+        Params q = make_params_packed(p, dtype);
+        if (q.status == nullptr) return cudaErrorMemoryAllocation;
+        q.state = dstate;
+        q.out_a = dk;
+        q.out_b = dv;
+        CUtensorMap tk, tv, tdk, tdv;
+        cudaError_t e;
+        if ((e = make_map_packed(&tk, k_rope, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdk, dk, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdv, dv, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        FBLA_TC_VARLEN_DISPATCH(launch_bwd_in, q, tk, tv, tdk, tdk, tdv, st);
+    }
     const bool dec = dk_rope != nullptr;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
