@@ -10,7 +10,10 @@
 // but not g (kernel.py:262-276), so its result depends on the autotuned GROUP_SIZE once there
 // are more blocks than one group; here g is rescaled too, which equals the reference whenever
 // one group covers all blocks.
+#include <cstdlib>
+
 #include "fbla_common.cuh"
+#include "pisa_mma.cuh"
 
 namespace fbla {
 namespace {
@@ -234,6 +237,12 @@ size_t fwd_smem_bytes(const PisaParams& p) {
 
 }  // namespace
 
+// Test hook: route fbla_pisa_fwd to the CUDA-core kernel whatever the shape (FBLA_PISA_GENERIC=1).
+static const bool g_pisa_force_generic = [] {
+    const char* e = getenv("FBLA_PISA_GENERIC");
+    return e != nullptr && e[0] == '1';
+}();
+
 struct PisaArgs {
     PisaParams kp;
     int bh;
@@ -312,10 +321,36 @@ int fbla_pisa_fwd(const fbla_pisa_problem* p, const void* q, const void* k, cons
     if (int rc = fbla::resolve_pisa(p, &a)) return rc;
     if (!q || !k || !v || !kc || !vc || !h || !indices || !o)
         return fbla::api_fail(FBLA_ERR_INVALID, "a tensor pointer is NULL");
-    const size_t smem = fbla::fwd_smem_bytes(a.kp);
     dim3 grid(a.kp.nt, a.bh);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaSuccess;
+    // tensor-core kernel for the common shape; the CUDA-core kernel serves everything else
+    const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                           reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
+                           reinterpret_cast<uintptr_t>(h)) & 15u) == 0;
+    if (a.dtype != FBLA_F32 && a.kp.bs == 64 && a.kp.dk == a.kp.dv && (a.kp.dk == 64 || a.kp.dk == 128) && aligned &&
+        !fbla::g_pisa_force_generic) {
+        fbla::pisa_mma::Params mp{a.kp.heads, a.kp.ns, a.kp.nt, a.kp.T, a.kp.scale};
+        auto run = [&](auto kern, size_t smem) {
+            if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess)
+                kern<<<grid, fbla::pisa_mma::kThreads, smem, st>>>(mp, q, k, v, kc, vc, h, indices, o, row_stats);
+        };
+        const bool bf = a.dtype == FBLA_BF16;
+        if (a.kp.dk == 64) {
+            const size_t smem = fbla::pisa_mma::smem_bytes<64>(a.kp.nt);
+            if (bf) run(fbla::pisa_mma::pisa_fwd_mma_kernel<64, true>, smem);
+            else run(fbla::pisa_mma::pisa_fwd_mma_kernel<64, false>, smem);
+        } else {
+            const size_t smem = fbla::pisa_mma::smem_bytes<128>(a.kp.nt);
+            if (bf) run(fbla::pisa_mma::pisa_fwd_mma_kernel<128, true>, smem);
+            else run(fbla::pisa_mma::pisa_fwd_mma_kernel<128, false>, smem);
+        }
+        fbla::note_launches(1);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "attention kernel: %s", cudaGetErrorString(e));
+    }
+    const size_t smem = fbla::fwd_smem_bytes(a.kp);
     PISA_BY_DTYPE(a.dtype, {
         auto kern = fbla::pisa_fwd_kernel<T>;
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

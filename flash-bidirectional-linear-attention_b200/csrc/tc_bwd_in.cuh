@@ -95,7 +95,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
     Params pv = p_in;
     if (VARLEN) {
         int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
-        build_plan(plan, p_in.cu, p_in.num_seqs, p_in.heads);
+        build_plan(plan, p_in.cu, p_in.num_seqs);
         pv.plan = plan;
     }
     const Params& p = pv;

@@ -87,9 +87,9 @@ struct Tile {
     float scale, inv_norm;
 };
 
-// plan[s] = heads * (128-token tiles of the sequences before s), plan[num_seqs] = all tiles; built by
-// every CTA for itself from cu_seqlens (all threads of the block must call this).
-__device__ __forceinline__ void build_plan(int32_t* plan, const int32_t* __restrict__ cu, int num_seqs, int heads) {
+// plan[s] = number of 128-token tiles of the sequences before s (per head), plan[num_seqs] = all of
+// them; built by every CTA for itself from cu_seqlens (all threads of the block must call this).
+__device__ __forceinline__ void build_plan(int32_t* plan, const int32_t* __restrict__ cu, int num_seqs) {
     for (int i = threadIdx.x; i <= num_seqs; i += blockDim.x) plan[i] = cu[i];
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -97,7 +97,7 @@ __device__ __forceinline__ void build_plan(int32_t* plan, const int32_t* __restr
         for (int s = 0; s < num_seqs; ++s) {
             const int next = plan[s + 1];
             plan[s] = acc;
-            acc += heads * ((next - prev + kTileTokens - 1) / kTileTokens);
+            acc += (next - prev + kTileTokens - 1) / kTileTokens;
             prev = next;
         }
         plan[num_seqs] = acc;
@@ -134,12 +134,18 @@ struct TileMap<false> {
     }
 };
 
+// Packed layout.  Token rows of one head are heads*D elements apart, so the heads of a token share
+// DRAM pages: CTA c works on head c % heads, and the heads*G CTAs of a launch split the per-head tile
+// list into G = gridDim.x / heads contiguous ranges, so that at any time the CTAs of a group stream
+// the same tokens (one head each).  Tile index g below counts tiles of ONE head.
 template <>
 struct TileMap<true> {
     __device__ static __forceinline__ void range(const Params& p, int& g0, int& g1) {
         const int total = p.plan[p.num_seqs];
-        const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
-        g0 = min(total, (int)blockIdx.x * per);
+        const int groups = (int)gridDim.x / p.heads;
+        const int grp = (int)blockIdx.x / p.heads;
+        const int per = (total + groups - 1) / groups;
+        g0 = min(total, grp * per);
         g1 = min(total, g0 + per);
     }
     __device__ static __forceinline__ Tile get(const Params& p, int g, int g0, int g1) {
@@ -151,11 +157,10 @@ struct TileMap<true> {
         }
         const int s = lo;
         const int a0 = p.plan[s];
-        const int nt = (p.plan[s + 1] - a0) / p.heads;
-        const int r = g - a0;
-        const int h = r / nt;
+        const int nt = p.plan[s + 1] - a0;
+        const int h = (int)blockIdx.x % p.heads;
         Tile t;
-        t.tile = r - h * nt;
+        t.tile = g - a0;
         t.unit = s * p.heads + h;
         const int bos = p.cu[s];
         const int len = p.cu[s + 1] - bos;
@@ -166,8 +171,8 @@ struct TileMap<true> {
         t.row_stride = p.heads;
         t.first = (g == g0) || t.tile == 0;
         t.last = (g == g1 - 1) || t.tile == nt - 1;
-        t.starts_here = (g - t.tile) >= g0;
-        t.ends_here = (g - t.tile + nt) <= g1;
+        t.starts_here = a0 >= g0;
+        t.ends_here = (a0 + nt) <= g1;
         const float inv_len = 1.f / (float)len;
         t.scale = p.scale_per_seq ? inv_len : p.scale;
         t.inv_norm = p.inv_norm_fixed > 0.f ? p.inv_norm_fixed : inv_len;

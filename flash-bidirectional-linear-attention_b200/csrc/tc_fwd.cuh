@@ -71,7 +71,7 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
     Params pv = p_in;
     if (VARLEN) {
         int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
-        build_plan(plan, p_in.cu, p_in.num_seqs, p_in.heads);
+        build_plan(plan, p_in.cu, p_in.num_seqs);
         pv.plan = plan;
     }
     const Params& p = pv;
@@ -196,38 +196,36 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
     }
 }
 
-// Packed layout: block b adds the pieces of the unit that starts inside CTA b's tile range and
-// continues into later CTAs (slot (b, 1), then slot (c, 0) of every later CTA the unit reaches),
-// in CTA order, and writes the unit's state.  `ctas` = grid size of the producing kernel.
+// Packed layout: block b = (group, head) adds the pieces of the unit that starts inside its tile
+// range and continues into later groups of the same head (slot (b, 1), then slot (b + heads*j, 0)
+// for every later group the unit reaches), in group order, and writes the unit's state.
+// `ctas` = grid size of the producing kernel.
 __global__ void __launch_bounds__(256)
 tc_reduce_varlen_kernel(const Params p_in, float* __restrict__ state, int ctas) {
     __shared__ int32_t plan_s[kMaxPackedSeqs + 1];
-    build_plan(plan_s, p_in.cu, p_in.num_seqs, p_in.heads);
-    Params p = p_in;
-    p.plan = plan_s;
-    const int total = p.plan[p.num_seqs];
+    build_plan(plan_s, p_in.cu, p_in.num_seqs);
+    const Params& p = p_in;
+    const int total = plan_s[p.num_seqs];
     if (total == 0) return;
-    const int per = (total + ctas - 1) / ctas;
-    const int b = blockIdx.x;
-    const int g0 = min(total, b * per), g1 = min(total, g0 + per);
+    const int groups = ctas / p.heads;
+    const int per = (total + groups - 1) / groups;
+    const int b = blockIdx.x, grp = b / p.heads, h = b % p.heads;
+    const int g0 = min(total, grp * per), g1 = min(total, g0 + per);
     if (g1 <= g0) return;
-    // the unit of this CTA's last tile
-    const int g = g1 - 1;
+    const int g = g1 - 1;                               // the unit of this CTA's last tile
     int lo = 0, hi = p.num_seqs;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (p.plan[mid] <= g) lo = mid; else hi = mid;
+        if (plan_s[mid] <= g) lo = mid; else hi = mid;
     }
-    const int a0 = p.plan[lo];
-    const int nt = (p.plan[lo + 1] - a0) / p.heads;
-    const int h = (g - a0) / nt;
-    const int us = a0 + h * nt, ue = us + nt;          // global tile range of the unit
-    if (ue <= g1 || us < g0) return;                   // complete here, or owned by an earlier block
+    const int us = plan_s[lo], ue = plan_s[lo + 1];     // per-head tile range of the sequence
+    if (ue <= g1 || us < g0) return;                   // complete here, or owned by an earlier group
     const int unit = lo * p.heads + h;
     const int stride = p.state_stride;
     for (int e = threadIdx.x; e < stride; e += 256) {
         float s = p.part[((size_t)b * 2 + 1) * stride + e];
-        for (int c = b + 1; c < ctas && c * per < ue; ++c) s += p.part[((size_t)c * 2) * stride + e];
+        for (int gg = grp + 1; gg < groups && gg * per < ue; ++gg)
+            s += p.part[((size_t)(gg * p.heads + h) * 2) * stride + e];
         state[(size_t)unit * stride + e] = s;
     }
 }
@@ -296,7 +294,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
     Params pv = p_in;
     if (VARLEN) {
         int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
-        build_plan(plan, p_in.cu, p_in.num_seqs, p_in.heads);
+        build_plan(plan, p_in.cu, p_in.num_seqs);
         pv.plan = plan;
     }
     const Params& p = pv;

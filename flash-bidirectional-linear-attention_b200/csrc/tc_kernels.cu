@@ -302,7 +302,7 @@ cudaError_t make_map_packed(CUtensorMap* m, const void* base, int dtype, int D, 
 Params make_params_packed(const KParams& p, int dtype) {
     Schedule s{};
     s.units = p.units;
-    s.ctas = sm_count();
+    s.ctas = (sm_count() / p.heads) * p.heads;       // groups of `heads` CTAs, one head each
     Params q = make_params(p, dtype, s);
     q.cu = p.cu;
     q.plan = nullptr;
@@ -321,7 +321,8 @@ Params make_params_packed(const KParams& p, int dtype) {
 bool tc_supported(const KParams& p, int dtype) {
     if (dtype != FBLA_BF16 && dtype != FBLA_F16) return false;
     if (p.cu != nullptr &&
-        (!p.normalize || p.seq_len >= (1LL << 31) - 256 || p.units / p.heads > kMaxPackedSeqs))
+        (!p.normalize || p.seq_len >= (1LL << 31) - 256 || p.units / p.heads > kMaxPackedSeqs ||
+         p.heads > sm_count()))
         return false;
     if ((p.dk != 64 && p.dk != 128) || (p.dv != 64 && p.dv != 128)) return false;
     if (p.seq_len < 1 || p.units < 1) return false;
