@@ -1,0 +1,110 @@
+"""Operator timings in the format of the reference's benchmark table
+(``benchmarks/ops/benchmark_linear_attn.py``: forward and forward+backward milliseconds of
+``linear_attention`` over T in {1024, 4096, 16384, 32768}, bf16, H=16, D=64), extended to the
+other operators.  Timing: CUDA events around back-to-back calls of the public API, median of
+``--reps`` repetitions after warm-up; inputs are larger than L2 from T=4096 up at B=8.
+
+    python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|simple_la|decoupled_la|varlen|pisa|all]
+"""
+import argparse
+import os
+import statistics
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.nn.functional as F
+
+from flash_bla.ops.linear_attn.decoupled import decoupled_la
+from flash_bla.ops.linear_attn.fused import linear_attention
+from flash_bla.ops.linear_attn.varlen import varlen_linear_attention
+from flash_bla.ops.piecewise_attn.kernel import piecewise_sparse_attention
+from flash_bla.ops.simple_la.fused import simple_la
+
+
+def timed(fn, reps, inner=4):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(inner):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1) / inner)
+    return statistics.median(out)
+
+
+def row(name, shape, fwd, fwd_bwd, tokens, nbytes_fwd, nbytes_all):
+    print(f"{name:14s} {shape:28s} fwd {fwd:8.4f} ms ({nbytes_fwd / fwd / 1e6:6.0f} GB/s)   fwd+bwd {fwd_bwd:8.4f} ms "
+          f"({nbytes_all / fwd_bwd / 1e6:6.0f} GB/s, {tokens / fwd_bwd * 1e3:.3e} tokens/s)", flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--dim", type=int, default=64)
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--op", default="all")
+    args = ap.parse_args()
+    B, H, D = args.batch, args.heads, args.dim
+    dev, dt = "cuda", torch.bfloat16
+    pos = lambda *s: (F.elu(torch.randn(*s, device=dev)) + 1).to(dt).requires_grad_()
+    gau = lambda *s: torch.randn(*s, device=dev).to(dt).requires_grad_()
+
+    def both(make_out, leaves, do):
+        def fb():
+            for x in leaves:
+                x.grad = None
+            make_out().backward(do)
+        with torch.no_grad():
+            f = timed(make_out, args.reps)
+        return f, timed(fb, args.reps)
+
+    if args.op in ("all", "linear_attn"):
+        for T in (1024, 4096, 16384, 32768):
+            q, k, v = pos(B, H, T, D), pos(B, H, T, D), gau(B, H, T, D)
+            do = torch.randn_like(v)
+            P = B * H * T * D * 2
+            f, fb = both(lambda: linear_attention(q, k, v), (q, k, v), do)
+            row("linear_attn", f"B{B} H{H} T{T} D{D}", f, fb, B * T, 4 * P, 11 * P)
+    if args.op in ("all", "simple_la"):
+        for (b, h, T, d) in ((4, 32, 32768, 128), (B, H, 32768, D)):
+            q, k, v = gau(b, h, T, d), gau(b, h, T, d), gau(b, h, T, d)
+            do = torch.randn_like(v)
+            P = b * h * T * d * 2
+            f, fb = both(lambda: simple_la(q, k, v), (q, k, v), do)
+            row("simple_la", f"B{b} H{h} T{T} D{d}", f, fb, b * T, 4 * P, 11 * P)
+    if args.op in ("all", "decoupled_la"):
+        for T in (4096, 32768):
+            q, k, qr, kr, v = pos(B, H, T, D), pos(B, H, T, D), gau(B, H, T, D), gau(B, H, T, D), gau(B, H, T, D)
+            do = torch.randn_like(v)
+            P = B * H * T * D * 2
+            f, fb = both(lambda: decoupled_la(q, k, qr, kr, v), (q, k, qr, kr, v), do)
+            row("decoupled_la", f"B{B} H{H} T{T} D{D}", f, fb, B * T, 6 * P, 16 * P)
+    if args.op in ("all", "varlen"):
+        g = torch.Generator().manual_seed(0)
+        lengths = torch.randint(256, 16385, (32,), generator=g)
+        cu = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)]).to(torch.int32).to(dev)
+        tot, mx = int(lengths.sum()), int(lengths.max())
+        q, k, v = pos(tot, H, D), pos(tot, H, D), gau(tot, H, D)
+        do = torch.randn_like(v)
+        P = tot * H * D * 2
+        f, fb = both(lambda: varlen_linear_attention(q, k, v, cu, mx), (q, k, v), do)
+        row("varlen", f"32 seqs, {tot} tok, H{H} D{D}", f, fb, tot, 4 * P, 11 * P)
+    if args.op in ("all", "pisa"):
+        b, h, T, d = 2, 24, 4608, 128
+        q, k, v = gau(b, h, T, d), gau(b, h, T, d), gau(b, h, T, d)
+        do = torch.randn_like(v)
+        P = b * h * T * d * 2
+        f, fb = both(lambda: piecewise_sparse_attention(q, k, v), (q, k, v), do)
+        row("pisa", f"B{b} H{h} T{T} D{d} bs64 d0.1", f, fb, b * T, 7 * P, 7 * P)
+
+
+if __name__ == "__main__":
+    main()

@@ -306,6 +306,21 @@ int fbla_decoupled_la_bwd_in(const fbla_problem* p, const void* k_rope, const vo
     return bwd_in(p, OP_DECOUPLED, k_rope, v, dstate, dk, dk_rope, dv, s);
 }
 
+// ---- both passes of a direction in one call (saves a host round trip per pass) -----------
+int fbla_linear_attn_fwd(const fbla_problem* p, const void* q, const void* k, const void* v, void* o, float* state,
+                         void* ws, size_t ws_bytes, fbla_stream_t s) {
+    const OpKind op = kind_of(p);
+    if (int rc = fwd_state(p, op, k, nullptr, v, state, ws, ws_bytes, s)) return rc;
+    return fwd_out(p, op, q, nullptr, state, o, s);
+}
+int fbla_linear_attn_bwd(const fbla_problem* p, const void* q, const void* k, const void* v, const void* d_o,
+                         const float* state, void* dq, void* dk, void* dv, float* dstate, void* ws, size_t ws_bytes,
+                         fbla_stream_t s) {
+    const OpKind op = kind_of(p);
+    if (int rc = bwd_state(p, op, q, nullptr, d_o, state, dq, nullptr, dstate, ws, ws_bytes, s)) return rc;
+    return bwd_in(p, op, k, v, dstate, dk, nullptr, dv, s);
+}
+
 // ---- varlen_linear_attention -----------------------------------------------------------
 int fbla_varlen_linear_attn_fwd_state(const fbla_problem* p, const void* k, const void* v, float* state,
                                       void* ws, size_t ws_bytes, fbla_stream_t s) {

@@ -36,6 +36,25 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// The driver call needs a CUDA context bound to the calling thread.  A thread that has made no
+// context-binding runtime call yet (an autograd worker whose first work is this library) has none
+// and gets CUDA_ERROR_INVALID_CONTEXT: bind the current device's primary context and try again.
+CUresult encode_tiled(CUtensorMap* m, CUtensorMapDataType dt, const void* base, const cuuint64_t* dims,
+                      const cuuint64_t* strides, const cuuint32_t* box) {
+    EncodeTiledFn fn = encode_fn();
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = CUDA_ERROR_INVALID_CONTEXT;
+    for (int attempt = 0; attempt < 2 && r == CUDA_ERROR_INVALID_CONTEXT; ++attempt) {
+        if (attempt == 1) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) break;
+        }
+        r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, FBLA_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    return r;
+}
+
 // (units, T, D) 16-bit tensor viewed as a 3-D map {D, T, units}; one box = 64 features x 128
 // tokens of one unit, written to shared memory in the 128-byte-swizzled layout.  Tokens past T
 // read as zero and are dropped on stores.
@@ -76,16 +95,12 @@ cudaError_t make_map(CUtensorMap* m, const void* base, int dtype, int D, int64_t
 }
 
 cudaError_t encode_map(CUtensorMap* m, const void* base, int dtype, int D, int64_t T, int units) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return cudaErrorNotSupported;
+    if (encode_fn() == nullptr) return cudaErrorNotSupported;
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)units};
     const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)T * D * 2};
     const cuuint32_t box[3] = {64, (cuuint32_t)kTileTokens, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = dtype == FBLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, FBLA_L2_PROMOTION,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode_tiled(m, dt, base, dims, strides, box);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
@@ -286,15 +301,12 @@ cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtenso
 // (total_tokens, heads, D) 16-bit tensor as a 3-D map {D, heads, total_tokens}; one box = 64 features
 // of one head over 128 consecutive tokens, same shared-memory tile as the fixed-length box.
 cudaError_t make_map_packed(CUtensorMap* m, const void* base, int dtype, int D, int heads, int64_t tokens) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return cudaErrorNotSupported;
+    if (encode_fn() == nullptr) return cudaErrorNotSupported;
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)tokens};
     const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)heads * D * 2};
     const cuuint32_t box[3] = {64, 1, (cuuint32_t)kTileTokens};
-    const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = dtype == FBLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, FBLA_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode_tiled(m, dt, base, dims, strides, box);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 

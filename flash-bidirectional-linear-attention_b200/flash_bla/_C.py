@@ -83,6 +83,7 @@ def exported_symbols():
              "fbla_workspace_bytes", "fbla_kernel_path"]
     for op in OPS:
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
+    names += ["fbla_linear_attn_fwd", "fbla_linear_attn_bwd"]
     names.append("fbla_linear_attn_fwd_state_noalloc")
     names += ["fbla_pisa_block_stats", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd"]
     return names
@@ -114,6 +115,10 @@ def lib():
                 f = getattr(L, f"fbla_{op}_{name}")
                 f.restype = ctypes.c_int
                 f.argtypes = [_P] + args
+        L.fbla_linear_attn_fwd.restype = ctypes.c_int
+        L.fbla_linear_attn_fwd.argtypes = [_P, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]
+        L.fbla_linear_attn_bwd.restype = ctypes.c_int
+        L.fbla_linear_attn_bwd.argtypes = [_P] + [_vp] * 10 + [_sz, _vp]
         L.fbla_linear_attn_fwd_state_noalloc.restype = ctypes.c_int
         L.fbla_linear_attn_fwd_state_noalloc.argtypes = [_P, _vp, _vp, _vp, _vp]   # k, v, state, stream
         _PP = ctypes.POINTER(PisaProblem)

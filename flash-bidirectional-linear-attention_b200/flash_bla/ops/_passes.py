@@ -116,6 +116,57 @@ def bwd_in(op, prob, k, v, dstate, dk, dv, dk_rope=None):
     _C.check(rc)
 
 
+# ---- one call per direction (single GPU: nothing happens between the two passes) -------------
+_ws_cache = {}
+
+
+def _sizes(prob):
+    """(state floats, workspace bytes) of a problem; the library is asked once per shape."""
+    key = (prob.dtype, prob.batch, prob.heads, prob.dk, prob.dv, prob.seq_len, prob.num_seqs, prob.normalize,
+           prob.flags, prob.cu_seqlens is not None)
+    got = _ws_cache.get(key)
+    if got is None:
+        L = _C.lib()
+        got = (L.fbla_state_floats(ctypes.byref(prob)), L.fbla_workspace_bytes(ctypes.byref(prob)))
+        if got[0] < 0 or got[1] < 0:
+            _C.check(1)
+        if len(_ws_cache) > 256:
+            _ws_cache.clear()
+        _ws_cache[key] = got
+    return got
+
+
+def forward(prob, q, k, v):
+    """fwd_state + fwd_out of linear_attention / simple_la / varlen; returns (o, state)."""
+    _require_cuda(q, k, v)
+    n_state, n_ws = _sizes(prob)
+    dev = q.device
+    state = torch.empty(n_state, dtype=torch.float32, device=dev)
+    ws = torch.empty(n_ws, dtype=torch.uint8, device=dev) if n_ws else None
+    o = torch.empty_like(v)
+    with torch.cuda.device_of(q):
+        rc = _C.lib().fbla_linear_attn_fwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                           state.data_ptr(), _C.ptr(ws), n_ws, _C.stream_of(q))
+    _C.check(rc)
+    return o, state
+
+
+def backward(prob, q, k, v, d_o, state):
+    """bwd_state + bwd_in; returns (dq, dk, dv)."""
+    _require_cuda(q, k, v, d_o, state)
+    n_state, n_ws = _sizes(prob)
+    dev = q.device
+    dstate = torch.empty(n_state, dtype=torch.float32, device=dev)
+    ws = torch.empty(n_ws, dtype=torch.uint8, device=dev) if n_ws else None
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    with torch.cuda.device_of(q):
+        rc = _C.lib().fbla_linear_attn_bwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(),
+                                           state.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                           dstate.data_ptr(), _C.ptr(ws), n_ws, _C.stream_of(q))
+    _C.check(rc)
+    return dq, dk, dv
+
+
 def kernel_path(prob):
     """1 when the tensor-core kernels serve ``prob``, 0 for the CUDA-core kernels."""
     return _C.lib().fbla_kernel_path(ctypes.byref(prob))

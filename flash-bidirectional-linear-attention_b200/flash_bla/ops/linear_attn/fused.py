@@ -38,8 +38,7 @@ class LinearAttnFunction(torch.autograd.Function):
     def forward(ctx, q, k, v, scale, eps):
         _check(q, k, v)
         prob = _problem(q, v, scale, eps)
-        state = P.fwd_state(_OP, prob, k, v)
-        o = P.fwd_out(_OP, prob, q, state, torch.empty_like(v))
+        o, state = P.forward(prob, q, k, v)
         # The fp32 state is a few KB per head; keeping it avoids pass 1 in backward.
         ctx.save_for_backward(q, k, v, state)
         ctx.scale, ctx.eps = scale, eps
@@ -50,10 +49,7 @@ class LinearAttnFunction(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, state = ctx.saved_tensors
         prob = _problem(q, v, ctx.scale, ctx.eps)
-        dq = torch.empty_like(q)
-        dstate = P.bwd_state(_OP, prob, q, do, state, dq)
-        dk, dv = torch.empty_like(k), torch.empty_like(v)
-        P.bwd_in(_OP, prob, k, v, dstate, dk, dv)
+        dq, dk, dv = P.backward(prob, q, k, v, do, state)
         return dq, dk, dv, None, None
 
 

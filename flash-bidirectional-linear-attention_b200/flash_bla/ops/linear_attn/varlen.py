@@ -30,8 +30,7 @@ class VarlenLinearAttnFunction(torch.autograd.Function):
         # max_seqlen is only an upper bound; the kernels clip at each sequence's end.
         max_seqlen = min(int(max_seqlen), q.shape[0]) if q.shape[0] > 0 else 1
         prob = _problem(q, v, cu_seqlens, max_seqlen, scale, eps)
-        state = P.fwd_state(_OP, prob, k, v)
-        o = P.fwd_out(_OP, prob, q, state, torch.empty_like(v))
+        o, state = P.forward(prob, q, k, v)
         ctx.save_for_backward(q, k, v, cu_seqlens, state)
         ctx.max_seqlen, ctx.scale, ctx.eps = max_seqlen, scale, eps
         return o
@@ -41,10 +40,7 @@ class VarlenLinearAttnFunction(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, cu_seqlens, state = ctx.saved_tensors
         prob = _problem(q, v, cu_seqlens, ctx.max_seqlen, ctx.scale, ctx.eps)
-        dq = torch.empty_like(q)
-        dstate = P.bwd_state(_OP, prob, q, do, state, dq)
-        dk, dv = torch.empty_like(k), torch.empty_like(v)
-        P.bwd_in(_OP, prob, k, v, dstate, dk, dv)
+        dq, dk, dv = P.backward(prob, q, k, v, do, state)
         return dq, dk, dv, None, None, None, None
 
 

@@ -28,8 +28,7 @@ class SimpleLinearAttnFunction(torch.autograd.Function):
         if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
             raise ValueError("expected q, k of shape (B, H, L, K) and v of shape (B, H, L, V)")
         prob = _problem(q, v, scale)
-        state = P.fwd_state(_OP, prob, k, v)
-        o = P.fwd_out(_OP, prob, q, state, torch.empty_like(v))
+        o, state = P.forward(prob, q, k, v)
         ctx.save_for_backward(q, k, v, state)
         ctx.scale = scale
         return o
@@ -39,10 +38,7 @@ class SimpleLinearAttnFunction(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, state = ctx.saved_tensors
         prob = _problem(q, v, ctx.scale)
-        dq = torch.empty_like(q)
-        dstate = P.bwd_state(_OP, prob, q, do, state, dq)
-        dk, dv = torch.empty_like(k), torch.empty_like(v)
-        P.bwd_in(_OP, prob, k, v, dstate, dk, dv)
+        dq, dk, dv = P.backward(prob, q, k, v, do, state)
         return dq, dk, dv, None
 
 

@@ -110,6 +110,16 @@ int fbla_linear_attn_bwd_state(const fbla_problem *p, const void *q, const void 
 int fbla_linear_attn_bwd_in(const fbla_problem *p, const void *k, const void *v,
                             const float *dstate, void *dk, void *dv, fbla_stream_t stream);
 
+/* Both passes of one direction in a single call, for callers on one GPU (nothing to exchange
+ * between the passes): forward = fwd_state + fwd_out, backward = bwd_state + bwd_in.  They serve
+ * linear_attention, simple_la (normalize = 0) and varlen_linear_attention (cu_seqlens set) alike;
+ * `state` / `dstate` are outputs of the first pass and inputs of the second.                   */
+int fbla_linear_attn_fwd(const fbla_problem *p, const void *q, const void *k, const void *v, void *o,
+                         float *state, void *workspace, size_t workspace_bytes, fbla_stream_t stream);
+int fbla_linear_attn_bwd(const fbla_problem *p, const void *q, const void *k, const void *v,
+                         const void *d_o, const float *state, void *dq, void *dk, void *dv,
+                         float *dstate, void *workspace, size_t workspace_bytes, fbla_stream_t stream);
+
 /* Forward state pass for callers that cannot hand over a workspace and must not allocate: same
  * result as fbla_linear_attn_fwd_state, with the scratch in an 8 MiB device array inside the
  * library (held by every GPU that loads it).  No counterpart in the reference.  Refuses problems

@@ -255,3 +255,35 @@ def test_empty_and_errors():
                          torch.rand(1, 1, 4, 8, device="cuda"))
     with pytest.raises(RuntimeError):
         linear_attention(torch.rand(1, 1, 4, 8), torch.rand(1, 1, 4, 8), torch.rand(1, 1, 4, 8))
+
+
+def test_first_call_from_a_fresh_thread():
+    """A thread that has made no CUDA call of its own (an autograd worker) may be the first caller.
+
+    The tensor-map encoder is a driver call and needs a context bound to the thread; every buffer is
+    allocated here so that the worker's only CUDA work is the library's.
+    """
+    import threading
+    B, H, T, D = 2, 16, 1024, 64
+    q, k, v, d_o = (x.cuda() for x in make_inputs(21, (B, H, T, D), (B, H, T, D), torch.bfloat16))
+    prob = P.make_problem(q, batch=B, heads=H, seq_len=T, dk=D, dv=D, normalize=True, scale=D ** -0.5, eps=1e-6)
+    o, state = P.forward(prob, q, k, v)
+    ref = [x.cpu() for x in (o,) + tuple(P.backward(prob, q, k, v, d_o, state))]
+    del o, state        # their blocks go back to the caching allocator: the worker allocates nothing new
+    torch.cuda.synchronize()
+    out, err = [], []
+
+    def worker():
+        try:
+            o, state = P.forward(prob, q, k, v)
+            out.append((o,) + tuple(P.backward(prob, q, k, v, d_o, state)))
+            torch.cuda.synchronize()
+        except Exception as e:      # surfaced in the main thread below
+            err.append(e)
+
+    th = threading.Thread(target=worker)
+    th.start()
+    th.join()
+    assert not err, err
+    for got, want in zip(out[0], ref):
+        assert torch.equal(got.cpu(), want)
