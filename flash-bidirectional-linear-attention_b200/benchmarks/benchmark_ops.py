@@ -5,13 +5,30 @@ other operators.  Timing: CUDA events around back-to-back calls of the public AP
 ``--reps`` repetitions after warm-up; inputs are larger than L2 from T=4096 up at B=8.
 
     python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|simple_la|decoupled_la|varlen|pisa|all]
+                                       [--long] [--impl b200|reference [--ref-path DIR]]
+
+``--long`` adds ``simple_la`` at B4 H32 T262144 D128 (8.6 GB per tensor, about 70 GB on the device).
+``--impl reference`` times the reference's own Triton operators instead, imported from ``--ref-path``
+(an installed copy of the reference package; default ``baseline/_ref`` at the repository root), on the
+same GPU with the same inputs and timer.  Its piecewise operator has no backward: that column is nan.
 """
 import argparse
 import os
 import statistics
 import sys
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _early(flag, default):
+    return sys.argv[sys.argv.index(flag) + 1] if flag in sys.argv[:-1] else default
+
+
+IMPL = _early("--impl", "b200")
+if IMPL == "reference":
+    sys.path.insert(0, os.path.abspath(_early("--ref-path", os.path.join(os.path.dirname(_PKG), "baseline", "_ref"))))
+else:
+    sys.path.insert(0, _PKG)
 
 import torch
 import torch.nn.functional as F
@@ -51,8 +68,17 @@ def main():
     ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--op", default="all")
+    ap.add_argument("--long", action="store_true")
+    ap.add_argument("--lengths", default="1024,4096,16384,32768", help="T values of the linear_attn rows")
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--ref-path", default=None)
     args = ap.parse_args()
     B, H, D = args.batch, args.heads, args.dim
+    print(f"# impl={IMPL} package={os.path.dirname(os.path.dirname(sys.modules[linear_attention.__module__].__file__))}")
+    if IMPL == "reference":
+        import triton
+        if hasattr(triton, "set_allocator"):    # the piecewise kernel's tensor descriptors need scratch memory
+            triton.set_allocator(lambda size, align, stream: torch.empty(size, dtype=torch.int8, device="cuda"))
     dev, dt = "cuda", torch.bfloat16
     pos = lambda *s: (F.elu(torch.randn(*s, device=dev)) + 1).to(dt).requires_grad_()
     gau = lambda *s: torch.randn(*s, device=dev).to(dt).requires_grad_()
@@ -64,17 +90,19 @@ def main():
             make_out().backward(do)
         with torch.no_grad():
             f = timed(make_out, args.reps)
+        if do is None:
+            return f, float("nan")
         return f, timed(fb, args.reps)
 
     if args.op in ("all", "linear_attn"):
-        for T in (1024, 4096, 16384, 32768):
+        for T in [int(x) for x in args.lengths.split(",")]:
             q, k, v = pos(B, H, T, D), pos(B, H, T, D), gau(B, H, T, D)
             do = torch.randn_like(v)
             P = B * H * T * D * 2
             f, fb = both(lambda: linear_attention(q, k, v), (q, k, v), do)
             row("linear_attn", f"B{B} H{H} T{T} D{D}", f, fb, B * T, 4 * P, 11 * P)
     if args.op in ("all", "simple_la"):
-        for (b, h, T, d) in ((4, 32, 32768, 128), (B, H, 32768, D)):
+        for (b, h, T, d) in ((4, 32, 32768, 128), (B, H, 32768, D)) + (((4, 32, 262144, 128),) if args.long else ()):
             q, k, v = gau(b, h, T, d), gau(b, h, T, d), gau(b, h, T, d)
             do = torch.randn_like(v)
             P = b * h * T * d * 2
@@ -102,7 +130,7 @@ def main():
         q, k, v = gau(b, h, T, d), gau(b, h, T, d), gau(b, h, T, d)
         do = torch.randn_like(v)
         P = b * h * T * d * 2
-        f, fb = both(lambda: piecewise_sparse_attention(q, k, v), (q, k, v), do)
+        f, fb = both(lambda: piecewise_sparse_attention(q, k, v), (q, k, v), None if IMPL == "reference" else do)
         row("pisa", f"B{b} H{h} T{T} D{d} bs64 d0.1", f, fb, b * T, 7 * P, 7 * P)
 
 

@@ -14,6 +14,7 @@
 
 #include "fbla_common.cuh"
 #include "pisa_mma.cuh"
+#include "pisa_mma_bwd.cuh"
 
 namespace fbla {
 namespace {
@@ -738,6 +739,64 @@ size_t bwd_kv_smem_bytes(const PisaParams& p) {
 }  // namespace
 }  // namespace fbla
 
+namespace fbla {
+namespace {
+
+bool pisa_mma_shape(const PisaArgs& a) {
+    return a.dtype != FBLA_F32 && a.kp.bs == 64 && a.kp.dk == a.kp.dv && (a.kp.dk == 64 || a.kp.dk == 128) &&
+           !g_pisa_force_generic;
+}
+
+size_t round64(size_t n) { return (n + 63) / 64 * 64; }
+
+// Scratch layout (fp32 elements, every part starting on a 256-byte boundary):
+//   dkc [BH,NT,dk] | dvc [BH,NT,dv] | dh [BH,dk,dv] | drow [BH,T]
+//   tensor-core path only: | dr [BH,T,dv] 16-bit | workspace of the state pass that forms dh
+struct BwdScratch {
+    size_t dkc, dvc, dh, drow, dr, ws, total;
+    int64_t ws_bytes;
+    fbla_problem state_problem;
+};
+
+BwdScratch bwd_scratch(const PisaArgs& a) {
+    const PisaParams& kp = a.kp;
+    BwdScratch s{};
+    s.dkc = 0;
+    s.dvc = s.dkc + round64((size_t)a.bh * kp.nt * kp.dk);
+    s.dh = s.dvc + round64((size_t)a.bh * kp.nt * kp.dv);
+    s.drow = s.dh + round64((size_t)a.bh * kp.dk * kp.dv);
+    s.dr = s.drow + round64((size_t)a.bh * kp.T);
+    s.ws = s.dr;
+    s.total = s.dr;
+    s.ws_bytes = 0;
+    if (pisa_mma_shape(a)) {
+        fbla_problem& sp = s.state_problem;
+        sp = fbla_problem{};
+        sp.dtype = a.dtype;
+        sp.batch = a.bh / kp.heads;
+        sp.heads = kp.heads;
+        sp.dk = kp.dk;
+        sp.dv = kp.dv;
+        sp.seq_len = kp.T;
+        sp.scale = 1.f;
+        sp.normalize = 0;
+        s.ws_bytes = fbla_workspace_bytes(&sp);
+        if (s.ws_bytes < 0) s.ws_bytes = 0;
+        s.ws = s.dr + round64(((size_t)a.bh * kp.T * kp.dv + 1) / 2);
+        s.total = s.ws + round64(((size_t)s.ws_bytes + 3) / 4);
+    }
+    return s;
+}
+
+}  // namespace
+}  // namespace fbla
+
+extern "C" int64_t fbla_pisa_bwd_scratch_floats(const fbla_pisa_problem* p) {
+    fbla::PisaArgs a;
+    if (fbla::resolve_pisa(p, &a)) return -1;
+    return (int64_t)fbla::bwd_scratch(a).total;
+}
+
 extern "C" int fbla_pisa_bwd(const fbla_pisa_problem* p, const void* q, const void* k, const void* v, const void* o,
                              const void* d_o, const float* kc, const float* vc, const float* h, const int32_t* indices,
                              const float* row_stats, void* dq, void* dk, void* dv, float* scratch,
@@ -747,23 +806,73 @@ extern "C" int fbla_pisa_bwd(const fbla_pisa_problem* p, const void* q, const vo
     if (!q || !k || !v || !o || !d_o || !kc || !vc || !h || !indices || !row_stats || !dq || !dk || !dv || !scratch)
         return fbla::api_fail(FBLA_ERR_INVALID, "a tensor pointer is NULL");
     const fbla::PisaParams& kp = a.kp;
-    // scratch: dkc [BH,NT,K] | dvc [BH,NT,V] | dh [BH,K,V] (zeroed here, filled with atomics) | drow [BH,T]
-    const size_t n_dkc = (size_t)a.bh * kp.nt * kp.dk, n_dvc = (size_t)a.bh * kp.nt * kp.dv;
-    const size_t n_dh = (size_t)a.bh * kp.dk * kp.dv, n_row = (size_t)a.bh * kp.T;
-    if (scratch_floats < n_dkc + n_dvc + n_dh + n_row)
-        return fbla::api_fail(FBLA_ERR_WORKSPACE, "scratch of %lld floats needed, %lld given",
-                              (long long)(n_dkc + n_dvc + n_dh + n_row), (long long)scratch_floats);
-    float* dkc = scratch;
-    float* dvc = dkc + n_dkc;
-    float* dh = dvc + n_dvc;
-    float* drow = dh + n_dh;
+    const fbla::BwdScratch lay = fbla::bwd_scratch(a);
+    if (scratch_floats < lay.total)
+        return fbla::api_fail(FBLA_ERR_WORKSPACE, "scratch of %lld floats needed, %lld given", (long long)lay.total,
+                              (long long)scratch_floats);
+    float* dkc = scratch + lay.dkc;
+    float* dvc = scratch + lay.dvc;
+    float* dh = scratch + lay.dh;
+    float* drow = scratch + lay.drow;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * (n_dkc + n_dvc + n_dh), st);
+    dim3 grid(kp.nt, a.bh);
+    const uintptr_t all_ptrs = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                               reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o) | reinterpret_cast<uintptr_t>(kc) |
+                               reinterpret_cast<uintptr_t>(vc) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dq) |
+                               reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) |
+                               reinterpret_cast<uintptr_t>(scratch) | reinterpret_cast<uintptr_t>(row_stats);
+    if (fbla::pisa_mma_shape(a) && (all_ptrs & 15u) == 0) {
+        // dh comes from the state pass, which overwrites it: only dkc, dvc are accumulated into
+        cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * lay.dh, st);
+        if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "memset: %s", cudaGetErrorString(e));
+        void* dr = scratch + lay.dr;
+        void* ws = scratch + lay.ws;
+        fbla::pisa_mma::Params mp{kp.heads, kp.ns, kp.nt, kp.T, kp.scale};
+        const bool bf = a.dtype == FBLA_BF16;
+        auto run_q = [&](auto kern, size_t smem) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess)
+                kern<<<grid, fbla::pisa_mma::kThreads, smem, st>>>(mp, q, k, v, o, d_o, kc, vc, h, indices, row_stats, dq,
+                                                                  dr, dkc, dvc, drow);
+        };
+        auto run_kv = [&](auto kern, size_t smem) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess)
+                kern<<<grid, fbla::pisa_mma::kThreads, smem, st>>>(mp, q, k, v, d_o, kc, vc, indices, row_stats, drow, dkc,
+                                                                  dvc, dh, dk, dv);
+        };
+        if (kp.dk == 64) {
+            const size_t smem = fbla::pisa_mma::bwd_q_smem_bytes<64>(kp.nt);
+            if (bf) run_q(fbla::pisa_mma::pisa_bwd_q_mma_kernel<64, true>, smem);
+            else run_q(fbla::pisa_mma::pisa_bwd_q_mma_kernel<64, false>, smem);
+        } else {
+            const size_t smem = fbla::pisa_mma::bwd_q_smem_bytes<128>(kp.nt);
+            if (bf) run_q(fbla::pisa_mma::pisa_bwd_q_mma_kernel<128, true>, smem);
+            else run_q(fbla::pisa_mma::pisa_bwd_q_mma_kernel<128, false>, smem);
+        }
+        fbla::note_launches(1);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "backward query kernel: %s", cudaGetErrorString(e));
+        // dh = q^T dr
+        if (int rc = fbla_simple_la_fwd_state(&lay.state_problem, q, dr, dh, ws, (size_t)lay.ws_bytes, stream)) return rc;
+        if (kp.dk == 64) {
+            const size_t smem = fbla::pisa_mma::bwd_kv_smem_bytes<64>(kp.nt);
+            if (bf) run_kv(fbla::pisa_mma::pisa_bwd_kv_mma_kernel<64, true>, smem);
+            else run_kv(fbla::pisa_mma::pisa_bwd_kv_mma_kernel<64, false>, smem);
+        } else {
+            const size_t smem = fbla::pisa_mma::bwd_kv_smem_bytes<128>(kp.nt);
+            if (bf) run_kv(fbla::pisa_mma::pisa_bwd_kv_mma_kernel<128, true>, smem);
+            else run_kv(fbla::pisa_mma::pisa_bwd_kv_mma_kernel<128, false>, smem);
+        }
+        fbla::note_launches(1);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "backward key kernel: %s", cudaGetErrorString(e));
+    }
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * lay.drow, st);
     if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "memset: %s", cudaGetErrorString(e));
     const size_t smem1 = fbla::bwd_q_smem_bytes(kp), smem2 = fbla::bwd_kv_smem_bytes(kp);
     if (smem1 > 227 * 1024 || smem2 > 227 * 1024)
         return fbla::api_fail(FBLA_ERR_UNSUPPORTED, "block_size, dk, dv too large for the backward kernels");
-    dim3 grid(kp.nt, a.bh);
     PISA_BY_DTYPE(a.dtype, {
         auto k1 = fbla::pisa_bwd_q_kernel<T>;
         auto k2 = fbla::pisa_bwd_kv_kernel<T>;

@@ -220,7 +220,7 @@ pisa_fwd_mma_kernel(Params p, const void* __restrict__ q, const void* __restrict
         __syncthreads();
         const int cb = idx[n];
         const int bos = cb * kBS;
-        const int nvalid = max(0, min(kBS, p.T - bos));
+        const int nvalid = (cb < 0 || cb >= p.nt) ? 0 : min(kBS, p.T - bos);    // a bad index selects nothing
         load_tile16<D>(ks, static_cast<const uint8_t*>(k) + (base_row + bos) * D * 2, nvalid);
         load_tile16<D>(vs, static_cast<const uint8_t*>(v) + (base_row + bos) * D * 2, nvalid);
         __syncthreads();

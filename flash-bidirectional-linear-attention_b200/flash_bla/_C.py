@@ -85,7 +85,8 @@ def exported_symbols():
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
     names += ["fbla_linear_attn_fwd", "fbla_linear_attn_bwd"]
     names.append("fbla_linear_attn_fwd_state_noalloc")
-    names += ["fbla_pisa_block_stats", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd"]
+    names += ["fbla_pisa_block_stats", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd",
+              "fbla_pisa_bwd_scratch_floats"]
     return names
 
 
@@ -126,6 +127,8 @@ def lib():
             f = getattr(L, name)
             f.restype = ctypes.c_int
             f.argtypes = [_PP] + [_vp] * n_ptr          # tensor pointers, then the stream
+        L.fbla_pisa_bwd_scratch_floats.restype = ctypes.c_int64
+        L.fbla_pisa_bwd_scratch_floats.argtypes = [_PP]
         L.fbla_pisa_bwd.restype = ctypes.c_int
         L.fbla_pisa_bwd.argtypes = [_PP] + [_vp] * 14 + [_sz, _vp]   # 14 tensors, scratch size, stream
         _lib = L

@@ -119,7 +119,9 @@ def attention_backward(q, k, v, o, do, kc, vc, h, indices, stats, block_size, sc
     nt = idx.shape[-2]
     prob = _problem(q, v, block_size, idx.shape[-1], scale)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    n = B * H * (nt * K + nt * V + K * V + T)
+    n = _C.lib().fbla_pisa_bwd_scratch_floats(ctypes.byref(prob))
+    if n < 0:
+        _C.check(1)
     scratch = torch.empty(n, dtype=torch.float32, device=q.device)
     with torch.cuda.device_of(q):
         _C.check(_C.lib().fbla_pisa_bwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),

@@ -213,7 +213,10 @@ int fbla_pisa_fwd(const fbla_pisa_problem *p, const void *q, const void *k, cons
 /* Backward of fbla_pisa_fwd with the block selection held constant; gradients flow through the
  * block statistics as well.  The reference has no backward for this operator (no counterpart).
  * o, d_o: forward output and its gradient; row_stats: as written by fbla_pisa_fwd.
- * scratch: fp32, at least batch*heads*(NT*dk + NT*dv + dk*dv + seq_len) elements.            */
+ * scratch: fp32, 256-byte aligned, at least fbla_pisa_bwd_scratch_floats() elements (holds the
+ * gradients of the block statistics, the per-row terms and, on the tensor-core path, the rows
+ * from which the gradient of h is formed); contents are undefined afterwards.                */
+int64_t fbla_pisa_bwd_scratch_floats(const fbla_pisa_problem *p);
 int fbla_pisa_bwd(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,
                   const void *o, const void *d_o, const float *kc, const float *vc, const float *h,
                   const int32_t *indices, const float *row_stats, void *dq, void *dk, void *dv,

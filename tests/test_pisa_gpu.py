@@ -68,10 +68,14 @@ BWD_CASES = [
     (1, 2, 150, 32, 24, 32, 0.25),     # ragged last block, dk != dv
     (2, 1, 320, 64, 64, 64, 0.2),
     (1, 1, 640, 128, 128, 64, 0.1),
+    (1, 2, 300, 64, 64, 64, 0.2),      # tensor-core shapes with a ragged last block
+    (1, 2, 1000, 128, 128, 64, 0.1),
+    (1, 1, 4608, 128, 128, 64, 0.1),   # more than 64 blocks: two chunks of block statistics
+    (1, 1, 4500, 64, 64, 64, 0.05),
 ]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("case", BWD_CASES)
 def test_backward_matches_oracle(case, dtype):
     from flash_bla.ops.piecewise_attn.kernel import attention_backward
