@@ -253,7 +253,7 @@ def run_ours(args):
     total_gbs = sum(algo_bytes.values()) / (sum(acc.values()) * 1e-3) / 1e9
     # DRAM bytes (read + write) per launch from the ncu capture summarised in
     # profiles/ncu_linear_attn_bf16_b8h16d64.md (taken at T = 8192, proportional to T)
-    ncu_traffic_at_8192 = {"fwd_state": 276.3e6, "fwd_out": 220.5e6, "bwd_state": 377.9e6, "bwd_in": 493.5e6}
+    ncu_traffic_at_8192 = {"fwd_state": 273.5e6, "fwd_out": 220.6e6, "bwd_state": 377.3e6, "bwd_in": 490.0e6}
     traffic = ncu_traffic_at_8192[dom] * (T / 8192.0) if (B, H, D) == (8, 16, 64) else None
     roofline = {"bound": "hbm", "kernel": dom, "achieved": passes[dom]["gbs"], "peak": peak, "unit": "GB/s",
                 "frac": passes[dom]["gbs"] / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
