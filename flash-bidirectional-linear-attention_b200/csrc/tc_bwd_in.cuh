@@ -69,7 +69,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
     using Cfg = BwdInCfg<DK, DV, MODE>;
     using Map = TileMap<VARLEN>;
     // packed layout: rows are strided and tiles may end inside the next sequence -> guarded stores
-    constexpr bool kDirectOut = Cfg::kDirect || VARLEN;
+    constexpr bool kDirectOut = Cfg::kDirect;      // no staged tiles at all
     constexpr int NS = Cfg::kStages;
     constexpr int NO = Cfg::kOutBufs;
     extern __shared__ uint8_t smem_raw[];
@@ -258,6 +258,9 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             }
             uint8_t* ob = outbuf + ob_i * Cfg::kOutBytes;
             const bool tok_ok = row < t.valid;
+            // packed layout: only full tiles go through the staged TMA store; a tile that ends inside the
+            // next sequence leaves in row-guarded 32-byte stores
+            const bool direct = kDirectOut || (VARLEN && t.valid != kTileTokens);
             const size_t grow = (size_t)(t.row0 + (long long)row * t.row_stride);   // this thread's row in the (rows, D) view
             // dk (or dk_rope) tile
 #pragma unroll
@@ -278,7 +281,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     w4[j].z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
                     w4[j].w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
                 }
-                if (kDirectOut) {
+                if (direct) {
                     if (tok_ok) {
                         uint8_t* dst = static_cast<uint8_t*>(p.out_a) + (grow * DK + c0) * 2;
                         ptx::st_global_32B(dst, w4[0], w4[1]);
@@ -307,7 +310,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                     w4[j].z = pack2(v[8 * j + 4], v[8 * j + 5], BF16);
                     w4[j].w = pack2(v[8 * j + 6], v[8 * j + 7], BF16);
                 }
-                if (kDirectOut) {
+                if (direct) {
                     if (tok_ok) {
                         uint8_t* dst = static_cast<uint8_t*>(p.out_b) + (grow * DV + c0) * 2;
                         ptx::st_global_32B(dst, w4[0], w4[1]);
@@ -327,17 +330,19 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             ptx::mbar_arrive(&out_written[ob_i]);
             if (!kDirectOut && issuer) {
                 if (!ptx::mbar_wait(&out_written[ob_i], pho, ab, 423)) break;
-                const int t0 = tile * kTileTokens;
+                if (!direct) {
 #pragma unroll
-                for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_store_3d(&tm_dkr, ob + b * kBlockBytes, b * 64, t0, unit);
+                    for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_store_3d(&tm_dkr, ob + b * kBlockBytes, b * 64, t.c1, t.c2);
 #pragma unroll
-                for (int b = 0; b < Cfg::kVB; ++b)
-                    ptx::tma_store_3d(&tm_dv, ob + (Cfg::kKB + b) * kBlockBytes, b * 64, t0, unit);
-                if (MODE == kDecoupled) {
+                    for (int b = 0; b < Cfg::kVB; ++b)
+                        ptx::tma_store_3d(&tm_dv, ob + (Cfg::kKB + b) * kBlockBytes, b * 64, t.c1, t.c2);
+                    if (MODE == kDecoupled) {
 #pragma unroll
-                    for (int b = 0; b < Cfg::kKB; ++b) ptx::tma_store_3d(&tm_dk, constbuf + b * kBlockBytes, b * 64, t0, unit);
+                        for (int b = 0; b < Cfg::kKB; ++b)
+                            ptx::tma_store_3d(&tm_dk, constbuf + b * kBlockBytes, b * 64, t.c1, t.c2);
+                    }
                 }
-                ptx::tma_store_commit();
+                ptx::tma_store_commit();        // an empty group keeps the wait_read bookkeeping uniform
             }
         }
         if (!kDirectOut && issuer) ptx::tma_store_wait_all<0>();

@@ -445,17 +445,16 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                 rz = 1.f / (zc[0] + zc[1] + p.eps);
             }
             // the staged tile of two tiles ago must have been read by its store
-            if (!VARLEN) {
-                if (issuer) {
-                    ptx::tma_store_wait_read<1>();
-                    ptx::mbar_arrive(&out_free[a]);
-                }
-                if (!ptx::mbar_wait(&out_free[a], ph2, ab, 222)) break;
+            if (issuer) {
+                ptx::tma_store_wait_read<1>();
+                ptx::mbar_arrive(&out_free[a]);
             }
-            // packed layout: rows are heads*dv apart and a tile may end inside the next sequence, so
-            // the output leaves in guarded 32-byte stores instead of a staged tile
+            if (!ptx::mbar_wait(&out_free[a], ph2, ab, 222)) break;
+            // packed layout: a tile may end inside the next sequence; such a tile leaves in row-guarded
+            // 32-byte stores, every full tile as a staged tile through the TMA store like the fixed layout
             uint8_t* orow = static_cast<uint8_t*>(p.out_a) + (size_t)(t.row0 + (long long)row * t.row_stride) * DV * 2;
             const bool row_ok = row < t.valid;
+            const bool staged = !VARLEN || t.valid == kTileTokens;
             uint8_t* ob = outbuf + a * Cfg::kOutBytes;
 #pragma unroll
             for (int c0 = 0; c0 < DV; c0 += 32) {
@@ -480,10 +479,10 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                     w.z = pack2(v[8 * j + 4] * rz, v[8 * j + 5] * rz, BF16);
                     w.w = pack2(v[8 * j + 6] * rz, v[8 * j + 7] * rz, BF16);
                     const int chunk = ((c0 & 63) >> 3) + j;
-                    if (!VARLEN) *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
+                    if (staged) *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = w;
                     keep[j] = w;
                 }
-                if (VARLEN && row_ok) {
+                if (!staged && row_ok) {
                     ptx::st_global_32B(orow + c0 * 2, keep[0], keep[1]);
                     ptx::st_global_32B(orow + c0 * 2 + 32, keep[2], keep[3]);
                 }
@@ -492,15 +491,16 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
             ptx::mbar_arrive(&tempty[a]);
             ptx::fence_proxy_async_smem();
             ptx::mbar_arrive(&out_written[a]);
-            if (!VARLEN && issuer) {
+            if (issuer) {
                 if (!ptx::mbar_wait(&out_written[a], ph2, ab, 223)) break;
+                if (staged) {
 #pragma unroll
-                for (int b = 0; b < Cfg::kVB; ++b)
-                    ptx::tma_store_3d(&tm_o, ob + b * kBlockBytes, b * 64, tile * kTileTokens, unit);
-                ptx::tma_store_commit();
+                    for (int b = 0; b < Cfg::kVB; ++b) ptx::tma_store_3d(&tm_o, ob + b * kBlockBytes, b * 64, t.c1, t.c2);
+                }
+                ptx::tma_store_commit();        // an empty group keeps the wait_read<1> bookkeeping uniform
             }
         }
-        if (!VARLEN && issuer) ptx::tma_store_wait_all<0>();
+        if (issuer) ptx::tma_store_wait_all<0>();
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
