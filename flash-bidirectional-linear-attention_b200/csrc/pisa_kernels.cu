@@ -227,7 +227,7 @@ pisa_fwd_kernel(PisaParams p, const T* __restrict__ q, const T* __restrict__ k, 
             }
         }
         if (row_stats != nullptr && lane == 0)
-            *reinterpret_cast<float4*>(row_stats + row * 4) = make_float4(m[ri], den, g[ri], 0.f);
+            *reinterpret_cast<float4*>(row_stats + row * 4) = make_float4(m[ri], den, g[ri], 1.f / den);
     }
 }
 

@@ -72,6 +72,24 @@ __device__ __forceinline__ void load_tile16(uint8_t* tile, const void* src, int 
         *reinterpret_cast<uint4*>(tile + tile_off<D>(r, c)) = v;
     }
 }
+// Asynchronous variant (cp.async, 16 bytes per request): the caller commits the group and waits for it
+// before the tile is read.  Rows past `nrows` are zeroed with ordinary stores.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+template <int D>
+__device__ __forceinline__ void load_tile16_async(uint8_t* tile, const void* src, int nrows) {
+    constexpr int CH = D / 8;
+    for (int i = threadIdx.x; i < kBS * CH; i += kThreads) {
+        const int r = i / CH, c = i - r * CH;
+        if (r < nrows)
+            cp_async16(smem_addr(tile) + tile_off<D>(r, c), static_cast<const uint8_t*>(src) + (size_t)r * D * 2 + c * 16);
+        else
+            *reinterpret_cast<uint4*>(tile + tile_off<D>(r, c)) = make_uint4(0, 0, 0, 0);
+    }
+}
 // Same from fp32 rows (block statistics, first-order state), converting to the 16-bit type.
 template <int D, bool BF16>
 __device__ __forceinline__ void load_tile32(uint8_t* tile, const float* src, int nrows, int tile_rows) {
@@ -96,10 +114,13 @@ pisa_fwd_mma_kernel(Params p, const void* __restrict__ q, const void* __restrict
     constexpr int NT8 = D / 8;        // n-tiles of the output
     constexpr int KS = D / 16;        // k-steps over the feature dim
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kTile = kBS * D * 2;
     uint8_t* qs = smem;                         // [64][D]   queries; reused to stage the output
-    uint8_t* ks = qs + kBS * D * 2;             // [64][D]   keys / block means      } together [D][D] for h
-    uint8_t* vs = ks + kBS * D * 2;             // [64][D]   values / block sums     }
-    unsigned char* sel = vs + kBS * D * 2;      // [nt] selected?
+    uint8_t* kv0 = qs + kTile;                  // two (keys, values) buffer pairs: the selected blocks are
+    uint8_t* kv1 = kv0 + 2 * kTile;             // prefetched with cp.async one block ahead
+    uint8_t* ks = kv0;                          // [64][D]   keys / block means      } together [D][D] for h
+    uint8_t* vs = ks + kTile;                   // [64][D]   values / block sums     }
+    unsigned char* sel = kv1 + 2 * kTile;       // [nt] selected?
 
     const int i_blk = blockIdx.x, bh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,10 +163,12 @@ pisa_fwd_mma_kernel(Params p, const void* __restrict__ q, const void* __restrict
         for (int n = 0; n < 8; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+        // groups of 16 keys past `nvalid` are skipped (their scores stay 0 and are masked below)
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk) {
 #pragma unroll
             for (int n2 = 0; n2 < 4; ++n2) {        // two 8-key tiles per ldmatrix.x4
+                if (n2 * 16 >= nvalid) continue;
                 uint32_t b[4];
                 const int key = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
                 ldsm_x4(b, smem_addr(ks) + tile_off<D>(key, 2 * kk + ((lane >> 3) & 1)));
@@ -204,6 +227,7 @@ pisa_fwd_mma_kernel(Params p, const void* __restrict__ q, const void* __restrict
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
+            if (kk * 16 >= nvalid) continue;        // weights of these keys are all zero
 #pragma unroll
             for (int n2 = 0; n2 < NT8 / 2; ++n2) {
                 uint32_t b[4];
@@ -215,17 +239,30 @@ pisa_fwd_mma_kernel(Params p, const void* __restrict__ q, const void* __restrict
         }
     };
 
-    // ---- phase 1: exact attention on the selected key blocks ----
-    for (int n = 0; n < p.ns; ++n) {
-        __syncthreads();
+    // ---- phase 1: exact attention on the selected key blocks (block n+1 in flight during block n) ----
+    auto valid_rows = [&](int n) {
         const int cb = idx[n];
-        const int bos = cb * kBS;
-        const int nvalid = (cb < 0 || cb >= p.nt) ? 0 : min(kBS, p.T - bos);    // a bad index selects nothing
-        load_tile16<D>(ks, static_cast<const uint8_t*>(k) + (base_row + bos) * D * 2, nvalid);
-        load_tile16<D>(vs, static_cast<const uint8_t*>(v) + (base_row + bos) * D * 2, nvalid);
-        __syncthreads();
-        block(nvalid, false, 0);
+        return (cb < 0 || cb >= p.nt) ? 0 : min(kBS, p.T - cb * kBS);    // a bad index selects nothing
+    };
+    auto prefetch = [&](int n) {
+        uint8_t* buf = (n & 1) ? kv1 : kv0;
+        const int nvalid = valid_rows(n);
+        const size_t off = (base_row + (size_t)(nvalid ? idx[n] : 0) * kBS) * D * 2;
+        load_tile16_async<D>(buf, static_cast<const uint8_t*>(k) + off, nvalid);
+        load_tile16_async<D>(buf + kTile, static_cast<const uint8_t*>(v) + off, nvalid);
+        cp_async_commit();
+    };
+    if (p.ns > 0) prefetch(0);
+    for (int n = 0; n < p.ns; ++n) {
+        cp_async_wait_all();
+        __syncthreads();            // block n has landed; every warp is done with block n-1
+        if (n + 1 < p.ns) prefetch(n + 1);
+        ks = (n & 1) ? kv1 : kv0;
+        vs = ks + kTile;
+        block(valid_rows(n), false, 0);
     }
+    ks = kv0;
+    vs = ks + kTile;
     // ---- phase 2: zeroth order on the unselected blocks, 64 blocks at a time ----
     for (int c0 = 0; c0 < p.nt; c0 += kBS) {
         __syncthreads();
@@ -299,7 +336,7 @@ pisa_fwd_mma_kernel(Params p, const void* __restrict__ q, const void* __restrict
                 const int row = r_lo + 8 * r;
                 if (row < nrows)
                     *reinterpret_cast<float4*>(row_stats + (base_row + t0 + row) * 4) =
-                        make_float4(m_run[r], l_row[r] + g_row[r], g_row[r], 0.f);
+                        make_float4(m_run[r], l_row[r] + g_row[r], g_row[r], rden[r]);
             }
         }
     }
@@ -315,7 +352,7 @@ pisa_fwd_mma_kernel(Params p, const void* __restrict__ q, const void* __restrict
 }
 
 template <int D>
-constexpr size_t smem_bytes(int nt) { return (size_t)3 * kBS * D * 2 + (size_t)nt + 16; }
+constexpr size_t smem_bytes(int nt) { return (size_t)5 * kBS * D * 2 + (size_t)nt + 16; }
 
 }  // namespace pisa_mma
 }  // namespace fbla

@@ -59,10 +59,15 @@ template <int D>
 constexpr int scratch_tile_bytes() { return kBS * D * 2 > 2 * kBS * 64 * 2 ? kBS * D * 2 : 2 * kBS * 64 * 2; }
 template <int D>
 constexpr size_t bwd_q_smem_bytes(int nt) {
-    return (size_t)4 * kBS * D * 2 + scratch_tile_bytes<D>() + (size_t)nt + 16;
+    return (size_t)6 * kBS * D * 2 + scratch_tile_bytes<D>() + (size_t)nt + 16;
 }
 template <int D>
-constexpr size_t bwd_kv_smem_bytes(int nt) { return (size_t)4 * kBS * D * 2 + kBS * 16 + (size_t)nt + 16; }
+constexpr size_t bwd_kv_smem_bytes(int nt) {
+    return (size_t)6 * kBS * D * 2 + 2 * kBS * (16 + 4) + (size_t)((nt + 3) / 4 * 4) + (size_t)nt * 4 + 32;
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
 
 // ------------------------------------------------------------------------------------------------
 template <int D, bool BF16>
@@ -80,7 +85,9 @@ pisa_bwd_q_mma_kernel(Params p, const void* __restrict__ q, const void* __restri
     uint8_t* ks = dos + kTile;          // [64][D] keys / block means      } together [D][D] for h
     uint8_t* vs = ks + kTile;           // [64][D] values / block sums     }
     uint8_t* ts = vs + kTile;           // [64][D] o, then dr; later two [64][64] tiles: scale*da and pi/den
-    unsigned char* sel = ts + scratch_tile_bytes<D>();
+    uint8_t* kvb = ts + scratch_tile_bytes<D>();    // second (keys, values) pair: selected blocks are prefetched
+    unsigned char* sel = kvb + 2 * kTile;
+    uint8_t* const kva = ks;
 
     const int i_blk = blockIdx.x, bh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -98,6 +105,20 @@ pisa_bwd_q_mma_kernel(Params p, const void* __restrict__ q, const void* __restri
     load_tile16<D>(ts, static_cast<const uint8_t*>(o) + tile_g, nrows);
     load_square32<D, BF16>(ks, h + (size_t)bh * D * D);
     for (int i = threadIdx.x; i < p.nt; i += kThreads) sel[i] = 0;
+    // selected block n is loaded with cp.async while block n-1 is processed; even n -> kvb, odd n -> (ks, vs)
+    auto valid_rows = [&](int n) {
+        const int cb = idx[n];
+        return (cb < 0 || cb >= p.nt) ? 0 : min(kBS, p.T - cb * kBS);    // a bad index selects nothing
+    };
+    auto prefetch = [&](int n) {
+        uint8_t* buf = (n & 1) ? kva : kvb;
+        const int nvalid = valid_rows(n);
+        const size_t off = (base_row + (size_t)(nvalid ? idx[n] : 0) * kBS) * D * 2;
+        load_tile16_async<D>(buf, static_cast<const uint8_t*>(k) + off, nvalid);
+        load_tile16_async<D>(buf + kTile, static_cast<const uint8_t*>(v) + off, nvalid);
+        cp_async_commit();
+    };
+    if (p.ns > 0) prefetch(0);
     __syncthreads();
     for (int i = threadIdx.x; i < p.ns; i += kThreads) {
         const int c = idx[i];
@@ -283,16 +304,17 @@ pisa_bwd_q_mma_kernel(Params p, const void* __restrict__ q, const void* __restri
 
     // ---- exact part ----
     for (int n = 0; n < p.ns; ++n) {
-        __syncthreads();
-        const int cb = idx[n];
-        const int bos = cb * kBS;
-        const int nvalid = (cb < 0 || cb >= p.nt) ? 0 : min(kBS, p.T - bos);    // a bad index selects nothing
-        load_tile16<D>(ks, static_cast<const uint8_t*>(k) + (base_row + bos) * D * 2, nvalid);
-        load_tile16<D>(vs, static_cast<const uint8_t*>(v) + (base_row + bos) * D * 2, nvalid);
-        __syncthreads();
+        cp_async_wait_all();
+        __syncthreads();            // block n has landed; every warp is done with block n-1 (and with h)
+        if (n + 1 < p.ns) prefetch(n + 1);
+        ks = (n & 1) ? kva : kvb;
+        vs = ks + kTile;
+        const int nvalid = valid_rows(n);
         half_block(0, nvalid, false, 0);
         if (nvalid > 32) half_block(32, nvalid, false, 0);
     }
+    ks = kva;
+    vs = ks + kTile;
     // ---- zeroth-order part, 64 blocks at a time; dkc, dvc of the chunk ----
     for (int c0 = 0; c0 < p.nt; c0 += kBS) {
         __syncthreads();
@@ -301,7 +323,7 @@ pisa_bwd_q_mma_kernel(Params p, const void* __restrict__ q, const void* __restri
         load_tile32<D, BF16>(vs, vc + ((size_t)bh * p.nt + c0) * D, nvalid, kBS);
         __syncthreads();
         half_block(0, nvalid, true, c0);
-        half_block(32, nvalid, true, c0);
+        if (nvalid > 32) half_block(32, nvalid, true, c0);     // columns >= 32 are read below only by warps 2, 3
         __syncthreads();
         // warp w: blocks c0 + 16 w .. + 15.   dkc_c += sum_rows das[row][c] q[row],  dvc_c += sum_rows pis[row][c] dO[row]
         if (warp * 16 < nvalid) {
@@ -371,10 +393,13 @@ pisa_bwd_kv_mma_kernel(Params p, const void* __restrict__ q, const void* __restr
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ks = smem;                 // [64][D] keys of this block; later k - kc, then dk
     uint8_t* vs = ks + kTile;           // [64][D] values;             later v - vc/len, then dv
-    uint8_t* qs = vs + kTile;           // [64][D] q of one query block      } together [D][D] for dh
-    uint8_t* dos = qs + kTile;          // [64][D] dO of one query block     }
-    float4* rst = reinterpret_cast<float4*>(dos + kTile);    // [64] (m, 1/den, dD, -) of the query rows
-    unsigned char* hit = reinterpret_cast<unsigned char*>(rst + kBS);
+    uint8_t* qd0 = vs + kTile;          // two (q, dO) tile pairs of the visiting query blocks, filled one block
+    uint8_t* qd1 = qd0 + 2 * kTile;     // ahead with cp.async; qd0 later holds dh as a [D][D] tile
+    float4* rst = reinterpret_cast<float4*>(qd1 + 2 * kTile);    // [2][64] (m, den, g, 1/den) of the query rows
+    float* dds = reinterpret_cast<float*>(rst + 2 * kBS);        // [2][64] dD of the query rows
+    int* hlist = reinterpret_cast<int*>(dds + 2 * kBS);          // query blocks that selected this key block
+    unsigned char* hit = reinterpret_cast<unsigned char*>(hlist + p.nt);
+    __shared__ int n_hit;
 
     const int c_blk = blockIdx.x, bh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -393,6 +418,15 @@ pisa_bwd_kv_mma_kernel(Params p, const void* __restrict__ q, const void* __restr
         for (int n = 0; n < p.ns; ++n) any |= (idx[n] == c_blk);
         hit[i] = any ? 1 : 0;
     }
+    __syncthreads();
+    if (threadIdx.x == 0) {             // in block order: the accumulation order is fixed
+        int n = 0;
+        for (int i = 0; i < p.nt; ++i)
+            if (hit[i]) hlist[n++] = i;
+        n_hit = n;
+    }
+    __syncthreads();
+    const int nh = n_hit;
     float dka[NT8][4], dva[NT8][4];
 #pragma unroll
     for (int n = 0; n < NT8; ++n)
@@ -400,22 +434,35 @@ pisa_bwd_kv_mma_kernel(Params p, const void* __restrict__ q, const void* __restr
         for (int e = 0; e < 4; ++e) { dka[n][e] = 0.f; dva[n][e] = 0.f; }
     const int arow = warp * 16 + (lane & 15);       // A-fragment row of this lane (key)
 
-    for (int i_blk = 0; i_blk < p.nt; ++i_blk) {
-        __syncthreads();                            // also orders the hit[] writes before the first read
-        if (!hit[i_blk]) continue;                  // uniform over the CTA
-        const int t0 = i_blk * kBS;
+    auto prefetch = [&](int j) {
+        const int t0 = hlist[j] * kBS;
         const int nrows = min(kBS, p.T - t0);
-        load_tile16<D>(qs, static_cast<const uint8_t*>(q) + (base_row + t0) * D * 2, nrows);
-        load_tile16<D>(dos, static_cast<const uint8_t*>(d_o) + (base_row + t0) * D * 2, nrows);
+        uint8_t* buf = (j & 1) ? qd1 : qd0;
+        load_tile16_async<D>(buf, static_cast<const uint8_t*>(q) + (base_row + t0) * D * 2, nrows);
+        load_tile16_async<D>(buf + kTile, static_cast<const uint8_t*>(d_o) + (base_row + t0) * D * 2, nrows);
         for (int r = threadIdx.x; r < kBS; r += kThreads) {
-            float4 st = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4* st = rst + (j & 1) * kBS + r;
+            float* dd = dds + (j & 1) * kBS + r;
             if (r < nrows) {
-                const float4 rs = *reinterpret_cast<const float4*>(row_stats + (base_row + t0 + r) * 4);
-                st = make_float4(rs.x, 1.f / rs.y, drow[base_row + t0 + r], 1.f);
+                cp_async16(smem_addr(st), row_stats + (base_row + t0 + r) * 4);
+                cp_async4(smem_addr(dd), drow + base_row + t0 + r);
+            } else {                    // 1/den = 0 and dD = 0 make a padded row contribute nothing
+                *st = make_float4(0.f, 1.f, 0.f, 0.f);
+                *dd = 0.f;
             }
-            rst[r] = st;
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    if (nh > 0) prefetch(0);
+    for (int j = 0; j < nh; ++j) {
+        cp_async_wait_all();
+        __syncthreads();                // block j has landed; every warp is done with block j-1
+        if (j + 1 < nh) prefetch(j + 1);
+        const uint8_t* qs = (j & 1) ? qd1 : qd0;
+        const uint8_t* dos = qs + kTile;
+        const float4* rs = rst + (j & 1) * kBS;
+        const float* dd = dds + (j & 1) * kBS;
+        const int nrows = min(kBS, p.T - hlist[j] * kBS);
 #pragma unroll 1
         for (int r0 = 0; r0 < kBS; r0 += 32) {
             if (r0 >= nrows) break;
@@ -448,10 +495,10 @@ pisa_bwd_kv_mma_kernel(Params p, const void* __restrict__ q, const void* __restr
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int r = r0 + n * 8 + col0 + (e & 1);
-                    const float4 st = rst[r];
-                    const float pj = st.w != 0.f ? exp2f(st_[n][e] * sm - st.x) : 0.f;
-                    pe[e] = pj * st.y;
-                    de[e] = pj * (dpt[n][e] * st.y + st.z) * p.scale;
+                    const float4 st = rs[r];
+                    const float pj = exp2f(st_[n][e] * sm - st.x);
+                    pe[e] = pj * st.w;
+                    de[e] = pj * (dpt[n][e] * st.w + dd[r]) * p.scale;
                 }
                 pack_split<BF16>(pe[0], pe[1], pa[n >> 1][(n & 1) * 2 + 0], pl[n >> 1][(n & 1) * 2 + 0]);
                 pack_split<BF16>(pe[2], pe[3], pa[n >> 1][(n & 1) * 2 + 1], pl[n >> 1][(n & 1) * 2 + 1]);
@@ -482,6 +529,7 @@ pisa_bwd_kv_mma_kernel(Params p, const void* __restrict__ q, const void* __restr
             }
         }
     }
+    uint8_t* qs = qd0;                  // from here on the [D][D] tile of dh
     // ---- statistics terms: dk += dkc/len + (v - vc/len) dh^T,   dv += dvc + (k - kc) dh ----
     __syncthreads();
     load_square32<D, BF16>(qs, dh + (size_t)bh * D * D);

@@ -190,7 +190,7 @@ int fbla_varlen_linear_attn_bwd_in(const fbla_problem *p, const void *k, const v
  *   kv (batch, heads, dk, dv) = K^T V (the state of fbla_simple_la_fwd_state);
  *   h (batch, heads, dk, dv) = kv - sum_c kc_c (x) vc_c = sum_c (K_c - kc_c)^T V_c;
  *   indices int32 (batch, heads, NT, num_selected); NT = ceil(seq_len / block_size).
- *   row_stats fp32 (batch, heads, seq_len, 4): running max (log2 domain), denominator, g, unused;
+ *   row_stats fp32 (batch, heads, seq_len, 4): running max (log2 domain), denominator, g, 1/denominator;
  *   may be NULL when no backward follows.                                                   */
 typedef struct fbla_pisa_problem {
     int32_t dtype;          /* enum fbla_dtype of q, k, v, o                        */
