@@ -304,13 +304,18 @@ def run_ours(args):
         cv, _ = time_cpu(T, 3, 1)
         cpu = cpu_baseline_dict(cv, T)
 
+    exchange_kind = "NCCL all-reduce"
+    if world > 1:
+        from flash_bla.ops import sharded
+        if any(e is not None for e in sharded._exchanges.values()):
+            exchange_kind = "one peer-memory kernel per direction (NVLink loads)"
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"linear_attn fwd+bwd bf16 B{B}-H{H}-D{D} T={T} per GPU"
-                                       + (f", T-sharded global T={T_global}, NCCL all-reduce of the state"
-                                          if world > 1 else ""),
+                                       + (f", T-sharded global T={T_global}, state summed over ranks by "
+                                          + exchange_kind if world > 1 else ""),
                            "l2": "inputs larger than L2 (4 x %d MB per step)" % (tensor_bytes // 2 ** 20),
                            "kernel_path": "tcgen05+TMA" if path == 1 else "cuda-core"},
                 "roofline": roofline, "passes": passes, "cpu_baseline": cpu, "e2e": e2e,

@@ -366,6 +366,7 @@ namespace fbla {
 #endif
 
 int tc_device_status() { return g_status_host != nullptr ? *g_status_host : 0; }
+int* tc_status_word() { return status_word(); }
 
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v, float* state,
                          void* ws, cudaStream_t st) {

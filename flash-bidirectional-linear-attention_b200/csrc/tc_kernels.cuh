@@ -11,6 +11,8 @@ bool tc_supported(const KParams& p, int dtype);
 bool tc_supported_decoupled(const KParams& p);
 // Status word written by a kernel whose bounded wait gave up (0 = none did).
 int tc_device_status();
+// Device-visible address of that word (NULL if the pinned allocation failed).
+int* tc_status_word();
 int64_t tc_workspace_bytes(const KParams& p);
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
                          float* state, void* ws, cudaStream_t st);

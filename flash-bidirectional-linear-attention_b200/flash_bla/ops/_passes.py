@@ -55,11 +55,25 @@ def _state_like(prob, like):
     return torch.empty(n, dtype=torch.float32, device=like.device)
 
 
-def fwd_state(op, prob, k, v, k_rope=None):
+def state_floats(prob):
+    n = _C.lib().fbla_state_floats(ctypes.byref(prob))
+    if n < 0:
+        _C.check(1)
+    return n
+
+
+def _check_state(prob, out):
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.numel() != state_floats(prob):
+        raise ValueError("state buffer must be contiguous fp32 with fbla_state_floats() elements")
+    return out
+
+
+def fwd_state(op, prob, k, v, k_rope=None, out=None):
+    """``out``: optional preallocated fp32 state buffer (e.g. memory that peer GPUs have mapped)."""
     _require_cuda(k, v, k_rope)
     L = _C.lib()
     with torch.cuda.device_of(k):
-        state = _state_like(prob, k)
+        state = _state_like(prob, k) if out is None else _check_state(prob, out)
         ws, n = _workspace(prob, k)
         f = getattr(L, f"fbla_{op}_fwd_state")
         if op == "decoupled_la":
@@ -84,11 +98,11 @@ def fwd_out(op, prob, q, state, o, q_rope=None):
     return o
 
 
-def bwd_state(op, prob, q, d_o, state, dq, q_rope=None, dq_rope=None):
+def bwd_state(op, prob, q, d_o, state, dq, q_rope=None, dq_rope=None, out=None):
     _require_cuda(q, d_o, state, dq, q_rope, dq_rope)
     L = _C.lib()
     with torch.cuda.device_of(q):
-        dstate = _state_like(prob, q)
+        dstate = _state_like(prob, q) if out is None else _check_state(prob, out)
         ws, n = _workspace(prob, q)
         f = getattr(L, f"fbla_{op}_bwd_state")
         if op == "decoupled_la":

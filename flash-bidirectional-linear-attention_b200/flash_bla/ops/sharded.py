@@ -5,14 +5,20 @@ attention is a dk x dv matrix per (batch, head) whatever the sequence length, a
 sequence split along T over the ranks of a process group needs exactly one
 exchange per direction:
 
-    forward : local [S_r | sum k_r]  --all_reduce(SUM)-->  global state  -> local o
-    backward: local dq and [dS_r | sum dz q_r]  --all_reduce(SUM)-->  -> local dk, dv
+    forward : local [S_r | sum k_r]  --sum over ranks-->  global state  -> local o
+    backward: local dq and [dS_r | sum dz q_r]  --sum over ranks-->  -> local dk, dv
+
+On NCCL groups of GPUs of one node the sum is one kernel that reads the peers' states over NVLink
+(``fbla_peer_state_sum``, symmetric memory); elsewhere, or with ``FBLA_PEER_EXCHANGE=0``, it is
+``all_reduce(SUM)``.
 
 The key mean and the default scale use the GLOBAL sequence length.  Batch, head
 and whole-sequence (varlen) sharding need no communication at all: each rank
 calls the plain operator on its own slice; ``partition_sequences`` balances packed
 sequences over ranks by token count.
 """
+import os
+import warnings
 from typing import List, Optional, Sequence
 
 import torch
@@ -37,6 +43,88 @@ def _all_reduce(t, group):
     return t
 
 
+class _PeerExchange:
+    """State sum over the GPUs of one node through peer memory (``fbla_peer_state_sum``).
+
+    Two symmetric-memory buffers of ``n`` floats (used alternately) and one array of flag words per
+    rank, all mapped by every peer.  Not safe for exchanges issued on several streams at once.
+    """
+
+    def __init__(self, group, device, n):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm
+        from flash_bla import _C
+        self._C, self._ct = _C, ctypes
+        self.n = n
+        self.data = symm.empty(2 * n, dtype=torch.float32, device=device)
+        self.flags = symm.empty(64, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        hd = symm.rendezvous(self.data, group)
+        hf = symm.rendezvous(self.flags, group)
+        self.world, self.rank = hd.world_size, hd.rank
+        if self.world > 16:
+            raise RuntimeError("at most 16 ranks")
+        self._hd, self._hf = hd, hf
+        arr = ctypes.c_void_p * self.world
+        self._bufs = [arr(*[int(p) + b * n * 4 for p in hd.buffer_ptrs]) for b in (0, 1)]
+        self._flags = arr(*[int(p) for p in hf.buffer_ptrs])
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+
+    def buffer(self):
+        """The buffer the next exchange reads; the producing pass writes the local state into it."""
+        b = (self.epoch + 1) & 1
+        return self.data[b * self.n:(b + 1) * self.n]
+
+    def sum(self):
+        self.epoch += 1
+        out = torch.empty(self.n, dtype=torch.float32, device=self.data.device)
+        with torch.cuda.device_of(out):
+            rc = self._C.lib().fbla_peer_state_sum(self.world, self.rank, self._bufs[self.epoch & 1], self._flags,
+                                                   self.n, self.epoch, out.data_ptr(), self._C.stream_of(out))
+        self._C.check(rc)
+        return out
+
+
+_exchanges = {}
+
+
+def _peer_exchange(group, device, n):
+    """The exchange object for (group, device, state size), or None when the group is not an NCCL
+    group of more than one GPU rank, the switch ``FBLA_PEER_EXCHANGE=0`` is set, or setting it up
+    failed on any rank (decided collectively, so that all ranks take the same path)."""
+    if not (dist.is_available() and dist.is_initialized()) or device.type != "cuda":
+        return None
+    if dist.get_world_size(group) < 2 or dist.get_backend(group) != "nccl":
+        return None
+    if os.environ.get("FBLA_PEER_EXCHANGE", "1") == "0":
+        return None
+    key = (id(group) if group is not None else 0, device.index, n)
+    if key not in _exchanges:
+        ex = None
+        try:
+            # peers are read with plain loads; no multicast object is needed or wanted
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            ex = _PeerExchange(group if group is not None else dist.group.WORLD, device, n)
+        except Exception as e:          # noqa: BLE001 - any failure means "use the library all-reduce"
+            warnings.warn(f"peer-memory state exchange unavailable ({type(e).__name__}: {e}); using all_reduce")
+        ok = torch.tensor([1 if ex is not None else 0], device=device, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)   # also: every rank's flags are zeroed by now
+        _exchanges[key] = ex if int(ok.item()) == 1 else None
+    return _exchanges[key]
+
+
+def _summed_state(produce, prob, like, group):
+    """Runs ``produce(out)`` (a state pass; ``out`` None = allocate) and returns the sum of the
+    resulting states over the group."""
+    n = _backend.state_floats(prob) if hasattr(_backend, "state_floats") else 0
+    ex = _peer_exchange(group, like.device, n) if n else None
+    if ex is None:
+        return _all_reduce(produce(None), group)
+    produce(ex.buffer())
+    return ex.sum()
+
+
 class _SeqSharded(torch.autograd.Function):
     """linear_attention / simple_la on a T-shard; ``normalize`` selects which."""
 
@@ -48,7 +136,7 @@ class _SeqSharded(torch.autograd.Function):
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1],
                                      normalize=normalize, scale=scale, eps=eps, norm_len=norm_len,
                                      flags=_backend.default_flags())
-        state = _all_reduce(_backend.fwd_state(op, prob, k, v), group)
+        state = _summed_state(lambda out: _backend.fwd_state(op, prob, k, v, out=out), prob, q, group)
         o = _backend.fwd_out(op, prob, q, state, torch.empty_like(v))
         ctx.save_for_backward(q, k, v, state)
         ctx.args = (scale, eps, norm_len, normalize, group)
@@ -65,7 +153,7 @@ class _SeqSharded(torch.autograd.Function):
                                      normalize=normalize, scale=scale, eps=eps, norm_len=norm_len,
                                      flags=_backend.default_flags())
         dq = torch.empty_like(q)
-        dstate = _all_reduce(_backend.bwd_state(op, prob, q, do, state, dq), group)
+        dstate = _summed_state(lambda out: _backend.bwd_state(op, prob, q, do, state, dq, out=out), prob, q, group)
         dk, dv = torch.empty_like(k), torch.empty_like(v)
         _backend.bwd_in(op, prob, k, v, dstate, dk, dv)
         return dq, dk, dv, None, None, None, None, None
@@ -79,7 +167,8 @@ class _SeqShardedDecoupled(torch.autograd.Function):
         B, H, L, K = q.shape
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
                                      scale=scale, eps=eps, norm_len=norm_len, flags=_backend.default_flags())
-        state = _all_reduce(_backend.fwd_state("decoupled_la", prob, k, v, k_rope=k_rope), group)
+        state = _summed_state(lambda out: _backend.fwd_state("decoupled_la", prob, k, v, k_rope=k_rope, out=out),
+                              prob, q, group)
         o = _backend.fwd_out("decoupled_la", prob, q, state, torch.empty_like(v), q_rope=q_rope)
         ctx.save_for_backward(q, q_rope, k_rope, v, state)
         ctx.args = (scale, eps, norm_len, group)
@@ -94,8 +183,8 @@ class _SeqShardedDecoupled(torch.autograd.Function):
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
                                      scale=scale, eps=eps, norm_len=norm_len, flags=_backend.default_flags())
         dq, dq_rope = torch.empty_like(q), torch.empty_like(q_rope)
-        dstate = _all_reduce(_backend.bwd_state("decoupled_la", prob, q, do, state, dq, q_rope=q_rope,
-                                                dq_rope=dq_rope), group)
+        dstate = _summed_state(lambda out: _backend.bwd_state("decoupled_la", prob, q, do, state, dq, q_rope=q_rope,
+                                                              dq_rope=dq_rope, out=out), prob, q, group)
         dk, dk_rope, dv = torch.empty_like(k_rope), torch.empty_like(k_rope), torch.empty_like(v)
         _backend.bwd_in("decoupled_la", prob, k_rope, v, dstate, dk, dv, dk_rope=dk_rope)
         return dq, dk, dq_rope, dk_rope, dv, None, None, None, None

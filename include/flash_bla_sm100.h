@@ -222,6 +222,27 @@ int fbla_pisa_bwd(const fbla_pisa_problem *p, const void *q, const void *k, cons
                   const int32_t *indices, const float *row_stats, void *dq, void *dk, void *dv,
                   float *scratch, size_t scratch_floats, fbla_stream_t stream);
 
+/* ---- multi-GPU: sum of the sequence-sharded states over the GPUs of one node ---------------
+ * The reference runs on one GPU (no counterpart).  A sequence split along T over `world` ranks
+ * needs the sum of the ranks' fp32 states between *_fwd_state and *_fwd_out (and between
+ * *_bwd_state and *_bwd_in).  This call does it in one kernel with plain loads from the peers'
+ * memory (NVLink), where a library all-reduce would cost several launches.
+ *   peer_states[r]: rank r's state buffer of n_floats floats, mapped into this process (this
+ *                   rank's own buffer at index `rank`); the local state must already have been
+ *                   written to it by earlier work on `stream`.
+ *   peer_flags[r] : rank r's array of at least `world` 32-bit words, mapped likewise, zero before
+ *                   the first exchange.
+ *   epoch         : 1, 2, 3, ... the same on every rank for the same exchange.
+ *   out           : ordinary device memory; receives sum_r peer_states[r], added in rank order
+ *                   (bit-identical on all ranks).
+ * Every rank of the group must make the matching call; each waits (at most about a second, then
+ * the device status word is set and later calls return FBLA_ERR_DEVICE) for all peers to enter
+ * theirs.  Use two buffers alternately for consecutive exchanges: a rank can enter exchange
+ * e+2 only after all peers have entered e+1, i.e. have finished reading the buffer of e.      */
+int fbla_peer_state_sum(int world, int rank, const void *const *peer_states,
+                        void *const *peer_flags, int64_t n_floats, uint32_t epoch, float *out,
+                        fbla_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,7 +29,7 @@ def _pack(prob, S, vec):
     return torch.cat(parts, -1).contiguous().view(-1).float()
 
 
-def fwd_state(op, prob, k, v, k_rope=None):
+def fwd_state(op, prob, k, v, k_rope=None, out=None):
     kr = (k if k_rope is None else k_rope).double()
     return _pack(prob, kr.transpose(-1, -2) @ v.double(), k.double().sum(-2))
 
@@ -46,7 +46,7 @@ def fwd_out(op, prob, q, state, o, q_rope=None):
     return o
 
 
-def bwd_state(op, prob, q, d_o, state, dq, q_rope=None, dq_rope=None):
+def bwd_state(op, prob, q, d_o, state, dq, q_rope=None, dq_rope=None, out=None):
     S, vec = _split(prob, state)
     qr = (q if q_rope is None else q_rope).double()
     t = d_o.double() @ (S.double() * prob.scale).transpose(-1, -2)

@@ -25,9 +25,12 @@ def _worker(rank, world, port, ret):
         from flash_bla.ops.linear_attn.fused import linear_attention
         from flash_bla.ops.simple_la.fused import simple_la
         from flash_bla.ops.sharded import seq_sharded_linear_attention, seq_sharded_simple_la
+        from flash_bla.ops import sharded
         errs = {}
-        for name, D, dtype in (("linear", 64, torch.bfloat16), ("simple", 128, torch.bfloat16),
-                               ("linear_f32", 32, torch.float32)):
+        # every case once with the peer-memory state exchange and once with NCCL's all-reduce
+        for mode, (name, D, dtype) in [(m, c) for m in ("1", "0") for c in (
+                ("linear", 64, torch.bfloat16), ("simple", 128, torch.bfloat16), ("linear_f32", 32, torch.float32))]:
+            os.environ["FBLA_PEER_EXCHANGE"] = mode
             g = torch.Generator(device="cuda").manual_seed(7)
             B, H, T = 2, 4, 2048
             q = torch.rand(B, H, T, D, device="cuda", generator=g).add_(0.1).to(dtype)
@@ -45,6 +48,7 @@ def _worker(rank, world, port, ret):
                 o_ref = simple_la(*full)
             o.backward(do[:, :, sl].contiguous())
             o_ref.backward(do)
+            grads = [x.grad.clone() for x in xs]
             # The sharded and the single-GPU run add the fp32 state in a different order, so 16-bit
             # outputs may land on neighbouring representable values: allow one unit in the last
             # place of the output type plus 0.2 % of the RMS (fp32: 1e-4 of the RMS).
@@ -55,7 +59,16 @@ def _worker(rank, world, port, ret):
                 rms = b.pow(2).mean().sqrt().item()
                 slack = ulp * b.abs() + (2e-3 if ulp else 1e-4) * rms
                 worst = max(worst, ((a - b).abs() / slack).max().item())
-            errs[name] = worst
+            errs[f"{name}/peer={mode}"] = worst
+            if mode == "1":     # three steps in a row: the two exchange buffers alternate, the epochs advance
+                for _ in range(3):
+                    for x in xs:
+                        x.grad = None
+                    o2 = (seq_sharded_linear_attention if name.startswith("linear") else seq_sharded_simple_la)(*xs)
+                    o2.backward(do[:, :, sl].contiguous())
+                    same = torch.equal(o2, o) and all(torch.equal(x.grad, g) for x, g in zip(xs, grads))
+                    errs[f"{name}/repeat"] = max(errs.get(f"{name}/repeat", 0.0), 0.0 if same else 2.0)
+        errs["peer_path_used"] = 0.0 if any(e is not None for e in sharded._exchanges.values()) else 2.0
         ret[rank] = errs
     finally:
         dist.destroy_process_group()
