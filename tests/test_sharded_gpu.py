@@ -74,9 +74,13 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+# FBLA_TEST_WORLD=4 or 8 runs the same check on more ranks (a box with that many GPUs)
+_WORLD = int(os.environ.get("FBLA_TEST_WORLD", "2"))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < _WORLD, reason="needs %d GPUs" % _WORLD)
 def test_two_gpu_sequence_sharding_matches_one_gpu():
-    world = 2
+    world = _WORLD
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert len(ret) == world
