@@ -56,6 +56,22 @@ def timed(fn, reps, inner=4):
     return statistics.median(out)
 
 
+def graphed(fn, leaves):
+    """``fn`` (a forward + backward) captured once in a CUDA graph; returns the replay callable."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    for x in leaves:
+        x.grad = None
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g.replay
+
+
 def row(name, shape, fwd, fwd_bwd, tokens, nbytes_fwd, nbytes_all):
     print(f"{name:14s} {shape:28s} fwd {fwd:8.4f} ms ({nbytes_fwd / fwd / 1e6:6.0f} GB/s)   fwd+bwd {fwd_bwd:8.4f} ms "
           f"({nbytes_all / fwd_bwd / 1e6:6.0f} GB/s, {tokens / fwd_bwd * 1e3:.3e} tokens/s)", flush=True)
@@ -69,6 +85,7 @@ def main():
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--op", default="all")
     ap.add_argument("--long", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="also time linear_attn fwd+bwd replayed from a CUDA graph")
     ap.add_argument("--lengths", default="1024,4096,16384,32768", help="T values of the linear_attn rows")
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--ref-path", default=None)
@@ -101,6 +118,13 @@ def main():
             P = B * H * T * D * 2
             f, fb = both(lambda: linear_attention(q, k, v), (q, k, v), do)
             row("linear_attn", f"B{B} H{H} T{T} D{D}", f, fb, B * T, 4 * P, 11 * P)
+            if args.graph:
+                def once():
+                    linear_attention(q, k, v).backward(do)
+                replay = graphed(once, (q, k, v))
+                tg = timed(replay, args.reps)
+                print(f"{'':14s} {'  replayed from a CUDA graph':28s} {'':33s}   fwd+bwd {tg:8.4f} ms "
+                      f"({11 * P / tg / 1e6:6.0f} GB/s, {B * T / tg * 1e3:.3e} tokens/s)", flush=True)
     if args.op in ("all", "simple_la"):
         for (b, h, T, d) in ((4, 32, 32768, 128), (B, H, 32768, D)) + (((4, 32, 262144, 128),) if args.long else ()):
             q, k, v = gau(b, h, T, d), gau(b, h, T, d), gau(b, h, T, d)

@@ -155,5 +155,29 @@ def ptr(t):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_of(t):
+    """cudaStream_t (as an int) of torch's current stream on the tensor's device."""
+    if _raw_stream is not None:
+        return _raw_stream(t.device.index)
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_no_guard = _NoGuard()
+
+
+def device_guard(t):
+    """Context that makes the tensor's device current; free when it already is."""
+    if t.device.index == torch.cuda.current_device():
+        return _no_guard
+    return torch.cuda.device_of(t)

@@ -72,7 +72,7 @@ def fwd_state(op, prob, k, v, k_rope=None, out=None):
     """``out``: optional preallocated fp32 state buffer (e.g. memory that peer GPUs have mapped)."""
     _require_cuda(k, v, k_rope)
     L = _C.lib()
-    with torch.cuda.device_of(k):
+    with _C.device_guard(k):
         state = _state_like(prob, k) if out is None else _check_state(prob, out)
         ws, n = _workspace(prob, k)
         f = getattr(L, f"fbla_{op}_fwd_state")
@@ -88,7 +88,7 @@ def fwd_state(op, prob, k, v, k_rope=None, out=None):
 def fwd_out(op, prob, q, state, o, q_rope=None):
     _require_cuda(q, state, o, q_rope)
     L = _C.lib()
-    with torch.cuda.device_of(q):
+    with _C.device_guard(q):
         f = getattr(L, f"fbla_{op}_fwd_out")
         if op == "decoupled_la":
             rc = f(ctypes.byref(prob), _C.ptr(q), _C.ptr(q_rope), _C.ptr(state), _C.ptr(o), _C.stream_of(q))
@@ -101,7 +101,7 @@ def fwd_out(op, prob, q, state, o, q_rope=None):
 def bwd_state(op, prob, q, d_o, state, dq, q_rope=None, dq_rope=None, out=None):
     _require_cuda(q, d_o, state, dq, q_rope, dq_rope)
     L = _C.lib()
-    with torch.cuda.device_of(q):
+    with _C.device_guard(q):
         dstate = _state_like(prob, q) if out is None else _check_state(prob, out)
         ws, n = _workspace(prob, q)
         f = getattr(L, f"fbla_{op}_bwd_state")
@@ -119,7 +119,7 @@ def bwd_in(op, prob, k, v, dstate, dk, dv, dk_rope=None):
     """``k`` is the key tensor the state was built from (k_rope when decoupled)."""
     _require_cuda(k, v, dstate, dk, dv, dk_rope)
     L = _C.lib()
-    with torch.cuda.device_of(k):
+    with _C.device_guard(k):
         f = getattr(L, f"fbla_{op}_bwd_in")
         if op == "decoupled_la":
             rc = f(ctypes.byref(prob), _C.ptr(k), _C.ptr(v), _C.ptr(dstate), _C.ptr(dk), _C.ptr(dk_rope),
@@ -158,7 +158,7 @@ def forward(prob, q, k, v):
     state = torch.empty(n_state, dtype=torch.float32, device=dev)
     ws = torch.empty(n_ws, dtype=torch.uint8, device=dev) if n_ws else None
     o = torch.empty_like(v)
-    with torch.cuda.device_of(q):
+    with _C.device_guard(q):
         rc = _C.lib().fbla_linear_attn_fwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                            state.data_ptr(), _C.ptr(ws), n_ws, _C.stream_of(q))
     _C.check(rc)
@@ -173,7 +173,7 @@ def backward(prob, q, k, v, d_o, state):
     dstate = torch.empty(n_state, dtype=torch.float32, device=dev)
     ws = torch.empty(n_ws, dtype=torch.uint8, device=dev) if n_ws else None
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    with torch.cuda.device_of(q):
+    with _C.device_guard(q):
         rc = _C.lib().fbla_linear_attn_bwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(),
                                            state.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                            dstate.data_ptr(), _C.ptr(ws), n_ws, _C.stream_of(q))

@@ -46,7 +46,7 @@ def block_statistics(q, k, v, block_size):
     qc = torch.empty(B, H, nt, K, dtype=torch.float32, device=q.device)
     kc = torch.empty_like(qc)
     vc = torch.empty(B, H, nt, V, dtype=torch.float32, device=q.device)
-    with torch.cuda.device_of(q):
+    with _C.device_guard(q):
         _C.check(_C.lib().fbla_pisa_block_stats(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                                 qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), _C.stream_of(q)))
     return qc, kc, vc
@@ -62,7 +62,7 @@ def first_order_state(k, v, kc, vc, block_size):
     kv = P.fwd_state("simple_la", sp, k, v)
     prob = _problem(k, v, block_size, 1, 1.0)
     h = torch.empty(B, H, K, V, dtype=torch.float32, device=k.device)
-    with torch.cuda.device_of(k):
+    with _C.device_guard(k):
         _C.check(_C.lib().fbla_pisa_first_order_state(ctypes.byref(prob), kv.data_ptr(), kc.data_ptr(), vc.data_ptr(),
                                                       h.data_ptr(), _C.stream_of(k)))
     return h
@@ -101,7 +101,7 @@ def attention_forward(q, k, v, kc, vc, h, indices, block_size, scale, want_stats
     prob = _problem(q, v, block_size, idx.shape[-1], scale)
     o = torch.empty_like(v)
     stats = torch.empty(B, H, T, 4, dtype=torch.float32, device=q.device) if want_stats else None
-    with torch.cuda.device_of(q):
+    with _C.device_guard(q):
         _C.check(_C.lib().fbla_pisa_fwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                         kc.contiguous().data_ptr(), vc.contiguous().data_ptr(),
                                         h.contiguous().data_ptr(), idx.data_ptr(), o.data_ptr(),
@@ -123,7 +123,7 @@ def attention_backward(q, k, v, o, do, kc, vc, h, indices, stats, block_size, sc
     if n < 0:
         _C.check(1)
     scratch = torch.empty(n, dtype=torch.float32, device=q.device)
-    with torch.cuda.device_of(q):
+    with _C.device_guard(q):
         _C.check(_C.lib().fbla_pisa_bwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                         do.data_ptr(), kc.contiguous().data_ptr(), vc.contiguous().data_ptr(),
                                         h.contiguous().data_ptr(), idx.data_ptr(), stats.data_ptr(), dq.data_ptr(),

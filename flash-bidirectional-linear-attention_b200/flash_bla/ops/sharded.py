@@ -79,7 +79,7 @@ class _PeerExchange:
     def sum(self):
         self.epoch += 1
         out = torch.empty(self.n, dtype=torch.float32, device=self.data.device)
-        with torch.cuda.device_of(out):
+        with self._C.device_guard(out):
             rc = self._C.lib().fbla_peer_state_sum(self.world, self.rank, self._bufs[self.epoch & 1], self._flags,
                                                    self.n, self.epoch, out.data_ptr(), self._C.stream_of(out))
         self._C.check(rc)
