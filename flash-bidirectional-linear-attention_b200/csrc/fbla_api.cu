@@ -54,6 +54,7 @@ int resolve(const fbla_problem* p, OpKind op, fbla::KParams* kp) {
     kp->normalize = p->normalize != 0;
     kp->inv_norm = p->norm_len > 0 ? (float)(1.0 / (double)p->norm_len) : 0.f;
     kp->state_stride = p->dk * p->dv + (kp->normalize ? p->dk : 0);
+    kp->unreduced = 0;
     if (op == OP_VARLEN) {
         if (p->cu_seqlens == nullptr) return fail(FBLA_ERR_INVALID, "cu_seqlens is NULL");
         if (p->num_seqs < 1) return fail(FBLA_ERR_INVALID, "num_seqs=%d must be positive", p->num_seqs);
@@ -126,11 +127,14 @@ int check_ws(const fbla_problem* p, const fbla::KParams& kp, void* ws, size_t ws
 // still be defined for the caller.
 bool is_empty(const fbla::KParams& kp) { return kp.units == 0 || kp.seq_len == 0; }
 
+const char* const kUnreducedNeedsTc = "the unreduced-state mode needs the tensor-core kernels (16-byte aligned tensors)";
+
 int fwd_state(const fbla_problem* p, OpKind op, const void* k, const void* k_rope, const void* v,
-              float* state, void* ws, size_t ws_bytes, fbla_stream_t stream) {
+              float* state, void* ws, size_t ws_bytes, fbla_stream_t stream, bool unreduced = false) {
     fbla::KParams kp;
     if (int rc = resolve(p, op, &kp)) return rc;
-    NOT_NULL(state);
+    kp.unreduced = unreduced;
+    if (!unreduced) NOT_NULL(state);
     cudaStream_t st = (cudaStream_t)stream;
     if (is_empty(kp)) {
         cudaError_t e = cudaMemsetAsync(state, 0, sizeof(float) * (size_t)kp.units * kp.state_stride, st);
@@ -141,15 +145,17 @@ int fwd_state(const fbla_problem* p, OpKind op, const void* k, const void* k_rop
     if (int rc = check_ws(p, kp, ws, ws_bytes)) return rc;
     if (int rc = check_device_status()) return rc;
     const bool tc = use_tc(p, kp) && aligned16(k, k_rope, v, ws) && (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
     cudaError_t e = tc ? fbla::tc_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st)
                        : fbla::simt_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward state pass");
 }
 
 int fwd_out(const fbla_problem* p, OpKind op, const void* q, const void* q_rope, const float* state, void* o,
-            fbla_stream_t stream) {
+            fbla_stream_t stream, bool unreduced = false) {
     fbla::KParams kp;
     if (int rc = resolve(p, op, &kp)) return rc;
+    kp.unreduced = unreduced;
     if (is_empty(kp)) return FBLA_OK;
     NOT_NULL(q);
     NOT_NULL(state);
@@ -157,6 +163,7 @@ int fwd_out(const fbla_problem* p, OpKind op, const void* q, const void* q_rope,
     cudaStream_t st = (cudaStream_t)stream;
     if (int rc = check_device_status()) return rc;
     const bool tc = use_tc(p, kp) && aligned16(q, q_rope, o) && (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
     cudaError_t e = tc ? fbla::tc_fwd_out(kp, p->dtype, q, q_rope, state, o, st)
                        : fbla::simt_fwd_out(kp, p->dtype, q, q_rope, state, o, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward output pass");
@@ -164,12 +171,14 @@ int fwd_out(const fbla_problem* p, OpKind op, const void* q, const void* q_rope,
 
 int bwd_state(const fbla_problem* p, OpKind op, const void* q, const void* q_rope, const void* d_o,
               const float* state, void* dq, void* dq_rope, float* dstate, void* ws, size_t ws_bytes,
-              fbla_stream_t stream) {
+              fbla_stream_t stream, bool unreduced = false) {
     fbla::KParams kp;
     if (int rc = resolve(p, op, &kp)) return rc;
-    NOT_NULL(dstate);
+    kp.unreduced = unreduced;
+    if (!unreduced) NOT_NULL(dstate);
     cudaStream_t st = (cudaStream_t)stream;
     if (is_empty(kp)) {
+        if (dstate == nullptr) return FBLA_OK;
         cudaError_t e = cudaMemsetAsync(dstate, 0, sizeof(float) * (size_t)kp.units * kp.state_stride, st);
         return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "memset of the state gradient");
     }
@@ -185,15 +194,17 @@ int bwd_state(const fbla_problem* p, OpKind op, const void* q, const void* q_rop
     if (int rc = check_device_status()) return rc;
     const bool tc = use_tc(p, kp) && aligned16(q, q_rope, d_o, dq, dq_rope, ws) &&
                     (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
     cudaError_t e = tc ? fbla::tc_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st)
                        : fbla::simt_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward state pass");
 }
 
 int bwd_in(const fbla_problem* p, OpKind op, const void* k_rope, const void* v, const float* dstate, void* dk,
-           void* dk_rope, void* dv, fbla_stream_t stream) {
+           void* dk_rope, void* dv, fbla_stream_t stream, bool unreduced = false) {
     fbla::KParams kp;
     if (int rc = resolve(p, op, &kp)) return rc;
+    kp.unreduced = unreduced;
     if (is_empty(kp)) return FBLA_OK;
     NOT_NULL(k_rope);
     NOT_NULL(v);
@@ -205,6 +216,7 @@ int bwd_in(const fbla_problem* p, OpKind op, const void* k_rope, const void* v, 
     if (int rc = check_device_status()) return rc;
     const bool tc = use_tc(p, kp) && aligned16(k_rope, v, dk, dk_rope, dv) &&
                     (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
+    if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
     cudaError_t e = tc ? fbla::tc_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st)
                        : fbla::simt_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward input pass");
@@ -307,18 +319,27 @@ int fbla_decoupled_la_bwd_in(const fbla_problem* p, const void* k_rope, const vo
 }
 
 // ---- both passes of a direction in one call (saves a host round trip per pass) -----------
+int fbla_unreduced_state(const fbla_problem* p) {
+    if (p == nullptr || !(p->flags & FBLA_FLAG_UNREDUCED)) return 0;
+    const OpKind op = kind_of(p);
+    fbla::KParams kp;
+    if (op == OP_VARLEN || resolve(p, op, &kp) != FBLA_OK) return 0;
+    return (use_tc(p, kp) && !is_empty(kp) && workspace_need(p, kp) > 0) ? 1 : 0;
+}
 int fbla_linear_attn_fwd(const fbla_problem* p, const void* q, const void* k, const void* v, void* o, float* state,
                          void* ws, size_t ws_bytes, fbla_stream_t s) {
     const OpKind op = kind_of(p);
-    if (int rc = fwd_state(p, op, k, nullptr, v, state, ws, ws_bytes, s)) return rc;
-    return fwd_out(p, op, q, nullptr, state, o, s);
+    const bool u = fbla_unreduced_state(p) != 0;
+    if (int rc = fwd_state(p, op, k, nullptr, v, state, ws, ws_bytes, s, u)) return rc;
+    return fwd_out(p, op, q, nullptr, u ? static_cast<const float*>(ws) : state, o, s, u);
 }
 int fbla_linear_attn_bwd(const fbla_problem* p, const void* q, const void* k, const void* v, const void* d_o,
                          const float* state, void* dq, void* dk, void* dv, float* dstate, void* ws, size_t ws_bytes,
                          fbla_stream_t s) {
     const OpKind op = kind_of(p);
-    if (int rc = bwd_state(p, op, q, nullptr, d_o, state, dq, nullptr, dstate, ws, ws_bytes, s)) return rc;
-    return bwd_in(p, op, k, v, dstate, dk, nullptr, dv, s);
+    const bool u = fbla_unreduced_state(p) != 0;
+    if (int rc = bwd_state(p, op, q, nullptr, d_o, state, dq, nullptr, dstate, ws, ws_bytes, s, u)) return rc;
+    return bwd_in(p, op, k, v, u ? static_cast<const float*>(ws) : dstate, dk, nullptr, dv, s, u);
 }
 
 // ---- varlen_linear_attention -----------------------------------------------------------

@@ -28,6 +28,8 @@ struct KParams {
     float eps;
     int normalize;
     int state_stride;     // floats per unit in state / dstate
+    int unreduced;        // tensor-core kernels, fixed length: the state stays in its per-segment pieces
+                          // (the consuming pass adds them while staging; no reduce kernel)
 };
 
 struct UnitGeom {

@@ -16,19 +16,25 @@ namespace tc {
 // With SPLIT a second copy holding the rounding residual (x - high part, again 16-bit) is written
 // DV/64 blocks further on: issuing every MMA once per copy restores ~16 bits of the fp32 state.
 template <int DK, int DV, bool SPLIT>
-__device__ __forceinline__ void stage_matrix_sw128(uint8_t* dst, const float* __restrict__ src, float scale,
-                                                   int is_bf16, int et) {
-    for (int i = et; i < DK * DV / 2; i += kEpiThreads) {
-        const int k = (2 * i) / DV, v = (2 * i) - k * DV;
-        float2 x = *reinterpret_cast<const float2*>(src + 2 * i);
-        x.x *= scale;
-        x.y *= scale;
-        const uint32_t h = pack2(x.x, x.y, is_bf16);
-        uint8_t* at = dst + (v >> 6) * (DK * 128) + ptx::sw128_offset(k, v & 63);
-        *reinterpret_cast<uint32_t*>(at) = h;
-        if (SPLIT) {
-            const float2 hf = unpack2(h, is_bf16);
-            *reinterpret_cast<uint32_t*>(at + (DV / 64) * (DK * 128)) = pack2(x.x - hf.x, x.y - hf.y, is_bf16);
+__device__ __forceinline__ void stage_matrix_sw128(uint8_t* dst, const StateSrc& src, float scale, int is_bf16,
+                                                   int et) {
+    for (int i0 = et; i0 < DK * DV / 2; i0 += 16 * kEpiThreads) {
+        float2 xs[16];
+        src.template load2<16>(2 * i0, 2 * kEpiThreads, xs);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int i = i0 + u * kEpiThreads;
+            const int k = (2 * i) / DV, v = (2 * i) - k * DV;
+            float2 x = xs[u];
+            x.x *= scale;
+            x.y *= scale;
+            const uint32_t h = pack2(x.x, x.y, is_bf16);
+            uint8_t* at = dst + (v >> 6) * (DK * 128) + ptx::sw128_offset(k, v & 63);
+            *reinterpret_cast<uint32_t*>(at) = h;
+            if (SPLIT) {
+                const float2 hf = unpack2(h, is_bf16);
+                *reinterpret_cast<uint32_t*>(at + (DV / 64) * (DK * 128)) = pack2(x.x - hf.x, x.y - hf.y, is_bf16);
+            }
         }
     }
 }
@@ -220,7 +226,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
             const uint32_t ph2 = (uint32_t)(it >> 1) & 1u;
             const uint32_t pho = (uint32_t)(it / NO) & 1u;
             if (first) {
-                const float* st = p.state + (size_t)unit * p.state_stride;
+                const StateSrc st = state_source(p, unit);
                 // `vec` (and the constant tile) of the previous unit are read by every epilogue thread
                 // until it has arrived on out_written of the previous tile
                 if (it > 0 && !ptx::mbar_wait(&out_written[(it - 1) % NO], (uint32_t)((it - 1) / NO) & 1u, ab, 424)) break;

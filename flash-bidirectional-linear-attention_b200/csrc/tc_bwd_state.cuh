@@ -294,7 +294,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     if (!ptx::mbar_wait(&tfull[(it - 1) % NB], (uint32_t)((it - 1) / NB) & 1u, ab, 326)) break;
                     if (!ptx::mbar_wait(&out_written[a ^ 1], (uint32_t)((it - 1) >> 1) & 1u, ab, 327)) break;
                 }
-                const float* st = p.state + (size_t)unit * p.state_stride;
+                const StateSrc st = state_source(p, unit);
                 stage_matrix_sw128<DK, DV, true>(bop, st, t.scale, BF16, et);
                 if (MODE != kSimple) {
                     for (int i = et; i < DK; i += kEpiThreads) km[i] = st[DK * DV + i] * t.inv_norm;

@@ -61,6 +61,7 @@ struct Params {
     float* part;
     float* state_out;     // packed layout: reducing kernels write whole-unit states here directly
     const float* state;
+    const float* state_parts;   // non-null: `state` is not used, the consuming pass adds the per-segment pieces itself
     int state_stride;     // floats per unit in state / partial slots
     // kernels that write an output with plain global stores (no staged tile): its base address
     void* out_a;
@@ -73,6 +74,72 @@ struct Params {
     int scale_per_seq;    // scale = 1 / length of the sequence
     float inv_norm_fixed; // > 0: divide the key sum by this length for every sequence; 0: by its own
 };
+
+// The state of one unit as a consuming pass reads it: one vector, or the per-segment pieces that the
+// reducing pass left (added here in CTA order, the order tc_reduce_partials_kernel uses, so both
+// routes give the same bits).
+struct StateSrc {
+    const float* p;
+    int n;
+    size_t stride;
+    __device__ __forceinline__ float operator[](int i) const {
+        float a = p[i];
+        for (int j = 1; j < n; ++j) a += p[(size_t)j * stride + i];
+        return a;
+    }
+    // N values first + u * step (u = 0..N-1) at once: all loads of one piece are in flight together
+    // before the next piece is added (the sum per element still runs in piece order).
+    template <int N>
+    __device__ __forceinline__ void load(int first, int step, float (&x)[N]) const {
+#pragma unroll
+        for (int u = 0; u < N; ++u) x[u] = p[first + u * step];
+        for (int j = 1; j < n; ++j) {
+            const float* pj = p + (size_t)j * stride;
+            float y[N];
+#pragma unroll
+            for (int u = 0; u < N; ++u) y[u] = pj[first + u * step];
+#pragma unroll
+            for (int u = 0; u < N; ++u) x[u] += y[u];
+        }
+    }
+    template <int N>
+    __device__ __forceinline__ void load2(int first, int step, float2 (&x)[N]) const {    // first, step even
+#pragma unroll
+        for (int u = 0; u < N; ++u) x[u] = *reinterpret_cast<const float2*>(p + first + u * step);
+        for (int j = 1; j < n; ++j) {
+            const float* pj = p + (size_t)j * stride;
+            float2 y[N];
+#pragma unroll
+            for (int u = 0; u < N; ++u) y[u] = *reinterpret_cast<const float2*>(pj + first + u * step);
+#pragma unroll
+            for (int u = 0; u < N; ++u) {
+                x[u].x += y[u].x;
+                x[u].y += y[u].y;
+            }
+        }
+    }
+    __device__ __forceinline__ float2 pair(int i) const {     // i even
+        float2 a = *reinterpret_cast<const float2*>(p + i);
+        for (int j = 1; j < n; ++j) {
+            const float2 b = *reinterpret_cast<const float2*>(p + (size_t)j * stride + i);
+            a.x += b.x;
+            a.y += b.y;
+        }
+        return a;
+    }
+};
+__device__ __forceinline__ StateSrc state_source(const Params& p, int unit) {
+    StateSrc s;
+    if (p.state_parts != nullptr) {
+        s.p = p.state_parts + (size_t)unit * p.sch.slots_per_unit * p.state_stride;
+        s.n = last_cta_of_unit(p.sch, unit) - first_cta_of_unit(p.sch, unit) + 1;
+    } else {
+        s.p = p.state + (size_t)unit * p.state_stride;
+        s.n = 1;
+    }
+    s.stride = (size_t)p.state_stride;
+    return s;
+}
 
 // One 128-token tile of the work list, as every role of a kernel sees it.
 struct Tile {

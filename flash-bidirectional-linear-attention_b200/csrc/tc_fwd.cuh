@@ -409,15 +409,21 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
             if (first) {
                 // Every MMA of the previous segment has completed (its accumulators were drained
                 // below), so the B operand can be rewritten for this unit.
-                const float* st = p.state + (size_t)unit * p.state_stride;
-                for (int i = et; i < DK * DV; i += kEpiThreads) {
-                    const int k = i / DV, v = i - k * DV;
-                    const float x = st[i] * t.scale;
-                    const uint16_t h = pack1(x, BF16);
-                    *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(v, k & 63)) = h;
-                    // rounding residual: a second B operand accumulated into the same columns
-                    *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(DV + v, k & 63)) =
-                        pack1(x - unpack1(h, BF16), BF16);
+                const StateSrc st = state_source(p, unit);
+                for (int i0 = et; i0 < DK * DV; i0 += 32 * kEpiThreads) {
+                    float xs[32];
+                    st.template load<32>(i0, kEpiThreads, xs);
+#pragma unroll
+                    for (int u = 0; u < 32; ++u) {
+                        const int i = i0 + u * kEpiThreads;
+                        const int k = i / DV, v = i - k * DV;
+                        const float x = xs[u] * t.scale;
+                        const uint16_t h = pack1(x, BF16);
+                        *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(v, k & 63)) = h;
+                        // rounding residual: a second B operand accumulated into the same columns
+                        *reinterpret_cast<uint16_t*>(bop + (k >> 6) * Cfg::kBopBlock + ptx::sw128_offset(DV + v, k & 63)) =
+                            pack1(x - unpack1(h, BF16), BF16);
+                    }
                 }
                 if (MODE != kSimple) {
                     for (int i = et; i < 16 * DK; i += kEpiThreads) {

@@ -163,6 +163,7 @@ Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) 
     q.status = status;
     q.part = nullptr;
     q.state = nullptr;
+    q.state_parts = nullptr;
     q.state_stride = p.state_stride;
     q.out_a = nullptr;
     q.out_b = nullptr;
@@ -405,6 +406,7 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
     if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
     auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, tkr, tk, tv, st); };
     if ((e = launch()) != cudaSuccess) return e;
+    if (p.unreduced) return cudaSuccess;        // the pieces in `ws` are the result
     return reduce_partials(q, state, st);
 }
 
@@ -427,6 +429,7 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
     Params q = make_params(p, dtype, s);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = state;
+    if (p.unreduced) q.state_parts = state;
     q.out_a = o;
     CUtensorMap tqr, tq, to;
     cudaError_t e;
@@ -464,6 +467,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     Params q = make_params(p, dtype, s);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = state;
+    if (p.unreduced) q.state_parts = state;
     q.part = static_cast<float*>(ws);
     q.out_a = dec ? dq_rope : dq;
     q.out_b = dq;
@@ -476,6 +480,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     if ((e = make_map(&tdqr, dec ? dq_rope : dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, tqr, tq, tdo, tdq, tdqr, st); };
     if ((e = launch()) != cudaSuccess) return e;
+    if (p.unreduced) return cudaSuccess;
     return reduce_partials(q, dstate, st);
 }
 
@@ -501,6 +506,7 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
     Params q = make_params(p, dtype, s);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = dstate;
+    if (p.unreduced) q.state_parts = dstate;
     q.out_a = dec ? dk_rope : dk;      // kernels without a staged output tile store through these
     q.out_b = dv;
     CUtensorMap tkr, tv, tdk, tdkr, tdv;

@@ -14,6 +14,7 @@ LIB_PATH = os.environ.get("FLASH_BLA_LIB") or os.path.join(_HERE, "lib", "libfla
 
 F32, BF16, F16 = 0, 1, 2
 FLAG_GENERIC = 1
+FLAG_UNREDUCED = 2
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
@@ -111,6 +112,8 @@ def lib():
             getattr(L, n).argtypes = [_P]
         L.fbla_kernel_path.restype = ctypes.c_int
         L.fbla_kernel_path.argtypes = [_P]
+        L.fbla_unreduced_state.restype = ctypes.c_int
+        L.fbla_unreduced_state.argtypes = [_P]
         for op in OPS:
             sigs = _DECOUPLED_SIGNATURES if op == "decoupled_la" else _SIGNATURES
             for name, args in sigs.items():

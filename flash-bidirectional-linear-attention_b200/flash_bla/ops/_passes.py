@@ -11,6 +11,7 @@ A caller that shards the sequence over ranks all-reduces ``state`` / ``dstate``
 between the two passes (see ``flash_bla.ops.sharded``).
 """
 import ctypes
+import os
 
 import torch
 
@@ -131,17 +132,23 @@ def bwd_in(op, prob, k, v, dstate, dk, dv, dk_rope=None):
 
 
 # ---- one call per direction (single GPU: nothing happens between the two passes) -------------
+# On the tensor-core kernels the state is left in the per-segment pieces of the reducing pass
+# (FLAG_UNREDUCED): the consuming pass adds them itself, which saves a kernel per direction.  What
+# forward() returns as "state" is then the workspace (a uint8 tensor) and backward() recognises it
+# by that dtype.  FBLA_REDUCED_STATE=1 in the environment switches this off.
 _ws_cache = {}
+_want_unreduced = os.environ.get("FBLA_REDUCED_STATE", "0") != "1"
 
 
 def _sizes(prob):
-    """(state floats, workspace bytes) of a problem; the library is asked once per shape."""
+    """(state floats, workspace bytes, unreduced?) of a problem; the library is asked once per shape."""
     key = (prob.dtype, prob.batch, prob.heads, prob.dk, prob.dv, prob.seq_len, prob.num_seqs, prob.normalize,
            prob.flags, prob.cu_seqlens is not None)
     got = _ws_cache.get(key)
     if got is None:
         L = _C.lib()
-        got = (L.fbla_state_floats(ctypes.byref(prob)), L.fbla_workspace_bytes(ctypes.byref(prob)))
+        got = (L.fbla_state_floats(ctypes.byref(prob)), L.fbla_workspace_bytes(ctypes.byref(prob)),
+               L.fbla_unreduced_state(ctypes.byref(prob)) == 1)
         if got[0] < 0 or got[1] < 0:
             _C.check(1)
         if len(_ws_cache) > 256:
@@ -153,30 +160,38 @@ def _sizes(prob):
 def forward(prob, q, k, v):
     """fwd_state + fwd_out of linear_attention / simple_la / varlen; returns (o, state)."""
     _require_cuda(q, k, v)
-    n_state, n_ws = _sizes(prob)
+    if _want_unreduced:
+        prob.flags |= _C.FLAG_UNREDUCED
+    n_state, n_ws, unreduced = _sizes(prob)
     dev = q.device
-    state = torch.empty(n_state, dtype=torch.float32, device=dev)
     ws = torch.empty(n_ws, dtype=torch.uint8, device=dev) if n_ws else None
+    state = None if unreduced else torch.empty(n_state, dtype=torch.float32, device=dev)
     o = torch.empty_like(v)
     with _C.device_guard(q):
         rc = _C.lib().fbla_linear_attn_fwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                           state.data_ptr(), _C.ptr(ws), n_ws, _C.stream_of(q))
+                                           _C.ptr(state), _C.ptr(ws), n_ws, _C.stream_of(q))
     _C.check(rc)
-    return o, state
+    return o, (ws if unreduced else state)
 
 
 def backward(prob, q, k, v, d_o, state):
-    """bwd_state + bwd_in; returns (dq, dk, dv)."""
+    """bwd_state + bwd_in; returns (dq, dk, dv).  ``state`` is what ``forward`` returned."""
     _require_cuda(q, k, v, d_o, state)
-    n_state, n_ws = _sizes(prob)
+    if state.dtype == torch.uint8:
+        prob.flags |= _C.FLAG_UNREDUCED
+    else:
+        prob.flags &= ~_C.FLAG_UNREDUCED
+    n_state, n_ws, unreduced = _sizes(prob)
+    if unreduced != (state.dtype == torch.uint8):
+        raise RuntimeError("the kernel path changed between forward and backward (unreduced state saved)")
     dev = q.device
-    dstate = torch.empty(n_state, dtype=torch.float32, device=dev)
+    dstate = None if unreduced else torch.empty(n_state, dtype=torch.float32, device=dev)
     ws = torch.empty(n_ws, dtype=torch.uint8, device=dev) if n_ws else None
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     with _C.device_guard(q):
         rc = _C.lib().fbla_linear_attn_bwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(),
                                            state.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                           dstate.data_ptr(), _C.ptr(ws), n_ws, _C.stream_of(q))
+                                           _C.ptr(dstate), _C.ptr(ws), n_ws, _C.stream_of(q))
     _C.check(rc)
     return dq, dk, dv
 

@@ -56,7 +56,8 @@ enum fbla_status {
 };
 
 enum fbla_flags {
-    FBLA_FLAG_GENERIC = 1      /* force the CUDA-core (fp32 FMA) kernels              */
+    FBLA_FLAG_GENERIC = 1,     /* force the CUDA-core (fp32 FMA) kernels              */
+    FBLA_FLAG_UNREDUCED = 2    /* fbla_linear_attn_fwd / _bwd: see fbla_unreduced_state() */
 };
 
 typedef struct fbla_problem {
@@ -113,7 +114,17 @@ int fbla_linear_attn_bwd_in(const fbla_problem *p, const void *k, const void *v,
 /* Both passes of one direction in a single call, for callers on one GPU (nothing to exchange
  * between the passes): forward = fwd_state + fwd_out, backward = bwd_state + bwd_in.  They serve
  * linear_attention, simple_la (normalize = 0) and varlen_linear_attention (cu_seqlens set) alike;
- * `state` / `dstate` are outputs of the first pass and inputs of the second.                   */
+ * `state` / `dstate` are outputs of the first pass and inputs of the second.
+ *
+ * With FBLA_FLAG_UNREDUCED in p->flags and fbla_unreduced_state(p) == 1 (tensor-core kernels,
+ * fixed length) the state is never reduced to one vector per unit: the reducing pass leaves its
+ * per-segment pieces in the workspace and the consuming pass adds them while it stages the state
+ * (same order, same bits), which saves one kernel per direction.  Then
+ *   fbla_linear_attn_fwd: `state` is not written (may be NULL); the WORKSPACE holds the state and
+ *                         must be kept for the backward;
+ *   fbla_linear_attn_bwd: `state` is that forward workspace; `dstate` is not written (may be NULL).
+ * When fbla_unreduced_state(p) is 0 the flag has no effect.                                     */
+int fbla_unreduced_state(const fbla_problem *p);
 int fbla_linear_attn_fwd(const fbla_problem *p, const void *q, const void *k, const void *v, void *o,
                          float *state, void *workspace, size_t workspace_bytes, fbla_stream_t stream);
 int fbla_linear_attn_bwd(const fbla_problem *p, const void *q, const void *k, const void *v,

@@ -328,3 +328,26 @@ def test_cuda_graph_replay_matches_eager():
     o.backward(d_o)
     for a, b in zip(got, (o, eq.grad, ek.grad, ev.grad)):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("shape", [(8, 16, 1024, 64, 64), (2, 4, 4096, 128, 64), (1, 3, 700, 64, 128), (2, 2, 33000, 128, 128)])
+@pytest.mark.parametrize("op", ["linear_attn", "simple_la"])
+def test_unreduced_state_route_gives_the_same_bits(shape, op):
+    """The one-call entry points may leave the state in per-segment pieces that the consuming pass adds
+    itself; both routes add in the same order, so outputs and gradients are bit-identical."""
+    B, H, T, K, V = shape
+    q, k, v, d_o = (x.cuda() for x in make_inputs(41, (B, H, T, K), (B, H, T, V), torch.bfloat16))
+    fn = linear_attention if op == "linear_attn" else simple_la
+    res = []
+    saved = P._want_unreduced
+    try:
+        for want in (True, False):
+            P._want_unreduced = want
+            xs = [x.clone().requires_grad_() for x in (q, k, v)]
+            o = fn(*xs)
+            o.backward(d_o)
+            res.append([o] + [x.grad for x in xs])
+    finally:
+        P._want_unreduced = saved
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
