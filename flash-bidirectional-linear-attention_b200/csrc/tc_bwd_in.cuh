@@ -98,8 +98,10 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ptx::griddep_launch();
     Params pv = p_in;
     if (VARLEN) {
+        ptx::griddep_wait();                // cu_seqlens may come from the previous kernel
         int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
         build_plan(plan, p_in.cu, p_in.num_seqs);
         pv.plan = plan;
@@ -139,6 +141,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (!VARLEN) ptx::griddep_wait();       // everything above overlaps the previous kernel's tail
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer: v tile then kr tile ----------------

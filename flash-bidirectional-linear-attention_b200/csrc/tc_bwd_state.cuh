@@ -100,8 +100,10 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ptx::griddep_launch();
     Params pv = p_in;
     if (VARLEN) {
+        ptx::griddep_wait();                // cu_seqlens may come from the previous kernel
         int32_t* plan = reinterpret_cast<int32_t*>(smem_raw + (Cfg::kSmemBytes - kPlanBytes));
         build_plan(plan, p_in.cu, p_in.num_seqs);
         pv.plan = plan;
@@ -150,6 +152,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (!VARLEN) ptx::griddep_wait();       // everything above overlaps the previous kernel's tail
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer: qr tile, (q tile,) dO tile ----------------

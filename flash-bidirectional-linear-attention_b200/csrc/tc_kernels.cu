@@ -4,7 +4,9 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
+#include <utility>
 
 #include "tc_bwd_in.cuh"
 #include "tc_bwd_state.cuh"
@@ -189,6 +191,28 @@ cudaError_t set_smem(K kernel, int bytes, bool (&done)[64]) {
     return e;
 }
 
+// Launch with the programmatic-serialization attribute: the kernel may become resident while the
+// previous kernel of the stream is still draining (it calls griddepcontrol.wait before it touches
+// global memory).  FBLA_NO_PDL=1 in the environment restores ordinary launches.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, int smem, cudaStream_t st, Args&&... args) {
+    static const bool plain = [] {
+        const char* e = getenv("FBLA_NO_PDL");
+        return e != nullptr && e[0] == '1';
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = plain ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 int mode_of(const KParams& p, bool decoupled) { return !p.normalize ? kSimple : (decoupled ? kDecoupled : kLinear); }
 
 cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
@@ -208,9 +232,9 @@ cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUte
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tkr, tk, tv, q);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tk, tv, q);
     note_launches(1);
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
@@ -223,9 +247,9 @@ cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtens
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tqr, tq, to, q);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tqr, tq, to, q);
     note_launches(1);
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
@@ -238,9 +262,9 @@ cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUte
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    kernel<<<q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st>>>(tqr, tq, tdo, tdq, tdqr, q);
+    e = launch_dependent(kernel, q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st, tqr, tq, tdo, tdq, tdqr, q);
     note_launches(1);
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
@@ -253,9 +277,9 @@ cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtenso
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    kernel<<<q.sch.ctas, kThreads, Cfg::kSmemBytes, st>>>(tkr, tv, tdk, tdkr, tdv, q);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tv, tdk, tdkr, tdv, q);
     note_launches(1);
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // Expands to a switch over (dk, dv, mode, 16-bit type); `CALL` names one of the launch_* templates.

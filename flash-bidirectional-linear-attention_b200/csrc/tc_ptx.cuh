@@ -217,6 +217,13 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 }
 
 // 32-byte global store (one full sector per thread).
+// Programmatic dependent launch: `griddep_launch` lets the next kernel of the stream (if it was
+// launched with the programmatic-serialization attribute) start its prologue as soon as SM
+// resources free up; `griddep_wait` blocks until the previous kernel of the stream has completed
+// and its writes are visible.  Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void st_global_32B(void* ptr, const uint4& a, const uint4& b) {
     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a.x), "r"(a.y), "r"(a.z),
                  "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
