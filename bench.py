@@ -87,7 +87,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.001)
+            time.sleep(0.005)
 
     def stop(self):
         self._stop_evt.set()

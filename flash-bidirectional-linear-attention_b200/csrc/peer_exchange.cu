@@ -61,11 +61,19 @@ peer_state_sum_kernel(PeerTable t, int world, int rank, long long n4, unsigned i
     }
     __syncthreads();
     if (gave_up) return;
+    // All peers' loads of an element are issued before the first add (NVLink latency is paid once, not
+    // `world` times); the adds then run in rank order.  __ldcg = L2 only: a peer's line may differ from
+    // the one read two exchanges ago.
     for (long long i = (long long)blockIdx.x * kPeerThreads + threadIdx.x; i < n4; i += (long long)gridDim.x * kPeerThreads) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < world; ++r) {
-            const float4 x = __ldcg(t.buf[r] + i);      // L2 only: a peer's line may differ from the one read two exchanges ago
-            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        for (int r0 = 0; r0 < world; r0 += 8) {
+            float4 x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (r0 + u < world) x[u] = __ldcg(t.buf[r0 + u] + i);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (r0 + u < world) { acc.x += x[u].x; acc.y += x[u].y; acc.z += x[u].z; acc.w += x[u].w; }
         }
         out[i] = acc;
     }
@@ -99,7 +107,7 @@ extern "C" int fbla_peer_state_sum(int world, int rank, const void* const* peer_
         return fbla::api_fail(FBLA_ERR_DEVICE, "a kernel gave up a bounded wait (site %d); results are invalid", s);
     const long long n4 = n_floats / 4;
     long long blocks = (n4 + fbla::kPeerThreads - 1) / fbla::kPeerThreads;
-    if (blocks > 296) blocks = 296;
+    if (blocks > 592) blocks = 592;
     fbla::peer_state_sum_kernel<<<(unsigned)blocks, fbla::kPeerThreads, 0, (cudaStream_t)stream>>>(
         t, world, rank, n4, epoch, reinterpret_cast<float4*>(out), fbla::tc_status_word());
     fbla::note_launches(1);
