@@ -4,7 +4,7 @@
 other operators.  Timing: CUDA events around back-to-back calls of the public API, median of
 ``--reps`` repetitions after warm-up; inputs are larger than L2 from T=4096 up at B=8.
 
-    python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|simple_la|decoupled_la|varlen|pisa|all]
+    python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|blhd|simple_la|decoupled_la|varlen|pisa|all]
                                        [--long] [--impl b200|reference [--ref-path DIR]]
 
 ``--long`` adds ``simple_la`` at B4 H32 T262144 D128 (8.6 GB per tensor, about 70 GB on the device).
@@ -125,6 +125,21 @@ def main():
                 tg = timed(replay, args.reps)
                 print(f"{'':14s} {'  replayed from a CUDA graph':28s} {'':33s}   fwd+bwd {tg:8.4f} ms "
                       f"({11 * P / tg / 1e6:6.0f} GB/s, {B * T / tg * 1e3:.3e} tokens/s)", flush=True)
+    if args.op in ("all", "blhd") and IMPL != "reference":
+        # projection-layout inputs (B, L, H, D): the op on them as they are, against the reference layers' route
+        # (permute + contiguous into (B, H, L, D), the op, permute back)
+        for T in (4096, 32768):
+            q, k, v = pos(B, T, H, D), pos(B, T, H, D), gau(B, T, H, D)
+            do = torch.randn_like(v)
+            P = B * H * T * D * 2
+            f, fb = both(lambda: linear_attention(q, k, v, layout="blhd"), (q, k, v), do)
+            row("linear_attn", f"(B,L,H,D) in place, T{T}", f, fb, B * T, 4 * P, 11 * P)
+
+            def via_copies():
+                qq, kk, vv = (x.permute(0, 2, 1, 3).contiguous() for x in (q, k, v))
+                return linear_attention(qq, kk, vv).permute(0, 2, 1, 3).contiguous()
+            f, fb = both(via_copies, (q, k, v), do)
+            row("linear_attn", f"(B,L,H,D) via permutes, T{T}", f, fb, B * T, 4 * P, 11 * P)
     if args.op in ("all", "simple_la"):
         for (b, h, T, d) in ((4, 32, 32768, 128), (B, H, 32768, D)) + (((4, 32, 262144, 128),) if args.long else ()):
             q, k, v = gau(b, h, T, d), gau(b, h, T, d), gau(b, h, T, d)

@@ -81,6 +81,44 @@ pisa_first_order_kernel(PisaParams p, const float* __restrict__ kv, const float*
     h[(size_t)bh * p.dk * p.dv + i] = kv[(size_t)bh * p.dk * p.dv + i] - s;
 }
 
+// p-norm of each block's first-order state hc_c = (K_c - kc_c)^T V_c over its dk*dv entries (the
+// selection bias of use_bias=True).  One CTA per (block, batch*head): the centred keys and the values
+// of the block sit in shared memory as fp32, every thread forms dk*dv/256 entries of hc_c.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pisa_block_hnorm_kernel(PisaParams p, const T* __restrict__ k, const T* __restrict__ v, const float* __restrict__ kc,
+                        float pnorm, float* __restrict__ hnorm) {
+    extern __shared__ float smem[];
+    const int K = p.dk, V = p.dv;
+    float* ks = smem;                   // [bs][K]  k - kc
+    float* vs = ks + p.bs * K;          // [bs][V]
+    __shared__ float red[8];
+    const int c = blockIdx.x, bh = blockIdx.y;
+    const int t0 = c * p.bs;
+    const int len = min(p.bs, p.T - t0);
+    const size_t row0 = (size_t)bh * p.T + t0;
+    const float* kcb = kc + ((size_t)bh * p.nt + c) * K;
+    for (int i = threadIdx.x; i < len * K; i += 256) ks[i] = to_f<T>(k[row0 * K + i]) - kcb[i % K];
+    for (int i = threadIdx.x; i < len * V; i += 256) vs[i] = to_f<T>(v[row0 * V + i]);
+    __syncthreads();
+    float acc = 0.f;
+    for (int e = threadIdx.x; e < K * V; e += 256) {
+        const int a = e / V, b = e - a * V;
+        float h = 0.f;
+        for (int t = 0; t < len; ++t) h = fmaf(ks[t * K + a], vs[t * V + b], h);
+        const float m = fabsf(h);
+        acc += pnorm == 2.f ? m * m : (pnorm == 1.f ? m : __powf(m, pnorm));
+    }
+    acc = wsum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int w = 0; w < 8; ++w) s += red[w];
+        hnorm[(size_t)bh * p.nt + c] = pnorm == 2.f ? sqrtf(s) : (pnorm == 1.f ? s : __powf(s, 1.f / pnorm));
+    }
+}
+
 // One CTA per (query block, batch*head); warp w owns query rows w, w+8, ...; inside a group of 32
 // keys the lanes own one key each for the logits and a slice of the value columns for p.V.
 template <typename T>
@@ -301,6 +339,26 @@ int fbla_pisa_block_stats(const fbla_pisa_problem* p, const void* q, const void*
     fbla::note_launches(1);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "block statistics: %s", cudaGetErrorString(e));
+}
+
+int fbla_pisa_block_hnorm(const fbla_pisa_problem* p, const void* k, const void* v, const float* kc, float pnorm,
+                          float* hnorm, fbla_stream_t stream) {
+    fbla::PisaArgs a;
+    if (int rc = fbla::resolve_pisa(p, &a)) return rc;
+    if (!k || !v || !kc || !hnorm) return fbla::api_fail(FBLA_ERR_INVALID, "a tensor pointer is NULL");
+    if (!(pnorm > 0.f)) return fbla::api_fail(FBLA_ERR_INVALID, "the norm order must be positive");
+    dim3 grid(a.kp.nt, a.bh);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t smem = sizeof(float) * (size_t)a.kp.bs * (a.kp.dk + a.kp.dv);
+    cudaError_t e = cudaSuccess;
+    PISA_BY_DTYPE(a.dtype, {
+        auto kern = fbla::pisa_block_hnorm_kernel<T>;
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) kern<<<grid, 256, smem, st>>>(a.kp, (const T*)k, (const T*)v, kc, pnorm, hnorm);
+    });
+    fbla::note_launches(1);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "block norms: %s", cudaGetErrorString(e));
 }
 
 int fbla_pisa_first_order_state(const fbla_pisa_problem* p, const float* kv, const float* kc, const float* vc,

@@ -86,7 +86,7 @@ def exported_symbols():
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
     names += ["fbla_linear_attn_fwd", "fbla_linear_attn_bwd"]
     names.append("fbla_linear_attn_fwd_state_noalloc")
-    names += ["fbla_pisa_block_stats", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd",
+    names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd",
               "fbla_pisa_bwd_scratch_floats"]
     names.append("fbla_peer_state_sum")
     return names
@@ -131,6 +131,8 @@ def lib():
             f = getattr(L, name)
             f.restype = ctypes.c_int
             f.argtypes = [_PP] + [_vp] * n_ptr          # tensor pointers, then the stream
+        L.fbla_pisa_block_hnorm.restype = ctypes.c_int
+        L.fbla_pisa_block_hnorm.argtypes = [_PP, _vp, _vp, _vp, ctypes.c_float, _vp, _vp]   # k, v, kc, p, hnorm, stream
         L.fbla_peer_state_sum.restype = ctypes.c_int
         L.fbla_peer_state_sum.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
                                           ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64, ctypes.c_uint32, _vp, _vp]

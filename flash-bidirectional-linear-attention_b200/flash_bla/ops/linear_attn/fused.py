@@ -59,6 +59,7 @@ def linear_attention(
     v: torch.Tensor,
     scale: Optional[float] = None,
     eps: float = 1e-6,
+    layout: str = "bhld",
 ) -> torch.Tensor:
     r"""
     Args:
@@ -67,7 +68,36 @@ def linear_attention(
         v: values of shape `(B, H, L, V)`
         scale: multiplies the values inside the state; defaults to `1 / L`.
         eps: added to the normaliser `q . mean_t k`.
+        layout: `"bhld"` (the reference's layout, default) or `"blhd"`: q, k `(B, L, H, K)`, v and the
+            result `(B, L, H, V)` -- the layout a projection followed by a head split produces, so the
+            caller's `permute(0, 2, 1, 3).contiguous()` copies (reference layers, e.g.
+            `flash_bla/layers/mlla.py:74-80`) are not needed.  Served by the packed-sequence kernels.
     """
+    if layout == "blhd":
+        return _linear_attention_blhd(q, k, v, scale, eps)
+    if layout != "bhld":
+        raise ValueError(f"layout must be 'bhld' or 'blhd', got {layout!r}")
     if scale is None:
         scale = k.shape[-2] ** -1.0
     return LinearAttnFunction.apply(q, k, v, scale, eps)
+
+
+_cu_cache = {}
+
+
+def _linear_attention_blhd(q, k, v, scale, eps):
+    # (B, L, H, D) contiguous is the packed layout with B sequences of L tokens each.
+    from flash_bla.ops.linear_attn.varlen import VarlenLinearAttnFunction
+    if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
+        raise ValueError(f"expected q, k of shape (B, L, H, K) and v of shape (B, L, H, V); got "
+                         f"{tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    B, L, H, K = q.shape
+    key = (B, L, q.device)
+    cu = _cu_cache.get(key)
+    if cu is None:
+        if len(_cu_cache) > 64:
+            _cu_cache.clear()
+        cu = _cu_cache[key] = torch.arange(0, (B + 1) * L, max(L, 1), dtype=torch.int32, device=q.device)[:B + 1]
+    o = VarlenLinearAttnFunction.apply(q.reshape(B * L, H, K), k.reshape(B * L, H, K), v.reshape(B * L, H, v.shape[-1]),
+                                       cu, max(L, 1), None if scale is None else float(scale), eps)
+    return o.view(B, L, H, v.shape[-1])

@@ -68,6 +68,21 @@ def first_order_state(k, v, kc, vc, block_size):
     return h
 
 
+def block_state_norms(k, v, kc, block_size, p=2):
+    """fp32 ``(B,H,NT)``: p-norm of every block's first-order state (K_c - kc_c)^T V_c over its K*V
+    entries (``torch.norm(hc.flatten(-2, -1), p=p, dim=-1)`` in the reference, kernel.py:172-173),
+    without materialising the per-block states."""
+    k, v = k.contiguous(), v.contiguous()
+    B, H, T, K = k.shape
+    prob = _problem(k, v, block_size, 1, 1.0)
+    nt = kc.shape[-2]
+    out = torch.empty(B, H, nt, dtype=torch.float32, device=k.device)
+    with _C.device_guard(k):
+        _C.check(_C.lib().fbla_pisa_block_hnorm(ctypes.byref(prob), k.data_ptr(), v.data_ptr(), kc.contiguous().data_ptr(),
+                                                float(p), out.data_ptr(), _C.stream_of(k)))
+    return out
+
+
 def chunk_reduce(q, k, v, chunk_size):
     """Block means of q and k and block sums of v, in the dtype of the inputs."""
     qc, kc, vc = block_statistics(q, k, v, chunk_size)
@@ -76,18 +91,22 @@ def chunk_reduce(q, k, v, chunk_size):
 
 def fused_chunk_reduce(q, k, v, chunk_size, use_bias=False, p=2):
     """``(qc, kc, vc, h, bias)`` in the dtype of the inputs; ``bias`` is ``None`` unless ``use_bias``."""
-    if use_bias:
-        raise NotImplementedError("use_bias=True (per-block norm of the first-order state) is not built yet")
     qc, kc, vc = block_statistics(q, k, v, chunk_size)
     h = first_order_state(k.contiguous(), v.contiguous(), kc, vc, chunk_size)
-    return qc.to(q.dtype), kc.to(k.dtype), vc.to(v.dtype), h.to(v.dtype), None
+    bias = None
+    if use_bias:        # (B, H, 1, NT), as the reference's h_norm[..., None, :]
+        bias = block_state_norms(k, v, kc, chunk_size, p).to(v.dtype)[..., None, :]
+    return qc.to(q.dtype), kc.to(k.dtype), vc.to(v.dtype), h.to(v.dtype), bias
 
 
-def select_blocks(qc, kc, scale, density, dtype):
+def select_blocks(qc, kc, scale, density, dtype, bias=None):
     """Indices ``(B,H,NT,NS)`` of the key blocks each query block attends exactly: top-k of the
-    block-mean scores computed in the dtype of the inputs, ``NS = max(1, int(density * NT))``."""
+    block-mean scores computed in the dtype of the inputs, ``NS = max(1, int(density * NT))``.
+    ``bias`` ``(B,H,1,NT)``: rank ``softmax(score + log(bias + 1e-5))`` instead (kernel.py:314-315)."""
     nt = kc.shape[-2]
     score = torch.einsum('bhid,bhjd->bhij', qc.to(dtype), (kc * scale).to(dtype))
+    if bias is not None:
+        score = torch.softmax(score + torch.log(bias.to(dtype) + 1e-5), dim=-1)
     top_k = max(1, int(density * nt))
     return torch.topk(score, k=top_k, dim=-1).indices
 
@@ -136,11 +155,12 @@ class PiecewiseSparseAttnFunction(torch.autograd.Function):
     block indices as constants."""
 
     @staticmethod
-    def forward(ctx, q, k, v, density, block_size, scale):
+    def forward(ctx, q, k, v, density, block_size, scale, use_bias=False):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         qc, kc, vc = block_statistics(q, k, v, block_size)
         h = first_order_state(k, v, kc, vc, block_size)
-        indices = select_blocks(qc, kc, scale, density, q.dtype)
+        bias = block_state_norms(k, v, kc, block_size)[..., None, :] if use_bias else None
+        indices = select_blocks(qc, kc, scale, density, q.dtype, bias)
         o, stats = attention_forward(q, k, v, kc, vc, h, indices, block_size, scale, want_stats=True)
         ctx.save_for_backward(q, k, v, o, kc, vc, h, indices, stats)
         ctx.block_size, ctx.scale = block_size, scale
@@ -150,7 +170,7 @@ class PiecewiseSparseAttnFunction(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, kc, vc, h, indices, stats = ctx.saved_tensors
         dq, dk, dv = attention_backward(q, k, v, o, do, kc, vc, h, indices, stats, ctx.block_size, ctx.scale)
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
 def piecewise_sparse_attention(q, k, v, density=0.1, block_size=64, scale=None, use_bias=False):
@@ -163,9 +183,7 @@ def piecewise_sparse_attention(q, k, v, density=0.1, block_size=64, scale=None, 
         use_bias: add the log of the blocks' first-order norm to the selection scores.
     Returns the attention output `(B, H, T, V)`.
     """
-    if use_bias:
-        raise NotImplementedError("use_bias=True (per-block norm of the first-order state) is not built yet")
     _check(q, k, v)
     K = k.shape[-1]
     scale = K ** -0.5 if scale is None else scale
-    return PiecewiseSparseAttnFunction.apply(q, k, v, density, block_size, scale)
+    return PiecewiseSparseAttnFunction.apply(q, k, v, density, block_size, scale, bool(use_bias))

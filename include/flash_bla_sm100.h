@@ -215,6 +215,11 @@ typedef struct fbla_pisa_problem {
 
 int fbla_pisa_block_stats(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,
                           float *qc, float *kc, float *vc, fbla_stream_t stream);
+/* hnorm (batch, heads, NT) fp32: p-norm (order `pnorm` > 0) of each block's first-order state
+ * (K_c - kc_c)^T V_c over its dk*dv entries -- the selection bias of use_bias=True
+ * (kernel.py:118 and :172-173, where the reference materialises all the per-block states).    */
+int fbla_pisa_block_hnorm(const fbla_pisa_problem *p, const void *k, const void *v, const float *kc,
+                          float pnorm, float *hnorm, fbla_stream_t stream);
 int fbla_pisa_first_order_state(const fbla_pisa_problem *p, const float *kv, const float *kc,
                                 const float *vc, float *h, fbla_stream_t stream);
 int fbla_pisa_fwd(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,

@@ -218,13 +218,36 @@ def pisa_block_stats(q, k, v, block_size: int, acc=torch.float64):
     return torch.stack(qc, -2), torch.stack(kc, -2), torch.stack(vc, -2), h
 
 
-def pisa_select(qc, kc, scale: float, density: float):
-    """Indices of the top-scoring key blocks per query block; kernel.py:313-318
-    (``use_bias=False`` branch)."""
-    nt = kc.shape[-2]
+def pisa_block_hnorm(k, v, block_size: int, p: float = 2, acc=torch.float64):
+    """p-norm of every block's first-order state ``hc_c = (K_c - kc_c)^T V_c`` taken over
+    its dk*dv entries: the selection bias of ``use_bias=True``; kernel.py:118 (hc),
+    :172-173 (norm).  Shape (..., NT)."""
+    k_, v_ = _f(k, acc), _f(v, acc)
+    T = k_.shape[-2]
+    nt = (T + block_size - 1) // block_size
+    out = []
+    for c in range(nt):
+        lo, hi = c * block_size, min(T, (c + 1) * block_size)
+        kb, vb = k_[..., lo:hi, :], v_[..., lo:hi, :]
+        hc = (kb - kb.mean(dim=-2, keepdim=True)).transpose(-2, -1) @ vb
+        out.append(torch.norm(hc.flatten(-2, -1), p=p, dim=-1))
+    return torch.stack(out, -1)
+
+
+def pisa_scores(qc, kc, scale: float, h_norm=None):
+    """Block scores the selection ranks; with the bias of ``use_bias=True`` they are
+    ``softmax(score + log(h_norm + 1e-5))`` over the key blocks.  kernel.py:313-315."""
     score = torch.einsum('...id,...jd->...ij', qc, kc * scale)
+    if h_norm is not None:
+        score = torch.softmax(score + torch.log(h_norm[..., None, :] + 1e-5), dim=-1)
+    return score
+
+
+def pisa_select(qc, kc, scale: float, density: float, h_norm=None):
+    """Indices of the top-scoring key blocks per query block; kernel.py:313-318."""
+    nt = kc.shape[-2]
     top_k = max(1, int(density * nt))
-    return torch.topk(score, k=top_k, dim=-1).indices
+    return torch.topk(pisa_scores(qc, kc, scale, h_norm), k=top_k, dim=-1).indices
 
 
 def pisa_fwd_given(q, k, v, kc, vc, h, indices, block_size: int, scale: float,

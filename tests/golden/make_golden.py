@@ -121,7 +121,9 @@ def main(ref_root):
     for name, (B, H, T, K, V), bs, density in [
         ("pisa_a", (1, 2, 160, 16, 16), 16, 0.3),     # T multiple of the block
         ("pisa_b", (1, 1, 150, 32, 32), 32, 0.25),    # ragged last block
+        ("pisa_c", (1, 2, 200, 16, 32), 32, 0.3),     # use_bias=True (selection biased by the block norms of hc)
     ]:
+        use_bias = name == "pisa_c"
         g = torch.Generator().manual_seed(5)
         q = torch.randn(B, H, T, K, generator=g)
         k = torch.randn(B, H, T, K, generator=g)
@@ -136,6 +138,11 @@ def main(ref_root):
             q, k, v, qc, kc, vc, hc, T, N=NT, K=K, V=V, BT=bs, BK=K, BV=V)
         h = hc.sum(dim=2)
         score = torch.einsum('bhid,bhjd->bhij', qc, kc * scale)
+        extra = {}
+        if use_bias:       # kernel.py:172-173 and :314-315
+            h_norm = torch.norm(hc.flatten(-2, -1), p=2, dim=-1)
+            score = torch.softmax(score + torch.log(h_norm[..., None, :] + 1e-5), dim=-1)
+            extra = dict(h_norm=_np(h_norm), score=_np(score))
         top_k = max(1, int(density * NT))
         indices = torch.topk(score, k=top_k, dim=-1).indices
         o = torch.empty_like(v)
@@ -144,7 +151,7 @@ def main(ref_root):
             NT=NT, NS=top_k, GROUP_SIZE=32)
         np.savez(os.path.join(HERE, name + ".npz"), q=_np(q), k=_np(k), v=_np(v), qc=_np(qc),
                  kc=_np(kc), vc=_np(vc), h=_np(h), indices=indices.numpy(), o=_np(o),
-                 block_size=np.int64(bs), density=np.float64(density), scale=np.float64(scale))
+                 block_size=np.int64(bs), density=np.float64(density), scale=np.float64(scale), **extra)
     print("golden fixtures written to", HERE)
 
 

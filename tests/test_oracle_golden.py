@@ -84,6 +84,22 @@ def test_pisa_forward(name):
     assert O.rel_l2(o, g["o"]) < 1e-4
 
 
+def test_pisa_forward_with_bias():
+    """use_bias=True: the selection ranks softmax(score + log(norm of each block's first-order state))."""
+    g = load("pisa_c")
+    bs = int(g["block_size"])
+    qc, kc, vc, h = O.pisa_block_stats(g["q"], g["k"], g["v"], bs)
+    h_norm = O.pisa_block_hnorm(g["k"], g["v"], bs)
+    assert O.rel_l2(h_norm, g["h_norm"]) < 1e-4
+    assert O.rel_l2(O.pisa_scores(qc, kc, g["scale"], h_norm), g["score"]) < 1e-4
+    idx = O.pisa_select(qc, kc, g["scale"], g["density"], h_norm)
+    assert torch.equal(idx.sort(-1).values, g["indices"].sort(-1).values)
+    # the bias changes the selection on this fixture, i.e. the case does exercise it
+    assert not torch.equal(O.pisa_select(qc, kc, g["scale"], g["density"]).sort(-1).values, g["indices"].sort(-1).values)
+    o, _ = O.pisa_fwd(g["q"], g["k"], g["v"], g["density"], bs, g["scale"], indices=g["indices"])
+    assert O.rel_l2(o, g["o"]) < 1e-4
+
+
 def test_pisa_backward_matches_finite_differences():
     torch.manual_seed(0)
     q, k, v = (torch.randn(1, 1, 40, 8, dtype=torch.float64) for _ in range(3))

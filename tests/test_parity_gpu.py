@@ -351,3 +351,20 @@ def test_unreduced_state_route_gives_the_same_bits(shape, op):
         P._want_unreduced = saved
     for a, b in zip(*res):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(2, 1000, 4, 64, 64), (3, 257, 2, 32, 48), (1, 4096, 16, 64, 128)])
+def test_linear_attention_blhd_layout(shape, dtype):
+    """layout="blhd" takes (B, L, H, D) tensors as they are; results match the oracle on the permuted tensors."""
+    B, L, H, K, V = shape
+    q, k, v, d_o = make_inputs(51, (B, H, L, K), (B, H, L, V), dtype)
+    rq, rk, rv = (x.double() for x in (q, k, v))
+    ro = O.linear_attn_fwd(rq, rk, rv, None, 1e-6)
+    rdq, rdk, rdv = O.linear_attn_bwd(rq, rk, rv, d_o.double(), None, 1e-6)
+    xs = [x.cuda().permute(0, 2, 1, 3).contiguous().requires_grad_() for x in (q, k, v)]
+    o = linear_attention(*xs, layout="blhd")
+    assert o.shape == (B, L, H, V) and o.is_contiguous()
+    o.backward(d_o.cuda().permute(0, 2, 1, 3).contiguous())
+    for got, ref, name in ((o, ro, "o"), (xs[0].grad, rdq, "dq"), (xs[1].grad, rdk, "dk"), (xs[2].grad, rdv, "dv")):
+        check(got.permute(0, 2, 1, 3), ref, dtype, f"blhd{shape}.{name}")

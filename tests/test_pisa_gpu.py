@@ -31,6 +31,26 @@ def test_golden(name):
     assert O.rel_l2(o2.cpu(), g["o"]) < 1e-4
 
 
+def test_golden_with_bias():
+    """use_bias=True against the reference-generated fixture: block norms, biased selection, output."""
+    from flash_bla.ops.piecewise_attn.kernel import block_state_norms
+    g = load_golden("pisa_c")
+    bs = int(g["block_size"])
+    q, k, v = (g[x].cuda() for x in ("q", "k", "v"))
+    qc, kc, vc = block_statistics(q, k, v, bs)
+    hn = block_state_norms(k, v, kc, bs)
+    assert O.rel_l2(hn.cpu(), g["h_norm"]) < 1e-5
+    for p_ in (1, 3):
+        assert O.rel_l2(block_state_norms(k, v, kc, bs, p_).cpu(), O.pisa_block_hnorm(g["k"], g["v"], bs, p_)) < 1e-4
+    idx = select_blocks(qc, kc, g["scale"], g["density"], torch.float32, hn[..., None, :])
+    assert torch.equal(idx.sort(-1).values.cpu(), g["indices"].sort(-1).values)
+    o = piecewise_sparse_attention(q, k, v, density=g["density"], block_size=bs, scale=g["scale"], use_bias=True)
+    assert O.rel_l2(o.cpu(), g["o"]) < 1e-4
+    # and it differs from the unbiased operator on this fixture
+    o0 = piecewise_sparse_attention(q, k, v, density=g["density"], block_size=bs, scale=g["scale"])
+    assert O.rel_l2(o0.cpu(), g["o"]) > 1e-3
+
+
 CASES = [
     (1, 2, 300, 64, 64, 64, 0.2),
     (2, 2, 1000, 128, 128, 64, 0.1),
@@ -118,7 +138,7 @@ def test_reference_surface():
     q = torch.randn(1, 2, 128, 32, device="cuda")
     qc, kc, vc, h, bias = fused_chunk_reduce(q, q, q, 32)
     assert qc.shape == (1, 2, 4, 32) and h.shape == (1, 2, 32, 32) and bias is None and qc.dtype == q.dtype
-    with pytest.raises(NotImplementedError):
-        piecewise_sparse_attention(q, q, q, use_bias=True)
+    *_, bias = fused_chunk_reduce(q, q, q, 32, use_bias=True)
+    assert bias.shape == (1, 2, 1, 4) and bias.dtype == q.dtype
     with pytest.raises(RuntimeError):
         piecewise_sparse_attention(q.cpu(), q.cpu(), q.cpu())
