@@ -88,7 +88,7 @@ def exported_symbols():
     names.append("fbla_linear_attn_fwd_state_noalloc")
     names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd",
               "fbla_pisa_bwd_scratch_floats"]
-    names.append("fbla_peer_state_sum")
+    names += ["fbla_peer_state_sum", "fbla_peer_state_sum2"]
     return names
 
 
@@ -131,6 +131,9 @@ def lib():
             f = getattr(L, name)
             f.restype = ctypes.c_int
             f.argtypes = [_PP] + [_vp] * n_ptr          # tensor pointers, then the stream
+        L.fbla_peer_state_sum2.restype = ctypes.c_int
+        L.fbla_peer_state_sum2.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.POINTER(ctypes.c_void_p)] * 3 + \
+            [ctypes.c_int64, ctypes.c_uint32, _vp, _vp]
         L.fbla_pisa_block_hnorm.restype = ctypes.c_int
         L.fbla_pisa_block_hnorm.argtypes = [_PP, _vp, _vp, _vp, ctypes.c_float, _vp, _vp]   # k, v, kc, p, hnorm, stream
         L.fbla_peer_state_sum.restype = ctypes.c_int

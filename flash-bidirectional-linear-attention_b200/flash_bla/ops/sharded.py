@@ -56,7 +56,7 @@ class _PeerExchange:
         from flash_bla import _C
         self._C, self._ct = _C, ctypes
         self.n = n
-        self.data = symm.empty(2 * n, dtype=torch.float32, device=device)
+        self.data = symm.empty(3 * n, dtype=torch.float32, device=device)     # two state buffers, one gather buffer
         self.flags = symm.empty(64, dtype=torch.int32, device=device)
         self.flags.zero_()
         hd = symm.rendezvous(self.data, group)
@@ -67,7 +67,10 @@ class _PeerExchange:
         self._hd, self._hf = hd, hf
         arr = ctypes.c_void_p * self.world
         self._bufs = [arr(*[int(p) + b * n * 4 for p in hd.buffer_ptrs]) for b in (0, 1)]
+        self._gather = arr(*[int(p) + 2 * n * 4 for p in hd.buffer_ptrs])
         self._flags = arr(*[int(p) for p in hf.buffer_ptrs])
+        # more than two ranks: each rank adds one slice and hands it round (two rounds of flags)
+        self.two_phase = self.world > 2 and os.environ.get("FBLA_PEER_ONE_PHASE", "0") != "1"
         self.epoch = 0
         torch.cuda.synchronize(device)
 
@@ -80,8 +83,13 @@ class _PeerExchange:
         self.epoch += 1
         out = torch.empty(self.n, dtype=torch.float32, device=self.data.device)
         with self._C.device_guard(out):
-            rc = self._C.lib().fbla_peer_state_sum(self.world, self.rank, self._bufs[self.epoch & 1], self._flags,
-                                                   self.n, self.epoch, out.data_ptr(), self._C.stream_of(out))
+            if self.two_phase:
+                rc = self._C.lib().fbla_peer_state_sum2(self.world, self.rank, self._bufs[self.epoch & 1], self._gather,
+                                                        self._flags, self.n, self.epoch, out.data_ptr(),
+                                                        self._C.stream_of(out))
+            else:
+                rc = self._C.lib().fbla_peer_state_sum(self.world, self.rank, self._bufs[self.epoch & 1], self._flags,
+                                                       self.n, self.epoch, out.data_ptr(), self._C.stream_of(out))
         self._C.check(rc)
         return out
 

@@ -259,6 +259,18 @@ int fbla_peer_state_sum(int world, int rank, const void *const *peer_states,
                         void *const *peer_flags, int64_t n_floats, uint32_t epoch, float *out,
                         fbla_stream_t stream);
 
+/* The same sum in two phases, for more than two ranks: each rank adds its own 1/world slice from
+ * all peers and stores it into every peer's gather buffer, a second round of flags follows, then
+ * each rank copies its gather buffer to `out` (2 (world-1)/world of the state crosses NVLink per
+ * rank instead of world-1 times the state).
+ *   peer_gather[r]: rank r's gather buffer of n_floats floats, mapped into this process;
+ *   peer_flags[r] : rank r's array of at least 64 32-bit words (first round [0,16), second round
+ *                   [16,32), word 48 a device-local counter), all zero before the first exchange.
+ * One state buffer and one gather buffer suffice (the second round of flags orders the reuse).  */
+int fbla_peer_state_sum2(int world, int rank, const void *const *peer_states,
+                         void *const *peer_gather, void *const *peer_flags, int64_t n_floats,
+                         uint32_t epoch, float *out, fbla_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
