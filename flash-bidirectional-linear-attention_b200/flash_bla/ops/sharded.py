@@ -70,7 +70,7 @@ class _PeerExchange:
         self._gather = arr(*[int(p) + 2 * n * 4 for p in hd.buffer_ptrs])
         self._flags = arr(*[int(p) for p in hf.buffer_ptrs])
         # more than two ranks: each rank adds one slice and hands it round (two rounds of flags)
-        self.two_phase = self.world > 2 and os.environ.get("FBLA_PEER_TWO_PHASE", "0") == "1"
+        self.two_phase = os.environ.get("FBLA_PEER_TWO_PHASE", "0") == "1"
         self.epoch = 0
         torch.cuda.synchronize(device)
 
