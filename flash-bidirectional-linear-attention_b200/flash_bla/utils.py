@@ -2,6 +2,7 @@
 ``flash_bla/utils.py`` (``contiguous`` :9-15, ``get_abs_err`` :45-46,
 ``get_err_ratio`` :49-52, ``assert_close`` :55-67)."""
 import functools
+import os
 import warnings
 
 import torch
@@ -47,6 +48,8 @@ def assert_close(prefix, ref, tri, ratio, warning=False, err_atol=1e-6):
         return abs_err
     err_ratio = get_err_ratio(ref, tri)
     msg = f"{prefix:>8} diff: {abs_err:.6f} ratio: {err_ratio:.6f}"
+    if os.environ.get("FLASH_BLA_PRINT_ERR") == "1":     # lets a harness read the measured error
+        print(msg, flush=True)
     if warning or err_ratio < 0.01 or abs_err <= 0.3:
         if err_ratio > ratio:
             warnings.warn(msg)
