@@ -66,19 +66,51 @@ pisa_block_stats_kernel(PisaParams p, const T* __restrict__ q, const T* __restri
     if (d < p.dv) vc[blk * p.dv + d] = sv;
 }
 
-// h = K^T V - sum_c kc_c (x) vc_c
+// h = K^T V - sum_c kc_c (x) vc_c.  One CTA per (16 rows of h, batch*head): the block statistics are
+// staged through shared memory 64 blocks at a time; a thread owns one row and dv/16 columns.
+constexpr int kFoRows = 16;
 __global__ void __launch_bounds__(256)
 pisa_first_order_kernel(PisaParams p, const float* __restrict__ kv, const float* __restrict__ kc,
                         const float* __restrict__ vc, float* __restrict__ h) {
-    const int bh = blockIdx.y;
-    const int i = blockIdx.x * 256 + threadIdx.x;
-    if (i >= p.dk * p.dv) return;
-    const int a = i / p.dv, b = i - a * p.dv;
+    __shared__ float ks[kChunkRows][kFoRows];
+    __shared__ float vs[kChunkRows][128];
+    const int bh = blockIdx.y, a0 = blockIdx.x * kFoRows;
+    const int r = threadIdx.x >> 4, cg = threadIdx.x & 15;      // row a0 + r, columns cg, cg + 16, ...
     const float* kcb = kc + (size_t)bh * p.nt * p.dk;
     const float* vcb = vc + (size_t)bh * p.nt * p.dv;
-    float s = 0.f;
-    for (int c = 0; c < p.nt; ++c) s = fmaf(kcb[c * p.dk + a], vcb[c * p.dv + b], s);
-    h[(size_t)bh * p.dk * p.dv + i] = kv[(size_t)bh * p.dk * p.dv + i] - s;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int c0 = 0; c0 < p.nt; c0 += kChunkRows) {
+        const int nc = min(kChunkRows, p.nt - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc * kFoRows; i += 256) {
+            const int c = i / kFoRows, a = i - c * kFoRows;
+            ks[c][a] = (a0 + a < p.dk) ? kcb[(size_t)(c0 + c) * p.dk + a0 + a] : 0.f;
+        }
+        for (int i = threadIdx.x; i < nc * p.dv; i += 256) {
+            const int c = i / p.dv, b = i - c * p.dv;
+            vs[c][b] = vcb[(size_t)(c0 + c) * p.dv + b];
+        }
+        __syncthreads();
+        for (int c = 0; c < nc; ++c) {
+            const float kk = ks[c][r];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int b = cg + 16 * j;
+                if (b < p.dv) acc[j] = fmaf(kk, vs[c][b], acc[j]);
+            }
+        }
+    }
+    if (a0 + r >= p.dk) return;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int b = cg + 16 * j;
+        if (b < p.dv) {
+            const size_t at = (size_t)bh * p.dk * p.dv + (size_t)(a0 + r) * p.dv + b;
+            h[at] = kv[at] - acc[j];
+        }
+    }
 }
 
 // p-norm of each block's first-order state hc_c = (K_c - kc_c)^T V_c over its dk*dv entries (the
@@ -366,7 +398,7 @@ int fbla_pisa_first_order_state(const fbla_pisa_problem* p, const float* kv, con
     fbla::PisaArgs a;
     if (int rc = fbla::resolve_pisa(p, &a)) return rc;
     if (!kv || !kc || !vc || !h) return fbla::api_fail(FBLA_ERR_INVALID, "a tensor pointer is NULL");
-    dim3 grid((a.kp.dk * a.kp.dv + 255) / 256, a.bh);
+    dim3 grid((a.kp.dk + fbla::kFoRows - 1) / fbla::kFoRows, a.bh);
     fbla::pisa_first_order_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a.kp, kv, kc, vc, h);
     fbla::note_launches(1);
     const cudaError_t e = cudaGetLastError();
