@@ -24,20 +24,6 @@ namespace tc {
 // producer warp, MMA-1 warp, two epilogue warpgroups, MMA-2 warp
 constexpr int kBwdStateThreads = 64 + 2 * kEpiThreads + 32;
 
-#ifdef FBLA_PROFILE
-// Debug builds only: cycle counts of the epilogue phases of one thread (CTA 1, warpgroup 0).
-__device__ long long g_prof_bwd_state[16];
-#define FBLA_PROF_MARK(i)                                              \
-    do {                                                               \
-        if (prof_on) {                                                 \
-            const long long now_ = clock64();                          \
-            g_prof_bwd_state[i] += now_ - prof_t;                      \
-            prof_t = now_;                                             \
-        }                                                              \
-    } while (0)
-#else
-#define FBLA_PROF_MARK(i) do { } while (0)
-#endif
 
 template <int DK, int DV, int MODE>
 struct BwdStateCfg {
@@ -272,16 +258,11 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
         const bool issuer = (et == 0);
         uint8_t* ob = outbuf + wg * Cfg::kOutBytes;
         const int a = wg;                                   // staged tile / out_* barriers of this warpgroup
-#ifdef FBLA_PROFILE
-        const bool prof_on = (blockIdx.x == 1 && wg == 0 && et == 0);
-        long long prof_t = clock64();
-#endif
         int nseg = 0;                                       // segments opened so far in this CTA's range
         for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const Tile t = Map::get(p, g, g0, g1);
             if (t.first) ++nseg;
             if ((it & 1) != wg) continue;
-            FBLA_PROF_MARK(7);
             const int unit = t.unit;
             const bool first = t.first, last = t.last;
             const int s = it % NS;
@@ -317,12 +298,9 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             }
             // km of this unit was written by whichever warpgroup opened the segment
             if (!ptx::mbar_wait(bop_ready, seg & 1u, ab, 328)) break;
-            FBLA_PROF_MARK(6);
             if (!ptx::mbar_wait(&full[s], ph, ab, 321)) break;       // the qr tile is read below
-            FBLA_PROF_MARK(9);
             if (!ptx::mbar_wait(&tfull[tb], pht, ab, 322)) break;
             ptx::tc_fence_after_sync();
-            FBLA_PROF_MARK(0);
             uint8_t* stg = stages + s * Cfg::kStageBytes;
             uint8_t* qr_row = stg + row * 128;                        // + block * kBlockBytes + swizzled chunk
             const uint32_t t_acc = t_lane + tb * Cfg::kTCols;
@@ -430,12 +408,9 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     rz = 1.f / z;
                     dz = -w * rz * rz;
                 }
-                FBLA_PROF_MARK(1);
                 if (!wait_out_free()) break;
-                FBLA_PROF_MARK(2);
                 emit32(0, t_lo, qa);
                 emit32(32, t_hi, qb);
-                FBLA_PROF_MARK(3);
             } else {
                 // two passes over the accumulator: first qr . t, then the outputs
                 float w = 0.f;
@@ -490,17 +465,12 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             ptx::fence_proxy_async_smem();
             ptx::mbar_arrive(&qs_ready[s]);
             ptx::mbar_arrive(&out_written[a]);
-            FBLA_PROF_MARK(4);
             if (!Cfg::kDirect && issuer) {
                 if (!ptx::mbar_wait(&out_written[a], ph2, ab, 324)) break;
 #pragma unroll
                 for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t.c1, t.c2);
                 ptx::tma_store_commit();
             }
-            FBLA_PROF_MARK(5);
-#ifdef FBLA_PROFILE
-            if (prof_on) g_prof_bwd_state[8] += 1;
-#endif
             if (last) {
                 if (!ptx::mbar_wait(acc_full, seg & 1u, ab, 325)) break;
                 ptx::tc_fence_after_sync();

@@ -376,19 +376,6 @@ int64_t tc_workspace_bytes(const KParams& p) {
     return (int64_t)s.units * s.slots_per_unit * p.state_stride * (int64_t)sizeof(float);
 }
 
-#ifdef FBLA_PROFILE
-}  // namespace fbla
-extern "C" int fbla_debug_read_profile(long long* out, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, fbla::tc::g_prof_bwd_state, sizeof(long long) * 16);
-    if (reset) {
-        long long z[16] = {0};
-        cudaMemcpyToSymbol(fbla::tc::g_prof_bwd_state, z, sizeof(z));
-    }
-    return 0;
-}
-namespace fbla {
-#endif
 
 int tc_device_status() { return g_status_host != nullptr ? *g_status_host : 0; }
 int* tc_status_word() { return status_word(); }
