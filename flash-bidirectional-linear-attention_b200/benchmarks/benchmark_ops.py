@@ -4,7 +4,7 @@
 other operators.  Timing: CUDA events around back-to-back calls of the public API, median of
 ``--reps`` repetitions after warm-up; inputs are larger than L2 from T=4096 up at B=8.
 
-    python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|blhd|simple_la|decoupled_la|varlen|pisa|all]
+    python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|fp32|blhd|simple_la|decoupled_la|varlen|pisa|all]
                                        [--long] [--impl b200|reference [--ref-path DIR]]
 
 ``--long`` adds ``simple_la`` at B4 H32 T262144 D128 (8.6 GB per tensor, about 70 GB on the device).
@@ -125,6 +125,15 @@ def main():
                 tg = timed(replay, args.reps)
                 print(f"{'':14s} {'  replayed from a CUDA graph':28s} {'':33s}   fwd+bwd {tg:8.4f} ms "
                       f"({11 * P / tg / 1e6:6.0f} GB/s, {B * T / tg * 1e3:.3e} tokens/s)", flush=True)
+    if args.op in ("all", "fp32"):
+        # fp32 inputs (the 1e-5 parity case): B2 H4 T1024 D64 as the reference's CPU-runnable configuration, and a
+        # streaming-size case
+        for (b, h, T, d) in ((2, 4, 1024, 64), (8, 16, 4096, 64)):
+            q, k, v = (x.detach().float().requires_grad_() for x in (pos(b, h, T, d), pos(b, h, T, d), gau(b, h, T, d)))
+            do = torch.randn_like(v)
+            P = b * h * T * d * 4
+            f, fb = both(lambda: linear_attention(q, k, v), (q, k, v), do)
+            row("linear_attn", f"fp32 B{b} H{h} T{T} D{d}", f, fb, b * T, 4 * P, 11 * P)
     if args.op in ("all", "blhd") and IMPL != "reference":
         # projection-layout inputs (B, L, H, D): the op on them as they are, against the reference layers' route
         # (permute + contiguous into (B, H, L, D), the op, permute back)
