@@ -14,8 +14,16 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kTT = 16;           // tokens staged per step in the reducing passes
-constexpr int kReduceChunk = 512; // tokens per slice in the reducing passes
+constexpr int kReduceChunk = 512; // most tokens per slice in the reducing passes (fewer when there are few units)
 constexpr int kOutTokens = 128;   // tokens per block in the streaming passes
+
+// Tokens per slice: 512, halved (down to 64) while the launch would have fewer than ~2 CTAs per SM of a
+// large GPU.  A function of the problem only, so the workspace size and the order of the sums are fixed.
+__host__ __device__ inline int chunk_of(const KParams& p) {
+    int chunk = kReduceChunk;
+    while (chunk > 64 && (long long)p.units * ((p.max_len + chunk - 1) / chunk) < 296) chunk >>= 1;
+    return chunk;
+}
 
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
@@ -91,8 +99,9 @@ simt_fwd_state_kernel(KParams p, const T* __restrict__ k, const T* __restrict__ 
 
     const int u = blockIdx.y, sl = blockIdx.x;
     const UnitGeom g = unit_geom(p, u);
-    const int t_begin = sl * kReduceChunk;
-    const int t_end = min(g.len, t_begin + kReduceChunk);
+    const int chunk = chunk_of(p);
+    const int t_begin = sl * chunk;
+    const int t_end = min(g.len, t_begin + chunk);
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
 
     float acc[R][R];
@@ -205,8 +214,9 @@ simt_bwd_state_kernel(KParams p, const T* __restrict__ q, const T* __restrict__ 
 
     const int u = blockIdx.y, sl = blockIdx.x;
     const UnitGeom g = unit_geom(p, u);
-    const int t_begin = sl * kReduceChunk;
-    const int t_end = min(g.len, t_begin + kReduceChunk);
+    const int chunk = chunk_of(p);
+    const int t_begin = sl * chunk;
+    const int t_end = min(g.len, t_begin + chunk);
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool decoupled = (dqr != nullptr);
@@ -354,7 +364,10 @@ simt_bwd_in_kernel(KParams p, const T* __restrict__ kr, const T* __restrict__ v,
     }
 }
 
-inline int slices_of(const KParams& p) { return (p.max_len + kReduceChunk - 1) / kReduceChunk; }
+inline int slices_of(const KParams& p) {
+    const int chunk = chunk_of(p);
+    return (p.max_len + chunk - 1) / chunk;
+}
 
 template <typename K>
 cudaError_t opt_in_smem(K kernel, size_t bytes) {
