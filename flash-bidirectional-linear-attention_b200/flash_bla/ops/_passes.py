@@ -196,6 +196,33 @@ def backward(prob, q, k, v, d_o, state):
     return dq, dk, dv
 
 
+# Head dims the tensor-core kernels do not take (anything but 64 and 128; the reference's layers use 32) would
+# run on the CUDA-core kernels at a fraction of the bandwidth.  For 16-bit inputs of streaming size it is
+# cheaper to zero-pad the feature dim up to 64 / 128 -- zero key features add nothing to the state or the
+# normaliser, zero value features give zero output columns -- and slice the result; autograd handles both ends.
+_PAD_MIN_ROWS = 1 << 17      # batch * heads * tokens from which padding pays (below, launch cost dominates)
+
+
+def padded_dims(q, v):
+    """(K', V') to pad the feature dims to, or None when the tensors are served as they are."""
+    if q.dtype not in (torch.float16, torch.bfloat16) or not q.is_cuda or q.dim() != 4:
+        return None
+    # opt-in for now: FBLA_PAD_SMALL_DIMS=1
+    if _default_flags & _C.FLAG_GENERIC or os.environ.get("FBLA_PAD_SMALL_DIMS", "0") != "1":
+        return None
+    K, V = q.shape[-1], v.shape[-1]
+    if K in (64, 128) and V in (64, 128):
+        return None
+    if K > 128 or V > 128 or q.shape[0] * q.shape[1] * q.shape[2] < _PAD_MIN_ROWS:
+        return None
+    up = lambda d: 64 if d <= 64 else 128
+    return up(K), up(V)
+
+
+def pad_last(x, d):
+    return x if x.shape[-1] == d else torch.nn.functional.pad(x, (0, d - x.shape[-1]))
+
+
 def kernel_path(prob):
     """1 when the tensor-core kernels serve ``prob``, 0 for the CUDA-core kernels."""
     return _C.lib().fbla_kernel_path(ctypes.byref(prob))

@@ -75,4 +75,8 @@ def decoupled_la(
     """
     if scale is None:
         scale = k.shape[-2] ** -1.0
+    pad = P.padded_dims(q, v) if (k.shape == q.shape == q_rope.shape == k_rope.shape) else None
+    if pad is not None and pad == (64, 64):      # the decoupled tensor-core kernels exist at 64 x 64 only
+        o = DecoupledLAFunction.apply(*(P.pad_last(x, 64) for x in (q, k, q_rope, k_rope, v)), scale, eps)
+        return o[..., :v.shape[-1]]
     return DecoupledLAFunction.apply(q, k, q_rope, k_rope, v, scale, eps)

@@ -79,6 +79,10 @@ def linear_attention(
         raise ValueError(f"layout must be 'bhld' or 'blhd', got {layout!r}")
     if scale is None:
         scale = k.shape[-2] ** -1.0
+    pad = P.padded_dims(q, v) if k.shape == q.shape else None
+    if pad is not None:
+        o = LinearAttnFunction.apply(P.pad_last(q, pad[0]), P.pad_last(k, pad[0]), P.pad_last(v, pad[1]), scale, eps)
+        return o[..., :v.shape[-1]]
     return LinearAttnFunction.apply(q, k, v, scale, eps)
 
 

@@ -59,4 +59,8 @@ def simple_la(
     """
     if scale is None:
         scale = q.shape[-1] ** -0.5
+    pad = P.padded_dims(q, v) if k.shape == q.shape else None
+    if pad is not None:
+        o = SimpleLinearAttnFunction.apply(P.pad_last(q, pad[0]), P.pad_last(k, pad[0]), P.pad_last(v, pad[1]), scale)
+        return o[..., :v.shape[-1]]
     return SimpleLinearAttnFunction.apply(q, k, v, scale)

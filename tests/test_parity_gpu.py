@@ -368,3 +368,26 @@ def test_linear_attention_blhd_layout(shape, dtype):
     o.backward(d_o.cuda().permute(0, 2, 1, 3).contiguous())
     for got, ref, name in ((o, ro, "o"), (xs[0].grad, rdq, "dq"), (xs[1].grad, rdk, "dk"), (xs[2].grad, rdv, "dv")):
         check(got.permute(0, 2, 1, 3), ref, dtype, f"blhd{shape}.{name}")
+
+
+@pytest.mark.skipif(__import__("os").environ.get("FBLA_PAD_SMALL_DIMS", "0") != "1",
+                    reason="the padded route is opt-in (FBLA_PAD_SMALL_DIMS=1)")
+@pytest.mark.parametrize("shape", [(2, 8, 8192, 32, 32), (1, 16, 8192, 48, 24), (1, 16, 8192, 96, 32)])
+def test_small_head_dims_take_the_padded_tensor_core_route(shape):
+    """16-bit inputs of streaming size whose head dims are not 64 / 128 are zero-padded onto the tensor-core
+    kernels; outputs and gradients keep the caller's shapes and match the oracle."""
+    B, H, T, K, V = shape
+    dtype = torch.bfloat16
+    q, k, v, d_o = make_inputs(61, (B, H, T, K), (B, H, T, V), dtype)
+    assert P.padded_dims(q.cuda(), v.cuda()) is not None
+    rq, rk, rv = (x.double() for x in (q, k, v))
+    refs = (O.linear_attn_fwd(rq, rk, rv, None, 1e-6),) + tuple(O.linear_attn_bwd(rq, rk, rv, d_o.double(), None, 1e-6))
+    xs = [x.cuda().requires_grad_() for x in (q, k, v)]
+    o = linear_attention(*xs)
+    o.backward(d_o.cuda())
+    assert o.shape == (B, H, T, V) and all(x.grad.shape == x.shape for x in xs)
+    for got, ref, name in zip((o, xs[0].grad, xs[1].grad, xs[2].grad), refs, ("o", "dq", "dk", "dv")):
+        check(got, ref, dtype, f"padded{shape}.{name}")
+    # simple_la: default scale from the caller's key dim, not the padded one
+    ref_o = O.simple_la_fwd(rq, rk, rv, None)
+    check(simple_la(q.cuda(), k.cuda(), v.cuda()), ref_o, dtype, f"padded{shape}.simple_la")
