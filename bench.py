@@ -6,30 +6,40 @@ One step = one forward + backward of ``linear_attention`` over one batch of synt
 inputs (q, k = elu(N(0,1))+1, v, dO ~ N(0,1), seeded), T = 32768 tokens per rank.
 With N > 1 (launched by torch.distributed.run, one rank per GPU) the sequence is
 sharded along T: every rank holds 32768 tokens of a global sequence of N*32768, and
-the per-head state (and its gradient) is all-reduced once per direction over NCCL --
-weak scaling.  Rank 0 prints one JSON line.
+the per-head state (and its gradient) is summed over the ranks once per direction,
+inside the kernels, over NVLink -- weak scaling.  Rank 0 prints one JSON line.
 
 ``value``  : tokens/s (tokens = B * T_global) with inputs resident in HBM, public API
              (``linear_attention(...).backward(dO)``), CUDA-event timed, max over ranks.
+             The K steps are timed as a block, the block is repeated (>= 10 times, >= 0.2 s
+             in all) and the MEDIAN block is reported (``blocks`` has min / max).
 ``e2e``    : the same metric with pinned host buffers: every step copies q, k, v, dO
              host->device and o, dq, dk, dv device->host inside the timed region.
 ``roofline``: the slowest of the four kernels (timed one by one with CUDA events on the
              launching stream): algorithmic bytes / duration against the measured copy
              bandwidth of this machine pool.
-``cpu_baseline`` / ``--impl reference``: the reference's execution model on the host
-             cores -- the dense torch statement in bf16 with autograd backward -- on a
-             bounded sample of the same workload.
+``parity`` : (N > 1) a small sharded forward + backward checked against the single-GPU
+             operator on the gathered sequence and against the fp64 formula, before timing;
+             a failure ends the run with a non-zero exit code.
+``cfg3``   : simple_la bf16 B4-H32-D128 with a GLOBAL T of 262144 split over the N ranks
+             (strong scaling), the configuration whose 8.4 MB state is the large exchange.
+``triton_reference`` : (N = 1) the reference's own Triton ``linear_attention`` on the same GPU
+             and inputs, when an installed copy of the reference is found next to this file.
+``cpu_baseline`` / ``--impl reference``: the reference's torch path (``naive_linear_attn``,
+             bf16, autograd backward) on the host cores, on a bounded sample of the workload.
 """
 import argparse
 import json
 import os
 import statistics
+import subprocess
 import sys
 import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.join(ROOT, "flash-bidirectional-linear-attention_b200")
+REF = os.path.join(ROOT, "baseline", "_ref")
 for _p in (ROOT, PKG):
     if _p not in sys.path:
         sys.path.insert(0, _p)
@@ -43,6 +53,10 @@ METRIC = "linear_attn fwd+bwd tokens/s (bf16, B8-H16-D64)"
 UNIT = "tokens/s"
 CPU_SAMPLE_BATCH = 2          # the CPU arm runs B=2 of the 8 batch rows per step
 FALLBACK_HBM_GBS = 6650.0
+CFG3 = dict(B=4, H=32, D=128, T=262144)
+# DRAM bytes (read + write) of one launch of each pass at B8-H16-D64, T = 32768, from an ncu
+# capture of dram__bytes_read.sum + dram__bytes_write.sum (one launch per kernel).
+NCU_DRAM_BYTES_T32768 = {"fwd_state": None, "fwd_out": None, "bwd_state": None, "bwd_in": None}
 
 
 def peaks():
@@ -97,45 +111,74 @@ class ClockSampler(threading.Thread):
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def make_inputs(T, device, seed):
+def make_inputs(T, device, seed, shape=(B, H, D), positive=True):
+    b, h, d = shape
     g = torch.Generator(device=device).manual_seed(seed)
-    q = (F.elu(torch.randn(B, H, T, D, device=device, generator=g)) + 1).to(torch.bfloat16)
-    k = (F.elu(torch.randn(B, H, T, D, device=device, generator=g)) + 1).to(torch.bfloat16)
-    v = torch.randn(B, H, T, D, device=device, generator=g).to(torch.bfloat16)
-    do = torch.randn(B, H, T, D, device=device, generator=g).to(torch.bfloat16)
-    return q, k, v, do
+    q = torch.randn(b, h, T, d, device=device, generator=g)
+    k = torch.randn(b, h, T, d, device=device, generator=g)
+    if positive:
+        q, k = F.elu(q) + 1, F.elu(k) + 1
+    v = torch.randn(b, h, T, d, device=device, generator=g)
+    do = torch.randn(b, h, T, d, device=device, generator=g)
+    return [x.to(torch.bfloat16) for x in (q, k, v, do)]
 
 
 # ---------------------------------------------------------------------------------------
 # CPU arm: the reference's torch path on the host cores
 # ---------------------------------------------------------------------------------------
+def _reference_naive():
+    """``naive_linear_attn`` of the installed reference (plain torch), or None."""
+    path = os.path.join(REF, "flash_bla", "ops", "linear_attn", "naive.py")
+    if not os.path.exists(path):
+        return None
+    try:
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_ref_linear_attn_naive", path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod.naive_linear_attn
+    except Exception:
+        return None
+
+
 def cpu_step_factory(T):
-    from oracle import bla_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)
     q, k, v, do = make_inputs(T, "cpu", 0)
     q, k, v, do = (x[:CPU_SAMPLE_BATCH].contiguous() for x in (q, k, v, do))
+    naive = _reference_naive()
+    if naive is not None:
+        kind = "reference"
 
-    def step():
-        O.linear_attn_torch_fwd_bwd(q, k, v, do)
-    return step, CPU_SAMPLE_BATCH * T
+        def step():
+            xs = [x.clone().requires_grad_() for x in (q, k, v)]
+            naive(*xs).backward(do)
+    else:
+        from oracle import bla_oracle as O
+        kind = "port"
+
+        def step():
+            O.linear_attn_torch_fwd_bwd(q, k, v, do)
+    return step, CPU_SAMPLE_BATCH * T, kind
 
 
 def time_cpu(T, steps, warmup):
-    step, tokens = cpu_step_factory(T)
+    step, tokens, kind = cpu_step_factory(T)
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / steps
-    return tokens / dt, dt
+    return tokens / dt, dt, kind
 
 
-def cpu_baseline_dict(value, T):
-    return {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+def cpu_baseline_dict(value, T, kind):
+    what = ("the reference's naive_linear_attn (flash_bla/ops/linear_attn/naive.py of the installed reference)"
+            if kind == "reference" else "the reference's naive path restated in oracle/")
+    return {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
             "host_cpus": os.cpu_count(),
-            "sample": f"dense torch bf16 forward + autograd backward (the reference's naive path, restated in "
-                      f"oracle/) on B={CPU_SAMPLE_BATCH} of the {B} batch rows, H={H}, T={T}, D={D} per step"}
+            "sample": f"dense torch bf16 forward + autograd backward ({what}) on B={CPU_SAMPLE_BATCH} of the "
+                      f"{B} batch rows, H={H}, T={T}, D={D} per step"}
 
 
 def run_reference(args):
@@ -143,21 +186,180 @@ def run_reference(args):
     if rank != 0:
         return
     T = args.seq_len
-    value, dt = time_cpu(T, args.steps, max(1, args.warmup))
+    value, dt, kind = time_cpu(T, args.steps, max(1, args.warmup))
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"linear_attn fwd+bwd bf16 B{B}-H{H}-D{D} T={T}, CPU sample "
                                    f"B={CPU_SAMPLE_BATCH}"},
-            "cpu_baseline": cpu_baseline_dict(value, T),
+            "cpu_baseline": cpu_baseline_dict(value, T, kind),
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
 # ---------------------------------------------------------------------------------------
+# the reference's Triton kernels on this GPU (a child process, so a failure there is only a note)
+# ---------------------------------------------------------------------------------------
+_TRITON_CHILD = r"""
+import json, sys, time
+sys.path.insert(0, sys.argv[1])
+T = int(sys.argv[2])
+import torch, torch.nn.functional as F
+from flash_bla.ops.linear_attn.fused import linear_attention
+g = torch.Generator(device="cuda").manual_seed(1000)
+mk = lambda pos: (F.elu(torch.randn(8, 16, T, 64, device="cuda", generator=g)) + 1 if pos
+                  else torch.randn(8, 16, T, 64, device="cuda", generator=g)).to(torch.bfloat16)
+q, k, v, do = mk(True), mk(True), mk(False), mk(False)
+q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+def step():
+    q.grad = k.grad = v.grad = None
+    linear_attention(q, k, v).backward(do)
+t0 = time.time()
+for _ in range(3):
+    step()
+torch.cuda.synchronize()
+tune_s = time.time() - t0
+e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+best = []
+for _ in range(5):
+    e0.record()
+    for _ in range(10):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    best.append(e0.elapsed_time(e1) / 10)
+best.sort()
+print(json.dumps({"ms_per_step": best[len(best) // 2], "autotune_s": tune_s}))
+"""
+
+
+def triton_reference(T, ours_ms, limit_s=420):
+    if not os.path.isdir(os.path.join(REF, "flash_bla", "ops", "linear_attn")):
+        return {"unavailable": "no installed copy of the reference next to bench.py"}
+    try:
+        out = subprocess.run([sys.executable, "-c", _TRITON_CHILD, REF, str(T)], capture_output=True, text=True,
+                             timeout=limit_s)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"the reference's autotuning did not finish within {limit_s} s"}
+    if out.returncode != 0:
+        return {"unavailable": "the reference failed: " + (out.stderr.strip().splitlines() or ["?"])[-1][:200]}
+    try:
+        got = json.loads(out.stdout.strip().splitlines()[-1])
+    except Exception:
+        return {"unavailable": "unreadable output of the reference run"}
+    ms = got["ms_per_step"]
+    return {"what": "flash_bla.ops.linear_attn.fused.linear_attention of the installed reference (Triton, autotuned), "
+                    "same GPU, same input distribution, fwd+bwd, CUDA events, median of 5 x 10 steps",
+            "ms_per_step": ms, "value": B * T / (ms * 1e-3), "unit": UNIT, "autotune_s": got["autotune_s"],
+            "speedup_of_this_library": ms / ours_ms}
+
+
+# ---------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------
+def timed_blocks(step, steps, barrier, world, dev, min_blocks=10, min_total_s=0.2, max_blocks=200):
+    """Times `steps` back-to-back steps as one block (barrier + synchronize on both sides, CUDA
+    events, max over ranks) and repeats the block; returns the per-block milliseconds."""
+    blocks = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    while len(blocks) < min_blocks or (sum(blocks) < min_total_s * 1e3 and len(blocks) < max_blocks):
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        blocks.append(ms.item())
+    return blocks
+
+
+def parity_check(world, rank, dev):
+    """A small T-sharded forward + backward against (a) the single-GPU operator on the whole
+    sequence and (b) the fp64 formula for one (batch, head) unit.  Returns the record for the JSON
+    line; ``ok`` is the verdict."""
+    from flash_bla.ops.linear_attn.fused import linear_attention
+    from flash_bla.ops.sharded import seq_sharded_linear_attention
+    worst, worst_formula, cases = 0.0, 0.0, []
+    for dtype, name in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+        b, h, d, t_loc = 2, 4, 64, 2048
+        Tg = t_loc * world
+        g = torch.Generator(device=dev).manual_seed(4242)           # the same full problem on every rank
+        q = (F.elu(torch.randn(b, h, Tg, d, device=dev, generator=g)) + 1).to(dtype)
+        k = (F.elu(torch.randn(b, h, Tg, d, device=dev, generator=g)) + 1).to(dtype)
+        v = torch.randn(b, h, Tg, d, device=dev, generator=g).to(dtype)
+        do = torch.randn(b, h, Tg, d, device=dev, generator=g).to(dtype)
+        sl = slice(rank * t_loc, (rank + 1) * t_loc)
+        xs = [x[:, :, sl].contiguous().requires_grad_() for x in (q, k, v)]
+        o = seq_sharded_linear_attention(*xs, global_len=Tg)
+        o.backward(do[:, :, sl].contiguous())
+        mine = torch.stack([o.detach()] + [x.grad for x in xs])      # (4, b, h, t_loc, d)
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        if rank == 0:
+            got = torch.cat(parts, dim=3).float()                    # whole sequence, rank order
+            full = [x.clone().requires_grad_() for x in (q, k, v)]
+            o1 = linear_attention(*full)
+            o1.backward(do)
+            ref = torch.stack([o1.detach()] + [x.grad for x in full]).float()
+            ulp = {torch.bfloat16: 2.0 ** -7, torch.float32: 0.0}[dtype]
+            for i in range(4):
+                rms = ref[i].pow(2).mean().sqrt()
+                slack = ulp * ref[i].abs() + (2e-3 if ulp else 1e-4) * rms
+                worst = max(worst, ((got[i] - ref[i]).abs() / slack).max().item())
+            # fp64 formula, unit (0, 0): o = q S / (q kmean + eps), S = K^T V / T
+            q0, k0, v0 = (x[0, 0].double() for x in (q, k, v))
+            o64 = (q0 @ (k0.t() @ v0 / Tg)) / ((q0 * k0.mean(0)).sum(-1, keepdim=True) + 1e-6)
+            err = ((got[0, 0, 0].double() - o64).abs().max() / o64.pow(2).mean().sqrt()).item()
+            bar = 2e-2 if dtype == torch.bfloat16 else 1e-5
+            worst_formula = max(worst_formula, err / bar)
+            cases.append(f"{name} B{b}-H{h}-D{d} T={Tg}")
+    rec = {"cases": cases, "max_err_over_bar": worst, "formula_err_over_bar": worst_formula,
+           "bar": "vs the 1-GPU operator: one ulp of the output type + 0.2 % of the RMS (fp32: 1e-4 of the RMS); "
+                  "vs the fp64 formula: 2e-2 max-abs/RMS (bf16), 1e-5 (fp32)",
+           "ok": bool(worst <= 1.0 and worst_formula <= 1.0)}
+    flag = torch.tensor([1 if (rank != 0 or rec["ok"]) else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return rec, bool(flag.item())
+
+
+def run_cfg3(world, rank, dev, barrier, peak):
+    """simple_la bf16 B4-H32-D128, global T = 262144 split along T over the ranks."""
+    from flash_bla.ops.sharded import seq_sharded_simple_la
+    from flash_bla.ops.simple_la.fused import simple_la
+    c = CFG3
+    if c["T"] % world:
+        return {"skipped": f"T={c['T']} does not split over {world} ranks"}
+    t_loc = c["T"] // world
+    need = 9 * c["B"] * c["H"] * t_loc * c["D"] * 2
+    if torch.cuda.mem_get_info(dev)[0] < need * 1.1:
+        return {"skipped": f"needs {need / 2 ** 30:.0f} GiB free on the device"}
+    q, k, v, do = make_inputs(t_loc, dev, 3000 + rank, shape=(c["B"], c["H"], c["D"]), positive=False)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        o = seq_sharded_simple_la(q, k, v) if world > 1 else simple_la(q, k, v)
+        o.backward(do)
+
+    for _ in range(3):
+        step()
+    blocks = timed_blocks(lambda: step(), 5, barrier, world, dev, min_blocks=5, min_total_s=0.2, max_blocks=40)
+    ms = statistics.median(blocks) / 5
+    nbytes = 11 * c["B"] * c["H"] * t_loc * c["D"] * 2          # per rank
+    out = {"workload": f"simple_la fwd+bwd bf16 B{c['B']}-H{c['H']}-D{c['D']} global T={c['T']}, "
+                       f"{t_loc} tokens per GPU" + (", state (8.4 MB) summed over ranks inside the kernels" if world > 1 else ""),
+           "scaling": "strong", "ms_per_step": ms, "value": c["B"] * c["T"] / (ms * 1e-3), "unit": UNIT,
+           "algo_gbs_per_gpu": nbytes / (ms * 1e-3) / 1e9, "frac_of_peak": nbytes / (ms * 1e-3) / 1e9 / peak,
+           "blocks": {"n": len(blocks), "steps_each": 5, "min_ms": min(blocks) / 5, "max_ms": max(blocks) / 5}}
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -175,6 +377,21 @@ def run_ours(args):
     from flash_bla.ops.linear_attn.fused import linear_attention
     from flash_bla.ops.sharded import seq_sharded_linear_attention
 
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    parity = None
+    if world > 1:
+        parity, all_ok = parity_check(world, rank, dev)
+        if not all_ok:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": world, "parity": parity,
+                                  "error": "sharded results differ from the single-GPU operator"}), flush=True)
+            dist.destroy_process_group()
+            raise SystemExit(3)
+
     T = args.seq_len                      # tokens per rank
     T_global = T * world
     tokens = B * T_global
@@ -190,30 +407,20 @@ def run_ours(args):
         o.backward(do)
         return o
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
+    for _ in range(max(3, args.warmup)):
         step()
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
     launches0 = _C.lib().fbla_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    launches = _C.lib().fbla_launch_count() - launches0
+    blocks = timed_blocks(step, args.steps, barrier, world, dev)
+    launches = (_C.lib().fbla_launch_count() - launches0) // len(blocks)
     clocks = sampler.stop()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = ms.item() / args.steps
+    ms_per_step = statistics.median(blocks) / args.steps
     value = tokens / (ms_per_step * 1e-3)
+    block_info = {"n": len(blocks), "steps_each": args.steps, "reported": "median",
+                  "min_ms_per_step": min(blocks) / args.steps, "max_ms_per_step": max(blocks) / args.steps,
+                  "timed_s": sum(blocks) * 1e-3}
 
     # ---- the four kernels one by one (same inputs, CUDA events on the launching stream)
     prob = P.make_problem(q, batch=B, heads=H, seq_len=T, dk=D, dv=D, normalize=True, scale=1.0 / T_global,
@@ -251,14 +458,14 @@ def run_ours(args):
               for n in names}
     dom = max(names, key=lambda n: acc[n])
     total_gbs = sum(algo_bytes.values()) / (sum(acc.values()) * 1e-3) / 1e9
-    # DRAM bytes (read + write) per launch from the ncu capture summarised in
-    # profiles/ncu_linear_attn_bf16_b8h16d64.md (taken at T = 8192, proportional to T)
-    ncu_traffic_at_8192 = {"fwd_state": 273.5e6, "fwd_out": 220.6e6, "bwd_state": 377.3e6, "bwd_in": 490.0e6}
-    traffic = ncu_traffic_at_8192[dom] * (T / 8192.0) if (B, H, D) == (8, 16, 64) else None
+    traffic = NCU_DRAM_BYTES_T32768[dom] if (B, H, D, T) == (8, 16, 64, 32768) else None
     roofline = {"bound": "hbm", "kernel": dom, "achieved": passes[dom]["gbs"], "peak": peak, "unit": "GB/s",
                 "frac": passes[dom]["gbs"] / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                 "all_passes_gbs": total_gbs, "all_passes_frac": total_gbs / peak,
+                "step_gbs": 11 * tensor_bytes / (ms_per_step * 1e-3) / 1e9,
+                "step_frac": 11 * tensor_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
                 "frac_of_nominal_8000": total_gbs / 8000.0}
+    del o_buf, dq, dk, dv
 
     # ---- end to end: pinned host buffers, copies inside the timed region
     e2e_steps = max(4, min(args.steps, 8))
@@ -302,40 +509,65 @@ def run_ours(args):
     e2e_step(0)
     cur.wait_stream(s_out)
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(e2e_steps):
         e2e_step(i + 1)
     cur.wait_stream(s_out)
     e1.record()
     barrier()
-    ms2 = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    ms2_local = e0.elapsed_time(e1)
+    ms2 = torch.tensor([ms2_local], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
     e2e_value = tokens / (ms2.item() / e2e_steps * 1e-3)
+    # what limits it: bytes each rank moves per direction over its own PCIe link per second
+    link_gbs = 4 * tensor_bytes / (ms2.item() / e2e_steps * 1e-3) / 1e9
     e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * tensor_bytes * world,
-           "d2h_bytes_per_step": 4 * tensor_bytes * world, "steps": e2e_steps}
+           "d2h_bytes_per_step": 4 * tensor_bytes * world, "steps": e2e_steps,
+           "per_rank_h2d_gbs": link_gbs, "per_rank_d2h_gbs": link_gbs,
+           "limiter": "host<->device copies: %.0f GB/s in each direction at once per rank against %.2f ms of kernels "
+                      "per step; summed over ranks %.0f GB/s each way through the host's memory and PCIe root"
+                      % (link_gbs, ms_per_step, link_gbs * world)}
+    del sets, keep, host_in, host_out
+    torch.cuda.empty_cache()
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        cv, _ = time_cpu(T, 3, 1)
-        cpu = cpu_baseline_dict(cv, T)
-
-    exchange_kind = "NCCL all-reduce"
+    exchange_kind = None
     if world > 1:
         from flash_bla.ops import sharded
-        if any(e is not None for e in sharded._exchanges.values()):
-            exchange_kind = "one peer-memory kernel per direction (NVLink loads)"
+        kinds = {type(e).__name__ for e in sharded._exchanges.values() if e is not None}
+        exchange_kind = ("inside the kernels (peer stores over NVLink, two flag rounds)" if "_FusedExchange" in kinds
+                         else "one peer-memory kernel per direction" if kinds else "NCCL all-reduce")
+
+    peak_now = peak
+    cfg3 = None if args.no_cfg3 else run_cfg3(world, rank, dev, barrier, peak_now)
+
+    cpu = None
+    triton = None
+    if rank == 0 and world == 1:
+        if not args.no_cpu:
+            cv, _, kind = time_cpu(T, 3, 1)
+            cpu = cpu_baseline_dict(cv, T, kind)
+        if not args.no_triton:
+            triton = triton_reference(T, ms_per_step)
+
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"linear_attn fwd+bwd bf16 B{B}-H{H}-D{D} T={T} per GPU"
-                                       + (f", T-sharded global T={T_global}, state summed over ranks by "
+                                       + (f", T-sharded global T={T_global}, state summed over ranks "
                                           + exchange_kind if world > 1 else ""),
                            "l2": "inputs larger than L2 (4 x %d MB per step)" % (tensor_bytes // 2 ** 20),
                            "kernel_path": "tcgen05+TMA" if path == 1 else "cuda-core"},
-                "roofline": roofline, "passes": passes, "cpu_baseline": cpu, "e2e": e2e,
+                "blocks": block_info, "roofline": roofline, "passes": passes, "cpu_baseline": cpu, "e2e": e2e,
                 "gpu_launches": int(launches), "clocks": clocks}
+        if parity is not None:
+            line["parity"] = parity
+        if cfg3 is not None:
+            line["cfg3"] = cfg3
+        if triton is not None:
+            line["triton_reference"] = triton
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -344,11 +576,13 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cfg3", action="store_true", help="skip the simple_la T=262144 block")
+    ap.add_argument("--no-triton", action="store_true", help="skip the run of the reference's Triton kernels")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

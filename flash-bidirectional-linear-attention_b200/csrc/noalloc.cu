@@ -27,6 +27,7 @@ struct DeviceSide {
     bool ready = false;
     void* scratch = nullptr;
     int* status = nullptr;
+    int failed = 0;       // last non-zero status read back by fbla_noalloc_status (until cleared)
 };
 DeviceSide g_dev[64];
 std::mutex g_mu;
@@ -62,7 +63,8 @@ int set_up(DeviceSide** out) {
 // argument and without allocating: no cudaMalloc / cudaFree / cudaHostAlloc, no library that
 // allocates.
 //
-//  * Limit: the scratch the pass needs (fbla_workspace_bytes of the same problem) must not
+//  * Limit: the scratch the tensor-core kernels need for the problem (one fp32 state per segment
+//    of the tile schedule; never more than fbla_workspace_bytes of the same problem) must not
 //    exceed 8 MiB; larger problems are refused with FBLA_ERR_WORKSPACE and a message.  Only
 //    shapes served by the tensor-core kernels are accepted (16-bit inputs, dk, dv in {64, 128},
 //    16-byte aligned tensors): the CUDA-core kernels need far more scratch.
@@ -73,8 +75,10 @@ int set_up(DeviceSide** out) {
 //    is harmless -- each call overwrites every slot it later reads, nothing has to start at zero
 //    -- but two calls whose kernels overlap on the GPU (different streams, no dependency) race on
 //    it: order them.
-//  * A kernel whose bounded wait gives up records that in device memory; this entry point never
-//    synchronises, so such a failure is not reported through its return value.
+//  * A kernel whose bounded wait gives up records that in a device word of the library; this entry
+//    point never synchronises, so the failure is not in its own return value.
+//    fbla_noalloc_status() reads the word back (it synchronises; it allocates nothing); once it
+//    has seen a failure, this entry point returns FBLA_ERR_DEVICE until the word is cleared.
 extern "C" int fbla_linear_attn_fwd_state_noalloc(const fbla_problem* p, const void* k, const void* v,
                                                   float* state, fbla_stream_t stream) {
     fbla::KParams kp;
@@ -96,8 +100,33 @@ extern "C" int fbla_linear_attn_fwd_state_noalloc(const fbla_problem* p, const v
                               (long long)need, (long long)kScratchBytes);
     DeviceSide* d = nullptr;
     if (int rc = set_up(&d)) return rc;
+    if (d->failed != 0)
+        return fbla::api_fail(FBLA_ERR_DEVICE, "an earlier no-allocation call gave up a bounded wait (site %d); "
+                              "clear it with fbla_noalloc_status(&v, 1)", d->failed);
     const cudaError_t e = fbla::tc_fwd_state_status(kp, p->dtype, k, nullptr, v, state, d->scratch, d->status,
                                                     (cudaStream_t)stream);
     if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "forward state pass: %s", cudaGetErrorString(e));
+    return FBLA_OK;
+}
+
+// Reads the status word of the no-allocation entry point on the current device into *value (0 = no
+// kernel of it has given up a wait; otherwise the number of the wait) and, with `clear` non-zero,
+// resets it.  Synchronous 4-byte copies (the call waits for the device); nothing is allocated.
+extern "C" int fbla_noalloc_status(int* value, int clear) {
+    if (value == nullptr) return fbla::api_fail(FBLA_ERR_INVALID, "value is NULL");
+    DeviceSide* d = nullptr;
+    if (int rc = set_up(&d)) return rc;
+    int v = 0;
+    cudaError_t e = cudaMemcpy(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "reading the status word: %s", cudaGetErrorString(e));
+    *value = v;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (v != 0) d->failed = v;
+    if (clear) {
+        const int zero = 0;
+        e = cudaMemcpy(d->status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "clearing the status word: %s", cudaGetErrorString(e));
+        d->failed = 0;
+    }
     return FBLA_OK;
 }

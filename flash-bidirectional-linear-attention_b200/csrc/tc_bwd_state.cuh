@@ -97,7 +97,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
     const Params& p = pv;
     int g0, g1;
     Map::range(p, g0, g1);
-    const ptx::Abort ab{cta_abort, p.status};
+    const ptx::Abort ab{cta_abort, p.status, wait_limit(p)};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -481,9 +481,11 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             }
         }
         if (!Cfg::kDirect && issuer) ptx::tma_store_wait_all<0>();
+        if (!VARLEN && p.px.world > 1) __threadfence_system();   // the pieces went to peers' memory
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (!VARLEN && p.px.world > 1 && threadIdx.x == 0) peer_signal_pieces(p.px);
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, Cfg::kTmemCols);

@@ -79,7 +79,7 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
     const Params& p = pv;
     int g0, g1;
     Map::range(p, g0, g1);
-    const ptx::Abort ab{cta_abort, p.status};
+    const ptx::Abort ab{cta_abort, p.status, wait_limit(p)};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -190,9 +190,11 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
             ptx::mbar_arrive(acc_empty);
             ++seg;
         }
+        if (!VARLEN && p.px.world > 1) __threadfence_system();   // the pieces went to peers' memory
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (!VARLEN && p.px.world > 1 && threadIdx.x == 0) peer_signal_pieces(p.px);
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
@@ -305,7 +307,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
     const Params& p = pv;
     int g0, g1;
     Map::range(p, g0, g1);
-    const ptx::Abort ab{cta_abort, p.status};
+    const ptx::Abort ab{cta_abort, p.status, wait_limit(p)};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -406,7 +408,9 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
         const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool issuer = (et == 0);
         int seg = 0;
-        for (int g = g0, it = 0; g < g1; ++g, ++it) {
+        // sequence-sharded: the summed state is assembled first (the producer warp is already loading)
+        const bool gathered = (VARLEN || p.px.world <= 1) ? true : peer_gather_state(p, ab, et, 231);
+        for (int g = g0, it = 0; gathered && g < g1; ++g, ++it) {
             const Tile t = Map::get(p, g, g0, g1);
             const int unit = t.unit, tile = t.tile;
             const bool first = t.first;

@@ -152,6 +152,20 @@ int* status_word() {
 
 Params make_params(const KParams& p, int dtype, const Schedule& s, int* status);
 
+// How long a kernel of a sequence-sharded call waits for a peer before it gives up and reports
+// through the status word: FBLA_PEER_WAIT_MS in the environment, 5 s by default.  Ranks that may be
+// further apart than this (one of them writing a checkpoint, say) should meet at a host-side
+// barrier before the call.
+unsigned long long peer_wait_ns() {
+    static const unsigned long long ns = [] {
+        const char* e = getenv("FBLA_PEER_WAIT_MS");
+        double ms = e != nullptr ? atof(e) : 0.0;
+        if (!(ms > 0.0)) ms = 5000.0;
+        return (unsigned long long)(ms * 1e6);
+    }();
+    return ns;
+}
+
 Params make_params(const KParams& p, int dtype, const Schedule& s) { return make_params(p, dtype, s, status_word()); }
 
 Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) {
@@ -176,6 +190,22 @@ Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) 
     q.heads = p.heads;
     q.scale_per_seq = 0;
     q.inv_norm_fixed = 0.f;
+    q.px = PeerXchg{};
+    q.px.world = 1;
+    if (p.peer != nullptr && p.peer->world > 1) {
+        const PeerArgs& a = *p.peer;
+        q.px.world = a.world;
+        q.px.rank = a.rank;
+        q.px.units_per_rank = (p.units + a.world - 1) / a.world;
+        q.px.epoch = a.epoch;
+        q.px.wait_ns = peer_wait_ns();
+        for (int r = 0; r < a.world; ++r) {
+            q.px.recv[r] = static_cast<float*>(a.recv[r]);
+            q.px.full[r] = static_cast<float*>(a.full[r]);
+            q.px.flags[r] = static_cast<unsigned int*>(a.flags[r]);
+        }
+        q.px.state_copy = a.state_copy;
+    }
     return q;
 }
 
@@ -377,7 +407,17 @@ int64_t tc_workspace_bytes(const KParams& p) {
 }
 
 
-int tc_device_status() { return g_status_host != nullptr ? *g_status_host : 0; }
+int64_t tc_peer_recv_floats(const KParams& p, int world) {
+    const Schedule s = make_schedule(p, sm_count());
+    const int64_t upr = (p.units + world - 1) / world;
+    return (int64_t)world * upr * s.slots_per_unit * p.state_stride;
+}
+
+unsigned long long tc_peer_wait_ns() { return peer_wait_ns(); }
+int tc_device_status() { return g_status_host != nullptr ? *static_cast<volatile int*>(g_status_host) : 0; }
+void tc_clear_device_status() {
+    if (g_status_host != nullptr) *static_cast<volatile int*>(g_status_host) = 0;
+}
 int* tc_status_word() { return status_word(); }
 
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v, float* state,
@@ -417,7 +457,7 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
     if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
     auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, tkr, tk, tv, st); };
     if ((e = launch()) != cudaSuccess) return e;
-    if (p.unreduced) return cudaSuccess;        // the pieces in `ws` are the result
+    if (p.unreduced || p.peer != nullptr) return cudaSuccess;   // the pieces (in `ws` / at the peers) are the result
     return reduce_partials(q, state, st);
 }
 
@@ -439,7 +479,7 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
-    q.state = state;
+    q.state = p.peer != nullptr ? q.px.full[q.px.rank] : state;
     if (p.unreduced) q.state_parts = state;
     q.out_a = o;
     CUtensorMap tqr, tq, to;
@@ -491,7 +531,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     if ((e = make_map(&tdqr, dec ? dq_rope : dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, tqr, tq, tdo, tdq, tdqr, st); };
     if ((e = launch()) != cudaSuccess) return e;
-    if (p.unreduced) return cudaSuccess;
+    if (p.unreduced || p.peer != nullptr) return cudaSuccess;
     return reduce_partials(q, dstate, st);
 }
 
@@ -516,7 +556,7 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
-    q.state = dstate;
+    q.state = p.peer != nullptr ? q.px.full[q.px.rank] : dstate;
     if (p.unreduced) q.state_parts = dstate;
     q.out_a = dec ? dk_rope : dk;      // kernels without a staged output tile store through these
     q.out_b = dv;

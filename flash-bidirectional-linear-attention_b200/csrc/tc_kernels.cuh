@@ -14,6 +14,12 @@ int tc_device_status();
 // Device-visible address of that word (NULL if the pinned allocation failed).
 int* tc_status_word();
 int64_t tc_workspace_bytes(const KParams& p);
+// Sequence-sharded calls: floats of one receive buffer (fbla_peer_group.recv) for `world` ranks.
+int64_t tc_peer_recv_floats(const KParams& p, int world);
+// Limit of a kernel's wait for a peer GPU, nanoseconds (FBLA_PEER_WAIT_MS in the environment).
+unsigned long long tc_peer_wait_ns();
+// Clears the status word after a reported failure.
+void tc_clear_device_status();
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,
                          float* state, void* ws, cudaStream_t st);
 // Same pass with the kernels' status word supplied by the caller (device-accessible memory).

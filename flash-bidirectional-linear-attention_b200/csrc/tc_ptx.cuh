@@ -51,6 +51,7 @@ constexpr long long kWaitCycles = 1500000000LL;  // about a second
 struct Abort {
     volatile int* cta_flag;   // shared memory: some thread of this CTA gave up
     int* status;              // host-visible status word of the library
+    long long limit = kWaitCycles;   // cycles a wait may last (longer when the CTA also waits for peer GPUs)
 };
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, int where) {
@@ -64,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         if (spins > 4096) __nanosleep(200);
         if ((spins & 63) == 0) {
             if (*ab.cta_flag != 0) return false;
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > ab.limit) {
                 *ab.cta_flag = where;
                 *ab.status = where;
                 __threadfence_system();

@@ -55,6 +55,19 @@ class PisaProblem(ctypes.Structure):
     ]
 
 
+class PeerGroup(ctypes.Structure):
+    """Mirror of ``struct fbla_peer_group``."""
+    _fields_ = [
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32),
+        ("reserved", ctypes.c_int32),
+        ("recv", ctypes.POINTER(ctypes.c_void_p)),
+        ("full", ctypes.POINTER(ctypes.c_void_p)),
+        ("flags", ctypes.POINTER(ctypes.c_void_p)),
+    ]
+
+
 _P = ctypes.POINTER(Problem)
 _vp = ctypes.c_void_p
 _sz = ctypes.c_size_t
@@ -85,10 +98,12 @@ def exported_symbols():
     for op in OPS:
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
     names += ["fbla_linear_attn_fwd", "fbla_linear_attn_bwd"]
-    names.append("fbla_linear_attn_fwd_state_noalloc")
+    names += ["fbla_linear_attn_fwd_state_noalloc", "fbla_noalloc_status"]
     names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd",
               "fbla_pisa_bwd_scratch_floats"]
-    names += ["fbla_peer_state_sum", "fbla_peer_state_sum2"]
+    names += ["fbla_peer_state_sum", "fbla_seq_sharded_supported", "fbla_seq_sharded_recv_floats",
+              "fbla_seq_sharded_fwd_state", "fbla_seq_sharded_fwd_out", "fbla_seq_sharded_bwd_state",
+              "fbla_seq_sharded_bwd_in", "fbla_device_status", "fbla_clear_device_status", "fbla_unreduced_state"]
     return names
 
 
@@ -126,14 +141,29 @@ def lib():
         L.fbla_linear_attn_bwd.argtypes = [_P] + [_vp] * 10 + [_sz, _vp]
         L.fbla_linear_attn_fwd_state_noalloc.restype = ctypes.c_int
         L.fbla_linear_attn_fwd_state_noalloc.argtypes = [_P, _vp, _vp, _vp, _vp]   # k, v, state, stream
+        L.fbla_noalloc_status.restype = ctypes.c_int
+        L.fbla_noalloc_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
         _PP = ctypes.POINTER(PisaProblem)
         for name, n_ptr in (("fbla_pisa_block_stats", 7), ("fbla_pisa_first_order_state", 5), ("fbla_pisa_fwd", 10)):
             f = getattr(L, name)
             f.restype = ctypes.c_int
             f.argtypes = [_PP] + [_vp] * n_ptr          # tensor pointers, then the stream
-        L.fbla_peer_state_sum2.restype = ctypes.c_int
-        L.fbla_peer_state_sum2.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.POINTER(ctypes.c_void_p)] * 3 + \
-            [ctypes.c_int64, ctypes.c_uint32, _vp, _vp]
+        _PG = ctypes.POINTER(PeerGroup)
+        L.fbla_seq_sharded_supported.restype = ctypes.c_int
+        L.fbla_seq_sharded_supported.argtypes = [_P]
+        L.fbla_seq_sharded_recv_floats.restype = ctypes.c_int64
+        L.fbla_seq_sharded_recv_floats.argtypes = [_P, ctypes.c_int]
+        for name, args in (("fwd_state", [_vp, _vp, _vp, _PG, _vp]),                 # k, k_rope, v, group, stream
+                           ("fwd_out", [_vp, _vp, _PG, _vp, _vp, _vp]),              # q, q_rope, group, o, state_copy, stream
+                           ("bwd_state", [_vp, _vp, _vp, _vp, _PG, _vp, _vp, _vp]),  # q, q_rope, d_o, state, group, dq, dq_rope, stream
+                           ("bwd_in", [_vp, _vp, _PG, _vp, _vp, _vp, _vp])):         # k_rope, v, group, dk, dk_rope, dv, stream
+            f = getattr(L, "fbla_seq_sharded_" + name)
+            f.restype = ctypes.c_int
+            f.argtypes = [_P] + args
+        L.fbla_device_status.restype = ctypes.c_int
+        L.fbla_device_status.argtypes = []
+        L.fbla_clear_device_status.restype = None
+        L.fbla_clear_device_status.argtypes = []
         L.fbla_pisa_block_hnorm.restype = ctypes.c_int
         L.fbla_pisa_block_hnorm.argtypes = [_PP, _vp, _vp, _vp, ctypes.c_float, _vp, _vp]   # k, v, kc, p, hnorm, stream
         L.fbla_peer_state_sum.restype = ctypes.c_int

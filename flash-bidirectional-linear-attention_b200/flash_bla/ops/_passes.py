@@ -131,6 +131,46 @@ def bwd_in(op, prob, k, v, dstate, dk, dv, dk_rope=None):
     _C.check(rc)
 
 
+# ---- sequence-sharded passes: the state crosses GPUs inside the kernels ------------------------
+def sharded_supported(prob):
+    return _C.lib().fbla_seq_sharded_supported(ctypes.byref(prob)) == 1
+
+
+def sharded_fwd_state(prob, k, v, grp, k_rope=None):
+    _require_cuda(k, v, k_rope)
+    with _C.device_guard(k):
+        rc = _C.lib().fbla_seq_sharded_fwd_state(ctypes.byref(prob), _C.ptr(k), _C.ptr(k_rope), _C.ptr(v),
+                                                 ctypes.byref(grp), _C.stream_of(k))
+    _C.check(rc)
+
+
+def sharded_fwd_out(prob, q, grp, o, state_copy, q_rope=None):
+    _require_cuda(q, o, state_copy, q_rope)
+    with _C.device_guard(q):
+        rc = _C.lib().fbla_seq_sharded_fwd_out(ctypes.byref(prob), _C.ptr(q), _C.ptr(q_rope), ctypes.byref(grp),
+                                               _C.ptr(o), _C.ptr(state_copy), _C.stream_of(q))
+    _C.check(rc)
+    return o
+
+
+def sharded_bwd_state(prob, q, d_o, state, grp, dq, q_rope=None, dq_rope=None):
+    _require_cuda(q, d_o, state, dq, q_rope, dq_rope)
+    with _C.device_guard(q):
+        rc = _C.lib().fbla_seq_sharded_bwd_state(ctypes.byref(prob), _C.ptr(q), _C.ptr(q_rope), _C.ptr(d_o),
+                                                 _C.ptr(state), ctypes.byref(grp), _C.ptr(dq), _C.ptr(dq_rope),
+                                                 _C.stream_of(q))
+    _C.check(rc)
+
+
+def sharded_bwd_in(prob, k, v, grp, dk, dv, dk_rope=None):
+    """``k`` is the key tensor the state was built from (k_rope when decoupled)."""
+    _require_cuda(k, v, dk, dv, dk_rope)
+    with _C.device_guard(k):
+        rc = _C.lib().fbla_seq_sharded_bwd_in(ctypes.byref(prob), _C.ptr(k), _C.ptr(v), ctypes.byref(grp), _C.ptr(dk),
+                                              _C.ptr(dk_rope), _C.ptr(dv), _C.stream_of(k))
+    _C.check(rc)
+
+
 # ---- one call per direction (single GPU: nothing happens between the two passes) -------------
 # On the tensor-core kernels the state is left in the per-segment pieces of the reducing pass
 # (FLAG_UNREDUCED): the consuming pass adds them itself, which saves a kernel per direction.  What

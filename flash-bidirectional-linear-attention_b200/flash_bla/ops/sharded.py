@@ -8,9 +8,16 @@ exchange per direction:
     forward : local [S_r | sum k_r]  --sum over ranks-->  global state  -> local o
     backward: local dq and [dS_r | sum dz q_r]  --sum over ranks-->  -> local dk, dv
 
-On NCCL groups of GPUs of one node the sum is one kernel that reads the peers' states over NVLink
-(``fbla_peer_state_sum``, symmetric memory); elsewhere, or with ``FBLA_PEER_EXCHANGE=0``, it is
-``all_reduce(SUM)``.
+On NCCL groups of GPUs of one node, for the shapes the tensor-core kernels serve, there is no
+separate exchange at all: the reducing pass stores its pieces straight into the memory of the rank
+that owns each unit and the consuming pass begins by adding and redistributing them
+(``fbla_seq_sharded_*``, symmetric memory, plain peer stores over NVLink).  Other shapes on such
+groups use one kernel that reads the peers' states (``fbla_peer_state_sum``); elsewhere, or with
+``FBLA_PEER_EXCHANGE=0``, the sum is ``all_reduce(SUM)``.
+
+Every rank must make the same calls in the same order with the same local shapes.  A kernel waits
+for its peers for at most ``FBLA_PEER_WAIT_MS`` (default 5000); ranks that may drift further apart
+(one of them writing a checkpoint) should meet at ``dist.barrier()`` before the call.
 
 The key mean and the default scale use the GLOBAL sequence length.  Batch, head
 and whole-sequence (varlen) sharding need no communication at all: each rank
@@ -43,6 +50,13 @@ def _all_reduce(t, group):
     return t
 
 
+def _symm():
+    # peers are reached with plain loads and stores; no multicast object is needed or wanted
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    import torch.distributed._symmetric_memory as symm
+    return symm
+
+
 class _PeerExchange:
     """State sum over the GPUs of one node through peer memory (``fbla_peer_state_sum``).
 
@@ -52,11 +66,11 @@ class _PeerExchange:
 
     def __init__(self, group, device, n):
         import ctypes
-        import torch.distributed._symmetric_memory as symm
         from flash_bla import _C
-        self._C, self._ct = _C, ctypes
+        symm = _symm()
+        self._C = _C
         self.n = n
-        self.data = symm.empty(3 * n, dtype=torch.float32, device=device)     # two state buffers, one gather buffer
+        self.data = symm.empty(2 * n, dtype=torch.float32, device=device)
         self.flags = symm.empty(64, dtype=torch.int32, device=device)
         self.flags.zero_()
         hd = symm.rendezvous(self.data, group)
@@ -67,10 +81,7 @@ class _PeerExchange:
         self._hd, self._hf = hd, hf
         arr = ctypes.c_void_p * self.world
         self._bufs = [arr(*[int(p) + b * n * 4 for p in hd.buffer_ptrs]) for b in (0, 1)]
-        self._gather = arr(*[int(p) + 2 * n * 4 for p in hd.buffer_ptrs])
         self._flags = arr(*[int(p) for p in hf.buffer_ptrs])
-        # more than two ranks: each rank adds one slice and hands it round (two rounds of flags)
-        self.two_phase = os.environ.get("FBLA_PEER_TWO_PHASE", "0") == "1"
         self.epoch = 0
         torch.cuda.synchronize(device)
 
@@ -83,43 +94,125 @@ class _PeerExchange:
         self.epoch += 1
         out = torch.empty(self.n, dtype=torch.float32, device=self.data.device)
         with self._C.device_guard(out):
-            if self.two_phase:
-                rc = self._C.lib().fbla_peer_state_sum2(self.world, self.rank, self._bufs[self.epoch & 1], self._gather,
-                                                        self._flags, self.n, self.epoch, out.data_ptr(),
-                                                        self._C.stream_of(out))
-            else:
-                rc = self._C.lib().fbla_peer_state_sum(self.world, self.rank, self._bufs[self.epoch & 1], self._flags,
-                                                       self.n, self.epoch, out.data_ptr(), self._C.stream_of(out))
+            rc = self._C.lib().fbla_peer_state_sum(self.world, self.rank, self._bufs[self.epoch & 1], self._flags,
+                                                   self.n, self.epoch, out.data_ptr(), self._C.stream_of(out))
         self._C.check(rc)
         return out
+
+
+class _FusedExchange:
+    """Buffers of the exchange that runs inside the passes (``fbla_seq_sharded_*``) for one problem
+    shape: two (receive buffer, summed-state copy) pairs used alternately and one array of flag
+    words, in symmetric memory that every peer has mapped."""
+
+    def __init__(self, group, device, prob):
+        import ctypes
+        from flash_bla import _C
+        symm = _symm()
+        L = _C.lib()
+        world = dist.get_world_size(group)
+        self.n = int(L.fbla_state_floats(ctypes.byref(prob)))
+        self.n_recv = int(L.fbla_seq_sharded_recv_floats(ctypes.byref(prob), world))
+        if self.n <= 0 or self.n_recv <= 0:
+            raise RuntimeError("the fused exchange does not serve this problem")
+        per = self.n_recv + self.n
+        self.data = symm.empty(2 * per, dtype=torch.float32, device=device)
+        self.flags = symm.empty(64, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        hd = symm.rendezvous(self.data, group)
+        hf = symm.rendezvous(self.flags, group)
+        self.world, self.rank = hd.world_size, hd.rank
+        self._hd, self._hf = hd, hf
+        arr = ctypes.c_void_p * self.world
+        self._tables = []
+        self._groups = []
+        for b in (0, 1):
+            recv = arr(*[int(p) + b * per * 4 for p in hd.buffer_ptrs])
+            full = arr(*[int(p) + (b * per + self.n_recv) * 4 for p in hd.buffer_ptrs])
+            flags = arr(*[int(p) for p in hf.buffer_ptrs])
+            g = _C.PeerGroup()
+            g.world, g.rank, g.epoch, g.reserved = self.world, self.rank, 0, 0
+            g.recv = ctypes.cast(recv, ctypes.POINTER(ctypes.c_void_p))
+            g.full = ctypes.cast(full, ctypes.POINTER(ctypes.c_void_p))
+            g.flags = ctypes.cast(flags, ctypes.POINTER(ctypes.c_void_p))
+            self._tables.append((recv, full, flags))          # keep the arrays alive
+            self._groups.append(g)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+
+    def begin(self):
+        """Starts the next exchange: the group both of its passes are called with."""
+        self.epoch += 1
+        g = self._groups[self.epoch & 1]
+        g.epoch = self.epoch
+        return g
 
 
 _exchanges = {}
 
 
+def _peer_capable(group, device):
+    if not (dist.is_available() and dist.is_initialized()) or device.type != "cuda":
+        return False
+    if dist.get_world_size(group) < 2 or dist.get_backend(group) != "nccl":
+        return False
+    return os.environ.get("FBLA_PEER_EXCHANGE", "1") != "0"
+
+
+def _agreed(make, group, device, same=()):
+    """``make()`` on every rank; the result, or None when it failed on ANY rank or the integers in
+    ``same`` differ between ranks (decided collectively, so that all ranks take the same path)."""
+    ex = None
+    try:
+        ex = make()
+    except Exception as e:          # noqa: BLE001 - any failure means "use the library all-reduce"
+        warnings.warn(f"peer-memory state exchange unavailable ({type(e).__name__}: {e}); using all_reduce")
+    vals = [1 if ex is not None else 0]
+    for x in same:
+        vals += [int(x), -int(x)]
+    t = torch.tensor(vals, device=device, dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)   # also: every rank's flags are zeroed by now
+    t = t.tolist()
+    ok = t[0] == 1 and all(t[1 + 2 * i] == -t[2 + 2 * i] for i in range(len(same)))
+    return ex if ok else None
+
+
 def _peer_exchange(group, device, n):
     """The exchange object for (group, device, state size), or None when the group is not an NCCL
-    group of more than one GPU rank, the switch ``FBLA_PEER_EXCHANGE=0`` is set, or setting it up
-    failed on any rank (decided collectively, so that all ranks take the same path)."""
-    if not (dist.is_available() and dist.is_initialized()) or device.type != "cuda":
-        return None
-    if dist.get_world_size(group) < 2 or dist.get_backend(group) != "nccl":
-        return None
-    if os.environ.get("FBLA_PEER_EXCHANGE", "1") == "0":
+    group of more than one GPU rank, the switch ``FBLA_PEER_EXCHANGE=0`` is set, the state size is
+    not a multiple of four floats, or setting it up failed on any rank."""
+    if not _peer_capable(group, device) or n % 4 != 0 or dist.get_world_size(group) > 16:
         return None
     key = (id(group) if group is not None else 0, device.index, n)
     if key not in _exchanges:
-        ex = None
-        try:
-            # peers are read with plain loads; no multicast object is needed or wanted
-            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-            ex = _PeerExchange(group if group is not None else dist.group.WORLD, device, n)
-        except Exception as e:          # noqa: BLE001 - any failure means "use the library all-reduce"
-            warnings.warn(f"peer-memory state exchange unavailable ({type(e).__name__}: {e}); using all_reduce")
-        ok = torch.tensor([1 if ex is not None else 0], device=device, dtype=torch.int32)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)   # also: every rank's flags are zeroed by now
-        _exchanges[key] = ex if int(ok.item()) == 1 else None
+        grp = group if group is not None else dist.group.WORLD
+        _exchanges[key] = _agreed(lambda: _PeerExchange(grp, device, n), group, device)
     return _exchanges[key]
+
+
+def _fused_exchange(group, prob, tensors):
+    """The in-kernel exchange for this problem, or None when it does not apply (not an NCCL group of
+    2 to 8 GPUs, a shape the tensor-core kernels do not serve, ranks that disagree on the local
+    shape, or a set-up failure on any rank)."""
+    like = tensors[0]
+    if not hasattr(_backend, "sharded_fwd_state") or not _peer_capable(group, like.device):
+        return None
+    if dist.get_world_size(group) > 8 or not _backend.sharded_supported(prob):
+        return None
+    key = (id(group) if group is not None else 0, like.device.index, "fused", prob.dtype, prob.batch, prob.heads,
+           prob.seq_len, prob.dk, prob.dv, prob.normalize)
+    if key not in _exchanges:
+        grp = group if group is not None else dist.group.WORLD
+        sms = torch.cuda.get_device_properties(like.device).multi_processor_count
+        _exchanges[key] = _agreed(lambda: _FusedExchange(grp, like.device, prob), group, like.device,
+                                  same=(prob.seq_len, prob.batch, prob.heads, sms))
+    return _exchanges[key]
+
+
+def _aligned(*tensors):
+    """Contiguous tensors whose storage starts on a 16-byte boundary (what the tensor-core kernels
+    need); a view at an odd offset is copied."""
+    return [t if t is None or t.data_ptr() % 16 == 0 else t.clone() for t in tensors]
 
 
 def _summed_state(produce, prob, like, group):
@@ -144,8 +237,16 @@ class _SeqSharded(torch.autograd.Function):
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1],
                                      normalize=normalize, scale=scale, eps=eps, norm_len=norm_len,
                                      flags=_backend.default_flags())
-        state = _summed_state(lambda out: _backend.fwd_state(op, prob, k, v, out=out), prob, q, group)
-        o = _backend.fwd_out(op, prob, q, state, torch.empty_like(v))
+        fx = _fused_exchange(group, prob, (q, k, v))
+        if fx is not None:
+            q, k, v = _aligned(q, k, v)
+            grp = fx.begin()
+            _backend.sharded_fwd_state(prob, k, v, grp)
+            state = torch.empty(fx.n, dtype=torch.float32, device=q.device)
+            o = _backend.sharded_fwd_out(prob, q, grp, torch.empty_like(v), state)
+        else:
+            state = _summed_state(lambda out: _backend.fwd_state(op, prob, k, v, out=out), prob, q, group)
+            o = _backend.fwd_out(op, prob, q, state, torch.empty_like(v))
         ctx.save_for_backward(q, k, v, state)
         ctx.args = (scale, eps, norm_len, normalize, group)
         return o
@@ -160,10 +261,16 @@ class _SeqSharded(torch.autograd.Function):
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1],
                                      normalize=normalize, scale=scale, eps=eps, norm_len=norm_len,
                                      flags=_backend.default_flags())
-        dq = torch.empty_like(q)
-        dstate = _summed_state(lambda out: _backend.bwd_state(op, prob, q, do, state, dq, out=out), prob, q, group)
-        dk, dv = torch.empty_like(k), torch.empty_like(v)
-        _backend.bwd_in(op, prob, k, v, dstate, dk, dv)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        fx = _fused_exchange(group, prob, (q, k, v))
+        if fx is not None:
+            do, = _aligned(do)
+            grp = fx.begin()
+            _backend.sharded_bwd_state(prob, q, do, state, grp, dq)
+            _backend.sharded_bwd_in(prob, k, v, grp, dk, dv)
+        else:
+            dstate = _summed_state(lambda out: _backend.bwd_state(op, prob, q, do, state, dq, out=out), prob, q, group)
+            _backend.bwd_in(op, prob, k, v, dstate, dk, dv)
         return dq, dk, dv, None, None, None, None, None
 
 
@@ -175,9 +282,17 @@ class _SeqShardedDecoupled(torch.autograd.Function):
         B, H, L, K = q.shape
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
                                      scale=scale, eps=eps, norm_len=norm_len, flags=_backend.default_flags())
-        state = _summed_state(lambda out: _backend.fwd_state("decoupled_la", prob, k, v, k_rope=k_rope, out=out),
-                              prob, q, group)
-        o = _backend.fwd_out("decoupled_la", prob, q, state, torch.empty_like(v), q_rope=q_rope)
+        fx = _fused_exchange(group, prob, (q, k, v)) if (K, v.shape[-1]) == (64, 64) else None
+        if fx is not None:
+            q, k, q_rope, k_rope, v = _aligned(q, k, q_rope, k_rope, v)
+            grp = fx.begin()
+            _backend.sharded_fwd_state(prob, k, v, grp, k_rope=k_rope)
+            state = torch.empty(fx.n, dtype=torch.float32, device=q.device)
+            o = _backend.sharded_fwd_out(prob, q, grp, torch.empty_like(v), state, q_rope=q_rope)
+        else:
+            state = _summed_state(lambda out: _backend.fwd_state("decoupled_la", prob, k, v, k_rope=k_rope, out=out),
+                                  prob, q, group)
+            o = _backend.fwd_out("decoupled_la", prob, q, state, torch.empty_like(v), q_rope=q_rope)
         ctx.save_for_backward(q, q_rope, k_rope, v, state)
         ctx.args = (scale, eps, norm_len, group)
         return o
@@ -191,10 +306,17 @@ class _SeqShardedDecoupled(torch.autograd.Function):
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
                                      scale=scale, eps=eps, norm_len=norm_len, flags=_backend.default_flags())
         dq, dq_rope = torch.empty_like(q), torch.empty_like(q_rope)
-        dstate = _summed_state(lambda out: _backend.bwd_state("decoupled_la", prob, q, do, state, dq, q_rope=q_rope,
-                                                              dq_rope=dq_rope, out=out), prob, q, group)
         dk, dk_rope, dv = torch.empty_like(k_rope), torch.empty_like(k_rope), torch.empty_like(v)
-        _backend.bwd_in("decoupled_la", prob, k_rope, v, dstate, dk, dv, dk_rope=dk_rope)
+        fx = _fused_exchange(group, prob, (q, k_rope, v)) if (K, v.shape[-1]) == (64, 64) else None
+        if fx is not None:
+            do, = _aligned(do)
+            grp = fx.begin()
+            _backend.sharded_bwd_state(prob, q, do, state, grp, dq, q_rope=q_rope, dq_rope=dq_rope)
+            _backend.sharded_bwd_in(prob, k_rope, v, grp, dk, dv, dk_rope=dk_rope)
+        else:
+            dstate = _summed_state(lambda out: _backend.bwd_state("decoupled_la", prob, q, do, state, dq, q_rope=q_rope,
+                                                                  dq_rope=dq_rope, out=out), prob, q, group)
+            _backend.bwd_in("decoupled_la", prob, k_rope, v, dstate, dk, dv, dk_rope=dk_rope)
         return dq, dk, dq_rope, dk_rope, dv, None, None, None, None
 
 

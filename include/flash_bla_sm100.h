@@ -42,7 +42,7 @@
 extern "C" {
 #endif
 
-#define FBLA_ABI_VERSION 1
+#define FBLA_ABI_VERSION 2
 
 enum fbla_dtype { FBLA_F32 = 0, FBLA_BF16 = 1, FBLA_F16 = 2 };
 
@@ -134,11 +134,17 @@ int fbla_linear_attn_bwd(const fbla_problem *p, const void *q, const void *k, co
 /* Forward state pass for callers that cannot hand over a workspace and must not allocate: same
  * result as fbla_linear_attn_fwd_state, with the scratch in an 8 MiB device array inside the
  * library (held by every GPU that loads it).  No counterpart in the reference.  Refuses problems
- * whose fbla_workspace_bytes() exceeds 8 MiB or that the tensor-core kernels do not serve.  The
+ * that the tensor-core kernels do not serve or whose tensor-core scratch (one fp32 state per
+ * segment of the tile schedule, at most fbla_workspace_bytes()) exceeds 8 MiB.  The
  * first call on a device resolves the array's address and should precede any stream capture;
  * calls that overlap on the GPU race on the shared array.                                   */
 int fbla_linear_attn_fwd_state_noalloc(const fbla_problem *p, const void *k, const void *v,
                                        float *state, fbla_stream_t stream);
+/* The status word of that entry point on the current device: *value = 0 when none of its kernels
+ * gave up a bounded wait, else the number of the wait; clear != 0 resets it.  Synchronises the
+ * device (two 4-byte copies), allocates nothing.  Once a failure has been read, the entry point
+ * above returns FBLA_ERR_DEVICE until it is cleared.  No counterpart in the reference.        */
+int fbla_noalloc_status(int *value, int clear);
 
 /* ---- simple_la (no normaliser) -------------------------------------------------------
  * Replaces SimpleLinearAttnFunction.forward / .backward,
@@ -241,8 +247,8 @@ int fbla_pisa_bwd(const fbla_pisa_problem *p, const void *q, const void *k, cons
 /* ---- multi-GPU: sum of the sequence-sharded states over the GPUs of one node ---------------
  * The reference runs on one GPU (no counterpart).  A sequence split along T over `world` ranks
  * needs the sum of the ranks' fp32 states between *_fwd_state and *_fwd_out (and between
- * *_bwd_state and *_bwd_in).  This call does it in one kernel with plain loads from the peers'
- * memory (NVLink), where a library all-reduce would cost several launches.
+ * *_bwd_state and *_bwd_in).  For shapes the fused passes below do not serve (fp32, other feature
+ * dims) this call does it in one kernel with plain loads from the peers' memory (NVLink).
  *   peer_states[r]: rank r's state buffer of n_floats floats, mapped into this process (this
  *                   rank's own buffer at index `rank`); the local state must already have been
  *                   written to it by earlier work on `stream`.
@@ -251,25 +257,70 @@ int fbla_pisa_bwd(const fbla_pisa_problem *p, const void *q, const void *k, cons
  *   epoch         : 1, 2, 3, ... the same on every rank for the same exchange.
  *   out           : ordinary device memory; receives sum_r peer_states[r], added in rank order
  *                   (bit-identical on all ranks).
- * Every rank of the group must make the matching call; each waits (at most about a second, then
- * the device status word is set and later calls return FBLA_ERR_DEVICE) for all peers to enter
- * theirs.  Use two buffers alternately for consecutive exchanges: a rank can enter exchange
+ * Every rank of the group must make the matching call; each waits (bounded by FBLA_PEER_WAIT_MS,
+ * then `out` is filled with NaN, the device status word is set and later calls return
+ * FBLA_ERR_DEVICE) for all peers to enter theirs.  Use two buffers alternately for consecutive exchanges: a rank can enter exchange
  * e+2 only after all peers have entered e+1, i.e. have finished reading the buffer of e.      */
 int fbla_peer_state_sum(int world, int rank, const void *const *peer_states,
                         void *const *peer_flags, int64_t n_floats, uint32_t epoch, float *out,
                         fbla_stream_t stream);
 
-/* The same sum in two phases, for more than two ranks: each rank adds its own 1/world slice from
- * all peers and stores it into every peer's gather buffer, a second round of flags follows, then
- * each rank copies its gather buffer to `out` (2 (world-1)/world of the state crosses NVLink per
- * rank instead of world-1 times the state).
- *   peer_gather[r]: rank r's gather buffer of n_floats floats, mapped into this process;
- *   peer_flags[r] : rank r's array of at least 64 32-bit words (first round [0,16), second round
- *                   [16,32), word 48 a device-local counter), all zero before the first exchange.
- * One state buffer and one gather buffer suffice (the second round of flags orders the reuse).  */
-int fbla_peer_state_sum2(int world, int rank, const void *const *peer_states,
-                         void *const *peer_gather, void *const *peer_flags, int64_t n_floats,
-                         uint32_t epoch, float *out, fbla_stream_t stream);
+/* ---- multi-GPU: sequence-sharded passes with the exchange inside the kernels -----------------
+ * No counterpart in the reference (it runs on one GPU).  For what the tensor-core kernels serve
+ * (fixed length, 16-bit, dk, dv in {64, 128}; decoupled at 64 x 64) the state never goes through a
+ * separate reduction or collective: the reducing pass stores each per-segment piece straight into the
+ * memory of the rank that owns the unit (unit u belongs to rank u / ceil(units / world)), and the
+ * consuming pass begins by adding the pieces of its own units -- ranks in order, pieces in CTA order,
+ * so every rank holds the same bits -- storing the sums into every rank's copy, and waiting for the
+ * other ranks' sums.  Two flag rounds over NVLink, no extra launch, plain peer stores and local loads
+ * only (no multicast).
+ *   recv[r]  : rank r's receive buffer of fbla_seq_sharded_recv_floats() floats, 16-byte aligned;
+ *   full[r]  : rank r's copy of the summed state, fbla_state_floats() floats, 16-byte aligned;
+ *   flags[r] : rank r's 64 32-bit flag words, zero before the first exchange;
+ *   all three mapped into this process for every rank r (this rank's own memory at index `rank`);
+ *   epoch    : 1, 2, 3, ... the same on every rank for the same exchange (one exchange = one
+ *              *_fwd_state + *_fwd_out pair, or one *_bwd_state + *_bwd_in pair).
+ * Use two (recv, full) pairs alternately for consecutive exchanges and one flags array for all: a
+ * rank can start exchange e+2 only after every peer has finished e+1, i.e. has finished reading the
+ * buffers of e.  Every rank must make the same calls in the same order with the same problem (same
+ * local seq_len: the ranks' tile schedules must agree).  Each wait for a peer is bounded
+ * (FBLA_PEER_WAIT_MS in the environment, default 5000): after that the kernel gives up, its outputs
+ * are undefined, fbla_device_status() becomes non-zero and every later call returns FBLA_ERR_DEVICE
+ * until fbla_clear_device_status().  Ranks that may be further apart should meet at a host barrier
+ * first.  k_rope / q_rope / dq_rope / dk_rope are NULL except for decoupled_la; for the other
+ * operators *_bwd_in takes k in the k_rope position.
+ *   fbla_seq_sharded_fwd_out : state_copy (may be NULL) receives the summed state, fbla_state_floats()
+ *                              floats of ordinary memory -- what *_bwd_state takes as `state`.   */
+typedef struct fbla_peer_group {
+    int32_t world;          /* 2..8 ranks, GPUs of one node                   */
+    int32_t rank;
+    uint32_t epoch;
+    int32_t reserved;
+    void *const *recv;      /* [world] */
+    void *const *full;      /* [world] */
+    void *const *flags;     /* [world] */
+} fbla_peer_group;
+
+int fbla_seq_sharded_supported(const fbla_problem *p);
+int64_t fbla_seq_sharded_recv_floats(const fbla_problem *p, int world);
+int fbla_seq_sharded_fwd_state(const fbla_problem *p, const void *k, const void *k_rope, const void *v,
+                               const fbla_peer_group *group, fbla_stream_t stream);
+int fbla_seq_sharded_fwd_out(const fbla_problem *p, const void *q, const void *q_rope,
+                             const fbla_peer_group *group, void *o, float *state_copy,
+                             fbla_stream_t stream);
+int fbla_seq_sharded_bwd_state(const fbla_problem *p, const void *q, const void *q_rope, const void *d_o,
+                               const float *state, const fbla_peer_group *group, void *dq, void *dq_rope,
+                               fbla_stream_t stream);
+int fbla_seq_sharded_bwd_in(const fbla_problem *p, const void *k_rope, const void *v,
+                            const fbla_peer_group *group, void *dk, void *dk_rope, void *dv,
+                            fbla_stream_t stream);
+
+/* The status word the kernels write when a bounded wait gives up (0 = none did; otherwise a number
+ * naming the wait).  While it is non-zero every launching call returns FBLA_ERR_DEVICE.  Clear it
+ * once the cause is dealt with; results of the failed call are invalid.  No counterpart in the
+ * reference.                                                                                   */
+int fbla_device_status(void);
+void fbla_clear_device_status(void);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,108 @@
+"""Failure paths on the GPU, without faulting or hanging it: a wait for a peer that never answers
+runs into its (shortened) limit, the kernel returns, the status word names the wait, the next call
+is refused, and after clearing the status the library works again.  Each case runs in a child
+process (the wait limit is read from the environment once per process) on ONE GPU: the "peer" is a
+second set of buffers on the same device that nothing ever writes."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "flash-bidirectional-linear-attention_b200")
+
+_PRELUDE = """
+import ctypes, os, sys
+os.environ["FBLA_PEER_WAIT_MS"] = "100"
+sys.path.insert(0, %r)
+import torch
+from flash_bla import _C
+from flash_bla.ops import _passes as P
+from flash_bla.ops.linear_attn.fused import linear_attention
+L = _C.lib()
+torch.manual_seed(0)
+B, H, T, D = 1, 2, 512, 64
+q = (torch.rand(B, H, T, D, device="cuda") + 0.1).bfloat16()
+k = (torch.rand(B, H, T, D, device="cuda") + 0.1).bfloat16()
+v = torch.randn(B, H, T, D, device="cuda").bfloat16()
+
+def works_again():
+    o = linear_attention(q, k, v)
+    qf, kf, vf = q.float(), k.float(), v.float()
+    ref = (qf @ (kf.transpose(-1, -2) @ vf / T)) / ((qf * kf.mean(-2, keepdim=True)).sum(-1, keepdim=True) + 1e-6)
+    torch.cuda.synchronize()
+    assert ((o.float() - ref).abs().max() / ref.pow(2).mean().sqrt()).item() < 2e-2
+
+def refused():
+    try:
+        linear_attention(q, k, v)
+    except RuntimeError as e:
+        return "bounded wait" in str(e)
+    return False
+""" % PKG
+
+
+def _run(body):
+    code = _PRELUDE + textwrap.dedent(body)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "CHILD-OK" in out.stdout
+
+
+def test_sequence_sharded_pass_gives_up_on_a_silent_peer_and_recovers():
+    _run("""
+    prob = P.make_problem(q, batch=B, heads=H, seq_len=T, dk=D, dv=D, normalize=True, scale=1.0 / (2 * T),
+                          eps=1e-6, norm_len=2 * T)
+    assert L.fbla_seq_sharded_supported(ctypes.byref(prob)) == 1
+    n = L.fbla_state_floats(ctypes.byref(prob))
+    n_recv = L.fbla_seq_sharded_recv_floats(ctypes.byref(prob), 2)
+    assert n > 0 and n_recv >= 2 * n
+    recv = [torch.zeros(n_recv, device="cuda") for _ in range(2)]
+    full = [torch.zeros(n, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
+    arr = ctypes.c_void_p * 2
+    tabs = [arr(*[t.data_ptr() for t in ts]) for ts in (recv, full, flags)]
+    g = _C.PeerGroup()
+    g.world, g.rank, g.epoch, g.reserved = 2, 0, 1, 0
+    g.recv, g.full, g.flags = (ctypes.cast(t, ctypes.POINTER(ctypes.c_void_p)) for t in tabs)
+    o = torch.empty_like(v)
+    state = torch.empty(n, device="cuda")
+    st = _C.stream_of(q)
+    _C.check(L.fbla_seq_sharded_fwd_state(ctypes.byref(prob), k.data_ptr(), None, v.data_ptr(), ctypes.byref(g), st))
+    torch.cuda.synchronize()
+    assert L.fbla_device_status() == 0
+    assert flags[0][0].item() == 1 and flags[1][0].item() == 1      # rank 0 told both ranks; rank 1 stays silent
+    _C.check(L.fbla_seq_sharded_fwd_out(ctypes.byref(prob), q.data_ptr(), None, ctypes.byref(g), o.data_ptr(),
+                                        state.data_ptr(), st))
+    torch.cuda.synchronize()                                         # returns: the wait is bounded
+    assert L.fbla_device_status() == 231, L.fbla_device_status()
+    assert refused()
+    L.fbla_clear_device_status()
+    assert L.fbla_device_status() == 0
+    works_again()
+    print("CHILD-OK")
+    """)
+
+
+def test_state_sum_kernel_gives_up_on_a_silent_peer_and_recovers():
+    _run("""
+    n = 4096
+    bufs = [torch.ones(n, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
+    arr = ctypes.c_void_p * 2
+    out = torch.zeros(n, device="cuda")
+    rc = L.fbla_peer_state_sum(2, 0, arr(*[b.data_ptr() for b in bufs]), arr(*[f.data_ptr() for f in flags]), n, 1,
+                               out.data_ptr(), _C.stream_of(out))
+    _C.check(rc)
+    torch.cuda.synchronize()
+    assert L.fbla_device_status() == 901
+    assert torch.isnan(out).all()                                    # no sum without the peer
+    assert refused()
+    L.fbla_clear_device_status()
+    works_again()
+    print("CHILD-OK")
+    """)

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
     assert sorted(_C.exported_symbols()) == [n for n in names if n in _C.exported_symbols()]
-    assert lib.fbla_version() == 1
+    assert lib.fbla_version() == 2
 
 
 def test_problem_struct_matches_header_layout():

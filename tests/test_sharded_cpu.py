@@ -83,3 +83,51 @@ def test_partition_sequences_balances_tokens():
     cover = [list(shard_units(48, 8, r)) for r in range(8)]
     assert sum(cover, []) == list(range(48)) and all(len(c) == 6 for c in cover)
     assert [len(shard_units(10, 4, r)) for r in range(4)] == [3, 3, 2, 2]
+
+
+def _leaver(rank, world, port, ret):
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    import host_passes
+    from flash_bla.ops import sharded
+    sharded._backend = host_passes
+    if rank == 1:
+        ret[rank] = "left"            # leaves between steps, before the exchange, with nothing in flight
+        os._exit(0)
+    q = torch.rand(1, 1, 8, 4, dtype=torch.float64)
+    t0 = time.time()
+    try:
+        sharded.seq_sharded_linear_attention(q, q, q)
+        ret[rank] = "returned"
+    except Exception as e:            # noqa: BLE001 - whatever the process group raises
+        ret[rank] = "raised after %.1f s: %s" % (time.time() - t0, type(e).__name__)
+
+
+def test_a_rank_that_leaves_before_the_exchange_ends_the_others_call_with_an_error():
+    """Rank 1 exits before the state exchange; rank 0's call must end with an exception within the
+    process group's timeout instead of waiting for ever."""
+    world = 2
+    ret = mp.Manager().dict()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver, args=(r, world, _free_port_shared(), ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive
+    assert ret.get(1) == "left"
+    assert str(ret.get(0, "")).startswith("raised"), dict(ret)
+
+
+_shared_port = []
+
+
+def _free_port_shared():
+    if not _shared_port:
+        _shared_port.append(_free_port())
+    return _shared_port[0]

@@ -26,26 +26,31 @@ def _worker(rank, world, port, ret):
         from flash_bla.ops.simple_la.fused import simple_la
         from flash_bla.ops.sharded import seq_sharded_linear_attention, seq_sharded_simple_la
         from flash_bla.ops import sharded
+        from flash_bla import _C
+        from flash_bla.ops.linear_attn.decoupled import decoupled_la
+        from flash_bla.ops.sharded import seq_sharded_decoupled_la
         errs = {}
         # every case once with the peer-memory state exchange and once with NCCL's all-reduce
-        for mode, (name, D, dtype) in [(m, c) for m in ("1", "0") for c in (
-                ("linear", 64, torch.bfloat16), ("simple", 128, torch.bfloat16), ("linear_f32", 32, torch.float32))]:
+        cases = (("linear", 64, 64, torch.bfloat16), ("simple", 128, 128, torch.bfloat16),
+                 ("linear_128x64", 128, 64, torch.float16), ("decoupled", 64, 64, torch.bfloat16),
+                 ("simple_64x128", 64, 128, torch.bfloat16), ("linear_f32", 32, 32, torch.float32))
+        for mode, (name, DK, DV, dtype) in [(m, c) for m in ("1", "0") for c in cases]:
             os.environ["FBLA_PEER_EXCHANGE"] = mode
             g = torch.Generator(device="cuda").manual_seed(7)
-            B, H, T = 2, 4, 2048
-            q = torch.rand(B, H, T, D, device="cuda", generator=g).add_(0.1).to(dtype)
-            k = torch.rand(B, H, T, D, device="cuda", generator=g).add_(0.1).to(dtype)
-            v = torch.randn(B, H, T, D, device="cuda", generator=g).to(dtype)
-            do = torch.randn(B, H, T, D, device="cuda", generator=g).to(dtype)
+            B, H, T = 2, 5, 4096 * world                  # 10 units: they do not divide evenly over 4 or 8 ranks
+            n_qk = 4 if name == "decoupled" else 2
+            qk = [torch.rand(B, H, T, DK, device="cuda", generator=g).add_(0.1).to(dtype) for _ in range(n_qk)]
+            v = torch.randn(B, H, T, DV, device="cuda", generator=g).to(dtype)
+            do = torch.randn(B, H, T, DV, device="cuda", generator=g).to(dtype)
+            assert T % world == 0
             sl = slice(rank * T // world, (rank + 1) * T // world)
-            xs = [x[:, :, sl].contiguous().requires_grad_() for x in (q, k, v)]
-            full = [x.clone().requires_grad_() for x in (q, k, v)]
-            if name.startswith("linear"):
-                o = seq_sharded_linear_attention(*xs)
-                o_ref = linear_attention(*full)
-            else:
-                o = seq_sharded_simple_la(*xs)
-                o_ref = simple_la(*full)
+            xs = [x[:, :, sl].contiguous().requires_grad_() for x in qk + [v]]
+            full = [x.clone().requires_grad_() for x in qk + [v]]
+            sharded_fn, plain_fn = {"linear": (seq_sharded_linear_attention, linear_attention),
+                                    "simple": (seq_sharded_simple_la, simple_la),
+                                    "decoupled": (seq_sharded_decoupled_la, decoupled_la)}[name.split("_")[0]]
+            o = sharded_fn(*xs)
+            o_ref = plain_fn(*full)
             o.backward(do[:, :, sl].contiguous())
             o_ref.backward(do)
             grads = [x.grad.clone() for x in xs]
@@ -64,11 +69,14 @@ def _worker(rank, world, port, ret):
                 for _ in range(3):
                     for x in xs:
                         x.grad = None
-                    o2 = (seq_sharded_linear_attention if name.startswith("linear") else seq_sharded_simple_la)(*xs)
+                    o2 = sharded_fn(*xs)
                     o2.backward(do[:, :, sl].contiguous())
                     same = torch.equal(o2, o) and all(torch.equal(x.grad, g) for x, g in zip(xs, grads))
                     errs[f"{name}/repeat"] = max(errs.get(f"{name}/repeat", 0.0), 0.0 if same else 2.0)
-        errs["peer_path_used"] = 0.0 if any(e is not None for e in sharded._exchanges.values()) else 2.0
+        kinds = {type(e).__name__ for e in sharded._exchanges.values() if e is not None}
+        errs["fused_path_used"] = 0.0 if "_FusedExchange" in kinds else 2.0
+        errs["peer_path_used"] = 0.0 if "_PeerExchange" in kinds else 2.0
+        errs["device_status"] = float(_C.lib().fbla_device_status())
         ret[rank] = errs
     finally:
         dist.destroy_process_group()

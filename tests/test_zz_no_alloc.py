@@ -52,6 +52,10 @@ def test_two_calls_match_the_workspace_entry_point(dtype):
         assert torch.equal(got, ref)
         exact = torch.cat([(k.float().transpose(-1, -2) @ v.float()).flatten(-2), k.float().sum(-2)], -1).flatten()
         assert ((got - exact).norm() / exact.norm()).item() < 1e-5
+    # no kernel of the entry point gave up a wait: its status word reads zero
+    status = ctypes.c_int(-1)
+    _C.check(_C.lib().fbla_noalloc_status(ctypes.byref(status), 0))
+    assert status.value == 0
 
 
 def test_refuses_what_it_cannot_serve():
