@@ -242,8 +242,9 @@ pisa_fwd_kernel(PisaParams p, const T* __restrict__ q, const T* __restrict__ k, 
     for (int n = 0; n < p.ns; ++n) {
         __syncthreads();
         const int cb = idx[n];
-        const int bos = cb * p.bs;
-        const int nvalid = max(0, min(p.bs, p.T - bos));
+        const bool cb_ok = cb >= 0 && cb < p.nt;                   // a bad index selects nothing (and reads nothing)
+        const int bos = cb_ok ? cb * p.bs : 0;
+        const int nvalid = cb_ok ? max(0, min(p.bs, p.T - bos)) : 0;
         for (int i = threadIdx.x; i < p.bs * K; i += kPisaThreads) {
             const int r = i / K, d = i - r * K;
             kb[r * KP + d] = r < nvalid ? to_f<T>(k[(base_row + bos + r) * K + d]) : 0.f;
@@ -631,8 +632,9 @@ pisa_bwd_q_kernel(PisaParams p, const T* __restrict__ q, const T* __restrict__ k
     for (int n = 0; n < p.ns; ++n) {
         __syncthreads();
         const int cb = idx[n];
-        const int bos = cb * p.bs;
-        const int nvalid = max(0, min(p.bs, p.T - bos));
+        const bool cb_ok = cb >= 0 && cb < p.nt;                   // a bad index selects nothing (and reads nothing)
+        const int bos = cb_ok ? cb * p.bs : 0;
+        const int nvalid = cb_ok ? max(0, min(p.bs, p.T - bos)) : 0;
         for (int i = threadIdx.x; i < p.bs * K; i += kPisaThreads) {
             const int r = i / K, d = i - r * K;
             kb[r * KP + d] = r < nvalid ? to_f<T>(k[(base_row + bos + r) * K + d]) : 0.f;

@@ -62,7 +62,9 @@ __host__ __device__ inline int last_cta_of_unit(const Schedule& s, int unit) {
 //   flags[r] : rank r's flag words: [0, 8) "the reducing pass of rank q has stored all its pieces",
 //              [16, 24) "rank q has stored the sums of its units", [32], [33] CTA tickets of the
 //              local kernels.  Flags carry the exchange number `epoch` (1, 2, 3, ...).
-// world == 1 switches all of it off.
+// world == 1 switches all of it off.  The kernels take it as a kernel parameter of its own (its pointer
+// tables are indexed with run-time values, which a by-value copy of the parameters would pay for with
+// local memory).
 constexpr int kMaxPeers = 8;
 struct PeerXchg {
     int world, rank;
@@ -99,7 +101,6 @@ struct Params {
     int heads;
     int scale_per_seq;    // scale = 1 / length of the sequence
     float inv_norm_fixed; // > 0: divide the key sum by this length for every sequence; 0: by its own
-    PeerXchg px;          // fixed length only
 };
 
 // The state of one unit as a consuming pass reads it: one vector, or the per-segment pieces that the
@@ -284,15 +285,16 @@ struct TileMap<true> {
 //                  unit that starts here but continues in the next CTA to slot (cta, 1);
 //                  tc_reduce_varlen_kernel adds the pieces in CTA order.
 template <bool VARLEN>
-__device__ __forceinline__ float* segment_destination(const Params& p, const Tile& t, float* state_out) {
+__device__ __forceinline__ float* segment_destination(const Params& p, const PeerXchg& px, const Tile& t,
+                                                      float* state_out) {
     if (!VARLEN) {
         const int piece = (int)blockIdx.x - first_cta_of_unit(p.sch, t.unit);
-        if (p.px.world > 1) {
+        if (px.world > 1) {
             // sequence-sharded: straight into the receive buffer of the rank that sums this unit
-            const int owner = t.unit / p.px.units_per_rank;
-            const int local = t.unit - owner * p.px.units_per_rank;
-            const size_t slot = ((size_t)p.px.rank * p.px.units_per_rank + local) * p.sch.slots_per_unit + piece;
-            return p.px.recv[owner] + slot * p.state_stride;
+            const int owner = t.unit / px.units_per_rank;
+            const int local = t.unit - owner * px.units_per_rank;
+            const size_t slot = ((size_t)px.rank * px.units_per_rank + local) * p.sch.slots_per_unit + piece;
+            return px.recv[owner] + slot * p.state_stride;
         }
         const int slot = t.unit * p.sch.slots_per_unit + piece;
         return p.part + (size_t)slot * p.state_stride;
@@ -379,8 +381,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Cycles an in-CTA wait may last: a CTA of a sequence-sharded call may sit behind a wait for peer
 // GPUs, so its own waits must outlast that one (about two cycles per nanosecond).
-__device__ __forceinline__ long long wait_limit(const Params& p) {
-    return p.px.world > 1 ? ptx::kWaitCycles + 2 * (long long)p.px.wait_ns : ptx::kWaitCycles;
+__device__ __forceinline__ long long wait_limit(const PeerXchg& px) {
+    return px.world > 1 ? ptx::kWaitCycles + 2 * (long long)px.wait_ns : ptx::kWaitCycles;
 }
 // Barrier among the 128 epilogue threads only (the other warps of the CTA are in their own loops).
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -431,8 +433,8 @@ __device__ __forceinline__ void peer_signal_pieces(const PeerXchg& px) {
 // Afterwards p.state (= full[rank]) is complete.  The CTAs of one launch wait for one another in step
 // 3, so the grid must be resident as a whole (one CTA per SM at most, which the schedule guarantees).
 // Returns false when a wait gave up.
-__device__ __forceinline__ bool peer_gather_state(const Params& p, const ptx::Abort& ab, int et, int site) {
-    const PeerXchg& x = p.px;
+__device__ __forceinline__ bool peer_gather_state(const Params& p, const PeerXchg& x, const ptx::Abort& ab, int et,
+                                                  int site) {
     unsigned int* mine = x.flags[x.rank];
     if (et < x.world) peer_wait(mine + et, x, ab, site);
     epilogue_barrier();

@@ -190,22 +190,6 @@ Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) 
     q.heads = p.heads;
     q.scale_per_seq = 0;
     q.inv_norm_fixed = 0.f;
-    q.px = PeerXchg{};
-    q.px.world = 1;
-    if (p.peer != nullptr && p.peer->world > 1) {
-        const PeerArgs& a = *p.peer;
-        q.px.world = a.world;
-        q.px.rank = a.rank;
-        q.px.units_per_rank = (p.units + a.world - 1) / a.world;
-        q.px.epoch = a.epoch;
-        q.px.wait_ns = peer_wait_ns();
-        for (int r = 0; r < a.world; ++r) {
-            q.px.recv[r] = static_cast<float*>(a.recv[r]);
-            q.px.full[r] = static_cast<float*>(a.full[r]);
-            q.px.flags[r] = static_cast<unsigned int*>(a.flags[r]);
-        }
-        q.px.state_copy = a.state_copy;
-    }
     return q;
 }
 
@@ -243,6 +227,27 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, int 
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// The peer tables of a sequence-sharded call (world = 1: none).
+PeerXchg make_px(const KParams& p) {
+    PeerXchg x{};
+    x.world = 1;
+    if (p.peer != nullptr && p.peer->world > 1) {
+        const PeerArgs& a = *p.peer;
+        x.world = a.world;
+        x.rank = a.rank;
+        x.units_per_rank = (p.units + a.world - 1) / a.world;
+        x.epoch = a.epoch;
+        x.wait_ns = peer_wait_ns();
+        for (int r = 0; r < a.world; ++r) {
+            x.recv[r] = static_cast<float*>(a.recv[r]);
+            x.full[r] = static_cast<float*>(a.full[r]);
+            x.flags[r] = static_cast<unsigned int*>(a.flags[r]);
+        }
+        x.state_copy = a.state_copy;
+    }
+    return x;
+}
+
 int mode_of(const KParams& p, bool decoupled) { return !p.normalize ? kSimple : (decoupled ? kDecoupled : kLinear); }
 
 cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
@@ -254,7 +259,7 @@ cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
 
 // ---- per-shape launch helpers ----------------------------------------------------------------
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tk, const CUtensorMap& tv,
+cudaError_t launch_fwd_state(const Params& q, const PeerXchg& px, const CUtensorMap& tkr, const CUtensorMap& tk, const CUtensorMap& tv,
                              cudaStream_t st) {
     using Cfg = FwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -262,13 +267,13 @@ cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUte
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tk, tv, q);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tk, tv, q, px);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& to,
+cudaError_t launch_fwd_out(const Params& q, const PeerXchg& px, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& to,
                            cudaStream_t st) {
     using Cfg = FwdOutCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -277,13 +282,13 @@ cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtens
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tqr, tq, to, q);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tqr, tq, to, q, px);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
+cudaError_t launch_bwd_state(const Params& q, const PeerXchg& px, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
                              const CUtensorMap& tdq, const CUtensorMap& tdqr, cudaStream_t st) {
     using Cfg = BwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -292,13 +297,13 @@ cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUte
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st, tqr, tq, tdo, tdq, tdqr, q);
+    e = launch_dependent(kernel, q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st, tqr, tq, tdo, tdq, tdqr, q, px);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tv, const CUtensorMap& tdk,
+cudaError_t launch_bwd_in(const Params& q, const PeerXchg& px, const CUtensorMap& tkr, const CUtensorMap& tv, const CUtensorMap& tdk,
                           const CUtensorMap& tdkr, const CUtensorMap& tdv, cudaStream_t st) {
     using Cfg = BwdInCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -307,7 +312,7 @@ cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtenso
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tv, tdk, tdkr, tdv, q);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tv, tdk, tdkr, tdv, q, px);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -432,13 +437,14 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
         cudaError_t e;
         if ((e = cudaMemsetAsync(state, 0, sizeof(float) * (size_t)p.units * p.state_stride, st)) != cudaSuccess) return e;
         Params q = make_params_packed(p, dtype);
+        const PeerXchg px = make_px(p);
         q.status = status;
         q.state_out = state;
         q.part = static_cast<float*>(ws);
         CUtensorMap tk, tv;
         if ((e = make_map_packed(&tk, k, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_fwd_state, q, tk, tk, tv, st); };
+        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_fwd_state, q, px, tk, tk, tv, st); };
         if ((e = launch()) != cudaSuccess) return e;
         tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, state, q.sch.ctas);
         note_launches(1);
@@ -449,13 +455,14 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
     const Schedule s = make_schedule(p, sm_count());
     if (status == nullptr) return cudaErrorMemoryAllocation;
     Params q = make_params(p, dtype, s, status);
+    const PeerXchg px = make_px(p);
     q.part = static_cast<float*>(ws);
     CUtensorMap tkr, tk, tv;
     cudaError_t e;
     if ((e = make_map(&tkr, dec ? k_rope : k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tk, k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, tkr, tk, tv, st); };
+    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, px, tkr, tk, tv, st); };
     if ((e = launch()) != cudaSuccess) return e;
     if (p.unreduced || p.peer != nullptr) return cudaSuccess;   // the pieces (in `ws` / at the peers) are the result
     return reduce_partials(q, state, st);
@@ -465,6 +472,7 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
                        cudaStream_t st) {
     if (p.cu != nullptr) {
         Params q = make_params_packed(p, dtype);
+        const PeerXchg px = make_px(p);
         if (q.status == nullptr) return cudaErrorMemoryAllocation;
         q.state = state;
         q.out_a = o;
@@ -472,14 +480,15 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
         cudaError_t e;
         if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&to, o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        FBLA_TC_VARLEN_DISPATCH(launch_fwd_out, q, tq, tq, to, st);
+        FBLA_TC_VARLEN_DISPATCH(launch_fwd_out, q, px, tq, tq, to, st);
     }
     const bool dec = q_rope != nullptr && q_rope != q_;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
+    const PeerXchg px = make_px(p);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
-    q.state = p.peer != nullptr ? q.px.full[q.px.rank] : state;
+    q.state = p.peer != nullptr ? px.full[px.rank] : state;
     if (p.unreduced) q.state_parts = state;
     q.out_a = o;
     CUtensorMap tqr, tq, to;
@@ -487,7 +496,7 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
     if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tq, q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&to, o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    FBLA_TC_DISPATCH(launch_fwd_out, q, tqr, tq, to, st);
+    FBLA_TC_DISPATCH(launch_fwd_out, q, px, tqr, tq, to, st);
 }
 
 cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void* q_rope, const void* d_o,
@@ -496,6 +505,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
         cudaError_t e;
         if ((e = cudaMemsetAsync(dstate, 0, sizeof(float) * (size_t)p.units * p.state_stride, st)) != cudaSuccess) return e;
         Params q = make_params_packed(p, dtype);
+        const PeerXchg px = make_px(p);
         if (q.status == nullptr) return cudaErrorMemoryAllocation;
         q.state = state;
         q.state_out = dstate;
@@ -506,7 +516,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
         if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdo, d_o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdq, dq, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
-        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_bwd_state, q, tq, tq, tdo, tdq, tdq, st); };
+        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_bwd_state, q, px, tq, tq, tdo, tdq, tdq, st); };
         if ((e = launch()) != cudaSuccess) return e;
         tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, dstate, q.sch.ctas);
         note_launches(1);
@@ -516,6 +526,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
+    const PeerXchg px = make_px(p);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = state;
     if (p.unreduced) q.state_parts = state;
@@ -529,7 +540,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     if ((e = make_map(&tdo, d_o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdq, dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdqr, dec ? dq_rope : dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, tqr, tq, tdo, tdq, tdqr, st); };
+    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, px, tqr, tq, tdo, tdq, tdqr, st); };
     if ((e = launch()) != cudaSuccess) return e;
     if (p.unreduced || p.peer != nullptr) return cudaSuccess;
     return reduce_partials(q, dstate, st);
@@ -539,6 +550,7 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
                       void* dk_rope, void* dv, cudaStream_t st) {
     if (p.cu != nullptr) {
         Params q = make_params_packed(p, dtype);
+        const PeerXchg px = make_px(p);
         if (q.status == nullptr) return cudaErrorMemoryAllocation;
         q.state = dstate;
         q.out_a = dk;
@@ -549,14 +561,15 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
         if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdk, dk, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdv, dv, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        FBLA_TC_VARLEN_DISPATCH(launch_bwd_in, q, tk, tv, tdk, tdk, tdv, st);
+        FBLA_TC_VARLEN_DISPATCH(launch_bwd_in, q, px, tk, tv, tdk, tdk, tdv, st);
     }
     const bool dec = dk_rope != nullptr;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
+    const PeerXchg px = make_px(p);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
-    q.state = p.peer != nullptr ? q.px.full[q.px.rank] : dstate;
+    q.state = p.peer != nullptr ? px.full[px.rank] : dstate;
     if (p.unreduced) q.state_parts = dstate;
     q.out_a = dec ? dk_rope : dk;      // kernels without a staged output tile store through these
     q.out_b = dv;
@@ -567,7 +580,7 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
     if ((e = make_map(&tdk, dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdkr, dec ? dk_rope : dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdv, dv, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    FBLA_TC_DISPATCH(launch_bwd_in, q, tkr, tv, tdk, tdkr, tdv, st);
+    FBLA_TC_DISPATCH(launch_bwd_in, q, px, tkr, tv, tdk, tdkr, tdv, st);
 }
 
 }  // namespace fbla

@@ -198,6 +198,8 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool bf16, bool 
     return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
            ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+// (Both operands must have the same 16-bit format: a descriptor that mixes f16 and bf16 raises an
+// illegal-instruction fault on B200.)
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by a single thread.
 __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,

@@ -251,8 +251,17 @@ def pisa_select(qc, kc, scale: float, density: float, h_norm=None):
 
 
 def pisa_fwd_given(q, k, v, kc, vc, h, indices, block_size: int, scale: float,
-                   acc=torch.float64, differentiable: bool = False):
+                   acc=torch.float64, differentiable: bool = False,
+                   reference_group_size: Optional[int] = None):
     """Forward with block statistics and the selection given.
+
+    ``reference_group_size``: restate the reference kernel's evaluation order instead
+    of the formula below.  The kernel visits the unselected blocks in groups of
+    GROUP_SIZE (an autotuned constant, 32 or 128), and each time the running
+    maximum grows it rescales the numerator and ``l`` but NOT the ``g`` gathered
+    from earlier groups (kernel.py:262-276), so with more blocks than one group
+    its result depends on GROUP_SIZE and differs from the formula.  With one
+    group (NT <= GROUP_SIZE) both agree.
 
     Per query row: running max ``m`` over exact logits of the selected blocks
     and block-mean logits of the unselected blocks; ``p_ex = exp(s - m)`` on
@@ -284,12 +293,31 @@ def pisa_fwd_given(q, k, v, kc, vc, h, indices, block_size: int, scale: float,
         sel = torch.zeros(*lead, nt, dtype=torch.bool)
         sel.scatter_(-1, idx, True)
         s_ap = s_ap.masked_fill(sel[..., None, :], float('-inf'))
-        m = torch.maximum(s_ex.max(-1).values, s_ap.max(-1).values)[..., None]
+        if reference_group_size is None:
+            m = torch.maximum(s_ex.max(-1).values, s_ap.max(-1).values)[..., None]
+            p_ex = torch.exp(s_ex - m)
+            p_ap = torch.exp(s_ap - m)
+            g = (p_ap * lens).sum(-1, keepdim=True)
+            num = p_ex @ vv + p_ap @ vc_ + (qb @ h_) * (g * scale / T)
+            outs.append(num / (p_ex.sum(-1, keepdim=True) + g))
+            continue
+        # the reference kernel's order: exact phase, then groups of unselected blocks
+        m = s_ex.max(-1, keepdim=True).values
         p_ex = torch.exp(s_ex - m)
-        p_ap = torch.exp(s_ap - m)
-        g = (p_ap * lens).sum(-1, keepdim=True)
-        num = p_ex @ vv + p_ap @ vc_ + (qb @ h_) * (g * scale / T)
-        outs.append(num / (p_ex.sum(-1, keepdim=True) + g))
+        l = p_ex.sum(-1, keepdim=True)
+        num = p_ex @ vv
+        g = torch.zeros_like(l)
+        for c0 in range(0, nt, reference_group_size):
+            c1 = min(nt, c0 + reference_group_size)
+            s_grp = s_ap[..., c0:c1]
+            new_m = torch.maximum(m, s_grp.max(-1, keepdim=True).values)
+            alpha = torch.exp(m - new_m)
+            num, l, m = num * alpha, l * alpha, new_m               # kernel.py:264-267: g is left as it is
+            p_grp = torch.exp(s_grp - m)
+            num = num + p_grp @ vc_[..., c0:c1, :]
+            g = g + (p_grp * lens[c0:c1]).sum(-1, keepdim=True)
+        num = num + (qb @ h_) * (g * scale / T)
+        outs.append(num / (l + g))
     return torch.cat(outs, dim=-2)
 
 

@@ -14,6 +14,9 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 # RMS (max-abs) against an fp32/fp64 reference evaluated on the same rounded inputs.
 FP32_REL = 1e-5
 LOWP_MAXABS_OVER_RMS = 2e-2
+# 16-bit cases that exceeded the flat 2e-2 and passed under the rounding-floor clause of check();
+# the test session prints them at its end (conftest.py).
+LIFTED = []
 
 
 def load_golden(name):
@@ -23,6 +26,11 @@ def load_golden(name):
         a = z[k]
         out[k] = torch.from_numpy(a) if a.ndim else a.item()
     return out
+
+
+def bf16_from_bits(a):
+    """A uint16 array of bf16 bit patterns (how the larger fixtures store their inputs) as fp32."""
+    return torch.from_numpy(np.asarray(a).astype(np.int16)).view(torch.bfloat16).float()
 
 
 def golden_scale(g):
@@ -66,6 +74,8 @@ def check(got, ref, dtype, what="", magnitude=None):
         floor = O.max_abs_over_rms(ref.to(dtype), ref)
         bar = max(LOWP_MAXABS_OVER_RMS, 1.25 * floor)
         assert err <= bar, f"{what}: max-abs/rms {err:.3e} > {bar:.3e} (rounding floor {floor:.3e})"
+        if err > LOWP_MAXABS_OVER_RMS:          # passed only because of the floor clause: keep a record
+            LIFTED.append((what, str(dtype).replace("torch.", ""), err, floor))
 
 
 def run_op(fn, inputs, do):

@@ -100,6 +100,39 @@ def test_pisa_forward_with_bias():
     assert O.rel_l2(o, g["o"]) < 1e-4
 
 
+def test_pisa_dit_layer_pair_with_one_group():
+    """One (batch, head) pair of the DiT-layer configuration (T = 4608, D = 128, 72 blocks, 7 selected),
+    reference kernel run with GROUP_SIZE = 128: one group covers all blocks, the formula must hold."""
+    import numpy as np
+    from helpers import GOLDEN, bf16_from_bits
+    z = np.load(os.path.join(GOLDEN, "pisa_d.npz"))
+    q, k, v = (bf16_from_bits(z[n]) for n in ("q_bf16", "k_bf16", "v_bf16"))
+    bs, scale = int(z["block_size"]), float(z["scale"])
+    qc, kc, vc, h = O.pisa_block_stats(q, k, v, bs)
+    assert O.rel_l2(kc, torch.from_numpy(z["kc"])) < 1e-5 and O.rel_l2(vc, torch.from_numpy(z["vc"])) < 1e-5
+    assert O.rel_l2(h, torch.from_numpy(z["h"])) < 1e-5
+    idx = O.pisa_select(qc, kc, scale, float(z["density"]))
+    assert idx.shape[-1] == 7
+    assert torch.equal(idx.sort(-1).values, torch.from_numpy(z["indices"]).sort(-1).values)
+    o, _ = O.pisa_fwd(q, k, v, float(z["density"]), bs, scale, indices=torch.from_numpy(z["indices"]))
+    assert O.rel_l2(o[:, :, torch.from_numpy(z["o_rows"])], torch.from_numpy(z["o"])) < 1e-5
+
+
+def test_pisa_more_blocks_than_one_group_pins_the_reference_order():
+    """NT = 40 > GROUP_SIZE = 32: the reference kernel does not rescale the g of earlier groups when
+    the running maximum grows, so its output depends on GROUP_SIZE.  The oracle's restatement of that
+    order reproduces the fixture; the formula (what this library computes, and what the kernel gives
+    with one group) does not."""
+    g = load("pisa_e")
+    bs = int(g["block_size"])
+    args = (g["q"], g["k"], g["v"], g["kc"], g["vc"], g["h"], g["indices"], bs, g["scale"])
+    assert int(g["group_size"]) == 32 and g["kc"].shape[-2] == 40
+    assert O.rel_l2(O.pisa_fwd_given(*args, reference_group_size=32), g["o"]) < 1e-5
+    assert O.rel_l2(O.pisa_fwd_given(*args), g["o"]) > 1e-2
+    # one group covering everything is the formula again
+    assert O.rel_l2(O.pisa_fwd_given(*args, reference_group_size=64), O.pisa_fwd_given(*args)) < 1e-12
+
+
 def test_pisa_backward_matches_finite_differences():
     torch.manual_seed(0)
     q, k, v = (torch.randn(1, 1, 40, 8, dtype=torch.float64) for _ in range(3))

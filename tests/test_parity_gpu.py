@@ -69,6 +69,8 @@ LINEAR_SHAPES = [
     (1, 2, 640, 128, 32),     # DK = 2*d, DV = d/2 as PolaFormer calls it
     (1, 1, 200, 40, 40),
     (1, 2, 2048, 64, 64),
+    (1, 3, 19000, 64, 128),   # DK != DV on the tensor-core kernels, units spread over many CTAs
+    (1, 3, 19000, 128, 64),
 ]
 
 
@@ -97,7 +99,8 @@ def test_linear_attn(shape, dtype, generic):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(1, 2, 300, 64, 64), (2, 2, 257, 128, 128), (1, 2, 100, 24, 8)])
+@pytest.mark.parametrize("shape", [(1, 2, 300, 64, 64), (2, 2, 257, 128, 128), (1, 2, 100, 24, 8),
+                                   (1, 2, 5000, 64, 128), (1, 2, 5000, 128, 64)])
 @pytest.mark.parametrize("scale,eps", [(None, 1e-6), (0.02, 1e-4)])
 def test_linear_attn_scale_eps(shape, dtype, scale, eps):
     B, H, T, DK, DV = shape
@@ -120,7 +123,8 @@ def test_decoupled(shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(2, 2, 1000, 128, 128), (1, 2, 333, 64, 64), (1, 1, 50, 20, 36)])
+@pytest.mark.parametrize("shape", [(2, 2, 1000, 128, 128), (1, 2, 333, 64, 64), (1, 1, 50, 20, 36),
+                                   (1, 3, 19000, 64, 128), (1, 3, 19000, 128, 64)])
 def test_simple_la(shape, dtype):
     B, H, T, DK, DV = shape
     q, k, v, do = make_inputs(2, (B, H, T, DK), (B, H, T, DV), dtype, positive=False)
@@ -239,6 +243,70 @@ def test_full_size_properties_bf16():
     o_again.backward(do)
     assert torch.equal(o_again, o) and torch.equal(q2.grad, q.grad)
     assert torch.equal(k2.grad, k.grad) and torch.equal(v2.grad, v.grad)
+
+
+def test_full_size_simple_la_bf16():
+    """simple_la at B4-H32-D128, T = 262144 on one GPU (8.6 GB per tensor): two (b, h) slices against the CPU
+    oracle, linearity in v, run-to-run determinism."""
+    B, H, T, D = 4, 32, 262144, 128
+    if torch.cuda.mem_get_info()[0] < 100 * 2 ** 30:
+        pytest.skip("needs about 100 GB of free device memory")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q, k, v, do = (torch.randn(B, H, T, D, device="cuda", generator=g, dtype=torch.bfloat16) for _ in range(4))
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = simple_la(q, k, v)
+    o.backward(do)
+    for b, h in ((0, 0), (3, 31)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        qq, kk, vv, dd = (x[sl].detach().cpu() for x in (q, k, v, do))
+        check(o[sl], O.simple_la_fwd(qq, kk, vv), torch.bfloat16, "cfg3.o")
+        for got, r, key in zip((q.grad[sl], k.grad[sl], v.grad[sl]), O.simple_la_bwd(qq, kk, vv, dd), ("dq", "dk", "dv")):
+            check(got, r, torch.bfloat16, "cfg3." + key)
+    dq, dk, dv = q.grad, k.grad, v.grad
+    q.grad = k.grad = v.grad = None
+    o_again = simple_la(q, k, v)
+    o_again.backward(do)
+    assert torch.equal(o_again, o) and torch.equal(q.grad, dq) and torch.equal(k.grad, dk) and torch.equal(v.grad, dv)
+    del o_again, dq, dk, dv
+    q.grad = k.grad = v.grad = None
+    with torch.no_grad():
+        v.mul_(2)
+        o2 = simple_la(q, k, v)
+        assert torch.equal(o2, o * 2)
+
+
+def test_full_size_varlen_bf16():
+    """The packed configuration: 32 sequences with lengths drawn from [256, 16384] (seeded), H = 16, D = 64,
+    bf16.  The shortest, the longest and the two sequences around the middle boundary against the CPU
+    oracle; rewriting one sequence leaves every other sequence bit-identical."""
+    H, D = 16, 64
+    lengths = torch.randint(256, 16385, (32,), generator=torch.Generator().manual_seed(0))
+    cu = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)]).to(torch.int32)
+    tot = int(cu[-1])
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.nn.functional.elu(torch.randn(tot, H, D, device="cuda", generator=g)).add_(1).bfloat16()
+    k = torch.nn.functional.elu(torch.randn(tot, H, D, device="cuda", generator=g)).add_(1).bfloat16()
+    v = torch.randn(tot, H, D, device="cuda", generator=g).bfloat16()
+    do = torch.randn(tot, H, D, device="cuda", generator=g).bfloat16()
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    cud = cu.cuda()
+    o = varlen_linear_attention(q, k, v, cud, int(lengths.max()))
+    o.backward(do)
+    picks = sorted({int(lengths.argmin()), int(lengths.argmax()), 15, 16})
+    for s in picks:
+        lo, hi = int(cu[s]), int(cu[s + 1])
+        qq, kk, vv, dd = (x[lo:hi].detach().cpu().transpose(0, 1) for x in (q, k, v, do))     # (H, len, D)
+        check(o[lo:hi].transpose(0, 1), O.linear_attn_fwd(qq, kk, vv), torch.bfloat16, f"cfg4.o[{s}]")
+        for got, r, key in zip((q.grad, k.grad, v.grad), O.linear_attn_bwd(qq, kk, vv, dd), ("dq", "dk", "dv")):
+            check(got[lo:hi].transpose(0, 1), r, torch.bfloat16, f"cfg4.{key}[{s}]")
+    # no state leaks across the boundaries: change sequence 16 only
+    lo, hi = int(cu[16]), int(cu[17])
+    k2, v2 = k.detach().clone(), v.detach().clone()
+    k2[lo:hi] += 0.5
+    v2[lo:hi] *= -1.0
+    o2 = varlen_linear_attention(q.detach(), k2, v2, cud, int(lengths.max()))
+    assert torch.equal(o2[:lo], o.detach()[:lo]) and torch.equal(o2[hi:], o.detach()[hi:])
+    assert not torch.equal(o2[lo:hi], o.detach()[lo:hi])
 
 
 def test_empty_and_errors():

@@ -51,6 +51,46 @@ def test_golden_with_bias():
     assert O.rel_l2(o0.cpu(), g["o"]) > 1e-3
 
 
+def test_golden_dit_layer_pair_on_the_tensor_core_kernels():
+    """One (batch, head) pair of the DiT-layer configuration, bf16, against the output of the reference's
+    own kernel (GROUP_SIZE = 128, one group) on the same bf16-rounded inputs."""
+    import numpy as np
+    import os
+    from helpers import GOLDEN, bf16_from_bits
+    z = np.load(os.path.join(GOLDEN, "pisa_d.npz"))
+    q, k, v = (bf16_from_bits(z[n]).bfloat16().cuda() for n in ("q_bf16", "k_bf16", "v_bf16"))
+    bs, scale, density = int(z["block_size"]), float(z["scale"]), float(z["density"])
+    qc, kc, vc = block_statistics(q, k, v, bs)
+    assert O.rel_l2(kc.cpu(), torch.from_numpy(z["kc"])) < 1e-5 and O.rel_l2(vc.cpu(), torch.from_numpy(z["vc"])) < 1e-5
+    h = first_order_state(k, v, kc, vc, bs)
+    assert O.rel_l2(h.cpu(), torch.from_numpy(z["h"])) < 2e-3
+    rows = torch.from_numpy(z["o_rows"])
+    want = torch.from_numpy(z["o"])
+    o = attention_forward(q, k, v, kc, vc, h, torch.from_numpy(z["indices"]).cuda(), bs, scale)
+    check(o[:, :, rows.cuda()], want, torch.bfloat16, "pisa_d.o")
+    # the whole operator: its own selection (bf16 scores) may differ in a few near-ties from the fp32
+    # selection of the fixture, so most rows must agree, not all
+    o2 = piecewise_sparse_attention(q, k, v, density=density, block_size=bs, scale=scale)
+    err = (o2[:, :, rows.cuda()].float().cpu() - want).abs().amax(-1) / want.pow(2).mean().sqrt()
+    assert (err <= 2e-2).float().mean().item() > 0.9
+
+
+def test_more_blocks_than_one_group_follows_the_formula():
+    """NT = 40 > the reference's GROUP_SIZE = 32: the fixture holds the reference kernel's
+    order-dependent result (pinned by the oracle's restatement of that order in the CPU tests); this
+    library rescales g as well, i.e. computes the formula, and so differs from the fixture there."""
+    g = load_golden("pisa_e")
+    bs = int(g["block_size"])
+    q, k, v = (g[x].cuda() for x in ("q", "k", "v"))
+    qc, kc, vc = block_statistics(q, k, v, bs)
+    h = first_order_state(k, v, kc, vc, bs)
+    o = attention_forward(q, k, v, kc, vc, h, g["indices"].cuda(), bs, g["scale"]).cpu()
+    args = (g["q"], g["k"], g["v"], g["kc"], g["vc"], g["h"], g["indices"], bs, g["scale"])
+    assert O.rel_l2(o, O.pisa_fwd_given(*args)) < 1e-4
+    assert O.rel_l2(O.pisa_fwd_given(*args, reference_group_size=32), g["o"]) < 1e-5
+    assert O.rel_l2(o, g["o"]) > 1e-2
+
+
 CASES = [
     (1, 2, 300, 64, 64, 64, 0.2),
     (2, 2, 1000, 128, 128, 64, 0.1),
@@ -117,6 +157,77 @@ def test_backward_matches_oracle(case, dtype):
             assert err < 5e-5, f"pisa{case}.{name}: {err:.3e}"
         else:
             check(got, ref, dtype, f"pisa{case}.{name}")
+
+
+def test_full_size_dit_layer_bf16():
+    """The DiT-layer configuration at its full size (B2-H24, T = 4608, D = 128, block 64, density 0.1, bf16):
+    two (b, h) pairs of forward and backward against the CPU oracle (with the selection the library made),
+    (b, h) pairs independent of one another, forward bit-reproducible."""
+    B, H, T, D, bs, density = 2, 24, 4608, 128, 64, 0.1
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v, do = (torch.randn(B, H, T, D, device="cuda", generator=g).bfloat16() for _ in range(4))
+    scale = D ** -0.5
+    qc, kc, vc = block_statistics(q, k, v, bs)
+    idx = select_blocks(qc, kc, scale, density, torch.bfloat16)
+    assert idx.shape == (B, H, T // bs, 7)
+    xs = [x.clone().requires_grad_() for x in (q, k, v)]
+    o = piecewise_sparse_attention(*xs, density=density, block_size=bs)
+    o.backward(do)
+    for b, h in ((0, 0), (1, 23)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        qq, kk, vv, dd = (x[sl].cpu() for x in (q, k, v, do))
+        ref, _ = O.pisa_fwd(qq, kk, vv, density, bs, scale, indices=idx[sl].cpu())
+        check(o[sl], ref, torch.bfloat16, "cfg5.o")
+        for got, r, key in zip((x.grad[sl] for x in xs), O.pisa_bwd(qq, kk, vv, dd, idx[sl].cpu(), bs, scale),
+                               ("dq", "dk", "dv")):
+            check(got, r, torch.bfloat16, "cfg5." + key)
+    o_again = piecewise_sparse_attention(q, k, v, density=density, block_size=bs)
+    assert torch.equal(o_again, o.detach())
+    k2, v2 = k.clone(), v.clone()
+    k2[1, 5] += 0.25
+    v2[1, 5] *= -1.0
+    o2 = piecewise_sparse_attention(q, k2, v2, density=density, block_size=bs)
+    same = (o2 == o.detach()).flatten(2).all(dim=-1)
+    assert not same[1, 5]
+    same[1, 5] = True
+    assert same.all()
+
+
+@pytest.mark.parametrize("dtype,case", [(torch.float32, (1, 2, 192, 32, 32, 32)), (torch.bfloat16, (1, 2, 384, 64, 64, 64))])
+def test_out_of_range_block_indices_select_nothing(dtype, case):
+    """Indices come from the caller through the C ABI: -1 and NT must not be dereferenced.  A bad index
+    selects nothing, on the CUDA-core kernels (fp32) and on the tensor-core kernels (bf16) alike, so
+    the result equals the one with that entry replaced by a duplicate of a good one... which counts the
+    block once: compare the two kernel families with each other and require finite outputs."""
+    from flash_bla.ops.piecewise_attn.kernel import attention_backward
+    B, H, T, K, V, bs = case
+    g = torch.Generator().manual_seed(2)
+    q, k, v, do = (torch.randn(B, H, T, K, generator=g).to(dtype).cuda() for _ in range(4))
+    nt = T // bs
+    qc, kc, vc = block_statistics(q, k, v, bs)
+    h = first_order_state(k, v, kc, vc, bs)
+    idx = torch.empty(B, H, nt, 3, dtype=torch.int32, device="cuda")
+    idx[..., 0] = torch.arange(nt, device="cuda")          # the query block's own key block
+    idx[..., 1] = -1
+    idx[..., 2] = nt
+    scale = K ** -0.5
+    o, stats = attention_forward(q, k, v, kc, vc, h, idx, bs, scale, want_stats=True)
+    dq, dk, dv = attention_backward(q, k, v, o, do, kc, vc, h, idx, stats, bs, scale)
+    for t in (o, dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+    # the same selection without the bad entries, on the oracle
+    good = idx[..., :1].cpu().long()
+    ref, _ = O.pisa_fwd(q.cpu(), k.cpu(), v.cpu(), 0.0, bs, scale, indices=good)
+    if dtype == torch.float32:
+        assert O.rel_l2(o.cpu(), ref) < 2e-5
+    else:
+        check(o, ref, dtype, "bad-index.o")
+    rq, rk, rv = O.pisa_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), good, bs, scale)
+    for got, r, name in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
+        if dtype == torch.float32:
+            assert O.rel_l2(got.cpu(), r) < 5e-5, name
+        else:
+            check(got, r, dtype, "bad-index." + name)
 
 
 def test_autograd_end_to_end():

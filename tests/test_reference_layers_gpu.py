@@ -37,3 +37,20 @@ def test_reference_layer_self_check(layer, tmp_path):
     import re
     ratios = [float(x) for x in re.findall(r"ratio: ([0-9.eE+-]+)", r.stdout)]
     assert all(x < 1e-3 for x in ratios), r.stdout[-2000:]
+
+
+REF_VARLEN_TEST = os.path.join(ROOT, "baseline", "_ref", "tests", "ops", "test_varlen_linear_attn.py")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_VARLEN_TEST), reason="the reference's test file is not staged under baseline/_ref/tests")
+def test_reference_varlen_pytest_runs_unchanged(tmp_path):
+    """The reference's only pytest file (tests/ops/test_varlen_linear_attn.py: 32 parameter combinations of
+    varlen forward + backward against its dense torch statement, and the oversized-max_seqlen case), copied
+    as it is to a temporary directory and run in a child process with this package providing ``flash_bla``."""
+    shutil.copy(REF_VARLEN_TEST, tmp_path / "test_varlen_linear_attn.py")
+    env = dict(os.environ, PYTHONPATH=PKG)
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-p", "no:cacheprovider", "--rootdir", str(tmp_path),
+                        str(tmp_path / "test_varlen_linear_attn.py")], env=env, capture_output=True, text=True,
+                       timeout=900, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert "33 passed" in r.stdout, r.stdout[-1000:]
