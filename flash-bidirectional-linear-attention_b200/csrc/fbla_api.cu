@@ -459,6 +459,7 @@ int fbla_seq_sharded_bwd_in(const fbla_problem* p, const void* k_rope, const voi
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward input pass (sequence-sharded)");
 }
 
+void fbla_debug_peer_trace(uint64_t* dev) { fbla::tc_set_peer_trace(reinterpret_cast<unsigned long long*>(dev)); }
 int fbla_device_status(void) { return fbla::tc_device_status(); }
 void fbla_clear_device_status(void) { fbla::tc_clear_device_status(); }
 

@@ -75,6 +75,10 @@ struct PeerXchg {
     float* full[kMaxPeers];
     unsigned int* flags[kMaxPeers];
     float* state_copy;              // consuming pass: private copy of the summed state (may be null)
+    unsigned long long* trace;      // measurement aid (may be null): 16 timestamps of this exchange, written by
+                                    // one thread per kernel: [0] last CTA of the reducing pass signals,
+                                    // [8..12] consuming pass, CTA 0: gather entered, pieces of all ranks in
+                                    // place, own sums stored, sums of all ranks in place, private copy done
 };
 
 struct Params {
@@ -386,6 +390,23 @@ __device__ __forceinline__ long long wait_limit(const PeerXchg& px) {
 }
 // Barrier among the 128 epilogue threads only (the other warps of the CTA are in their own loops).
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// The same barrier, returning to every thread whether ANY of the 128 passed a true predicate: a
+// decision all of them take the same way (threads that left on different sides of it would meet at
+// different barriers afterwards).
+__device__ __forceinline__ bool epilogue_barrier_any(bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, 1, 128, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t"
+        "}"
+        : "=r"(out)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return out != 0;
+}
 
 // Waits until *flag has reached `epoch`, at most px.wait_ns; on giving up records `site` in the CTA's
 // abort flag and in the library's status word and returns false.
@@ -419,6 +440,7 @@ __device__ __forceinline__ void peer_signal_pieces(const PeerXchg& px) {
         mine[32] = 0;                       // every CTA has drawn: ready for the next launch
         __threadfence_system();
         for (int r = 0; r < px.world; ++r) st_release_sys(px.flags[r] + px.rank, px.epoch);
+        if (px.trace != nullptr) px.trace[0] = global_ns();
     }
 }
 
@@ -436,9 +458,11 @@ __device__ __forceinline__ void peer_signal_pieces(const PeerXchg& px) {
 __device__ __forceinline__ bool peer_gather_state(const Params& p, const PeerXchg& x, const ptx::Abort& ab, int et,
                                                   int site) {
     unsigned int* mine = x.flags[x.rank];
+    const bool tracer = x.trace != nullptr && blockIdx.x == 0 && et == 0;
+    if (tracer) x.trace[8] = global_ns();
     if (et < x.world) peer_wait(mine + et, x, ab, site);
-    epilogue_barrier();
-    if (*ab.cta_flag != 0) return false;
+    if (epilogue_barrier_any(*ab.cta_flag != 0)) return false;
+    if (tracer) x.trace[9] = global_ns();
     const int s4 = p.state_stride >> 2;                       // float4 per unit (the stride is a multiple of 4)
     const int u0 = x.rank * x.units_per_rank;
     const int u1 = min(p.sch.units, u0 + x.units_per_rank);
@@ -461,6 +485,7 @@ __device__ __forceinline__ bool peer_gather_state(const Params& p, const PeerXch
     }
     __threadfence_system();
     epilogue_barrier();
+    if (tracer) x.trace[10] = global_ns();
     if (et == 0) {
         const unsigned int ticket = atomicAdd(mine + 33, 1u);
         if (ticket == gridDim.x - 1) {
@@ -470,14 +495,18 @@ __device__ __forceinline__ bool peer_gather_state(const Params& p, const PeerXch
         }
     }
     if (et < x.world) peer_wait(mine + 16 + et, x, ab, site + 1);
-    epilogue_barrier();
-    if (*ab.cta_flag != 0) return false;
+    if (epilogue_barrier_any(*ab.cta_flag != 0)) return false;
+    if (tracer) x.trace[11] = global_ns();
     if (x.state_copy != nullptr) {
         const long long all4 = (long long)p.sch.units * s4;
         const float4* src = reinterpret_cast<const float4*>(x.full[x.rank]);
         float4* dst = reinterpret_cast<float4*>(x.state_copy);
         for (long long i = (long long)blockIdx.x * kEpiThreads + et; i < all4; i += (long long)gridDim.x * kEpiThreads)
             dst[i] = __ldcg(src + i);
+    }
+    if (x.trace != nullptr) {
+        epilogue_barrier();                 // all 128 threads: the copy of this CTA is complete
+        if (tracer) x.trace[12] = global_ns();
     }
     return true;
 }

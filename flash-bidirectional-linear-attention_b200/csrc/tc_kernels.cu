@@ -227,6 +227,10 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, int 
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// Measurement aid: when set, every sequence-sharded exchange records its timestamps in slot
+// (epoch mod 256) of this device buffer (16 64-bit words per slot).
+unsigned long long* g_peer_trace = nullptr;
+
 // The peer tables of a sequence-sharded call (world = 1: none).
 PeerXchg make_px(const KParams& p) {
     PeerXchg x{};
@@ -244,6 +248,7 @@ PeerXchg make_px(const KParams& p) {
             x.flags[r] = static_cast<unsigned int*>(a.flags[r]);
         }
         x.state_copy = a.state_copy;
+        x.trace = g_peer_trace != nullptr ? g_peer_trace + (size_t)(a.epoch & 255u) * 16 : nullptr;
     }
     return x;
 }
@@ -419,6 +424,7 @@ int64_t tc_peer_recv_floats(const KParams& p, int world) {
 }
 
 unsigned long long tc_peer_wait_ns() { return peer_wait_ns(); }
+void tc_set_peer_trace(unsigned long long* dev) { g_peer_trace = dev; }
 int tc_device_status() { return g_status_host != nullptr ? *static_cast<volatile int*>(g_status_host) : 0; }
 void tc_clear_device_status() {
     if (g_status_host != nullptr) *static_cast<volatile int*>(g_status_host) = 0;

@@ -18,6 +18,9 @@ int64_t tc_workspace_bytes(const KParams& p);
 int64_t tc_peer_recv_floats(const KParams& p, int world);
 // Limit of a kernel's wait for a peer GPU, nanoseconds (FBLA_PEER_WAIT_MS in the environment).
 unsigned long long tc_peer_wait_ns();
+// Measurement aid: device buffer of 256 x 16 64-bit words that receives the timestamps of the
+// sequence-sharded exchanges (NULL switches it off).
+void tc_set_peer_trace(unsigned long long* dev);
 // Clears the status word after a reported failure.
 void tc_clear_device_status();
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,

@@ -103,7 +103,8 @@ def exported_symbols():
               "fbla_pisa_bwd_scratch_floats"]
     names += ["fbla_peer_state_sum", "fbla_seq_sharded_supported", "fbla_seq_sharded_recv_floats",
               "fbla_seq_sharded_fwd_state", "fbla_seq_sharded_fwd_out", "fbla_seq_sharded_bwd_state",
-              "fbla_seq_sharded_bwd_in", "fbla_device_status", "fbla_clear_device_status", "fbla_unreduced_state"]
+              "fbla_seq_sharded_bwd_in", "fbla_device_status", "fbla_clear_device_status", "fbla_unreduced_state",
+              "fbla_debug_peer_trace"]
     return names
 
 
@@ -160,6 +161,8 @@ def lib():
             f = getattr(L, "fbla_seq_sharded_" + name)
             f.restype = ctypes.c_int
             f.argtypes = [_P] + args
+        L.fbla_debug_peer_trace.restype = None
+        L.fbla_debug_peer_trace.argtypes = [_vp]
         L.fbla_device_status.restype = ctypes.c_int
         L.fbla_device_status.argtypes = []
         L.fbla_clear_device_status.restype = None

@@ -315,6 +315,13 @@ int fbla_seq_sharded_bwd_in(const fbla_problem *p, const void *k_rope, const voi
                             const fbla_peer_group *group, void *dk, void *dk_rope, void *dv,
                             fbla_stream_t stream);
 
+/* Measurement aid (no counterpart in the reference): with a device buffer of 256 x 16 64-bit words
+ * set, exchange number e of the sequence-sharded passes records %globaltimer nanoseconds in slot
+ * e mod 256: word 0 when the last CTA of the reducing pass signals; words 8..12 in CTA 0 of the
+ * consuming pass: gather entered, pieces of all ranks in place, own sums stored, sums of all ranks
+ * in place, private copy done.  NULL switches it off.  Not thread-safe; one device per process.  */
+void fbla_debug_peer_trace(uint64_t *device_buffer);
+
 /* The status word the kernels write when a bounded wait gives up (0 = none did; otherwise a number
  * naming the wait).  While it is non-zero every launching call returns FBLA_ERR_DEVICE.  Clear it
  * once the cause is dealt with; results of the failed call are invalid.  No counterpart in the
