@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "fbla_common.cuh"
@@ -55,7 +56,6 @@ int resolve(const fbla_problem* p, OpKind op, fbla::KParams* kp) {
     kp->inv_norm = p->norm_len > 0 ? (float)(1.0 / (double)p->norm_len) : 0.f;
     kp->state_stride = p->dk * p->dv + (kp->normalize ? p->dk : 0);
     kp->unreduced = 0;
-    kp->peer = nullptr;
     if (op == OP_VARLEN) {
         if (p->cu_seqlens == nullptr) return fail(FBLA_ERR_INVALID, "cu_seqlens is NULL");
         if (p->num_seqs < 1) return fail(FBLA_ERR_INVALID, "num_seqs=%d must be positive", p->num_seqs);
@@ -343,7 +343,7 @@ int fbla_linear_attn_bwd(const fbla_problem* p, const void* q, const void* k, co
     return bwd_in(p, op, k, v, u ? static_cast<const float*>(ws) : dstate, dk, nullptr, dv, s, u);
 }
 
-// ---- sequence-sharded calls: the state crosses GPUs inside the passes -----------------------
+// ---- sequence-sharded calls on the tensor-core kernels ------------------------------------------
 namespace {
 
 OpKind sharded_kind(const fbla_problem* p, const void* rope) {
@@ -351,39 +351,37 @@ OpKind sharded_kind(const fbla_problem* p, const void* rope) {
     return rope != nullptr ? OP_DECOUPLED : OP_LINEAR;
 }
 
-// Validates the group and the problem for the sequence-sharded passes and resolves both.
+// Validates the group and the problem for the sequence-sharded calls and resolves both.
 int resolve_sharded(const fbla_problem* p, OpKind op, const fbla_peer_group* g, fbla::KParams* kp, fbla::PeerArgs* pa) {
     if (int rc = resolve(p, op, kp)) return rc;
     if (g == nullptr) return fail(FBLA_ERR_INVALID, "group is NULL");
     if (g->world < 2 || g->world > 8 || g->rank < 0 || g->rank >= g->world)
         return fail(FBLA_ERR_INVALID, "world %d / rank %d out of range (2 to 8 ranks)", g->world, g->rank);
     if (g->epoch == 0) return fail(FBLA_ERR_INVALID, "epoch must start at 1");
-    if (g->recv == nullptr || g->full == nullptr || g->flags == nullptr)
+    if (g->parts == nullptr || g->full == nullptr || g->flags == nullptr)
         return fail(FBLA_ERR_INVALID, "a pointer table of the group is NULL");
     if (p->cu_seqlens != nullptr || is_empty(*kp) || !use_tc(p, *kp) ||
         (op == OP_DECOUPLED && !fbla::tc_supported_decoupled(*kp)))
         return fail(FBLA_ERR_UNSUPPORTED,
-                    "the sequence-sharded passes serve what the tensor-core kernels serve (fixed length, 16-bit, "
+                    "the sequence-sharded calls serve what the tensor-core kernels serve (fixed length, 16-bit, "
                     "dk, dv in {64, 128}, decoupled at 64 x 64, at least one token)");
     pa->world = g->world;
     pa->rank = g->rank;
     pa->epoch = g->epoch;
-    pa->state_copy = nullptr;
     for (int r = 0; r < g->world; ++r) {
-        if (g->recv[r] == nullptr || g->full[r] == nullptr || g->flags[r] == nullptr)
+        if (g->parts[r] == nullptr || g->full[r] == nullptr || g->flags[r] == nullptr)
             return fail(FBLA_ERR_INVALID, "rank %d: NULL buffer or flag pointer", r);
-        if (((reinterpret_cast<uintptr_t>(g->recv[r]) | reinterpret_cast<uintptr_t>(g->full[r])) & 15u) != 0 ||
+        if (((reinterpret_cast<uintptr_t>(g->parts[r]) | reinterpret_cast<uintptr_t>(g->full[r])) & 15u) != 0 ||
             (reinterpret_cast<uintptr_t>(g->flags[r]) & 3u) != 0)
             return fail(FBLA_ERR_INVALID, "rank %d: buffers must be 16-byte aligned", r);
-        pa->recv[r] = g->recv[r];
+        pa->parts[r] = g->parts[r];
         pa->full[r] = g->full[r];
         pa->flags[r] = g->flags[r];
     }
-    kp->peer = pa;
     return check_device_status();
 }
 
-const char* const kShardedAlign = "the sequence-sharded passes need 16-byte aligned tensors";
+const char* const kShardedAlign = "the sequence-sharded calls need 16-byte aligned tensors";
 
 }  // namespace
 
@@ -393,10 +391,10 @@ int fbla_seq_sharded_supported(const fbla_problem* p) {
     return (!is_empty(kp) && use_tc(p, kp)) ? 1 : 0;
 }
 
-int64_t fbla_seq_sharded_recv_floats(const fbla_problem* p, int world) {
+int64_t fbla_seq_sharded_part_floats(const fbla_problem* p) {
     fbla::KParams kp;
-    if (world < 2 || world > 8 || !fbla_seq_sharded_supported(p) || resolve(p, kind_of(p), &kp) != FBLA_OK) return -1;
-    return fbla::tc_peer_recv_floats(kp, world);
+    if (!fbla_seq_sharded_supported(p) || resolve(p, kind_of(p), &kp) != FBLA_OK) return -1;
+    return fbla::tc_workspace_bytes(kp) / (int64_t)sizeof(float);
 }
 
 int fbla_seq_sharded_fwd_state(const fbla_problem* p, const void* k, const void* k_rope, const void* v,
@@ -408,22 +406,9 @@ int fbla_seq_sharded_fwd_state(const fbla_problem* p, const void* k, const void*
     NOT_NULL(k);
     NOT_NULL(v);
     if (!aligned16(k, k_rope, v)) return fail(FBLA_ERR_UNSUPPORTED, kShardedAlign);
-    const cudaError_t e = fbla::tc_fwd_state(kp, p->dtype, k, k_rope, v, nullptr, nullptr, (cudaStream_t)s);
+    kp.unreduced = 1;           // the pieces in this rank's piece buffer are the result
+    const cudaError_t e = fbla::tc_fwd_state(kp, p->dtype, k, k_rope, v, nullptr, pa.parts[pa.rank], (cudaStream_t)s);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward state pass (sequence-sharded)");
-}
-
-int fbla_seq_sharded_fwd_out(const fbla_problem* p, const void* q, const void* q_rope, const fbla_peer_group* g,
-                             void* o, float* state_copy, fbla_stream_t s) {
-    fbla::KParams kp;
-    fbla::PeerArgs pa;
-    const OpKind op = sharded_kind(p, q_rope);
-    if (int rc = resolve_sharded(p, op, g, &kp, &pa)) return rc;
-    NOT_NULL(q);
-    NOT_NULL(o);
-    if (!aligned16(q, q_rope, o, state_copy)) return fail(FBLA_ERR_UNSUPPORTED, kShardedAlign);
-    pa.state_copy = state_copy;
-    const cudaError_t e = fbla::tc_fwd_out(kp, p->dtype, q, q_rope, nullptr, o, (cudaStream_t)s);
-    return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward output pass (sequence-sharded)");
 }
 
 int fbla_seq_sharded_bwd_state(const fbla_problem* p, const void* q, const void* q_rope, const void* d_o,
@@ -439,27 +424,29 @@ int fbla_seq_sharded_bwd_state(const fbla_problem* p, const void* q, const void*
     NOT_NULL(dq);
     if (op == OP_DECOUPLED) NOT_NULL(dq_rope);
     if (!aligned16(q, q_rope, d_o, dq, dq_rope, state)) return fail(FBLA_ERR_UNSUPPORTED, kShardedAlign);
-    const cudaError_t e = fbla::tc_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, nullptr, nullptr,
+    // the state it reads is an ordinary reduced one; the pieces of the state GRADIENT stay unreduced
+    kp.unreduced = 2;
+    const cudaError_t e = fbla::tc_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, nullptr, pa.parts[pa.rank],
                                              (cudaStream_t)s);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward state pass (sequence-sharded)");
 }
 
-int fbla_seq_sharded_bwd_in(const fbla_problem* p, const void* k_rope, const void* v, const fbla_peer_group* g,
-                            void* dk, void* dk_rope, void* dv, fbla_stream_t s) {
+int fbla_seq_sharded_exchange(const fbla_problem* p, const fbla_peer_group* g, float* state_out, fbla_stream_t s) {
     fbla::KParams kp;
     fbla::PeerArgs pa;
-    const OpKind op = sharded_kind(p, dk_rope);
-    if (int rc = resolve_sharded(p, op, g, &kp, &pa)) return rc;
-    NOT_NULL(k_rope);
-    NOT_NULL(v);
-    NOT_NULL(dk);
-    NOT_NULL(dv);
-    if (!aligned16(k_rope, v, dk, dk_rope, dv)) return fail(FBLA_ERR_UNSUPPORTED, kShardedAlign);
-    const cudaError_t e = fbla::tc_bwd_in(kp, p->dtype, k_rope, v, nullptr, dk, dk_rope, dv, (cudaStream_t)s);
-    return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward input pass (sequence-sharded)");
+    if (int rc = resolve_sharded(p, kind_of(p), g, &kp, &pa)) return rc;
+    NOT_NULL(state_out);
+    if (!aligned16(state_out)) return fail(FBLA_ERR_INVALID, "state_out must be 16-byte aligned");
+    static const int forced = [] {
+        const char* e = getenv("FBLA_PEER_TWO_ROUND");
+        return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+    }();
+    const int two_round = forced >= 0 ? forced : 1;
+    const cudaError_t e = fbla::peer_piece_sum(pa, fbla::tc_piece_layout(kp), kp.state_stride, two_round, state_out,
+                                               (cudaStream_t)s);
+    return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "state exchange (sequence-sharded)");
 }
 
-void fbla_debug_peer_trace(uint64_t* dev) { fbla::tc_set_peer_trace(reinterpret_cast<unsigned long long*>(dev)); }
 int fbla_device_status(void) { return fbla::tc_device_status(); }
 void fbla_clear_device_status(void) { fbla::tc_clear_device_status(); }
 

@@ -15,14 +15,13 @@ namespace fbla {
 // Everything a kernel needs to locate the tokens of one unit.  A unit is one
 // (batch, head) pair in the fixed-length layout, one (sequence, head) pair in the
 // packed layout.
-// A sequence-sharded call: the peers' buffers (see fbla_peer_group in the public header), resolved.
+// A sequence-sharded exchange: the peers' buffers (see fbla_peer_group in the public header), resolved.
 struct PeerArgs {
     int world, rank;
     unsigned int epoch;
-    void* recv[8];
+    void* parts[8];
     void* full[8];
     void* flags[8];
-    float* state_copy;    // consuming passes: optional private copy of the summed state
 };
 
 struct KParams {
@@ -38,9 +37,9 @@ struct KParams {
     float eps;
     int normalize;
     int state_stride;     // floats per unit in state / dstate
-    int unreduced;        // tensor-core kernels, fixed length: the state stays in its per-segment pieces
-                          // (the consuming pass adds them while staging; no reduce kernel)
-    const PeerArgs* peer; // non-null: sequence-sharded call on the tensor-core kernels
+    int unreduced;        // tensor-core kernels, fixed length: 1 = the state stays in its per-segment pieces
+                          // (the consuming pass adds them while staging; no reduce kernel); 2 = only the
+                          // OUTPUT of a reducing pass stays in pieces, the state it reads is a reduced one
 };
 
 struct UnitGeom {

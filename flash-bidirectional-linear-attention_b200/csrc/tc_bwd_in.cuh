@@ -71,7 +71,7 @@ template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_v,
                  const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dkr,
-                 const __grid_constant__ CUtensorMap tm_dv, const Params p_in, const __grid_constant__ PeerXchg px) {
+                 const __grid_constant__ CUtensorMap tm_dv, const Params p_in) {
     using Cfg = BwdInCfg<DK, DV, MODE>;
     using Map = TileMap<VARLEN>;
     // packed layout: rows are strided and tiles may end inside the next sequence -> guarded stores
@@ -109,7 +109,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
     const Params& p = pv;
     int g0, g1;
     Map::range(p, g0, g1);
-    const ptx::Abort ab{cta_abort, p.status, wait_limit(px)};
+    const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -220,9 +220,7 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
         const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool issuer = (et == 0);
         int seg = 0;
-        // sequence-sharded: the summed state gradient is assembled first
-        const bool gathered = (VARLEN || px.world <= 1) ? true : peer_gather_state(p, px, ab, et, 431);
-        for (int g = g0, it = 0; gathered && g < g1; ++g, ++it) {
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const Tile t = Map::get(p, g, g0, g1);
             const int unit = t.unit, tile = t.tile;
             const bool first = t.first;

@@ -58,7 +58,7 @@ template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kBwdStateThreads, 1)
 tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
                     const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
-                    const __grid_constant__ CUtensorMap tm_dqr, const Params p_in, const __grid_constant__ PeerXchg px) {
+                    const __grid_constant__ CUtensorMap tm_dqr, const Params p_in) {
     using Cfg = BwdStateCfg<DK, DV, MODE>;
     using Map = TileMap<VARLEN>;
     constexpr int NS = Cfg::kStages;
@@ -97,7 +97,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
     const Params& p = pv;
     int g0, g1;
     Map::range(p, g0, g1);
-    const ptx::Abort ab{cta_abort, p.status, wait_limit(px)};
+    const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -474,18 +474,16 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             if (last) {
                 if (!ptx::mbar_wait(acc_full, seg & 1u, ab, 325)) break;
                 ptx::tc_fence_after_sync();
-                float* out = segment_destination<VARLEN>(p, px, t, p.state_out);
+                float* out = segment_destination<VARLEN>(p, t, p.state_out);
                 drain_state_acc<DK, DV, (MODE != kSimple ? 2 : 0)>(tmem + Cfg::kColS, DV, out, warp, lane);
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(acc_empty);
             }
         }
         if (!Cfg::kDirect && issuer) ptx::tma_store_wait_all<0>();
-        if (!VARLEN && px.world > 1) __threadfence_system();   // the pieces went to peers' memory
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (!VARLEN && px.world > 1 && threadIdx.x == 0) peer_signal_pieces(px);
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, Cfg::kTmemCols);

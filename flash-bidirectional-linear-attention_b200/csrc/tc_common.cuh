@@ -49,38 +49,6 @@ __host__ __device__ inline int last_cta_of_unit(const Schedule& s, int unit) {
     return (int)((((long long)unit + 1) * s.tiles_per_unit - 1) / s.tiles_per_cta);
 }
 
-// Sequence sharding over the GPUs of one node: how the per-segment states of this rank reach the
-// ranks that add them, and how the sums come back.  Unit u is summed by its owner, rank
-// u / units_per_rank.
-//   recv[r]  : rank r's receive buffer, [world][units_per_rank][slots_per_unit][state_stride] fp32 --
-//              the reducing pass of rank q stores the pieces of a unit that r owns into block q of
-//              recv[r] (plain stores to the peer's memory);
-//   full[r]  : rank r's copy of the summed state of ALL units, [units][state_stride] fp32 -- the head
-//              of the consuming pass adds the pieces of its own units (ranks in order, pieces in CTA
-//              order, so every rank ends up with the same bits) and stores the sums into full[] of
-//              every rank;
-//   flags[r] : rank r's flag words: [0, 8) "the reducing pass of rank q has stored all its pieces",
-//              [16, 24) "rank q has stored the sums of its units", [32], [33] CTA tickets of the
-//              local kernels.  Flags carry the exchange number `epoch` (1, 2, 3, ...).
-// world == 1 switches all of it off.  The kernels take it as a kernel parameter of its own (its pointer
-// tables are indexed with run-time values, which a by-value copy of the parameters would pay for with
-// local memory).
-constexpr int kMaxPeers = 8;
-struct PeerXchg {
-    int world, rank;
-    int units_per_rank;
-    unsigned int epoch;
-    unsigned long long wait_ns;     // limit of every wait for a peer
-    float* recv[kMaxPeers];
-    float* full[kMaxPeers];
-    unsigned int* flags[kMaxPeers];
-    float* state_copy;              // consuming pass: private copy of the summed state (may be null)
-    unsigned long long* trace;      // measurement aid (may be null): 16 timestamps of this exchange, written by
-                                    // one thread per kernel: [0] last CTA of the reducing pass signals,
-                                    // [8..12] consuming pass, CTA 0: gather entered, pieces of all ranks in
-                                    // place, own sums stored, sums of all ranks in place, private copy done
-};
-
 struct Params {
     Schedule sch;
     int seq_len;          // tokens per unit
@@ -110,15 +78,13 @@ struct Params {
 // The state of one unit as a consuming pass reads it: one vector, or the per-segment pieces that the
 // reducing pass left (added here in CTA order, the order tc_reduce_partials_kernel uses, so both
 // routes give the same bits).
-// All loads bypass L1 (every element is read once, and the state may have been written by another
-// GPU, with which only L2 is coherent).
 struct StateSrc {
     const float* p;
     int n;
     size_t stride;
     __device__ __forceinline__ float operator[](int i) const {
-        float a = __ldcg(p + i);
-        for (int j = 1; j < n; ++j) a += __ldcg(p + (size_t)j * stride + i);
+        float a = p[i];
+        for (int j = 1; j < n; ++j) a += p[(size_t)j * stride + i];
         return a;
     }
     // N values first + u * step (u = 0..N-1) at once: all loads of one piece are in flight together
@@ -126,12 +92,12 @@ struct StateSrc {
     template <int N>
     __device__ __forceinline__ void load(int first, int step, float (&x)[N]) const {
 #pragma unroll
-        for (int u = 0; u < N; ++u) x[u] = __ldcg(p + first + u * step);
+        for (int u = 0; u < N; ++u) x[u] = p[first + u * step];
         for (int j = 1; j < n; ++j) {
             const float* pj = p + (size_t)j * stride;
             float y[N];
 #pragma unroll
-            for (int u = 0; u < N; ++u) y[u] = __ldcg(pj + first + u * step);
+            for (int u = 0; u < N; ++u) y[u] = pj[first + u * step];
 #pragma unroll
             for (int u = 0; u < N; ++u) x[u] += y[u];
         }
@@ -139,12 +105,12 @@ struct StateSrc {
     template <int N>
     __device__ __forceinline__ void load2(int first, int step, float2 (&x)[N]) const {    // first, step even
 #pragma unroll
-        for (int u = 0; u < N; ++u) x[u] = __ldcg(reinterpret_cast<const float2*>(p + first + u * step));
+        for (int u = 0; u < N; ++u) x[u] = *reinterpret_cast<const float2*>(p + first + u * step);
         for (int j = 1; j < n; ++j) {
             const float* pj = p + (size_t)j * stride;
             float2 y[N];
 #pragma unroll
-            for (int u = 0; u < N; ++u) y[u] = __ldcg(reinterpret_cast<const float2*>(pj + first + u * step));
+            for (int u = 0; u < N; ++u) y[u] = *reinterpret_cast<const float2*>(pj + first + u * step);
 #pragma unroll
             for (int u = 0; u < N; ++u) {
                 x[u].x += y[u].x;
@@ -153,9 +119,9 @@ struct StateSrc {
         }
     }
     __device__ __forceinline__ float2 pair(int i) const {     // i even
-        float2 a = __ldcg(reinterpret_cast<const float2*>(p + i));
+        float2 a = *reinterpret_cast<const float2*>(p + i);
         for (int j = 1; j < n; ++j) {
-            const float2 b = __ldcg(reinterpret_cast<const float2*>(p + (size_t)j * stride + i));
+            const float2 b = *reinterpret_cast<const float2*>(p + (size_t)j * stride + i);
             a.x += b.x;
             a.y += b.y;
         }
@@ -289,18 +255,9 @@ struct TileMap<true> {
 //                  unit that starts here but continues in the next CTA to slot (cta, 1);
 //                  tc_reduce_varlen_kernel adds the pieces in CTA order.
 template <bool VARLEN>
-__device__ __forceinline__ float* segment_destination(const Params& p, const PeerXchg& px, const Tile& t,
-                                                      float* state_out) {
+__device__ __forceinline__ float* segment_destination(const Params& p, const Tile& t, float* state_out) {
     if (!VARLEN) {
-        const int piece = (int)blockIdx.x - first_cta_of_unit(p.sch, t.unit);
-        if (px.world > 1) {
-            // sequence-sharded: straight into the receive buffer of the rank that sums this unit
-            const int owner = t.unit / px.units_per_rank;
-            const int local = t.unit - owner * px.units_per_rank;
-            const size_t slot = ((size_t)px.rank * px.units_per_rank + local) * p.sch.slots_per_unit + piece;
-            return px.recv[owner] + slot * p.state_stride;
-        }
-        const int slot = t.unit * p.sch.slots_per_unit + piece;
+        const int slot = t.unit * p.sch.slots_per_unit + ((int)blockIdx.x - first_cta_of_unit(p.sch, t.unit));
         return p.part + (size_t)slot * p.state_stride;
     }
     if (t.starts_here && t.ends_here) return state_out + (size_t)t.unit * p.state_stride;
@@ -367,148 +324,6 @@ __device__ __forceinline__ void drain_state_acc(uint32_t tmem_acc, uint32_t vec_
         for (int j = 0; j < NVEC; ++j) s += v[j];
         if (row_ok) out[DK * DV + row] = s;
     }
-}
-
-// ---- sequence sharding: flags and sums over peer memory ---------------------------------------------
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Cycles an in-CTA wait may last: a CTA of a sequence-sharded call may sit behind a wait for peer
-// GPUs, so its own waits must outlast that one (about two cycles per nanosecond).
-__device__ __forceinline__ long long wait_limit(const PeerXchg& px) {
-    return px.world > 1 ? ptx::kWaitCycles + 2 * (long long)px.wait_ns : ptx::kWaitCycles;
-}
-// Barrier among the 128 epilogue threads only (the other warps of the CTA are in their own loops).
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// The same barrier, returning to every thread whether ANY of the 128 passed a true predicate: a
-// decision all of them take the same way (threads that left on different sides of it would meet at
-// different barriers afterwards).
-__device__ __forceinline__ bool epilogue_barrier_any(bool pred) {
-    uint32_t out;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        "setp.ne.b32 p, %1, 0;\n\t"
-        "bar.red.or.pred q, 1, 128, p;\n\t"
-        "selp.u32 %0, 1, 0, q;\n\t"
-        "}"
-        : "=r"(out)
-        : "r"((uint32_t)pred)
-        : "memory");
-    return out != 0;
-}
-
-// Waits until *flag has reached `epoch`, at most px.wait_ns; on giving up records `site` in the CTA's
-// abort flag and in the library's status word and returns false.
-__device__ __forceinline__ bool peer_wait(const unsigned int* flag, const PeerXchg& px, const ptx::Abort& ab,
-                                          int site) {
-    if ((int)(ld_acquire_sys(flag) - px.epoch) >= 0) return true;
-    const unsigned long long t0 = global_ns();
-    int spins = 0;
-    while ((int)(ld_acquire_sys(flag) - px.epoch) < 0) {
-        if ((++spins & 15) == 0) {
-            if (*ab.cta_flag != 0) return false;
-            if (global_ns() - t0 > px.wait_ns) {
-                *ab.cta_flag = site;
-                *ab.status = site;
-                __threadfence_system();
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-// End of a reducing pass of a sequence-sharded call, executed by ONE thread per CTA after every
-// thread that stored pieces has executed __threadfence_system() and the CTA has synchronised: the
-// last CTA of this rank to get here tells every rank that this rank's pieces are in place.
-__device__ __forceinline__ void peer_signal_pieces(const PeerXchg& px) {
-    unsigned int* mine = px.flags[px.rank];
-    __threadfence();
-    const unsigned int ticket = atomicAdd(mine + 32, 1u);
-    if (ticket == gridDim.x - 1) {
-        mine[32] = 0;                       // every CTA has drawn: ready for the next launch
-        __threadfence_system();
-        for (int r = 0; r < px.world; ++r) st_release_sys(px.flags[r] + px.rank, px.epoch);
-        if (px.trace != nullptr) px.trace[0] = global_ns();
-    }
-}
-
-// Head of a consuming pass of a sequence-sharded call, executed by the 128 epilogue threads of every
-// CTA (et = 0..127) before the first state is staged:
-//   1. wait until every rank's reducing pass has stored its pieces;
-//   2. add the pieces of the units this rank owns -- ranks in order, pieces in CTA order -- and store
-//      each sum into full[] of every rank (the CTAs of the grid share the elements);
-//   3. the last CTA to finish tells every rank; wait until every rank has said so;
-//   4. optionally copy the summed state of all units to private memory (the caller keeps it for the
-//      backward; full[] is overwritten two exchanges later).
-// Afterwards p.state (= full[rank]) is complete.  The CTAs of one launch wait for one another in step
-// 3, so the grid must be resident as a whole (one CTA per SM at most, which the schedule guarantees).
-// Returns false when a wait gave up.
-__device__ __forceinline__ bool peer_gather_state(const Params& p, const PeerXchg& x, const ptx::Abort& ab, int et,
-                                                  int site) {
-    unsigned int* mine = x.flags[x.rank];
-    const bool tracer = x.trace != nullptr && blockIdx.x == 0 && et == 0;
-    if (tracer) x.trace[8] = global_ns();
-    if (et < x.world) peer_wait(mine + et, x, ab, site);
-    if (epilogue_barrier_any(*ab.cta_flag != 0)) return false;
-    if (tracer) x.trace[9] = global_ns();
-    const int s4 = p.state_stride >> 2;                       // float4 per unit (the stride is a multiple of 4)
-    const int u0 = x.rank * x.units_per_rank;
-    const int u1 = min(p.sch.units, u0 + x.units_per_rank);
-    const long long n4 = (long long)max(0, u1 - u0) * s4;
-    for (long long i = (long long)blockIdx.x * kEpiThreads + et; i < n4; i += (long long)gridDim.x * kEpiThreads) {
-        const int ul = (int)(i / s4), e4 = (int)(i - (long long)ul * s4);
-        const int u = u0 + ul;
-        const int n = last_cta_of_unit(p.sch, u) - first_cta_of_unit(p.sch, u) + 1;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int q = 0; q < x.world; ++q) {
-            const float4* src = reinterpret_cast<const float4*>(
-                                    x.recv[x.rank] + ((size_t)q * x.units_per_rank + ul) * p.sch.slots_per_unit * p.state_stride) + e4;
-            for (int j = 0; j < n; ++j) {
-                const float4 y = __ldcg(src + (size_t)j * s4);
-                acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
-            }
-        }
-        for (int r = 0; r < x.world; ++r)
-            reinterpret_cast<float4*>(x.full[r] + (size_t)u * p.state_stride)[e4] = acc;
-    }
-    __threadfence_system();
-    epilogue_barrier();
-    if (tracer) x.trace[10] = global_ns();
-    if (et == 0) {
-        const unsigned int ticket = atomicAdd(mine + 33, 1u);
-        if (ticket == gridDim.x - 1) {
-            mine[33] = 0;
-            __threadfence_system();
-            for (int r = 0; r < x.world; ++r) st_release_sys(x.flags[r] + 16 + x.rank, x.epoch);
-        }
-    }
-    if (et < x.world) peer_wait(mine + 16 + et, x, ab, site + 1);
-    if (epilogue_barrier_any(*ab.cta_flag != 0)) return false;
-    if (tracer) x.trace[11] = global_ns();
-    if (x.state_copy != nullptr) {
-        const long long all4 = (long long)p.sch.units * s4;
-        const float4* src = reinterpret_cast<const float4*>(x.full[x.rank]);
-        float4* dst = reinterpret_cast<float4*>(x.state_copy);
-        for (long long i = (long long)blockIdx.x * kEpiThreads + et; i < all4; i += (long long)gridDim.x * kEpiThreads)
-            dst[i] = __ldcg(src + i);
-    }
-    if (x.trace != nullptr) {
-        epilogue_barrier();                 // all 128 threads: the copy of this CTA is complete
-        if (tracer) x.trace[12] = global_ns();
-    }
-    return true;
 }
 
 // Dynamic shared memory starts at an address the swizzled tiles can use (1024-byte aligned).

@@ -50,7 +50,7 @@ __device__ __forceinline__ void zero_tail_rows(uint8_t* blocks, int nblocks, int
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const Params p_in, const __grid_constant__ PeerXchg px) {
+                    const __grid_constant__ CUtensorMap tm_v, const Params p_in) {
     using Cfg = FwdStateCfg<DK, DV, MODE>;
     using Map = TileMap<VARLEN>;
     constexpr int NS = Cfg::kStages;
@@ -79,7 +79,7 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
     const Params& p = pv;
     int g0, g1;
     Map::range(p, g0, g1);
-    const ptx::Abort ab{cta_abort, p.status, wait_limit(px)};
+    const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -184,17 +184,15 @@ tc_fwd_state_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_cons
             if (!t.last) continue;
             if (!ptx::mbar_wait(acc_full, (uint32_t)seg & 1u, ab, 121)) break;
             ptx::tc_fence_after_sync();
-            float* out = segment_destination<VARLEN>(p, px, t, p.state_out);
+            float* out = segment_destination<VARLEN>(p, t, p.state_out);
             drain_state_acc<DK, DV, (MODE != kSimple ? 1 : 0)>(tmem, DV, out, warp, lane);
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(acc_empty);
             ++seg;
         }
-        if (!VARLEN && px.world > 1) __threadfence_system();   // the pieces went to peers' memory
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (!VARLEN && px.world > 1 && threadIdx.x == 0) peer_signal_pieces(px);
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, Cfg::kTmemCols);
@@ -275,7 +273,7 @@ struct FwdOutCfg {
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
-                  const __grid_constant__ CUtensorMap tm_o, const Params p_in, const __grid_constant__ PeerXchg px) {
+                  const __grid_constant__ CUtensorMap tm_o, const Params p_in) {
     using Cfg = FwdOutCfg<DK, DV, MODE>;
     using Map = TileMap<VARLEN>;
     constexpr int NS = Cfg::kStages;
@@ -307,7 +305,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
     const Params& p = pv;
     int g0, g1;
     Map::range(p, g0, g1);
-    const ptx::Abort ab{cta_abort, p.status, wait_limit(px)};
+    const ptx::Abort ab{cta_abort, p.status};
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -408,9 +406,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
         const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool issuer = (et == 0);
         int seg = 0;
-        // sequence-sharded: the summed state is assembled first (the producer warp is already loading)
-        const bool gathered = (VARLEN || px.world <= 1) ? true : peer_gather_state(p, px, ab, et, 231);
-        for (int g = g0, it = 0; gathered && g < g1; ++g, ++it) {
+        for (int g = g0, it = 0; g < g1; ++g, ++it) {
             const Tile t = Map::get(p, g, g0, g1);
             const int unit = t.unit, tile = t.tile;
             const bool first = t.first;

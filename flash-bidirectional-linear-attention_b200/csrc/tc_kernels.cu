@@ -152,20 +152,6 @@ int* status_word() {
 
 Params make_params(const KParams& p, int dtype, const Schedule& s, int* status);
 
-// How long a kernel of a sequence-sharded call waits for a peer before it gives up and reports
-// through the status word: FBLA_PEER_WAIT_MS in the environment, 5 s by default.  Ranks that may be
-// further apart than this (one of them writing a checkpoint, say) should meet at a host-side
-// barrier before the call.
-unsigned long long peer_wait_ns() {
-    static const unsigned long long ns = [] {
-        const char* e = getenv("FBLA_PEER_WAIT_MS");
-        double ms = e != nullptr ? atof(e) : 0.0;
-        if (!(ms > 0.0)) ms = 5000.0;
-        return (unsigned long long)(ms * 1e6);
-    }();
-    return ns;
-}
-
 Params make_params(const KParams& p, int dtype, const Schedule& s) { return make_params(p, dtype, s, status_word()); }
 
 Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) {
@@ -227,32 +213,6 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, int 
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-// Measurement aid: when set, every sequence-sharded exchange records its timestamps in slot
-// (epoch mod 256) of this device buffer (16 64-bit words per slot).
-unsigned long long* g_peer_trace = nullptr;
-
-// The peer tables of a sequence-sharded call (world = 1: none).
-PeerXchg make_px(const KParams& p) {
-    PeerXchg x{};
-    x.world = 1;
-    if (p.peer != nullptr && p.peer->world > 1) {
-        const PeerArgs& a = *p.peer;
-        x.world = a.world;
-        x.rank = a.rank;
-        x.units_per_rank = (p.units + a.world - 1) / a.world;
-        x.epoch = a.epoch;
-        x.wait_ns = peer_wait_ns();
-        for (int r = 0; r < a.world; ++r) {
-            x.recv[r] = static_cast<float*>(a.recv[r]);
-            x.full[r] = static_cast<float*>(a.full[r]);
-            x.flags[r] = static_cast<unsigned int*>(a.flags[r]);
-        }
-        x.state_copy = a.state_copy;
-        x.trace = g_peer_trace != nullptr ? g_peer_trace + (size_t)(a.epoch & 255u) * 16 : nullptr;
-    }
-    return x;
-}
-
 int mode_of(const KParams& p, bool decoupled) { return !p.normalize ? kSimple : (decoupled ? kDecoupled : kLinear); }
 
 cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
@@ -264,7 +224,7 @@ cudaError_t reduce_partials(const Params& q, float* state, cudaStream_t st) {
 
 // ---- per-shape launch helpers ----------------------------------------------------------------
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_fwd_state(const Params& q, const PeerXchg& px, const CUtensorMap& tkr, const CUtensorMap& tk, const CUtensorMap& tv,
+cudaError_t launch_fwd_state(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tk, const CUtensorMap& tv,
                              cudaStream_t st) {
     using Cfg = FwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -272,13 +232,13 @@ cudaError_t launch_fwd_state(const Params& q, const PeerXchg& px, const CUtensor
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tk, tv, q, px);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tk, tv, q);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_fwd_out(const Params& q, const PeerXchg& px, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& to,
+cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& to,
                            cudaStream_t st) {
     using Cfg = FwdOutCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -287,13 +247,13 @@ cudaError_t launch_fwd_out(const Params& q, const PeerXchg& px, const CUtensorMa
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tqr, tq, to, q, px);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tqr, tq, to, q);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_bwd_state(const Params& q, const PeerXchg& px, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
+cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
                              const CUtensorMap& tdq, const CUtensorMap& tdqr, cudaStream_t st) {
     using Cfg = BwdStateCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -302,13 +262,13 @@ cudaError_t launch_bwd_state(const Params& q, const PeerXchg& px, const CUtensor
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st, tqr, tq, tdo, tdq, tdqr, q, px);
+    e = launch_dependent(kernel, q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st, tqr, tq, tdo, tdq, tdqr, q);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
-cudaError_t launch_bwd_in(const Params& q, const PeerXchg& px, const CUtensorMap& tkr, const CUtensorMap& tv, const CUtensorMap& tdk,
+cudaError_t launch_bwd_in(const Params& q, const CUtensorMap& tkr, const CUtensorMap& tv, const CUtensorMap& tdk,
                           const CUtensorMap& tdkr, const CUtensorMap& tdv, cudaStream_t st) {
     using Cfg = BwdInCfg<DK, DV, MODE>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
@@ -317,7 +277,7 @@ cudaError_t launch_bwd_in(const Params& q, const PeerXchg& px, const CUtensorMap
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tv, tdk, tdkr, tdv, q, px);
+    e = launch_dependent(kernel, q.sch.ctas, kThreads, Cfg::kSmemBytes, st, tkr, tv, tdk, tdkr, tdv, q);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -417,14 +377,24 @@ int64_t tc_workspace_bytes(const KParams& p) {
 }
 
 
-int64_t tc_peer_recv_floats(const KParams& p, int world) {
+PieceLayout tc_piece_layout(const KParams& p) {
     const Schedule s = make_schedule(p, sm_count());
-    const int64_t upr = (p.units + world - 1) / world;
-    return (int64_t)world * upr * s.slots_per_unit * p.state_stride;
+    return PieceLayout{s.units, s.slots_per_unit, s.tiles_per_unit, s.tiles_per_cta};
 }
 
-unsigned long long tc_peer_wait_ns() { return peer_wait_ns(); }
-void tc_set_peer_trace(unsigned long long* dev) { g_peer_trace = dev; }
+// How long a kernel waits for a peer GPU before it gives up and reports through the status word:
+// FBLA_PEER_WAIT_MS in the environment, 5 s by default.  Ranks that may be further apart than this
+// (one of them writing a checkpoint, say) should meet at a host-side barrier before the call.
+unsigned long long tc_peer_wait_ns() {
+    static const unsigned long long ns = [] {
+        const char* e = getenv("FBLA_PEER_WAIT_MS");
+        double ms = e != nullptr ? atof(e) : 0.0;
+        if (!(ms > 0.0)) ms = 5000.0;
+        return (unsigned long long)(ms * 1e6);
+    }();
+    return ns;
+}
+
 int tc_device_status() { return g_status_host != nullptr ? *static_cast<volatile int*>(g_status_host) : 0; }
 void tc_clear_device_status() {
     if (g_status_host != nullptr) *static_cast<volatile int*>(g_status_host) = 0;
@@ -443,14 +413,13 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
         cudaError_t e;
         if ((e = cudaMemsetAsync(state, 0, sizeof(float) * (size_t)p.units * p.state_stride, st)) != cudaSuccess) return e;
         Params q = make_params_packed(p, dtype);
-        const PeerXchg px = make_px(p);
         q.status = status;
         q.state_out = state;
         q.part = static_cast<float*>(ws);
         CUtensorMap tk, tv;
         if ((e = make_map_packed(&tk, k, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_fwd_state, q, px, tk, tk, tv, st); };
+        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_fwd_state, q, tk, tk, tv, st); };
         if ((e = launch()) != cudaSuccess) return e;
         tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, state, q.sch.ctas);
         note_launches(1);
@@ -461,16 +430,15 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
     const Schedule s = make_schedule(p, sm_count());
     if (status == nullptr) return cudaErrorMemoryAllocation;
     Params q = make_params(p, dtype, s, status);
-    const PeerXchg px = make_px(p);
     q.part = static_cast<float*>(ws);
     CUtensorMap tkr, tk, tv;
     cudaError_t e;
     if ((e = make_map(&tkr, dec ? k_rope : k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tk, k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, px, tkr, tk, tv, st); };
+    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, tkr, tk, tv, st); };
     if ((e = launch()) != cudaSuccess) return e;
-    if (p.unreduced || p.peer != nullptr) return cudaSuccess;   // the pieces (in `ws` / at the peers) are the result
+    if (p.unreduced) return cudaSuccess;        // the pieces in `ws` are the result
     return reduce_partials(q, state, st);
 }
 
@@ -478,7 +446,6 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
                        cudaStream_t st) {
     if (p.cu != nullptr) {
         Params q = make_params_packed(p, dtype);
-        const PeerXchg px = make_px(p);
         if (q.status == nullptr) return cudaErrorMemoryAllocation;
         q.state = state;
         q.out_a = o;
@@ -486,23 +453,22 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
         cudaError_t e;
         if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&to, o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        FBLA_TC_VARLEN_DISPATCH(launch_fwd_out, q, px, tq, tq, to, st);
+        FBLA_TC_VARLEN_DISPATCH(launch_fwd_out, q, tq, tq, to, st);
     }
     const bool dec = q_rope != nullptr && q_rope != q_;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
-    const PeerXchg px = make_px(p);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
-    q.state = p.peer != nullptr ? px.full[px.rank] : state;
-    if (p.unreduced) q.state_parts = state;
+    q.state = state;
+    if (p.unreduced == 1) q.state_parts = state;
     q.out_a = o;
     CUtensorMap tqr, tq, to;
     cudaError_t e;
     if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tq, q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&to, o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    FBLA_TC_DISPATCH(launch_fwd_out, q, px, tqr, tq, to, st);
+    FBLA_TC_DISPATCH(launch_fwd_out, q, tqr, tq, to, st);
 }
 
 cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void* q_rope, const void* d_o,
@@ -511,7 +477,6 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
         cudaError_t e;
         if ((e = cudaMemsetAsync(dstate, 0, sizeof(float) * (size_t)p.units * p.state_stride, st)) != cudaSuccess) return e;
         Params q = make_params_packed(p, dtype);
-        const PeerXchg px = make_px(p);
         if (q.status == nullptr) return cudaErrorMemoryAllocation;
         q.state = state;
         q.state_out = dstate;
@@ -522,7 +487,7 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
         if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdo, d_o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdq, dq, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
-        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_bwd_state, q, px, tq, tq, tdo, tdq, tdq, st); };
+        auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_bwd_state, q, tq, tq, tdo, tdq, tdq, st); };
         if ((e = launch()) != cudaSuccess) return e;
         tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, dstate, q.sch.ctas);
         note_launches(1);
@@ -532,10 +497,9 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
-    const PeerXchg px = make_px(p);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
     q.state = state;
-    if (p.unreduced) q.state_parts = state;
+    if (p.unreduced == 1) q.state_parts = state;
     q.part = static_cast<float*>(ws);
     q.out_a = dec ? dq_rope : dq;
     q.out_b = dq;
@@ -546,9 +510,9 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     if ((e = make_map(&tdo, d_o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdq, dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdqr, dec ? dq_rope : dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, px, tqr, tq, tdo, tdq, tdqr, st); };
+    auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, tqr, tq, tdo, tdq, tdqr, st); };
     if ((e = launch()) != cudaSuccess) return e;
-    if (p.unreduced || p.peer != nullptr) return cudaSuccess;
+    if (p.unreduced) return cudaSuccess;
     return reduce_partials(q, dstate, st);
 }
 
@@ -556,7 +520,6 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
                       void* dk_rope, void* dv, cudaStream_t st) {
     if (p.cu != nullptr) {
         Params q = make_params_packed(p, dtype);
-        const PeerXchg px = make_px(p);
         if (q.status == nullptr) return cudaErrorMemoryAllocation;
         q.state = dstate;
         q.out_a = dk;
@@ -567,16 +530,15 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
         if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdk, dk, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         if ((e = make_map_packed(&tdv, dv, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        FBLA_TC_VARLEN_DISPATCH(launch_bwd_in, q, px, tk, tv, tdk, tdk, tdv, st);
+        FBLA_TC_VARLEN_DISPATCH(launch_bwd_in, q, tk, tv, tdk, tdk, tdv, st);
     }
     const bool dec = dk_rope != nullptr;
     const int mode = mode_of(p, dec);
     const Schedule s = make_schedule(p, sm_count());
     Params q = make_params(p, dtype, s);
-    const PeerXchg px = make_px(p);
     if (q.status == nullptr) return cudaErrorMemoryAllocation;
-    q.state = p.peer != nullptr ? px.full[px.rank] : dstate;
-    if (p.unreduced) q.state_parts = dstate;
+    q.state = dstate;
+    if (p.unreduced == 1) q.state_parts = dstate;
     q.out_a = dec ? dk_rope : dk;      // kernels without a staged output tile store through these
     q.out_b = dv;
     CUtensorMap tkr, tv, tdk, tdkr, tdv;
@@ -586,7 +548,7 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
     if ((e = make_map(&tdk, dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdkr, dec ? dk_rope : dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
     if ((e = make_map(&tdv, dv, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    FBLA_TC_DISPATCH(launch_bwd_in, q, px, tkr, tv, tdk, tdkr, tdv, st);
+    FBLA_TC_DISPATCH(launch_bwd_in, q, tkr, tv, tdk, tdkr, tdv, st);
 }
 
 }  // namespace fbla

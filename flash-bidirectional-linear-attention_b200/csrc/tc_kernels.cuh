@@ -14,13 +14,18 @@ int tc_device_status();
 // Device-visible address of that word (NULL if the pinned allocation failed).
 int* tc_status_word();
 int64_t tc_workspace_bytes(const KParams& p);
-// Sequence-sharded calls: floats of one receive buffer (fbla_peer_group.recv) for `world` ranks.
-int64_t tc_peer_recv_floats(const KParams& p, int world);
-// Limit of a kernel's wait for a peer GPU, nanoseconds (FBLA_PEER_WAIT_MS in the environment).
+// How the per-segment pieces of the reducing passes lie in the workspace (fixed length): unit u has
+// pieces (u * slots + j), j < n(u), n(u) = last_cta(u) - first_cta(u) + 1 with the two tile counts.
+struct PieceLayout {
+    int units, slots, tiles_per_unit, tiles_per_cta;
+};
+PieceLayout tc_piece_layout(const KParams& p);
+// The exchange kernel of the sequence-sharded tensor-core passes (peer_exchange.cu): sums the pieces of
+// all ranks into `out` ([units][state_stride] floats of ordinary memory).
+cudaError_t peer_piece_sum(const PeerArgs& g, const PieceLayout& lay, int state_stride, int two_round, float* out,
+                           cudaStream_t st);
+// Limit of a kernel's wait for a peer GPU, nanoseconds (FBLA_PEER_WAIT_MS in the environment, 5000).
 unsigned long long tc_peer_wait_ns();
-// Measurement aid: device buffer of 256 x 16 64-bit words that receives the timestamps of the
-// sequence-sharded exchanges (NULL switches it off).
-void tc_set_peer_trace(unsigned long long* dev);
 // Clears the status word after a reported failure.
 void tc_clear_device_status();
 cudaError_t tc_fwd_state(const KParams& p, int dtype, const void* k, const void* k_rope, const void* v,

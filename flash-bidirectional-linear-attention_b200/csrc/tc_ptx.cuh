@@ -51,7 +51,6 @@ constexpr long long kWaitCycles = 1500000000LL;  // about a second
 struct Abort {
     volatile int* cta_flag;   // shared memory: some thread of this CTA gave up
     int* status;              // host-visible status word of the library
-    long long limit = kWaitCycles;   // cycles a wait may last (longer when the CTA also waits for peer GPUs)
 };
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, int where) {
@@ -65,7 +64,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         if (spins > 4096) __nanosleep(200);
         if ((spins & 63) == 0) {
             if (*ab.cta_flag != 0) return false;
-            if (clock64() - t0 > ab.limit) {
+            if (clock64() - t0 > kWaitCycles) {
                 *ab.cta_flag = where;
                 *ab.status = where;
                 __threadfence_system();
@@ -198,7 +197,8 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool bf16, bool 
     return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
            ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-// (Both operands must have the same 16-bit format: a descriptor that mixes f16 and bf16 raises an
+
+// (Both operands must have the same 16-bit format: a descriptor that mixes f16 and bf16 raised an
 // illegal-instruction fault on B200.)
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by a single thread.

@@ -62,7 +62,7 @@ class PeerGroup(ctypes.Structure):
         ("rank", ctypes.c_int32),
         ("epoch", ctypes.c_uint32),
         ("reserved", ctypes.c_int32),
-        ("recv", ctypes.POINTER(ctypes.c_void_p)),
+        ("parts", ctypes.POINTER(ctypes.c_void_p)),
         ("full", ctypes.POINTER(ctypes.c_void_p)),
         ("flags", ctypes.POINTER(ctypes.c_void_p)),
     ]
@@ -101,10 +101,9 @@ def exported_symbols():
     names += ["fbla_linear_attn_fwd_state_noalloc", "fbla_noalloc_status"]
     names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd",
               "fbla_pisa_bwd_scratch_floats"]
-    names += ["fbla_peer_state_sum", "fbla_seq_sharded_supported", "fbla_seq_sharded_recv_floats",
-              "fbla_seq_sharded_fwd_state", "fbla_seq_sharded_fwd_out", "fbla_seq_sharded_bwd_state",
-              "fbla_seq_sharded_bwd_in", "fbla_device_status", "fbla_clear_device_status", "fbla_unreduced_state",
-              "fbla_debug_peer_trace"]
+    names += ["fbla_peer_state_sum", "fbla_seq_sharded_supported", "fbla_seq_sharded_part_floats",
+              "fbla_seq_sharded_fwd_state", "fbla_seq_sharded_bwd_state", "fbla_seq_sharded_exchange",
+              "fbla_device_status", "fbla_clear_device_status", "fbla_unreduced_state"]
     return names
 
 
@@ -152,17 +151,14 @@ def lib():
         _PG = ctypes.POINTER(PeerGroup)
         L.fbla_seq_sharded_supported.restype = ctypes.c_int
         L.fbla_seq_sharded_supported.argtypes = [_P]
-        L.fbla_seq_sharded_recv_floats.restype = ctypes.c_int64
-        L.fbla_seq_sharded_recv_floats.argtypes = [_P, ctypes.c_int]
+        L.fbla_seq_sharded_part_floats.restype = ctypes.c_int64
+        L.fbla_seq_sharded_part_floats.argtypes = [_P]
         for name, args in (("fwd_state", [_vp, _vp, _vp, _PG, _vp]),                 # k, k_rope, v, group, stream
-                           ("fwd_out", [_vp, _vp, _PG, _vp, _vp, _vp]),              # q, q_rope, group, o, state_copy, stream
                            ("bwd_state", [_vp, _vp, _vp, _vp, _PG, _vp, _vp, _vp]),  # q, q_rope, d_o, state, group, dq, dq_rope, stream
-                           ("bwd_in", [_vp, _vp, _PG, _vp, _vp, _vp, _vp])):         # k_rope, v, group, dk, dk_rope, dv, stream
+                           ("exchange", [_PG, _vp, _vp])):                           # group, state_out, stream
             f = getattr(L, "fbla_seq_sharded_" + name)
             f.restype = ctypes.c_int
             f.argtypes = [_P] + args
-        L.fbla_debug_peer_trace.restype = None
-        L.fbla_debug_peer_trace.argtypes = [_vp]
         L.fbla_device_status.restype = ctypes.c_int
         L.fbla_device_status.argtypes = []
         L.fbla_clear_device_status.restype = None

@@ -131,7 +131,7 @@ def bwd_in(op, prob, k, v, dstate, dk, dv, dk_rope=None):
     _C.check(rc)
 
 
-# ---- sequence-sharded passes: the state crosses GPUs inside the kernels ------------------------
+# ---- sequence-sharded passes on the tensor-core kernels: pieces, then one exchange kernel ---------
 def sharded_supported(prob):
     return _C.lib().fbla_seq_sharded_supported(ctypes.byref(prob)) == 1
 
@@ -144,13 +144,13 @@ def sharded_fwd_state(prob, k, v, grp, k_rope=None):
     _C.check(rc)
 
 
-def sharded_fwd_out(prob, q, grp, o, state_copy, q_rope=None):
-    _require_cuda(q, o, state_copy, q_rope)
-    with _C.device_guard(q):
-        rc = _C.lib().fbla_seq_sharded_fwd_out(ctypes.byref(prob), _C.ptr(q), _C.ptr(q_rope), ctypes.byref(grp),
-                                               _C.ptr(o), _C.ptr(state_copy), _C.stream_of(q))
+def sharded_exchange(prob, grp, like):
+    """Sum over the ranks of the pieces the preceding sharded state pass left: a new fp32 state tensor."""
+    out = torch.empty(state_floats(prob), dtype=torch.float32, device=like.device)
+    with _C.device_guard(like):
+        rc = _C.lib().fbla_seq_sharded_exchange(ctypes.byref(prob), ctypes.byref(grp), _C.ptr(out), _C.stream_of(like))
     _C.check(rc)
-    return o
+    return out
 
 
 def sharded_bwd_state(prob, q, d_o, state, grp, dq, q_rope=None, dq_rope=None):
@@ -159,15 +159,6 @@ def sharded_bwd_state(prob, q, d_o, state, grp, dq, q_rope=None, dq_rope=None):
         rc = _C.lib().fbla_seq_sharded_bwd_state(ctypes.byref(prob), _C.ptr(q), _C.ptr(q_rope), _C.ptr(d_o),
                                                  _C.ptr(state), ctypes.byref(grp), _C.ptr(dq), _C.ptr(dq_rope),
                                                  _C.stream_of(q))
-    _C.check(rc)
-
-
-def sharded_bwd_in(prob, k, v, grp, dk, dv, dk_rope=None):
-    """``k`` is the key tensor the state was built from (k_rope when decoupled)."""
-    _require_cuda(k, v, dk, dv, dk_rope)
-    with _C.device_guard(k):
-        rc = _C.lib().fbla_seq_sharded_bwd_in(ctypes.byref(prob), _C.ptr(k), _C.ptr(v), ctypes.byref(grp), _C.ptr(dk),
-                                              _C.ptr(dk_rope), _C.ptr(dv), _C.stream_of(k))
     _C.check(rc)
 
 

@@ -8,12 +8,12 @@ exchange per direction:
     forward : local [S_r | sum k_r]  --sum over ranks-->  global state  -> local o
     backward: local dq and [dS_r | sum dz q_r]  --sum over ranks-->  -> local dk, dv
 
-On NCCL groups of GPUs of one node, for the shapes the tensor-core kernels serve, there is no
-separate exchange at all: the reducing pass stores its pieces straight into the memory of the rank
-that owns each unit and the consuming pass begins by adding and redistributing them
-(``fbla_seq_sharded_*``, symmetric memory, plain peer stores over NVLink).  Other shapes on such
-groups use one kernel that reads the peers' states (``fbla_peer_state_sum``); elsewhere, or with
-``FBLA_PEER_EXCHANGE=0``, the sum is ``all_reduce(SUM)``.
+On NCCL groups of GPUs of one node the sum is ONE kernel that reads the peers' memory over NVLink
+(symmetric memory, plain peer loads): for the shapes the tensor-core kernels serve it adds the
+per-segment pieces the reducing pass left, without a reduction kernel in between, and from three ranks
+on sums each unit once at its owner (``fbla_seq_sharded_*``); other shapes use the one-round sum of the
+reduced states (``fbla_peer_state_sum``).  Elsewhere, or with ``FBLA_PEER_EXCHANGE=0``, the sum is
+``all_reduce(SUM)``.
 
 Every rank must make the same calls in the same order with the same local shapes.  A kernel waits
 for its peers for at most ``FBLA_PEER_WAIT_MS`` (default 5000); ranks that may drift further apart
@@ -101,9 +101,9 @@ class _PeerExchange:
 
 
 class _FusedExchange:
-    """Buffers of the exchange that runs inside the passes (``fbla_seq_sharded_*``) for one problem
-    shape: two (receive buffer, summed-state copy) pairs used alternately and one array of flag
-    words, in symmetric memory that every peer has mapped."""
+    """Buffers of the piece-level exchange (``fbla_seq_sharded_*``) for one problem shape: two (piece
+    buffer, owner-sum buffer) pairs used alternately and one array of flag words, in symmetric memory
+    that every peer has mapped."""
 
     def __init__(self, group, device, prob):
         import ctypes
@@ -112,10 +112,10 @@ class _FusedExchange:
         L = _C.lib()
         world = dist.get_world_size(group)
         self.n = int(L.fbla_state_floats(ctypes.byref(prob)))
-        self.n_recv = int(L.fbla_seq_sharded_recv_floats(ctypes.byref(prob), world))
-        if self.n <= 0 or self.n_recv <= 0:
+        self.n_parts = int(L.fbla_seq_sharded_part_floats(ctypes.byref(prob)))
+        if self.n <= 0 or self.n_parts <= 0:
             raise RuntimeError("the fused exchange does not serve this problem")
-        per = self.n_recv + self.n
+        per = self.n_parts + self.n
         self.data = symm.empty(2 * per, dtype=torch.float32, device=device)
         self.flags = symm.empty(64, dtype=torch.int32, device=device)
         self.flags.zero_()
@@ -127,15 +127,15 @@ class _FusedExchange:
         self._tables = []
         self._groups = []
         for b in (0, 1):
-            recv = arr(*[int(p) + b * per * 4 for p in hd.buffer_ptrs])
-            full = arr(*[int(p) + (b * per + self.n_recv) * 4 for p in hd.buffer_ptrs])
+            parts = arr(*[int(p) + b * per * 4 for p in hd.buffer_ptrs])
+            full = arr(*[int(p) + (b * per + self.n_parts) * 4 for p in hd.buffer_ptrs])
             flags = arr(*[int(p) for p in hf.buffer_ptrs])
             g = _C.PeerGroup()
             g.world, g.rank, g.epoch, g.reserved = self.world, self.rank, 0, 0
-            g.recv = ctypes.cast(recv, ctypes.POINTER(ctypes.c_void_p))
+            g.parts = ctypes.cast(parts, ctypes.POINTER(ctypes.c_void_p))
             g.full = ctypes.cast(full, ctypes.POINTER(ctypes.c_void_p))
             g.flags = ctypes.cast(flags, ctypes.POINTER(ctypes.c_void_p))
-            self._tables.append((recv, full, flags))          # keep the arrays alive
+            self._tables.append((parts, full, flags))          # keep the arrays alive
             self._groups.append(g)
         self.epoch = 0
         torch.cuda.synchronize(device)
@@ -242,8 +242,8 @@ class _SeqSharded(torch.autograd.Function):
             q, k, v = _aligned(q, k, v)
             grp = fx.begin()
             _backend.sharded_fwd_state(prob, k, v, grp)
-            state = torch.empty(fx.n, dtype=torch.float32, device=q.device)
-            o = _backend.sharded_fwd_out(prob, q, grp, torch.empty_like(v), state)
+            state = _backend.sharded_exchange(prob, grp, q)
+            o = _backend.fwd_out(op, prob, q, state, torch.empty_like(v))
         else:
             state = _summed_state(lambda out: _backend.fwd_state(op, prob, k, v, out=out), prob, q, group)
             o = _backend.fwd_out(op, prob, q, state, torch.empty_like(v))
@@ -267,7 +267,7 @@ class _SeqSharded(torch.autograd.Function):
             do, = _aligned(do)
             grp = fx.begin()
             _backend.sharded_bwd_state(prob, q, do, state, grp, dq)
-            _backend.sharded_bwd_in(prob, k, v, grp, dk, dv)
+            _backend.bwd_in(op, prob, k, v, _backend.sharded_exchange(prob, grp, q), dk, dv)
         else:
             dstate = _summed_state(lambda out: _backend.bwd_state(op, prob, q, do, state, dq, out=out), prob, q, group)
             _backend.bwd_in(op, prob, k, v, dstate, dk, dv)
@@ -287,8 +287,8 @@ class _SeqShardedDecoupled(torch.autograd.Function):
             q, k, q_rope, k_rope, v = _aligned(q, k, q_rope, k_rope, v)
             grp = fx.begin()
             _backend.sharded_fwd_state(prob, k, v, grp, k_rope=k_rope)
-            state = torch.empty(fx.n, dtype=torch.float32, device=q.device)
-            o = _backend.sharded_fwd_out(prob, q, grp, torch.empty_like(v), state, q_rope=q_rope)
+            state = _backend.sharded_exchange(prob, grp, q)
+            o = _backend.fwd_out("decoupled_la", prob, q, state, torch.empty_like(v), q_rope=q_rope)
         else:
             state = _summed_state(lambda out: _backend.fwd_state("decoupled_la", prob, k, v, k_rope=k_rope, out=out),
                                   prob, q, group)
@@ -312,7 +312,8 @@ class _SeqShardedDecoupled(torch.autograd.Function):
             do, = _aligned(do)
             grp = fx.begin()
             _backend.sharded_bwd_state(prob, q, do, state, grp, dq, q_rope=q_rope, dq_rope=dq_rope)
-            _backend.sharded_bwd_in(prob, k_rope, v, grp, dk, dv, dk_rope=dk_rope)
+            _backend.bwd_in("decoupled_la", prob, k_rope, v, _backend.sharded_exchange(prob, grp, q), dk, dv,
+                            dk_rope=dk_rope)
         else:
             dstate = _summed_state(lambda out: _backend.bwd_state("decoupled_la", prob, q, do, state, dq, q_rope=q_rope,
                                                                   dq_rope=dq_rope, out=out), prob, q, group)

@@ -265,62 +265,55 @@ int fbla_peer_state_sum(int world, int rank, const void *const *peer_states,
                         void *const *peer_flags, int64_t n_floats, uint32_t epoch, float *out,
                         fbla_stream_t stream);
 
-/* ---- multi-GPU: sequence-sharded passes with the exchange inside the kernels -----------------
- * No counterpart in the reference (it runs on one GPU).  For what the tensor-core kernels serve
- * (fixed length, 16-bit, dk, dv in {64, 128}; decoupled at 64 x 64) the state never goes through a
- * separate reduction or collective: the reducing pass stores each per-segment piece straight into the
- * memory of the rank that owns the unit (unit u belongs to rank u / ceil(units / world)), and the
- * consuming pass begins by adding the pieces of its own units -- ranks in order, pieces in CTA order,
- * so every rank holds the same bits -- storing the sums into every rank's copy, and waiting for the
- * other ranks' sums.  Two flag rounds over NVLink, no extra launch, plain peer stores and local loads
- * only (no multicast).
- *   recv[r]  : rank r's receive buffer of fbla_seq_sharded_recv_floats() floats, 16-byte aligned;
- *   full[r]  : rank r's copy of the summed state, fbla_state_floats() floats, 16-byte aligned;
+/* ---- multi-GPU: sequence-sharded calls for what the tensor-core kernels serve -----------------
+ * No counterpart in the reference (it runs on one GPU).  Fixed length, 16-bit, dk, dv in {64, 128}
+ * (decoupled at 64 x 64).  The reducing pass leaves its per-segment pieces in this rank's piece buffer
+ * (no reduction kernel); fbla_seq_sharded_exchange, one kernel, sums the pieces of all ranks into an
+ * ordinary state buffer, which the regular *_fwd_out / *_bwd_in (or *_bwd_state as `state`) then take.
+ * With two ranks every rank adds all units from both ranks' pieces after one flag round.  With more,
+ * each unit is summed once by its owner (rank u / ceil(units / world)) into full[owner], a second
+ * flag round follows and every rank reads the other units from their owners: 2 (world-1)/world of the
+ * state crosses NVLink per rank.  Either way a unit is added in one fixed order (ranks in order,
+ * pieces in CTA order): all ranks hold the same bits.  Plain peer loads only; nothing but flag words
+ * is stored to a peer; no multicast.
+ *   parts[r] : rank r's piece buffer of fbla_seq_sharded_part_floats() floats, 16-byte aligned;
+ *   full[r]  : rank r's buffer of fbla_state_floats() floats, 16-byte aligned;
  *   flags[r] : rank r's 64 32-bit flag words, zero before the first exchange;
  *   all three mapped into this process for every rank r (this rank's own memory at index `rank`);
- *   epoch    : 1, 2, 3, ... the same on every rank for the same exchange (one exchange = one
- *              *_fwd_state + *_fwd_out pair, or one *_bwd_state + *_bwd_in pair).
- * Use two (recv, full) pairs alternately for consecutive exchanges and one flags array for all: a
- * rank can start exchange e+2 only after every peer has finished e+1, i.e. has finished reading the
+ *   epoch    : 1, 2, 3, ... the same on every rank for the same exchange, counted per flags array.
+ * Use two (parts, full) pairs alternately for consecutive exchanges and one flags array for all: a
+ * rank can start exchange e+2 only after every peer has entered e+1, i.e. has finished reading the
  * buffers of e.  Every rank must make the same calls in the same order with the same problem (same
- * local seq_len: the ranks' tile schedules must agree).  Each wait for a peer is bounded
- * (FBLA_PEER_WAIT_MS in the environment, default 5000): after that the kernel gives up, its outputs
- * are undefined, fbla_device_status() becomes non-zero and every later call returns FBLA_ERR_DEVICE
- * until fbla_clear_device_status().  Ranks that may be further apart should meet at a host barrier
- * first.  k_rope / q_rope / dq_rope / dk_rope are NULL except for decoupled_la; for the other
- * operators *_bwd_in takes k in the k_rope position.
- *   fbla_seq_sharded_fwd_out : state_copy (may be NULL) receives the summed state, fbla_state_floats()
- *                              floats of ordinary memory -- what *_bwd_state takes as `state`.   */
+ * local seq_len: the ranks' tile schedules must agree).  The wait for the peers is bounded
+ * (FBLA_PEER_WAIT_MS in the environment, default 5000): after that the kernel fills state_out with
+ * NaN, fbla_device_status() becomes non-zero and every later call returns FBLA_ERR_DEVICE until
+ * fbla_clear_device_status(); the flags arrays of all ranks must then be zeroed and the epochs
+ * restarted.  Ranks that may be further apart should meet at a host barrier first.
+ * k_rope / q_rope / dq_rope are NULL except for decoupled_la.                                      */
 typedef struct fbla_peer_group {
     int32_t world;          /* 2..8 ranks, GPUs of one node                   */
     int32_t rank;
     uint32_t epoch;
     int32_t reserved;
-    void *const *recv;      /* [world] */
+    void *const *parts;     /* [world] */
     void *const *full;      /* [world] */
     void *const *flags;     /* [world] */
 } fbla_peer_group;
 
 int fbla_seq_sharded_supported(const fbla_problem *p);
-int64_t fbla_seq_sharded_recv_floats(const fbla_problem *p, int world);
+int64_t fbla_seq_sharded_part_floats(const fbla_problem *p);
+/* Pieces of [ S | sum k ] of this rank's tokens into parts[rank].                                   */
 int fbla_seq_sharded_fwd_state(const fbla_problem *p, const void *k, const void *k_rope, const void *v,
                                const fbla_peer_group *group, fbla_stream_t stream);
-int fbla_seq_sharded_fwd_out(const fbla_problem *p, const void *q, const void *q_rope,
-                             const fbla_peer_group *group, void *o, float *state_copy,
-                             fbla_stream_t stream);
+/* dq (and dq_rope) of this rank's tokens; pieces of the state gradient into parts[rank].  `state` is
+ * the summed state an earlier fbla_seq_sharded_exchange produced.                                  */
 int fbla_seq_sharded_bwd_state(const fbla_problem *p, const void *q, const void *q_rope, const void *d_o,
                                const float *state, const fbla_peer_group *group, void *dq, void *dq_rope,
                                fbla_stream_t stream);
-int fbla_seq_sharded_bwd_in(const fbla_problem *p, const void *k_rope, const void *v,
-                            const fbla_peer_group *group, void *dk, void *dk_rope, void *dv,
-                            fbla_stream_t stream);
-
-/* Measurement aid (no counterpart in the reference): with a device buffer of 256 x 16 64-bit words
- * set, exchange number e of the sequence-sharded passes records %globaltimer nanoseconds in slot
- * e mod 256: word 0 when the last CTA of the reducing pass signals; words 8..12 in CTA 0 of the
- * consuming pass: gather entered, pieces of all ranks in place, own sums stored, sums of all ranks
- * in place, private copy done.  NULL switches it off.  Not thread-safe; one device per process.  */
-void fbla_debug_peer_trace(uint64_t *device_buffer);
+/* state_out (fbla_state_floats() floats, ordinary memory, 16-byte aligned) = sum over the ranks of the
+ * pieces the preceding fbla_seq_sharded_fwd_state / _bwd_state of the same `group` left.           */
+int fbla_seq_sharded_exchange(const fbla_problem *p, const fbla_peer_group *group, float *state_out,
+                              fbla_stream_t stream);
 
 /* The status word the kernels write when a bounded wait gives up (0 = none did; otherwise a number
  * naming the wait).  While it is non-zero every launching call returns FBLA_ERR_DEVICE.  Clear it

@@ -53,39 +53,93 @@ def _run(body):
     assert "CHILD-OK" in out.stdout
 
 
-def test_sequence_sharded_pass_gives_up_on_a_silent_peer_and_recovers():
-    _run("""
-    prob = P.make_problem(q, batch=B, heads=H, seq_len=T, dk=D, dv=D, normalize=True, scale=1.0 / (2 * T),
-                          eps=1e-6, norm_len=2 * T)
-    assert L.fbla_seq_sharded_supported(ctypes.byref(prob)) == 1
+_GROUP = """
+def make_group(prob):
     n = L.fbla_state_floats(ctypes.byref(prob))
-    n_recv = L.fbla_seq_sharded_recv_floats(ctypes.byref(prob), 2)
-    assert n > 0 and n_recv >= 2 * n
-    recv = [torch.zeros(n_recv, device="cuda") for _ in range(2)]
+    n_parts = L.fbla_seq_sharded_part_floats(ctypes.byref(prob))
+    assert n > 0 and n_parts >= n
+    parts = [torch.zeros(n_parts, device="cuda") for _ in range(2)]
     full = [torch.zeros(n, device="cuda") for _ in range(2)]
     flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
     arr = ctypes.c_void_p * 2
-    tabs = [arr(*[t.data_ptr() for t in ts]) for ts in (recv, full, flags)]
+    tabs = [arr(*[t.data_ptr() for t in ts]) for ts in (parts, full, flags)]
     g = _C.PeerGroup()
     g.world, g.rank, g.epoch, g.reserved = 2, 0, 1, 0
-    g.recv, g.full, g.flags = (ctypes.cast(t, ctypes.POINTER(ctypes.c_void_p)) for t in tabs)
-    o = torch.empty_like(v)
-    state = torch.empty(n, device="cuda")
-    st = _C.stream_of(q)
-    _C.check(L.fbla_seq_sharded_fwd_state(ctypes.byref(prob), k.data_ptr(), None, v.data_ptr(), ctypes.byref(g), st))
+    g.parts, g.full, g.flags = (ctypes.cast(t, ctypes.POINTER(ctypes.c_void_p)) for t in tabs)
+    return g, parts, full, flags, tabs, n
+"""
+
+
+def test_sequence_sharded_exchange_gives_up_on_a_silent_peer_and_recovers():
+    _run(_GROUP + """
+prob = P.make_problem(q, batch=B, heads=H, seq_len=T, dk=D, dv=D, normalize=True, scale=1.0 / (2 * T),
+                      eps=1e-6, norm_len=2 * T)
+assert L.fbla_seq_sharded_supported(ctypes.byref(prob)) == 1
+g, parts, full, flags, tabs, n = make_group(prob)
+st = _C.stream_of(q)
+_C.check(L.fbla_seq_sharded_fwd_state(ctypes.byref(prob), k.data_ptr(), None, v.data_ptr(), ctypes.byref(g), st))
+state = torch.zeros(n, device="cuda")
+_C.check(L.fbla_seq_sharded_exchange(ctypes.byref(prob), ctypes.byref(g), state.data_ptr(), st))
+torch.cuda.synchronize()                                         # returns: the wait is bounded
+assert flags[0][0].item() == 1 and flags[1][0].item() == 1      # rank 0 told both ranks; rank 1 stays silent
+assert L.fbla_device_status() == 911, L.fbla_device_status()
+assert torch.isnan(state).all()                                  # no sum without the peer
+assert refused()
+L.fbla_clear_device_status()
+assert L.fbla_device_status() == 0
+works_again()
+print("CHILD-OK")
+""")
+
+
+@pytest.mark.parametrize("two_round", ["0", "1"])
+def test_sequence_sharded_calls_dry_run_with_the_peer_flags_preset(two_round):
+    """The sequence-sharded calls on one GPU: rank 0 of two, with rank 1's flags already at the exchange
+    number (nothing waits) and rank 1's pieces all zero, in the one-round and in the two-round form of the
+    exchange.  Outputs and gradients must be bit-identical to the plain operator (same pieces, same order
+    of addition; in the two-round form for the units rank 0 owns, the others come from rank 1's zeros)."""
+    _run("os.environ['FBLA_PEER_TWO_ROUND'] = '%s'\n" % two_round + _GROUP + """
+two_round = os.environ['FBLA_PEER_TWO_ROUND'] == '1'
+B, H = 1, 4                                           # rank 0 owns units 0 and 1
+q4 = (torch.rand(B, H, T, D, device="cuda") + 0.1).bfloat16()
+k4 = (torch.rand(B, H, T, D, device="cuda") + 0.1).bfloat16()
+v4 = torch.randn(B, H, T, D, device="cuda").bfloat16()
+do4 = torch.randn(B, H, T, D, device="cuda").bfloat16()
+prob = P.make_problem(q4, batch=B, heads=H, seq_len=T, dk=D, dv=D, normalize=True, scale=1.0 / T,
+                      eps=1e-6, norm_len=T)
+g, parts, full, flags, tabs, n = make_group(prob)
+st = _C.stream_of(q4)
+o, dq, dk, dv = (torch.empty_like(q4) for _ in range(4))
+xs = [x.clone().requires_grad_() for x in (q4, k4, v4)]
+want = linear_attention(*xs)
+want.backward(do4)
+own = slice(0, 2) if two_round else slice(0, 4)       # one round: rank 0 sums every unit itself
+for epoch in (1, 2, 3, 4):                            # two forward + backward rounds
+    g.epoch = epoch
+    flags[0][1] = epoch                               # "rank 1 has entered the exchange" (its pieces: all zero)
+    flags[0][17] = epoch                              # "rank 1 has summed its units"
+    if epoch % 2 == 1:
+        _C.check(L.fbla_seq_sharded_fwd_state(ctypes.byref(prob), k4.data_ptr(), None, v4.data_ptr(), ctypes.byref(g), st))
+        state = torch.full((n,), float("nan"), device="cuda")
+        _C.check(L.fbla_seq_sharded_exchange(ctypes.byref(prob), ctypes.byref(g), state.data_ptr(), st))
+        P.fwd_out("linear_attn", prob, q4, state, o)
+    else:
+        _C.check(L.fbla_seq_sharded_bwd_state(ctypes.byref(prob), q4.data_ptr(), None, do4.data_ptr(), state.data_ptr(),
+                                              ctypes.byref(g), dq.data_ptr(), None, st))
+        dstate = torch.full((n,), float("nan"), device="cuda")
+        _C.check(L.fbla_seq_sharded_exchange(ctypes.byref(prob), ctypes.byref(g), dstate.data_ptr(), st))
+        P.bwd_in("linear_attn", prob, k4, v4, dstate, dk, dv)
     torch.cuda.synchronize()
     assert L.fbla_device_status() == 0
-    assert flags[0][0].item() == 1 and flags[1][0].item() == 1      # rank 0 told both ranks; rank 1 stays silent
-    _C.check(L.fbla_seq_sharded_fwd_out(ctypes.byref(prob), q.data_ptr(), None, ctypes.byref(g), o.data_ptr(),
-                                        state.data_ptr(), st))
-    torch.cuda.synchronize()                                         # returns: the wait is bounded
-    assert L.fbla_device_status() == 231, L.fbla_device_status()
-    assert refused()
-    L.fbla_clear_device_status()
-    assert L.fbla_device_status() == 0
-    works_again()
-    print("CHILD-OK")
-    """)
+    if epoch % 2 == 1:
+        assert torch.isfinite(state).all()
+        assert torch.equal(o[:, own], want[:, own])
+    else:
+        assert torch.equal(dq[:, own], xs[0].grad[:, own])
+        assert torch.equal(dk[:, own], xs[1].grad[:, own]) and torch.equal(dv[:, own], xs[2].grad[:, own])
+    assert flags[0][32].item() == 0                   # the CTA ticket is back at zero
+print("CHILD-OK")
+""")
 
 
 def test_state_sum_kernel_gives_up_on_a_silent_peer_and_recovers():
@@ -104,68 +158,5 @@ def test_state_sum_kernel_gives_up_on_a_silent_peer_and_recovers():
     assert refused()
     L.fbla_clear_device_status()
     works_again()
-    print("CHILD-OK")
-    """)
-
-
-def test_sequence_sharded_passes_dry_run_with_the_peer_flags_preset():
-    """The whole head of the consuming pass on one GPU: rank 0 of two, with rank 1's flags already at the
-    exchange number (nothing waits) and rank 1's pieces all zero.  The units rank 0 owns must come out
-    exactly as the plain operator computes them (same pieces, same order of addition), forward and
-    backward, with the timestamp trace switched on."""
-    _run("""
-    B, H = 1, 4                                           # rank 0 owns units 0 and 1
-    q4 = (torch.rand(B, H, T, D, device="cuda") + 0.1).bfloat16()
-    k4 = (torch.rand(B, H, T, D, device="cuda") + 0.1).bfloat16()
-    v4 = torch.randn(B, H, T, D, device="cuda").bfloat16()
-    do4 = torch.randn(B, H, T, D, device="cuda").bfloat16()
-    prob = P.make_problem(q4, batch=B, heads=H, seq_len=T, dk=D, dv=D, normalize=True, scale=1.0 / T,
-                          eps=1e-6, norm_len=T)
-    n = L.fbla_state_floats(ctypes.byref(prob))
-    n_recv = L.fbla_seq_sharded_recv_floats(ctypes.byref(prob), 2)
-    recv = [torch.zeros(n_recv, device="cuda") for _ in range(2)]
-    full = [torch.zeros(n, device="cuda") for _ in range(2)]
-    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
-    trace = torch.zeros(256 * 16, dtype=torch.int64, device="cuda")
-    L.fbla_debug_peer_trace(trace.data_ptr())
-    arr = ctypes.c_void_p * 2
-    tabs = [arr(*[t.data_ptr() for t in ts]) for ts in (recv, full, flags)]
-    g = _C.PeerGroup()
-    g.world, g.rank, g.reserved = 2, 0, 0
-    g.recv, g.full, g.flags = (ctypes.cast(t, ctypes.POINTER(ctypes.c_void_p)) for t in tabs)
-    st = _C.stream_of(q4)
-    o, dq, dk, dv = (torch.empty_like(q4) for _ in range(4))
-    state = torch.empty(n, device="cuda")
-    xs = [x.clone().requires_grad_() for x in (q4, k4, v4)]
-    want = linear_attention(*xs)
-    want.backward(do4)
-    for epoch in (1, 2, 3, 4):                            # two forward + backward rounds
-        g.epoch = epoch
-        flags[0][1] = epoch                               # "rank 1 has stored its pieces" (all zero)
-        flags[0][17] = epoch                              # "rank 1 has stored its sums"
-        if epoch % 2 == 1:
-            _C.check(L.fbla_seq_sharded_fwd_state(ctypes.byref(prob), k4.data_ptr(), None, v4.data_ptr(), ctypes.byref(g), st))
-            _C.check(L.fbla_seq_sharded_fwd_out(ctypes.byref(prob), q4.data_ptr(), None, ctypes.byref(g), o.data_ptr(),
-                                                state.data_ptr(), st))
-        else:
-            _C.check(L.fbla_seq_sharded_bwd_state(ctypes.byref(prob), q4.data_ptr(), None, do4.data_ptr(), state.data_ptr(),
-                                                  ctypes.byref(g), dq.data_ptr(), None, st))
-            _C.check(L.fbla_seq_sharded_bwd_in(ctypes.byref(prob), k4.data_ptr(), v4.data_ptr(), ctypes.byref(g),
-                                               dk.data_ptr(), None, dv.data_ptr(), st))
-        torch.cuda.synchronize()
-        assert L.fbla_device_status() == 0
-        own = slice(0, 2)                                 # heads 0, 1 = the units of rank 0
-        if epoch % 2 == 1:
-            assert torch.equal(o[:, own], want[:, own])
-            assert torch.equal(state, full[0])            # the private copy is the gathered state
-        else:
-            assert torch.equal(dq[:, own], xs[0].grad[:, own])
-            assert torch.equal(dk[:, own], xs[1].grad[:, own]) and torch.equal(dv[:, own], xs[2].grad[:, own])
-        t = trace.view(256, 16)[epoch].tolist()
-        assert t[0] > 0 and t[8] > 0 and t[8] <= t[9] <= t[10] <= t[11], t
-        if epoch % 2 == 1:
-            assert t[12] >= t[11], t
-        assert flags[0][32].item() == 0 and flags[0][33].item() == 0      # both CTA tickets are back at zero
-    L.fbla_debug_peer_trace(None)
     print("CHILD-OK")
     """)
