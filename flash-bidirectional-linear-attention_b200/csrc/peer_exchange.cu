@@ -22,6 +22,8 @@
 // CTAs follow a device-local word.  Every wait is bounded: on giving up the kernel records it in the
 // status word and fills the result with NaN.  Each GPU runs exactly one of these kernels per exchange;
 // they wait on one another ACROSS GPUs only.
+#include <cstdlib>
+
 #include "fbla_common.cuh"
 #include "tc_kernels.cuh"
 
@@ -320,7 +322,11 @@ cudaError_t peer_piece_sum(const PeerArgs& g, const PieceLayout& lay, int state_
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    static const bool plain = [] {                      // FBLA_NO_PDL=1: ordinary launches everywhere
+        const char* e = getenv("FBLA_NO_PDL");
+        return e != nullptr && e[0] == '1';
+    }();
+    cfg.numAttrs = plain ? 0 : 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, peer_piece_sum_kernel, a);
     note_launches(1);
     return e != cudaSuccess ? e : cudaGetLastError();

@@ -46,7 +46,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Every wait in the kernels is bounded: after kWaitCycles without progress, or as soon as
 // another thread of the CTA has given up, the wait returns false, the caller leaves its
 // loop, and the kernel reports the failure through the status word instead of hanging.
-constexpr long long kWaitCycles = 1500000000LL;  // about a second
+constexpr long long kWaitCycles = 10000000000LL;  // about five seconds
 
 struct Abort {
     volatile int* cta_flag;   // shared memory: some thread of this CTA gave up
