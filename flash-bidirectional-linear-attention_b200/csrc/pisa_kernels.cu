@@ -356,6 +356,75 @@ static int resolve_pisa(const fbla_pisa_problem* p, PisaArgs* a) {
         default: { using T = __half; __VA_ARGS__; break; }                   \
     }
 
+// ---- block selection: scores of the block means, top-k per query block ------------------------------
+// One warp per query block.  score[j] = qc_i . (kc_j * scale), with the operands and the result rounded
+// to the element type of q, k, v the way the reference forms them (block means stored in that type, the
+// product taken in it; kernel.py:313); with a bias, score[j] + log(hnorm_j + 1e-5), whose softmax over j
+// the reference ranks (kernel.py:314-315: softmax is monotone, so the order is the same).  The ns largest
+// are written in descending order; equal scores go to the lower block index, NaN counts as smallest.
+constexpr int kSelectWarps = 4;
+constexpr int kSelectMaxBlocks = 1024;              // 32 scores per lane
+
+__device__ __forceinline__ float round_like(float x, int dtype) {
+    if (dtype == FBLA_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+    if (dtype == FBLA_F16) return __half2float(__float2half_rn(x));
+    return x;
+}
+
+// (score, block) as one integer whose order is: larger score first, then lower block index; 0 = nothing.
+__device__ __forceinline__ unsigned long long select_key(float x, int j) {
+    unsigned int u = __float_as_uint(x);
+    u = (x != x) ? 1u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+    if (u < 2u) u = (x != x) ? 1u : 2u;
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (unsigned int)j);
+}
+
+__global__ void __launch_bounds__(kSelectWarps * 32)
+pisa_select_kernel(PisaParams p, int dtype, const float* __restrict__ qc, const float* __restrict__ kc,
+                   const float* __restrict__ hnorm, int32_t* __restrict__ indices) {
+    extern __shared__ float qrow_all[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i_blk = blockIdx.x * kSelectWarps + warp, bh = blockIdx.y;
+    if (i_blk >= p.nt) return;
+    const int K = p.dk;
+    float* qrow = qrow_all + warp * K;
+    const float* qsrc = qc + ((size_t)bh * p.nt + i_blk) * K;
+    for (int d = lane; d < K; d += 32) qrow[d] = round_like(qsrc[d], dtype);
+    __syncwarp();
+    constexpr int kPer = kSelectMaxBlocks / 32;
+    unsigned long long key[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int j = u * 32 + lane;
+        key[u] = 0ull;
+        if (j < p.nt) {
+            const float* krow = kc + ((size_t)bh * p.nt + j) * K;
+            float acc = 0.f;
+            for (int d = 0; d < K; ++d) acc = fmaf(qrow[d], round_like(krow[d] * p.scale, dtype), acc);
+            acc = round_like(acc, dtype);
+            if (hnorm != nullptr)
+                acc = round_like(acc + round_like(logf(round_like(hnorm[(size_t)bh * p.nt + j], dtype) + 1e-5f), dtype), dtype);
+            key[u] = select_key(acc, j);
+        }
+    }
+    int32_t* out = indices + ((size_t)bh * p.nt + i_blk) * p.ns;
+    for (int n = 0; n < p.ns; ++n) {
+        unsigned long long best = 0ull;
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) best = key[u] > best ? key[u] : best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        const int at = (int)(0xffffffffu - (unsigned int)(best & 0xffffffffull));
+        if (lane == 0) out[n] = best != 0ull ? at : 0;
+#pragma unroll
+        for (int u = 0; u < kPer; ++u)
+            if (key[u] == best) key[u] = 0ull;          // retire the winner (keys are unique: they carry the index)
+    }
+}
+
 }  // namespace fbla
 
 extern "C" {
@@ -372,6 +441,22 @@ int fbla_pisa_block_stats(const fbla_pisa_problem* p, const void* q, const void*
     fbla::note_launches(1);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "block statistics: %s", cudaGetErrorString(e));
+}
+
+int fbla_pisa_select_blocks(const fbla_pisa_problem* p, const float* qc, const float* kc, const float* hnorm,
+                            int32_t* indices, fbla_stream_t stream) {
+    fbla::PisaArgs a;
+    if (int rc = fbla::resolve_pisa(p, &a)) return rc;
+    if (!qc || !kc || !indices) return fbla::api_fail(FBLA_ERR_INVALID, "a tensor pointer is NULL");
+    if (a.kp.nt > fbla::kSelectMaxBlocks || a.kp.ns > a.kp.nt)
+        return fbla::api_fail(FBLA_ERR_UNSUPPORTED, "block selection serves up to %d blocks (%d given) and at most as many "
+                              "selected blocks as there are blocks", fbla::kSelectMaxBlocks, a.kp.nt);
+    dim3 grid((a.kp.nt + fbla::kSelectWarps - 1) / fbla::kSelectWarps, a.bh);
+    const size_t smem = sizeof(float) * (size_t)fbla::kSelectWarps * a.kp.dk;
+    fbla::pisa_select_kernel<<<grid, fbla::kSelectWarps * 32, smem, (cudaStream_t)stream>>>(a.kp, a.dtype, qc, kc, hnorm, indices);
+    fbla::note_launches(1);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "block selection: %s", cudaGetErrorString(e));
 }
 
 int fbla_pisa_block_hnorm(const fbla_pisa_problem* p, const void* k, const void* v, const float* kc, float pnorm,

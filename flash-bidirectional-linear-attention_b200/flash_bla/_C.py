@@ -99,7 +99,7 @@ def exported_symbols():
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
     names += ["fbla_linear_attn_fwd", "fbla_linear_attn_bwd"]
     names += ["fbla_linear_attn_fwd_state_noalloc", "fbla_noalloc_status"]
-    names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_fwd", "fbla_pisa_bwd",
+    names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_select_blocks", "fbla_pisa_fwd", "fbla_pisa_bwd",
               "fbla_pisa_bwd_scratch_floats"]
     names += ["fbla_peer_state_sum", "fbla_seq_sharded_supported", "fbla_seq_sharded_part_floats",
               "fbla_seq_sharded_fwd_state", "fbla_seq_sharded_bwd_state", "fbla_seq_sharded_exchange",
@@ -168,6 +168,8 @@ def lib():
         L.fbla_peer_state_sum.restype = ctypes.c_int
         L.fbla_peer_state_sum.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
                                           ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64, ctypes.c_uint32, _vp, _vp]
+        L.fbla_pisa_select_blocks.restype = ctypes.c_int
+        L.fbla_pisa_select_blocks.argtypes = [_PP, _vp, _vp, _vp, _vp, _vp]      # qc, kc, hnorm, indices, stream
         L.fbla_pisa_bwd_scratch_floats.restype = ctypes.c_int64
         L.fbla_pisa_bwd_scratch_floats.argtypes = [_PP]
         L.fbla_pisa_bwd.restype = ctypes.c_int

@@ -238,8 +238,8 @@ def padded_dims(q, v):
     """(K', V') to pad the feature dims to, or None when the tensors are served as they are."""
     if q.dtype not in (torch.float16, torch.bfloat16) or not q.is_cuda or q.dim() != 4:
         return None
-    # opt-in for now: FBLA_PAD_SMALL_DIMS=1
-    if _default_flags & _C.FLAG_GENERIC or os.environ.get("FBLA_PAD_SMALL_DIMS", "0") != "1":
+    # FBLA_PAD_SMALL_DIMS=0 switches the route off (the CUDA-core kernels then serve these shapes)
+    if _default_flags & _C.FLAG_GENERIC or os.environ.get("FBLA_PAD_SMALL_DIMS", "1") == "0":
         return None
     K, V = q.shape[-1], v.shape[-1]
     if K in (64, 128) and V in (64, 128):

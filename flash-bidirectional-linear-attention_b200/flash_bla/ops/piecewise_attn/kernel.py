@@ -99,16 +99,36 @@ def fused_chunk_reduce(q, k, v, chunk_size, use_bias=False, p=2):
     return qc.to(q.dtype), kc.to(k.dtype), vc.to(v.dtype), h.to(v.dtype), bias
 
 
-def select_blocks(qc, kc, scale, density, dtype, bias=None):
+_SELECT_MAX_BLOCKS = 1024
+
+
+def select_blocks(qc, kc, scale, density, dtype, bias=None, use_torch=False):
     """Indices ``(B,H,NT,NS)`` of the key blocks each query block attends exactly: top-k of the
     block-mean scores computed in the dtype of the inputs, ``NS = max(1, int(density * NT))``.
-    ``bias`` ``(B,H,1,NT)``: rank ``softmax(score + log(bias + 1e-5))`` instead (kernel.py:314-315)."""
+    ``bias`` ``(B,H,1,NT)``: rank ``softmax(score + log(bias + 1e-5))`` instead (kernel.py:314-315).
+
+    One CUDA kernel (``fbla_pisa_select_blocks``, int32 indices, equal scores to the lower block) for up
+    to 1024 blocks; beyond that, or with ``use_torch``, the reference's einsum / softmax / topk."""
     nt = kc.shape[-2]
-    score = torch.einsum('bhid,bhjd->bhij', qc.to(dtype), (kc * scale).to(dtype))
-    if bias is not None:
-        score = torch.softmax(score + torch.log(bias.to(dtype) + 1e-5), dim=-1)
     top_k = max(1, int(density * nt))
-    return torch.topk(score, k=top_k, dim=-1).indices
+    if use_torch or not qc.is_cuda or nt > _SELECT_MAX_BLOCKS:
+        score = torch.einsum('bhid,bhjd->bhij', qc.to(dtype), (kc * scale).to(dtype))
+        if bias is not None:
+            score = torch.softmax(score + torch.log(bias.to(dtype) + 1e-5), dim=-1)
+        return torch.topk(score, k=top_k, dim=-1).indices
+    B, H, _, K = qc.shape
+    qc, kc = qc.float().contiguous(), kc.float().contiguous()
+    p = _C.PisaProblem()
+    p.dtype = _C.dtype_code(dtype)
+    p.batch, p.heads, p.dk, p.dv = B, H, K, K
+    p.block_size, p.num_selected, p.seq_len = 1, top_k, nt          # one "token" per block: NT blocks
+    p.scale = float(scale)
+    hn = None if bias is None else bias.float().reshape(B, H, nt).contiguous()
+    idx = torch.empty(B, H, nt, top_k, dtype=torch.int32, device=qc.device)
+    with _C.device_guard(qc):
+        _C.check(_C.lib().fbla_pisa_select_blocks(ctypes.byref(p), qc.data_ptr(), kc.data_ptr(), _C.ptr(hn),
+                                                  idx.data_ptr(), _C.stream_of(qc)))
+    return idx
 
 
 def attention_forward(q, k, v, kc, vc, h, indices, block_size, scale, want_stats=False):

@@ -226,6 +226,14 @@ int fbla_pisa_block_stats(const fbla_pisa_problem *p, const void *q, const void 
  * (kernel.py:118 and :172-173, where the reference materialises all the per-block states).    */
 int fbla_pisa_block_hnorm(const fbla_pisa_problem *p, const void *k, const void *v, const float *kc,
                           float pnorm, float *hnorm, fbla_stream_t stream);
+/* Block selection: indices int32 (batch, heads, NT, num_selected) of the num_selected highest-scoring
+ * key blocks per query block, in descending order of score.  score = qc . (kc * scale), operands and
+ * result rounded to p->dtype as the reference forms them (kernel.py:313); with hnorm (may be NULL) the
+ * score is score + log(hnorm + 1e-5), which ranks as the reference's softmax of it does
+ * (kernel.py:314-315).  Replaces the einsum / softmax / topk between the reference's two kernels
+ * (kernel.py:313-318); equal scores go to the lower block index.  Up to 1024 blocks.          */
+int fbla_pisa_select_blocks(const fbla_pisa_problem *p, const float *qc, const float *kc,
+                            const float *hnorm, int32_t *indices, fbla_stream_t stream);
 int fbla_pisa_first_order_state(const fbla_pisa_problem *p, const float *kv, const float *kc,
                                 const float *vc, float *h, fbla_stream_t stream);
 int fbla_pisa_fwd(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,

@@ -271,6 +271,7 @@ def pisa_fwd_given(q, k, v, kc, vc, h, indices, block_size: int, scale: float,
     kernel.py:216-292."""
     cast = (lambda x: x.to(acc)) if differentiable else (lambda x: _f(x, acc))
     q_, k_, v_, kc_, vc_, h_ = (cast(x) for x in (q, k, v, kc, vc, h))
+    indices = indices.long()
     T = k_.shape[-2]
     nt = kc_.shape[-2]
     lead = q_.shape[:-2]

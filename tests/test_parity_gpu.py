@@ -438,8 +438,8 @@ def test_linear_attention_blhd_layout(shape, dtype):
         check(got.permute(0, 2, 1, 3), ref, dtype, f"blhd{shape}.{name}")
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FBLA_PAD_SMALL_DIMS", "0") != "1",
-                    reason="the padded route is opt-in (FBLA_PAD_SMALL_DIMS=1)")
+@pytest.mark.skipif(__import__("os").environ.get("FBLA_PAD_SMALL_DIMS", "1") == "0",
+                    reason="the padded route is switched off (FBLA_PAD_SMALL_DIMS=0)")
 @pytest.mark.parametrize("shape", [(2, 8, 8192, 32, 32), (1, 16, 8192, 48, 24), (1, 16, 8192, 96, 32)])
 def test_small_head_dims_take_the_padded_tensor_core_route(shape):
     """16-bit inputs of streaming size whose head dims are not 64 / 128 are zero-padded onto the tensor-core

@@ -23,7 +23,7 @@ def test_golden(name):
         check(got, g[key], torch.float32, f"{name}.{key}")
     assert O.rel_l2(h.cpu(), g["h"]) < 1e-4
     idx = select_blocks(qc, kc, g["scale"], g["density"], torch.float32)
-    assert torch.equal(idx.sort(-1).values.cpu(), g["indices"].sort(-1).values)
+    assert torch.equal(idx.long().sort(-1).values.cpu(), g["indices"].sort(-1).values)
     o = attention_forward(q, k, v, kc, vc, h, g["indices"].cuda(), bs, g["scale"])
     assert O.rel_l2(o.cpu(), g["o"]) < 1e-4
     # the whole operator picks the same blocks here, so it must give the same output
@@ -43,7 +43,7 @@ def test_golden_with_bias():
     for p_ in (1, 3):
         assert O.rel_l2(block_state_norms(k, v, kc, bs, p_).cpu(), O.pisa_block_hnorm(g["k"], g["v"], bs, p_)) < 1e-4
     idx = select_blocks(qc, kc, g["scale"], g["density"], torch.float32, hn[..., None, :])
-    assert torch.equal(idx.sort(-1).values.cpu(), g["indices"].sort(-1).values)
+    assert torch.equal(idx.long().sort(-1).values.cpu(), g["indices"].sort(-1).values)
     o = piecewise_sparse_attention(q, k, v, density=g["density"], block_size=bs, scale=g["scale"], use_bias=True)
     assert O.rel_l2(o.cpu(), g["o"]) < 1e-4
     # and it differs from the unbiased operator on this fixture
@@ -228,6 +228,39 @@ def test_out_of_range_block_indices_select_nothing(dtype, case):
             assert O.rel_l2(got.cpu(), r) < 5e-5, name
         else:
             check(got, r, dtype, "bad-index." + name)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,density,bias", [((2, 3, 72, 128), 0.1, False), ((1, 2, 40, 16), 0.3, True),
+                                                ((1, 1, 1000, 64), 0.05, False), ((1, 2, 1, 8), 0.5, False)])
+def test_block_selection_kernel(shape, density, bias, dtype):
+    """The selection kernel against the reference's einsum / softmax / topk (the torch path of the same
+    function): same scores means the same blocks wherever the k-th score is not tied with the next one."""
+    B, H, NT, K = shape
+    g = torch.Generator().manual_seed(9)
+    qc = torch.randn(B, H, NT, K, generator=g).cuda()
+    kc = torch.randn(B, H, NT, K, generator=g).cuda()
+    hn = (torch.rand(B, H, 1, NT, generator=g) + 0.05).cuda() if bias else None
+    scale = K ** -0.5
+    got = select_blocks(qc, kc, scale, density, dtype, hn)
+    want = select_blocks(qc, kc, scale, density, dtype, hn, use_torch=True)
+    ns = max(1, int(density * NT))
+    assert got.dtype == torch.int32 and got.shape == (B, H, NT, ns) and want.shape == got.shape
+    assert int(got.min()) >= 0 and int(got.max()) < NT
+    # no block twice
+    assert (got.long().sort(-1).values.diff(dim=-1) > 0).all() or ns == 1
+    # scores as the reference forms them
+    score = torch.einsum('bhid,bhjd->bhij', qc.to(dtype), (kc * scale).to(dtype)).float()
+    if bias:
+        score = score + torch.log(hn.to(dtype) + 1e-5).float()
+    picked = torch.gather(score, -1, got.long())
+    # descending order, and nothing left out that beats the weakest pick
+    assert (picked.diff(dim=-1) <= 1e-6 * picked.abs().max()).all() or ns == 1
+    kth = torch.gather(score, -1, want.long()).min(-1).values
+    tol = 0.0 if dtype == torch.float32 and not bias else 2e-2 * score.abs().max().item()
+    assert (picked.min(-1).values >= kth - tol - 1e-6).all()
+    if dtype == torch.float32 and not bias:
+        assert torch.equal(got.long().sort(-1).values, want.sort(-1).values)
 
 
 def test_autograd_end_to_end():
