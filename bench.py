@@ -544,7 +544,9 @@ def run_ours(args):
         kinds = {type(e).__name__ for e in sharded._exchanges.values() if e is not None}
         exchange_kind = ("by one kernel per direction over the per-segment pieces (owner sums, peer loads over NVLink)"
                          if "_FusedExchange" in kinds
-                         else "by one peer-memory kernel per direction" if kinds else "by NCCL all-reduce")
+                         else "by one peer-memory kernel per direction" if kinds
+                         else "by NCCL all-reduce (the default beyond four ranks: measured faster than the "
+                              "library's own exchange kernel there)")
 
     peak_now = peak
     cfg3 = None if args.no_cfg3 else run_cfg3(world, rank, dev, barrier, peak_now)

@@ -12,8 +12,9 @@ On NCCL groups of GPUs of one node the sum is ONE kernel that reads the peers' m
 (symmetric memory, plain peer loads): for the shapes the tensor-core kernels serve it adds the
 per-segment pieces the reducing pass left, without a reduction kernel in between, and from three ranks
 on sums each unit once at its owner (``fbla_seq_sharded_*``); other shapes use the one-round sum of the
-reduced states (``fbla_peer_state_sum``).  Elsewhere, or with ``FBLA_PEER_EXCHANGE=0``, the sum is
-``all_reduce(SUM)``.
+reduced states (``fbla_peer_state_sum``).  That is the default up to four ranks; beyond (where NCCL's
+in-switch reduction measured faster), on other groups, or with ``FBLA_PEER_EXCHANGE=0``, the sum is
+``all_reduce(SUM)``; ``FBLA_PEER_EXCHANGE=1`` forces the kernels.
 
 Every rank must make the same calls in the same order with the same local shapes.  A kernel waits
 for its peers for at most ``FBLA_PEER_WAIT_MS`` (default 5000); ranks that may drift further apart
@@ -151,12 +152,25 @@ class _FusedExchange:
 _exchanges = {}
 
 
+# Up to this many ranks the library's own exchange kernel is used by default; beyond it NCCL's
+# all-reduce.  Measured on B200 (bf16 B8-H16-D64, 32768 tokens per rank, ms per forward + backward,
+# own kernel / NCCL): 2 ranks 1.041 / 1.043, 4 ranks 1.073 / 1.069, 8 ranks 1.111 / 1.089 -- NCCL adds
+# inside the NVSwitch, which two rounds of flags and peer loads do not beat at 8 ranks.
+_PEER_EXCHANGE_MAX_WORLD = 4
+
+
 def _peer_capable(group, device):
+    """FBLA_PEER_EXCHANGE: "1" = the library's exchange kernels on any NCCL group of one node, "0" = always
+    ``all_reduce``; unset = the kernels up to four ranks, ``all_reduce`` beyond."""
     if not (dist.is_available() and dist.is_initialized()) or device.type != "cuda":
         return False
-    if dist.get_world_size(group) < 2 or dist.get_backend(group) != "nccl":
+    world = dist.get_world_size(group)
+    if world < 2 or dist.get_backend(group) != "nccl":
         return False
-    return os.environ.get("FBLA_PEER_EXCHANGE", "1") != "0"
+    mode = os.environ.get("FBLA_PEER_EXCHANGE", "auto")
+    if mode == "0":
+        return False
+    return mode == "1" or world <= _PEER_EXCHANGE_MAX_WORLD
 
 
 def _agreed(make, group, device, same=()):
