@@ -25,7 +25,7 @@ namespace tc {
 constexpr int kBwdStateThreads = 64 + 2 * kEpiThreads + 32;
 
 
-template <int DK, int DV, int MODE>
+template <int DK, int DV, int MODE, bool VARLEN = false>
 struct BwdStateCfg {
     static constexpr int kKB = DK / 64, kVB = DV / 64;
     static constexpr int kBopOne = kVB * DK * 128;                          // one 16-bit copy of scale*S
@@ -36,10 +36,13 @@ struct BwdStateCfg {
     static constexpr int kQBlocks = kKB * (MODE == kDecoupled ? 2 : 1);
     static constexpr int kTmaBytes = (kQBlocks + kVB) * kBlockBytes;        // qr (, q), dO tiles
     static constexpr int kStageBytes = kTmaBytes + kDzBytes;
-    // dq leaves in 32-byte global stores straight from registers (one full sector per thread and
-    // store): measured as fast as a staged tile + TMA store, and the 16-32 KB per warpgroup it saves
-    // buy a deeper load pipeline.  (The staged path is kept behind kDirect = false.)
-    static constexpr bool kDirect = true;
+    // Fixed length: dq leaves in 32-byte global stores straight from registers (one full sector per
+    // thread and store): measured as fast as a staged tile + TMA store, and the 16-32 KB per warpgroup
+    // it saves buy a deeper load pipeline.  Packed layout: the rows of a head are heads*D elements apart,
+    // so every 32-byte store opens a DRAM page of its own; there full tiles are staged in shared memory
+    // and leave as one strided TMA store per warpgroup and tile (tiles that end inside the next sequence
+    // keep the row-guarded direct stores).  The 128 x 128 shape has no room for staging.
+    static constexpr bool kDirect = !(VARLEN && !(DK == 128 && DV == 128));
     static constexpr int kOutBytes = kDirect ? 0 : kQBlocks * kBlockBytes;  // per warpgroup
     static constexpr int kFixed = 1024 + kBopBytes + kVecBytes + kKmOpBytes + 2 * kOutBytes + 512 + kPlanBytes;
     static constexpr int kStagesRaw = (kSmemLimit - kFixed) / kStageBytes;
@@ -59,7 +62,7 @@ __global__ void __launch_bounds__(kBwdStateThreads, 1)
 tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
                     const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
                     const __grid_constant__ CUtensorMap tm_dqr, const Params p_in) {
-    using Cfg = BwdStateCfg<DK, DV, MODE>;
+    using Cfg = BwdStateCfg<DK, DV, MODE, VARLEN>;
     using Map = TileMap<VARLEN>;
     constexpr int NS = Cfg::kStages;
     constexpr int NB = Cfg::kTBufs;
@@ -305,6 +308,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             uint8_t* qr_row = stg + row * 128;                        // + block * kBlockBytes + swizzled chunk
             const uint32_t t_acc = t_lane + tb * Cfg::kTCols;
             const bool tok_ok = row < t.valid;
+            const bool staged = !Cfg::kDirect && t.valid == kTileTokens;            // full tile of the packed layout
             const size_t grow = (size_t)(t.row0 + (long long)row * t.row_stride);   // this thread's row in the (rows, D) view
             float rz = 1.f, dz = 0.f, z = 1.f;
 
@@ -341,7 +345,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                             qs[e] = (VARLEN && !tok_ok) ? 0u : pack2(rf.x * rz, rf.y * rz, BF16);
                         }
                     }
-                    if (Cfg::kDirect) {
+                    if (!staged) {
                         keep1[j] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
                         if (MODE == kDecoupled) keep2[j] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
                         if ((j & 1) && tok_ok) {       // two 16-byte chunks = one 32-byte sector per store
@@ -352,6 +356,8 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                         }
                     } else {
                         *reinterpret_cast<uint4*>(ob + row * 128 + off) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                        if (MODE == kDecoupled)
+                            *reinterpret_cast<uint4*>(ob + KB * kBlockBytes + row * 128 + off) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
                     }
                     if (MODE != kSimple) *reinterpret_cast<uint4*>(qr_row + off) = make_uint4(qs[0], qs[1], qs[2], qs[3]);
                 }
@@ -467,9 +473,16 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
             ptx::mbar_arrive(&out_written[a]);
             if (!Cfg::kDirect && issuer) {
                 if (!ptx::mbar_wait(&out_written[a], ph2, ab, 324)) break;
+                if (staged) {
 #pragma unroll
-                for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t.c1, t.c2);
-                ptx::tma_store_commit();
+                    for (int b = 0; b < KB; ++b) ptx::tma_store_3d(&tm_dqr, ob + b * kBlockBytes, b * 64, t.c1, t.c2);
+                    if (MODE == kDecoupled) {
+#pragma unroll
+                        for (int b = 0; b < KB; ++b)
+                            ptx::tma_store_3d(&tm_dq, ob + (KB + b) * kBlockBytes, b * 64, t.c1, t.c2);
+                    }
+                }
+                ptx::tma_store_commit();        // an empty group keeps the wait_read bookkeeping uniform
             }
             if (last) {
                 if (!ptx::mbar_wait(acc_full, seg & 1u, ab, 325)) break;

@@ -255,7 +255,7 @@ cudaError_t launch_fwd_out(const Params& q, const CUtensorMap& tqr, const CUtens
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
 cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUtensorMap& tq, const CUtensorMap& tdo,
                              const CUtensorMap& tdq, const CUtensorMap& tdqr, cudaStream_t st) {
-    using Cfg = BwdStateCfg<DK, DV, MODE>;
+    using Cfg = BwdStateCfg<DK, DV, MODE, VARLEN>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
     auto kernel = tc_bwd_state_kernel<DK, DV, MODE, BF16, VARLEN>;

@@ -254,11 +254,12 @@ def test_block_selection_kernel(shape, density, bias, dtype):
     if bias:
         score = score + torch.log(hn.to(dtype) + 1e-5).float()
     picked = torch.gather(score, -1, got.long())
-    # descending order, and nothing left out that beats the weakest pick
-    assert (picked.diff(dim=-1) <= 1e-6 * picked.abs().max()).all() or ns == 1
+    # descending order, and nothing left out that beats the weakest pick (16-bit scores and the biased
+    # form are rounded a little differently here and in torch: allow for that)
+    tol = 1e-6 * score.abs().max().item() if dtype == torch.float32 and not bias else 2e-2 * score.abs().max().item()
+    assert (picked.diff(dim=-1) <= tol).all() or ns == 1
     kth = torch.gather(score, -1, want.long()).min(-1).values
-    tol = 0.0 if dtype == torch.float32 and not bias else 2e-2 * score.abs().max().item()
-    assert (picked.min(-1).values >= kth - tol - 1e-6).all()
+    assert (picked.min(-1).values >= kth - tol).all()
     if dtype == torch.float32 and not bias:
         assert torch.equal(got.long().sort(-1).values, want.sort(-1).values)
 
