@@ -38,8 +38,8 @@ constexpr int kPeerThreads = 256;
 constexpr int kFlagRound1 = 0;         // [0, 16)  rank q has entered the exchange (its pieces can be read)
 constexpr int kFlagRound2 = 16;        // [16, 32) rank q has summed its units
 constexpr int kFlagTicket = 32;        // CTAs of this rank that have finished their share of the sums
-constexpr int kFlagGo1 = 40;           // device-local: round 1 complete (written by the polling thread)
-constexpr int kFlagGo2 = 41;           // device-local: round 2 complete
+constexpr int kFlagGo1 = 40;           // device-local: first flag round complete (written by the polling thread)
+constexpr int kFlagGo2 = 41;           // device-local: second flag round complete
 constexpr int kFlagAbort = 42;         // device-local: the polling thread gave up in this exchange
 
 __device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
@@ -166,7 +166,7 @@ peer_piece_sum_kernel(const __grid_constant__ PieceSum a) {
     // wait here until the reducing pass (the previous kernel of the stream) has completed
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // round 1: this rank's pieces were written by the previous kernel of the stream
+    // first flag round: this rank's pieces were written by the previous kernel of the stream
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         __threadfence_system();
         for (int r = 0; r < a.world; ++r) st_relaxed_sys(a.flags[r] + kFlagRound1 + a.rank, a.epoch);
@@ -203,7 +203,7 @@ peer_piece_sum_kernel(const __grid_constant__ PieceSum a) {
             for (int r = 0; r < a.world; ++r) st_relaxed_sys(a.flags[r] + kFlagRound2 + a.rank, a.epoch);
         }
     }
-    // round 2: the other ranks' sums
+    // second flag round: the other ranks' sums
     if (!wait_round(a, kFlagRound2, kFlagGo2, 912, &s_ok)) {
         for (long long i = tid; i < all4; i += nthreads) a.out[i] = make_float4(nan, nan, nan, nan);
         return;

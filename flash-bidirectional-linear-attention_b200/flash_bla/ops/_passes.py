@@ -191,7 +191,9 @@ def _sizes(prob):
 def forward(prob, q, k, v):
     """fwd_state + fwd_out of linear_attention / simple_la / varlen; returns (o, state)."""
     _require_cuda(q, k, v)
-    if _want_unreduced:
+    # the unreduced route needs the tensor-core kernels, and those need 16-byte aligned tensors (a contiguous
+    # view at an odd storage offset is served by the CUDA-core kernels, as the reference serves it)
+    if _want_unreduced and all(t.data_ptr() % 16 == 0 for t in (q, k, v)):
         prob.flags |= _C.FLAG_UNREDUCED
     n_state, n_ws, unreduced = _sizes(prob)
     dev = q.device
@@ -215,6 +217,8 @@ def backward(prob, q, k, v, d_o, state):
     n_state, n_ws, unreduced = _sizes(prob)
     if unreduced != (state.dtype == torch.uint8):
         raise RuntimeError("the kernel path changed between forward and backward (unreduced state saved)")
+    if unreduced and d_o.data_ptr() % 16 != 0:
+        d_o = d_o.clone()           # the saved pieces commit the backward to the tensor-core kernels
     dev = q.device
     dstate = None if unreduced else torch.empty(n_state, dtype=torch.float32, device=dev)
     ws = torch.empty(n_ws, dtype=torch.uint8, device=dev) if n_ws else None

@@ -309,6 +309,27 @@ def test_full_size_varlen_bf16():
     assert not torch.equal(o2[lo:hi], o.detach()[lo:hi])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_tensors_at_an_odd_storage_offset(dtype):
+    """Contiguous views whose storage does not start on a 16-byte boundary (a slice of a larger buffer) are
+    accepted, as the reference accepts them: the CUDA-core kernels serve them."""
+    B, H, T, D = 1, 2, 300, 64
+    q, k, v, do = make_inputs(71, (B, H, T, D), (B, H, T, D), dtype)
+    ref = [O.linear_attn_fwd(q, k, v)] + list(O.linear_attn_bwd(q, k, v, do))
+
+    def shifted(x):                     # same values, storage offset of one element
+        buf = torch.empty(x.numel() + 1, dtype=x.dtype, device="cuda")
+        buf[1:].copy_(x.reshape(-1))
+        out = buf[1:].view(x.shape)
+        assert out.is_contiguous() and out.data_ptr() % 16 != 0
+        return out
+    xs = [shifted(x).requires_grad_() for x in (q, k, v)]
+    o = linear_attention(*xs)
+    o.backward(shifted(do))
+    for got, r, key in zip((o, xs[0].grad, xs[1].grad, xs[2].grad), ref, ("o", "dq", "dk", "dv")):
+        check(got, r, dtype, f"offset.{key}")
+
+
 def test_empty_and_errors():
     # no tokens: nothing to compute (the default scale 1/L is undefined, as in the reference)
     q = torch.rand(1, 2, 0, 16, device="cuda", requires_grad=True)
