@@ -15,6 +15,8 @@
 #include "fbla_common.cuh"
 #include "pisa_mma.cuh"
 #include "pisa_mma_bwd.cuh"
+#include "pisa_tc.cuh"
+#include "tc_kernels.cuh"
 
 namespace fbla {
 namespace {
@@ -489,6 +491,35 @@ int fbla_pisa_first_order_state(const fbla_pisa_problem* p, const float* kv, con
     fbla::note_launches(1);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "first-order state: %s", cudaGetErrorString(e));
+}
+
+int64_t fbla_pisa_fwd_scratch_bytes(const fbla_pisa_problem* p) {
+    fbla::PisaArgs a;
+    if (fbla::resolve_pisa(p, &a)) return -1;
+    if (!fbla::pisa_tc_supported(a.dtype, a.kp.dk, a.kp.dv, a.kp.bs, a.kp.nt, a.kp.ns) || fbla::g_pisa_force_generic) return 0;
+    return fbla::pisa_tc_scratch_bytes(a.bh, a.kp.dk, a.kp.nt);
+}
+
+int fbla_pisa_fwd_ws(const fbla_pisa_problem* p, const void* q, const void* k, const void* v, const float* kc,
+                     const float* vc, const float* h, const int32_t* indices, void* o, float* row_stats, void* scratch,
+                     size_t scratch_bytes, fbla_stream_t stream) {
+    fbla::PisaArgs a;
+    if (int rc = fbla::resolve_pisa(p, &a)) return rc;
+    if (!q || !k || !v || !kc || !vc || !h || !indices || !o)
+        return fbla::api_fail(FBLA_ERR_INVALID, "a tensor pointer is NULL");
+    const int64_t need = fbla_pisa_fwd_scratch_bytes(p);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                           reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
+                           reinterpret_cast<uintptr_t>(h)) & 15u) == 0 &&
+                         (reinterpret_cast<uintptr_t>(scratch) & 127u) == 0;
+    if (need <= 0 || scratch == nullptr || (int64_t)scratch_bytes < need || !aligned)
+        return fbla_pisa_fwd(p, q, k, v, kc, vc, h, indices, o, row_stats, stream);
+    if (const int site = fbla::tc_device_status())
+        return fbla::api_fail(FBLA_ERR_DEVICE, "a kernel gave up a bounded wait (site %d); results are invalid", site);
+    const cudaError_t e = fbla::pisa_tc_fwd(a.dtype, a.bh, a.kp.dk, a.kp.nt, a.kp.ns, a.kp.T, a.kp.scale, q, k, v, kc, vc, h,
+                                            indices, o, row_stats, scratch, (cudaStream_t)stream);
+    fbla::note_launches(2);
+    return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "attention kernel: %s", cudaGetErrorString(e));
 }
 
 int fbla_pisa_fwd(const fbla_pisa_problem* p, const void* q, const void* k, const void* v, const float* kc,

@@ -106,6 +106,21 @@ cudaError_t encode_map(CUtensorMap* m, const void* base, int dtype, int D, int64
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+}  // namespace
+
+// Same view with a box of `box_rows` rows (the attention stage works on blocks of 64 tokens).
+cudaError_t tc_encode_map_rows(CUtensorMap* m, const void* base, int dtype, int D, int64_t rows, int units, int box_rows) {
+    if (encode_fn() == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)units};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows * D * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    const CUtensorMapDataType dt = dtype == FBLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = encode_tiled(m, dt, base, dims, strides, box);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+namespace {
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;

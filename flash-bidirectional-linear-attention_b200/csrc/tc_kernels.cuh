@@ -2,6 +2,8 @@
 // staged by TMA): 16-bit inputs with dk, dv in {64, 128}.
 #pragma once
 
+#include <cuda.h>
+
 #include "fbla_common.cuh"
 
 namespace fbla {
@@ -14,6 +16,9 @@ int tc_device_status();
 // Device-visible address of that word (NULL if the pinned allocation failed).
 int* tc_status_word();
 int64_t tc_workspace_bytes(const KParams& p);
+// TMA map of a (units, rows, D) 16-bit tensor as {D, rows, units}, box = 64 features x box_rows rows,
+// 128-byte swizzle; rows past the end read as zero and are dropped on stores.
+cudaError_t tc_encode_map_rows(CUtensorMap* m, const void* base, int dtype, int D, int64_t rows, int units, int box_rows);
 // How the per-segment pieces of the reducing passes lie in the workspace (fixed length): unit u has
 // pieces (u * slots + j), j < n(u), n(u) = last_cta(u) - first_cta(u) + 1 with the two tile counts.
 struct PieceLayout {

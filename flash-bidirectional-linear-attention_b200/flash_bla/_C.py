@@ -99,7 +99,7 @@ def exported_symbols():
         names += [f"fbla_{op}_{p}" for p in ("fwd_state", "fwd_out", "bwd_state", "bwd_in")]
     names += ["fbla_linear_attn_fwd", "fbla_linear_attn_bwd"]
     names += ["fbla_linear_attn_fwd_state_noalloc", "fbla_noalloc_status"]
-    names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_select_blocks", "fbla_pisa_fwd", "fbla_pisa_bwd",
+    names += ["fbla_pisa_block_stats", "fbla_pisa_block_hnorm", "fbla_pisa_first_order_state", "fbla_pisa_select_blocks", "fbla_pisa_fwd", "fbla_pisa_fwd_ws", "fbla_pisa_fwd_scratch_bytes", "fbla_pisa_bwd",
               "fbla_pisa_bwd_scratch_floats"]
     names += ["fbla_peer_state_sum", "fbla_seq_sharded_supported", "fbla_seq_sharded_part_floats",
               "fbla_seq_sharded_fwd_state", "fbla_seq_sharded_bwd_state", "fbla_seq_sharded_exchange",
@@ -148,6 +148,10 @@ def lib():
             f = getattr(L, name)
             f.restype = ctypes.c_int
             f.argtypes = [_PP] + [_vp] * n_ptr          # tensor pointers, then the stream
+        L.fbla_pisa_fwd_scratch_bytes.restype = ctypes.c_int64
+        L.fbla_pisa_fwd_scratch_bytes.argtypes = [_PP]
+        L.fbla_pisa_fwd_ws.restype = ctypes.c_int
+        L.fbla_pisa_fwd_ws.argtypes = [_PP] + [_vp] * 10 + [_sz, _vp]      # 9 tensors, scratch, its size, stream
         _PG = ctypes.POINTER(PeerGroup)
         L.fbla_seq_sharded_supported.restype = ctypes.c_int
         L.fbla_seq_sharded_supported.argtypes = [_P]

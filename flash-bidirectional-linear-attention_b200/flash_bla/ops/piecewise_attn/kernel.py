@@ -8,6 +8,7 @@ Same public surface as the reference module ``flash_bla/ops/piecewise_attn/kerne
 the two CUDA stages; everything that touches q, k, v runs in the sm_100a library.
 """
 import ctypes
+import os
 
 import torch
 
@@ -140,11 +141,14 @@ def attention_forward(q, k, v, kc, vc, h, indices, block_size, scale, want_stats
     prob = _problem(q, v, block_size, idx.shape[-1], scale)
     o = torch.empty_like(v)
     stats = torch.empty(B, H, T, 4, dtype=torch.float32, device=q.device) if want_stats else None
+    kc, vc, h = kc.contiguous(), vc.contiguous(), h.contiguous()
     with _C.device_guard(q):
-        _C.check(_C.lib().fbla_pisa_fwd(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                        kc.contiguous().data_ptr(), vc.contiguous().data_ptr(),
-                                        h.contiguous().data_ptr(), idx.data_ptr(), o.data_ptr(),
-                                        _C.ptr(stats), _C.stream_of(q)))
+        # the tcgen05 kernel wants 16-bit copies of the statistics: scratch from the caching allocator
+        need = 0 if os.environ.get("FBLA_PISA_TC", "1") == "0" else _C.lib().fbla_pisa_fwd_scratch_bytes(ctypes.byref(prob))
+        scratch = torch.empty(need, dtype=torch.uint8, device=q.device) if need > 0 else None
+        _C.check(_C.lib().fbla_pisa_fwd_ws(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                           kc.data_ptr(), vc.data_ptr(), h.data_ptr(), idx.data_ptr(), o.data_ptr(),
+                                           _C.ptr(stats), _C.ptr(scratch), max(need, 0), _C.stream_of(q)))
     return (o, stats) if want_stats else o
 
 

@@ -240,6 +240,17 @@ int fbla_pisa_fwd(const fbla_pisa_problem *p, const void *q, const void *k, cons
                   const float *kc, const float *vc, const float *h, const int32_t *indices,
                   void *o, float *row_stats, fbla_stream_t stream);
 
+/* fbla_pisa_fwd on the tcgen05 tensor cores (TMEM accumulators, operands by TMA) for 16-bit inputs
+ * with dk = dv in {64, 128}, block_size 64 and up to 2048 blocks: the caller passes 128-byte aligned
+ * scratch of fbla_pisa_fwd_scratch_bytes() bytes (16-bit copies of kc, vc and h; 0 = this shape has
+ * no such kernel, -1 = invalid problem).  With too little scratch or another shape the call is
+ * fbla_pisa_fwd.  Same results contract and same row_stats as fbla_pisa_fwd.                     */
+int64_t fbla_pisa_fwd_scratch_bytes(const fbla_pisa_problem *p);
+int fbla_pisa_fwd_ws(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,
+                     const float *kc, const float *vc, const float *h, const int32_t *indices,
+                     void *o, float *row_stats, void *scratch, size_t scratch_bytes,
+                     fbla_stream_t stream);
+
 /* Backward of fbla_pisa_fwd with the block selection held constant; gradients flow through the
  * block statistics as well.  The reference has no backward for this operator (no counterpart).
  * o, d_o: forward output and its gradient; row_stats: as written by fbla_pisa_fwd.
