@@ -364,8 +364,9 @@ static int resolve_pisa(const fbla_pisa_problem* p, PisaArgs* a) {
 // product taken in it; kernel.py:313); with a bias, score[j] + log(hnorm_j + 1e-5), whose softmax over j
 // the reference ranks (kernel.py:314-315: softmax is monotone, so the order is the same).  The ns largest
 // are written in descending order; equal scores go to the lower block index, NaN counts as smallest.
-constexpr int kSelectWarps = 4;
+constexpr int kSelectWarps = 8;
 constexpr int kSelectMaxBlocks = 1024;              // 32 scores per lane
+constexpr int kSelectChunk = 128;                   // key blocks staged in shared memory per pass
 
 __device__ __forceinline__ float round_like(float x, int dtype) {
     if (dtype == FBLA_BF16) return __bfloat162float(__float2bfloat16_rn(x));
@@ -381,39 +382,67 @@ __device__ __forceinline__ unsigned long long select_key(float x, int j) {
     return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (unsigned int)j);
 }
 
+// The CTA serves eight query blocks of one (batch, head): the key means, scaled and rounded, are staged
+// in shared memory 128 blocks at a time (rows padded by four floats, so that the lanes' 128-bit reads of
+// 32 different rows are free of bank conflicts), and every warp forms the scores of its query block from
+// there.  PER = score slots per lane (PER * 32 >= number of blocks).
+template <int PER>
 __global__ void __launch_bounds__(kSelectWarps * 32)
 pisa_select_kernel(PisaParams p, int dtype, const float* __restrict__ qc, const float* __restrict__ kc,
                    const float* __restrict__ hnorm, int32_t* __restrict__ indices) {
-    extern __shared__ float qrow_all[];
+    extern __shared__ __align__(16) float select_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int i_blk = blockIdx.x * kSelectWarps + warp, bh = blockIdx.y;
-    if (i_blk >= p.nt) return;
-    const int K = p.dk;
-    float* qrow = qrow_all + warp * K;
-    const float* qsrc = qc + ((size_t)bh * p.nt + i_blk) * K;
-    for (int d = lane; d < K; d += 32) qrow[d] = round_like(qsrc[d], dtype);
-    __syncwarp();
-    constexpr int kPer = kSelectMaxBlocks / 32;
-    unsigned long long key[kPer];
+    const bool valid = i_blk < p.nt;
+    const int K = p.dk, K4 = (K + 3) & ~3, KS = K4 + 4;
+    float* kcs = select_smem;                                   // [kSelectChunk][KS]
+    float* qrow = select_smem + kSelectChunk * KS + warp * K4;  // [K4], zero past K
+    if (valid) {
+        const float* qsrc = qc + ((size_t)bh * p.nt + i_blk) * K;
+        for (int d = lane; d < K4; d += 32) qrow[d] = d < K ? round_like(qsrc[d], dtype) : 0.f;
+    }
+    unsigned long long key[PER];
 #pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int j = u * 32 + lane;
-        key[u] = 0ull;
-        if (j < p.nt) {
-            const float* krow = kc + ((size_t)bh * p.nt + j) * K;
-            float acc = 0.f;
-            for (int d = 0; d < K; ++d) acc = fmaf(qrow[d], round_like(krow[d] * p.scale, dtype), acc);
-            acc = round_like(acc, dtype);
-            if (hnorm != nullptr)
-                acc = round_like(acc + round_like(logf(round_like(hnorm[(size_t)bh * p.nt + j], dtype) + 1e-5f), dtype), dtype);
-            key[u] = select_key(acc, j);
+    for (int u = 0; u < PER; ++u) key[u] = 0ull;
+#pragma unroll
+    for (int c = 0; c < PER / 4; ++c) {
+        const int c0 = c * kSelectChunk;
+        const int rows = min(kSelectChunk, p.nt - c0);
+        if (rows <= 0) continue;                    // uniform over the CTA
+        __syncthreads();
+        const float* src = kc + ((size_t)bh * p.nt + c0) * K;
+        for (int i = threadIdx.x; i < rows * K4; i += kSelectWarps * 32) {
+            const int r = i / K4, d = i - r * K4;
+            kcs[r * KS + d] = d < K ? round_like(src[(size_t)r * K + d] * p.scale, dtype) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int jl = u * 32 + lane, j = c0 + jl;
+            if (valid && jl < rows) {
+                const float4* krow = reinterpret_cast<const float4*>(kcs + jl * KS);
+                const float4* q4 = reinterpret_cast<const float4*>(qrow);
+                float acc = 0.f;
+                for (int d = 0; d < K4 / 4; ++d) {
+                    const float4 a = q4[d], b = krow[d];
+                    acc = fmaf(a.x, b.x, acc);
+                    acc = fmaf(a.y, b.y, acc);
+                    acc = fmaf(a.z, b.z, acc);
+                    acc = fmaf(a.w, b.w, acc);
+                }
+                acc = round_like(acc, dtype);
+                if (hnorm != nullptr)
+                    acc = round_like(acc + round_like(logf(round_like(hnorm[(size_t)bh * p.nt + j], dtype) + 1e-5f), dtype), dtype);
+                key[c * 4 + u] = select_key(acc, j);
+            }
         }
     }
+    if (!valid) return;
     int32_t* out = indices + ((size_t)bh * p.nt + i_blk) * p.ns;
     for (int n = 0; n < p.ns; ++n) {
         unsigned long long best = 0ull;
 #pragma unroll
-        for (int u = 0; u < kPer; ++u) best = key[u] > best ? key[u] : best;
+        for (int u = 0; u < PER; ++u) best = key[u] > best ? key[u] : best;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
@@ -422,7 +451,7 @@ pisa_select_kernel(PisaParams p, int dtype, const float* __restrict__ qc, const 
         const int at = (int)(0xffffffffu - (unsigned int)(best & 0xffffffffull));
         if (lane == 0) out[n] = best != 0ull ? at : 0;
 #pragma unroll
-        for (int u = 0; u < kPer; ++u)
+        for (int u = 0; u < PER; ++u)
             if (key[u] == best) key[u] = 0ull;          // retire the winner (keys are unique: they carry the index)
     }
 }
@@ -454,8 +483,16 @@ int fbla_pisa_select_blocks(const fbla_pisa_problem* p, const float* qc, const f
         return fbla::api_fail(FBLA_ERR_UNSUPPORTED, "block selection serves up to %d blocks (%d given) and at most as many "
                               "selected blocks as there are blocks", fbla::kSelectMaxBlocks, a.kp.nt);
     dim3 grid((a.kp.nt + fbla::kSelectWarps - 1) / fbla::kSelectWarps, a.bh);
-    const size_t smem = sizeof(float) * (size_t)fbla::kSelectWarps * a.kp.dk;
-    fbla::pisa_select_kernel<<<grid, fbla::kSelectWarps * 32, smem, (cudaStream_t)stream>>>(a.kp, a.dtype, qc, kc, hnorm, indices);
+    const int k4 = (a.kp.dk + 3) & ~3;
+    const size_t smem = sizeof(float) * ((size_t)fbla::kSelectChunk * (k4 + 4) + (size_t)fbla::kSelectWarps * k4);
+    auto run = [&](auto kern) {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return;
+        kern<<<grid, fbla::kSelectWarps * 32, smem, (cudaStream_t)stream>>>(a.kp, a.dtype, qc, kc, hnorm, indices);
+    };
+    if (a.kp.nt <= 128) run(fbla::pisa_select_kernel<4>);
+    else run(fbla::pisa_select_kernel<32>);
     fbla::note_launches(1);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FBLA_OK : fbla::api_fail(FBLA_ERR_CUDA, "block selection: %s", cudaGetErrorString(e));
