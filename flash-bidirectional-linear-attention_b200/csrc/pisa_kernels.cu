@@ -549,7 +549,8 @@ int fbla_pisa_fwd_ws(const fbla_pisa_problem* p, const void* q, const void* k, c
                            reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
                            reinterpret_cast<uintptr_t>(h)) & 15u) == 0 &&
                          (reinterpret_cast<uintptr_t>(scratch) & 127u) == 0;
-    if (need <= 0 || scratch == nullptr || (int64_t)scratch_bytes < need || !aligned)
+    // (the tensor-core kernel takes row maxima before scaling: it needs a positive scale)
+    if (need <= 0 || scratch == nullptr || (int64_t)scratch_bytes < need || !aligned || !(a.kp.scale > 0.f))
         return fbla_pisa_fwd(p, q, k, v, kc, vc, h, indices, o, row_stats, stream);
     if (const int site = fbla::tc_device_status())
         return fbla::api_fail(FBLA_ERR_DEVICE, "a kernel gave up a bounded wait (site %d); results are invalid", site);

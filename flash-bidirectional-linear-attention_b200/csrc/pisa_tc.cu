@@ -5,14 +5,15 @@
 // (exact softmax attention) and every group of 64 unselected blocks (their means as keys, their sums
 // as values: the zeroth-order term) is one iteration of the same loop:
 //     S = Q K^T          tcgen05.mma, M = 64, N = 64, accumulator in TMEM
-//     P = exp2(S - m)    one thread per query row reads its row of S from TMEM (no shuffles)
+//     P = exp2(S - m)    a warp reads its 16 rows of S from TMEM with all 32 lanes (16x256b shape)
 //     O (+)= P V         tcgen05.mma, P staged in shared memory, accumulator in TMEM
 // followed by r = Q h (the first-order term) and out = (O + r g scale / T) / (l + g).
 //
-//   warp 0      TMA producer: Q once, then a two-stage ring of (K, V) tiles, then h
+//   warp 0      TMA producer: Q once, then a three-deep ring of key tiles and a two-deep ring of
+//               value tiles (a key tile is free as soon as its scores are formed), then h
 //   warp 1      MMA issuer (one thread) and owner of the TMEM allocation
 //   warps 2-5   softmax and epilogue; with M = 64 the accumulator row r lives in TMEM lane
-//               (r % 16) + 32 * (r / 16), so lanes 0-15 of each warp carry one row each
+//               (r % 16) + 32 * (r / 16): each warp owns the 16 rows of its lane window
 //
 // The score MMA of iteration i + 1 is issued before the weights of iteration i are waited for, so
 // the softmax of one block overlaps the tensor-core work of its neighbours; S is double-buffered.
@@ -43,21 +44,22 @@ struct Params {
     int* status;
 };
 
-enum Bar { kQFull = 0, kKvFull = 1, kKvEmpty = 3, kSFull = 5, kSEmpty = 7, kPFull = 9, kPvDone = 10, kRFull = 11, kBars = 12 };
+constexpr int kKStages = 3, kVStages = 2;   // keys run further ahead than values: they are needed first
+enum Bar { kQFull = 0, kKFull = 1, kKEmpty = 4, kVFull = 7, kVEmpty = 9, kSFull = 11, kSEmpty = 13, kPFull = 15, kPvDone = 16, kRFull = 17, kBars = 18 };
 
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-        : "memory");
+// 16 TMEM lanes x 64 columns in the 16x256b shape (eight repetitions of eight columns): 32 registers per thread.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const float (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -72,13 +74,13 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     }
 }
 
-// Shared memory: [Q tile | 2 x (K tile, V tile) | P tile | barriers | bookkeeping]; tiles are
+// Shared memory: [Q tile | 3 K tiles | 2 V tiles | P tile | barriers | bookkeeping]; tiles are
 // D/64 swizzled blocks of [64 rows][64 elements].
 template <int D>
 constexpr int tile_bytes() { return kBS * D * 2; }
 template <int D>
 size_t smem_bytes(int nt, int ns) {
-    return 1024 + (size_t)5 * tile_bytes<D>() + kBlockBytes + 128 + (size_t)8 * ((nt + 63) / 64) + (size_t)4 * ns +
+    return 1024 + (size_t)(1 + kKStages + kVStages) * tile_bytes<D>() + kBlockBytes + 256 + (size_t)8 * ((nt + 63) / 64) + (size_t)4 * ns +
            (size_t)((nt + 15) & ~15);
 }
 
@@ -94,13 +96,14 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* q_t = sm;
-    uint8_t* kv_t = sm + kTile;
-    uint8_t* p_t = sm + 5 * kTile;
+    uint8_t* k_ring = sm + kTile;
+    uint8_t* v_ring = k_ring + kKStages * kTile;
+    uint8_t* p_t = v_ring + kVStages * kTile;
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_t + kBlockBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int nch = (p.nt + 63) / 64;
-    unsigned long long* sel_mask = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(bars) + 128);
+    unsigned long long* sel_mask = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(bars) + 256);
     int* sel_idx = reinterpret_cast<int*>(sel_mask + nch);
     unsigned char* sel = reinterpret_cast<unsigned char*>(sel_idx + p.ns);
 
@@ -111,9 +114,13 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(&bars[kQFull], 1);
+        for (int s = 0; s < kKStages; ++s) {
+            ptx::mbar_init(&bars[kKFull + s], 1);
+            ptx::mbar_init(&bars[kKEmpty + s], 1);
+        }
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(&bars[kKvFull + s], 1);
-            ptx::mbar_init(&bars[kKvEmpty + s], 1);
+            ptx::mbar_init(&bars[kVFull + s], 1);
+            ptx::mbar_init(&bars[kVEmpty + s], 1);
             ptx::mbar_init(&bars[kSFull + s], 1);
             ptx::mbar_init(&bars[kSEmpty + s], 128);
         }
@@ -156,33 +163,47 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             // ---------------- TMA producer ----------------
             ptx::mbar_arrive_expect_tx(&bars[kQFull], kTile);
             for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(q_t + cb * kBlockBytes, &tm_q, &bars[kQFull], cb * 64, qb * kBS, bh);
-            for (int i = 0; i <= NI; ++i) {
-                const int s = i & 1;
-                uint8_t* k_t = kv_t + s * 2 * kTile;
-                if (!ptx::mbar_wait(&bars[kKvEmpty + s], ((i >> 1) & 1) ^ 1, ab, 711)) break;
-                if (i < NI) {
-                    ptx::mbar_arrive_expect_tx(&bars[kKvFull + s], 2 * kTile);
-                    if (i < p.ns) {
-                        int c = sel_idx[i];
-                        if (c < 0 || c >= p.nt) c = 0;       // fetched, then masked out entirely
-                        for (int cb = 0; cb < kNB; ++cb) {
-                            ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_k, &bars[kKvFull + s], cb * 64, c * kBS, bh);
-                            ptx::tma_load_3d(k_t + kTile + cb * kBlockBytes, &tm_v, &bars[kKvFull + s], cb * 64, c * kBS, bh);
-                        }
-                    } else {
-                        const int r0 = (i - p.ns) * 64;
-                        for (int cb = 0; cb < kNB; ++cb) {
-                            ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_kc, &bars[kKvFull + s], cb * 64, r0, bh);
-                            ptx::tma_load_3d(k_t + kTile + cb * kBlockBytes, &tm_vc, &bars[kKvFull + s], cb * 64, r0, bh);
-                        }
-                    }
+            // Key tiles are numbered 0 .. NI - 1 (one per iteration), then the halves of h ([D][D], 64 rows
+            // each) as key tiles NI, NI + 1.  Issue order: K(t + 1) before V(t), so that the scores of the
+            // next iteration never wait for a load that was started only when its slot fell free.
+            const int n_keys = NI + kNB;
+            auto load_k = [&](int i) -> bool {
+                const int s = i % kKStages;
+                uint8_t* k_t = k_ring + s * kTile;
+                if (!ptx::mbar_wait(&bars[kKEmpty + s], ((i / kKStages) & 1) ^ 1, ab, 711)) return false;
+                ptx::mbar_arrive_expect_tx(&bars[kKFull + s], kTile);
+                if (i < p.ns) {
+                    int c = sel_idx[i];
+                    if (c < 0 || c >= p.nt) c = 0;           // fetched, then masked out entirely
+                    for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_k, &bars[kKFull + s], cb * 64, c * kBS, bh);
+                } else if (i < NI) {
+                    for (int cb = 0; cb < kNB; ++cb)
+                        ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_kc, &bars[kKFull + s], cb * 64, (i - p.ns) * 64, bh);
                 } else {
-                    // h ([D][D]): rows 0-63 into the key tile, rows 64-127 into the value tile
-                    ptx::mbar_arrive_expect_tx(&bars[kKvFull + s], kNB * kNB * kBlockBytes);
-                    for (int hb = 0; hb < kNB; ++hb)
-                        for (int cb = 0; cb < kNB; ++cb)
-                            ptx::tma_load_3d(k_t + hb * kTile + cb * kBlockBytes, &tm_h, &bars[kKvFull + s], cb * 64, hb * 64, bh);
+                    for (int cb = 0; cb < kNB; ++cb)
+                        ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_h, &bars[kKFull + s], cb * 64, (i - NI) * 64, bh);
                 }
+                return true;
+            };
+            auto load_v = [&](int i) -> bool {
+                const int s = i % kVStages;
+                uint8_t* v_t = v_ring + s * kTile;
+                if (!ptx::mbar_wait(&bars[kVEmpty + s], ((i / kVStages) & 1) ^ 1, ab, 712)) return false;
+                ptx::mbar_arrive_expect_tx(&bars[kVFull + s], kTile);
+                if (i < p.ns) {
+                    int c = sel_idx[i];
+                    if (c < 0 || c >= p.nt) c = 0;
+                    for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(v_t + cb * kBlockBytes, &tm_v, &bars[kVFull + s], cb * 64, c * kBS, bh);
+                } else {
+                    for (int cb = 0; cb < kNB; ++cb)
+                        ptx::tma_load_3d(v_t + cb * kBlockBytes, &tm_vc, &bars[kVFull + s], cb * 64, (i - p.ns) * 64, bh);
+                }
+                return true;
+            };
+            bool okay = load_k(0);
+            for (int t = 0; t < n_keys && okay; ++t) {
+                if (t + 1 < n_keys) okay = load_k(t + 1);
+                if (okay && t < NI) okay = load_v(t);
             }
         }
     } else if (warp == 1) {
@@ -192,11 +213,11 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             const uint32_t idesc_o = ptx::instr_desc(64, D, BF16, false, true);
             const uint32_t q_base = ptx::smem_u32(q_t), p_base = ptx::smem_u32(p_t);
             auto scores = [&](int i) -> bool {
-                const int s = i & 1;
-                if (!ptx::mbar_wait(&bars[kKvFull + s], (i >> 1) & 1, ab, 721)) return false;
+                const int s = i & 1, ks = i % kKStages;
+                if (!ptx::mbar_wait(&bars[kKFull + ks], (i / kKStages) & 1, ab, 721)) return false;
                 if (!ptx::mbar_wait(&bars[kSEmpty + s], ((i >> 1) & 1) ^ 1, ab, 722)) return false;
                 ptx::tc_fence_after_sync();
-                const uint32_t k_base = ptx::smem_u32(kv_t + s * 2 * kTile);
+                const uint32_t k_base = ptx::smem_u32(k_ring + ks * kTile);
 #pragma unroll
                 for (int kb = 0; kb < kNB; ++kb)
 #pragma unroll
@@ -206,120 +227,157 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                         ptx::mma_ss(tmem + kColS + s * 64, da, db, idesc_s, !(kb == 0 && kk == 0));
                     }
                 ptx::mma_commit(&bars[kSFull + s]);
+                ptx::mma_commit(&bars[kKEmpty + ks]);
                 return true;
             };
             bool okay = ptx::mbar_wait(&bars[kQFull], 0, ab, 720);
             if (okay && NI > 0) okay = scores(0);
             for (int i = 0; i < NI && okay; ++i) {
                 if (i + 1 < NI && !scores(i + 1)) { okay = false; break; }
+                if (!ptx::mbar_wait(&bars[kVFull + (i & 1)], (i >> 1) & 1, ab, 725)) { okay = false; break; }
                 if (!ptx::mbar_wait(&bars[kPFull], i & 1, ab, 723)) { okay = false; break; }
                 ptx::tc_fence_after_sync();
-                const uint32_t v_base = ptx::smem_u32(kv_t + (i & 1) * 2 * kTile + kTile);
+                const uint32_t v_base = ptx::smem_u32(v_ring + (i & 1) * kTile);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint64_t da = ptx::smem_desc(p_base + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     const uint64_t db = ptx::smem_desc(v_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
                     ptx::mma_ss(tmem + kColO, da, db, idesc_o, !(i == 0 && kk == 0));
                 }
-                ptx::mma_commit(&bars[kKvEmpty + (i & 1)]);
+                ptx::mma_commit(&bars[kVEmpty + (i & 1)]);
                 ptx::mma_commit(&bars[kPvDone]);
             }
-            if (okay && ptx::mbar_wait(&bars[kKvFull + (NI & 1)], (NI >> 1) & 1, ab, 724)) {
+            for (int kb = 0; kb < kNB && okay; ++kb)
+                okay = ptx::mbar_wait(&bars[kKFull + (NI + kb) % kKStages], ((NI + kb) / kKStages) & 1, ab, 724);
+            if (okay) {
                 // r = Q h into the columns of the score buffers (all scores have been read: the last
                 // weights were waited for above)
                 ptx::tc_fence_after_sync();
-                const uint32_t h_base = ptx::smem_u32(kv_t + (NI & 1) * 2 * kTile);
 #pragma unroll
-                for (int kb = 0; kb < kNB; ++kb)
+                for (int kb = 0; kb < kNB; ++kb) {
+                    const uint32_t h_base = ptx::smem_u32(k_ring + ((NI + kb) % kKStages) * kTile);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
                         const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(h_base + kb * kTile + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(h_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
                         ptx::mma_ss(tmem + kColS, da, db, idesc_o, !(kb == 0 && kk == 0));
                     }
+                }
                 ptx::mma_commit(&bars[kRFull]);
             }
         }
     } else {
-        // ---------------- softmax and epilogue: one query row per thread (lanes 0-15) ----------------
+        // ---------------- softmax and epilogue ----------------
+        // A warp owns 16 query rows (TMEM lanes 32 q .. 32 q + 15) and reads them in the 16x256b shape:
+        // thread t holds rows t / 4 and t / 4 + 8, and of every group of eight columns the two
+        // columns 2 (t % 4), 2 (t % 4) + 1 (registers 4 i .. 4 i + 3 for column group i: first row,
+        // then second row).  All 32 lanes carry data; row-wise maxima and sums take two shuffles.
         const int quarter = warp & 3;
-        const bool active = lane < 16;
-        const int row = quarter * 16 + (lane & 15);
+        const int c2 = (lane & 3) * 2;
+        const int row_a = quarter * 16 + (lane >> 2), row_b = row_a + 8;
         const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         const float sm2 = p.scale * 1.44269504f;
         const int nrows = min(kBS, p.T - qb * kBS);
         const int last_len = p.T - (p.nt - 1) * kBS;
-        float m_run = -INFINITY, l = 0.f, g = 0.f;
+        float m_run[2] = {-INFINITY, -INFINITY};      // running maxima of the scaled scores (log2 domain)
+        float l_part[2] = {0.f, 0.f}, g_part[2] = {0.f, 0.f};   // this thread's share of the row sums
         bool okay = true;
         for (int i = 0; i < NI; ++i) {
             const int b = i & 1;
-            float s[64];
+            float s[32];
             if (!ptx::mbar_wait(&bars[kSFull + b], (i >> 1) & 1, ab, 731)) { okay = false; break; }
             ptx::tc_fence_after_sync();
-            ptx::tmem_ld32(t_lane + kColS + b * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
-            ptx::tmem_ld32(t_lane + kColS + b * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+            tmem_ld_16x256b_x8(t_lane + kColS + b * 64, s);
             ptx::tmem_ld_wait();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&bars[kSEmpty + b]);
             const bool approx = i >= p.ns;
             int nvalid, jl = -1;
-            unsigned long long keep;
+            unsigned long long keep = ~0ull;
             if (!approx) {
                 const int cb = sel_idx[i];
                 nvalid = (cb < 0 || cb >= p.nt) ? 0 : min(kBS, p.T - cb * kBS);
-                keep = ~0ull;
             } else {
                 const int c0 = (i - p.ns) * 64;
                 nvalid = min(64, p.nt - c0);
                 keep = ~sel_mask[i - p.ns];
-                jl = p.nt - 1 - c0;                 // position of the (possibly shorter) last block, if in this group
+                if (last_len != kBS) jl = p.nt - 1 - c0;     // position of the shorter last block, if in this group
             }
             keep &= nvalid >= 64 ? ~0ull : ((1ull << nvalid) - 1ull);
-            float mx = -INFINITY;
+            const bool plain = keep == ~0ull && !approx;     // a full selected block: nothing to mask or weigh
+            const unsigned long long keep_t = keep >> c2;    // bit 8 i + (e & 1) = this thread's column of group i
+            float mx[2] = {-INFINITY, -INFINITY};
+            if (plain) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                s[j] = ((keep >> j) & 1ull) ? s[j] * sm2 : -INFINITY;
-                mx = fmaxf(mx, s[j]);
-            }
-            const float m_new = fmaxf(m_run, mx);
-            const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
-            m_run = m_new;
-            l *= alpha;
-            g *= alpha;
-            uint32_t pk[32];
-            float sum = 0.f, p_last = 0.f;
+                for (int x = 0; x < 32; ++x) mx[(x >> 1) & 1] = fmaxf(mx[(x >> 1) & 1], s[x]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 64; j += 2) {
-                const float p0 = (m_run == -INFINITY) ? 0.f : exp2f(s[j] - m_run);
-                const float p1 = (m_run == -INFINITY) ? 0.f : exp2f(s[j + 1] - m_run);
-                sum += p0 + p1;
-                p_last = (j == jl) ? p0 : ((j + 1 == jl) ? p1 : p_last);
-                pk[j >> 1] = pack2<BF16>(p0, p1);
+                for (int x = 0; x < 32; ++x) {
+                    if (!((keep_t >> ((x >> 2) * 8 + (x & 1))) & 1ull)) s[x] = -INFINITY;
+                    mx[(x >> 1) & 1] = fmaxf(mx[(x >> 1) & 1], s[x]);
+                }
             }
-            if (approx) g += sum * (float)kBS - p_last * (float)(kBS - last_len);
-            else l += sum;
+            float alpha[2], neg_m[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r] * sm2);        // scale > 0: the order is kept
+                alpha[r] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new);
+                m_run[r] = m_new;
+                l_part[r] *= alpha[r];
+                g_part[r] *= alpha[r];
+                neg_m[r] = (m_new == -INFINITY) ? 0.f : -m_new;          // exp2(-inf * sm2 + 0) = 0 for masked entries
+            }
+            uint32_t pk[16];
+            float sum[2] = {0.f, 0.f};
+            if (!approx) {
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    const int r = (x >> 1) & 1;
+                    const float p0 = exp2f(fmaf(s[x], sm2, neg_m[r]));
+                    const float p1 = exp2f(fmaf(s[x + 1], sm2, neg_m[r]));
+                    sum[r] += p0 + p1;
+                    pk[x >> 1] = pack2<BF16>(p0, p1);
+                }
+                l_part[0] += sum[0];
+                l_part[1] += sum[1];
+            } else {
+                const int jl_t = jl - c2;                    // this thread holds block jl iff 8 i + (e & 1) == jl_t
+                float p_last[2] = {0.f, 0.f};
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    const int r = (x >> 1) & 1;
+                    const float p0 = exp2f(fmaf(s[x], sm2, neg_m[r]));
+                    const float p1 = exp2f(fmaf(s[x + 1], sm2, neg_m[r]));
+                    sum[r] += p0 + p1;
+                    p_last[r] = ((x >> 2) * 8 == jl_t) ? p0 : (((x >> 2) * 8 + 1 == jl_t) ? p1 : p_last[r]);
+                    pk[x >> 1] = pack2<BF16>(p0, p1);
+                }
+                g_part[0] += sum[0] * (float)kBS - p_last[0] * (float)(kBS - last_len);
+                g_part[1] += sum[1] * (float)kBS - p_last[1] * (float)(kBS - last_len);
+            }
             if (i > 0) {
                 // the previous P V must be complete before P is overwritten and O is touched
                 if (!ptx::mbar_wait(&bars[kPvDone], (i - 1) & 1, ab, 732)) { okay = false; break; }
                 ptx::tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, active && alpha != 1.f)) {
+                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-                    for (int c = 0; c < D; c += 32) {
+                    for (int c = 0; c < D; c += 64) {
                         float o[32];
-                        ptx::tmem_ld32(t_lane + kColO + c, o);
+                        tmem_ld_16x256b_x8(t_lane + kColO + c, o);
                         ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) o[e] *= alpha;
-                        tmem_st32(t_lane + kColO + c, o);
+                        for (int x = 0; x < 32; ++x) o[x] *= alpha[(x >> 1) & 1];
+                        tmem_st_16x256b_x8(t_lane + kColO + c, o);
                     }
                     tmem_st_wait();
                 }
             }
-            if (active) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<uint4*>(p_t + row * 128 + (((c ^ row) & 7) << 4)) =
-                        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            for (int x = 0; x < 16; ++x) {
+                const int row = (x & 1) ? row_b : row_a;
+                *reinterpret_cast<uint32_t*>(p_t + row * 128 + ((((x >> 1) ^ row) & 7) << 4) + c2 * 2) = pk[x];
             }
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
@@ -328,31 +386,40 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (okay) okay = ptx::mbar_wait(&bars[kRFull], 0, ab, 733);
         if (okay) {
             ptx::tc_fence_after_sync();
-            const float corr = g * p.scale / (float)p.T;
-            const float rden = 1.f / (l + g);
+            float corr[2], rden[2], l_row[2], g_row[2];
 #pragma unroll
-            for (int c = 0; c < D; c += 32) {
-                float o[32], r[32];
-                ptx::tmem_ld32(t_lane + kColO + c, o);
-                ptx::tmem_ld32(t_lane + kColS + c, r);
+            for (int r = 0; r < 2; ++r) {
+                l_row[r] = l_part[r] + __shfl_xor_sync(0xffffffffu, l_part[r], 1);
+                l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+                g_row[r] = g_part[r] + __shfl_xor_sync(0xffffffffu, g_part[r], 1);
+                g_row[r] += __shfl_xor_sync(0xffffffffu, g_row[r], 2);
+                corr[r] = g_row[r] * p.scale / (float)p.T;
+                rden[r] = 1.f / (l_row[r] + g_row[r]);
+            }
+#pragma unroll
+            for (int c = 0; c < D; c += 64) {
+                float o[32], rr[32];
+                tmem_ld_16x256b_x8(t_lane + kColO + c, o);
+                tmem_ld_16x256b_x8(t_lane + kColS + c, rr);
                 ptx::tmem_ld_wait();
-                if (active) {
-                    uint8_t* blk = q_t + (c >> 6) * kBlockBytes + row * 128;      // the query tile is free: r = Q h is done
+                uint8_t* blk = q_t + (c >> 6) * kBlockBytes;      // the query tile is free: r = Q h is done
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int x = e * 8 + u * 2;
-                            w[u] = pack2<BF16>((o[x] + r[x] * corr) * rden, (o[x + 1] + r[x + 1] * corr) * rden);
-                        }
-                        const int chunk = ((c & 63) >> 3) + e;
-                        *reinterpret_cast<uint4*>(blk + (((chunk ^ row) & 7) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
+                for (int x = 0; x < 32; x += 2) {
+                    const int r = (x >> 1) & 1;
+                    const int row = r ? row_b : row_a;
+                    *reinterpret_cast<uint32_t*>(blk + row * 128 + ((((x >> 2) ^ row) & 7) << 4) + c2 * 2) =
+                        pack2<BF16>((o[x] + rr[x] * corr[r]) * rden[r], (o[x + 1] + rr[x + 1] * corr[r]) * rden[r]);
                 }
             }
-            if (active && row < nrows && row_stats != nullptr)
-                *reinterpret_cast<float4*>(row_stats + ((size_t)bh * p.T + qb * kBS + row) * 4) = make_float4(m_run, l + g, g, rden);
+            if ((lane & 3) == 0 && row_stats != nullptr) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int row = r ? row_b : row_a;
+                    if (row < nrows)
+                        *reinterpret_cast<float4*>(row_stats + ((size_t)bh * p.T + qb * kBS + row) * 4) =
+                            make_float4(m_run[r], l_row[r] + g_row[r], g_row[r], rden[r]);
+                }
+            }
             ptx::fence_proxy_async_smem();
         }
         ptx::tc_fence_before_sync();
