@@ -45,6 +45,17 @@ struct Params {
 };
 
 constexpr int kKStages = 3, kVStages = 2;   // keys run further ahead than values: they are needed first
+// Development aid (compile with -DFBLA_PISA_TRACE): one CTA writes clock64() stamps of its phases.
+#ifdef FBLA_PISA_TRACE
+__device__ long long g_pisa_trace[128];
+#define PISA_STAMP(slot)                                                                  \
+    do {                                                                                  \
+        if (blockIdx.x == 36 && blockIdx.y == 20 && (slot) < 128) g_pisa_trace[(slot)] = clock64(); \
+    } while (0)
+#else
+#define PISA_STAMP(slot) do { } while (0)
+#endif
+
 enum Bar { kQFull = 0, kKFull = 1, kKEmpty = 4, kVFull = 7, kVEmpty = 9, kSFull = 11, kSEmpty = 13, kPFull = 15, kPvDone = 16, kRFull = 17, kBars = 18 };
 
 // 16 TMEM lanes x 64 columns in the 16x256b shape (eight repetitions of eight columns): 32 registers per thread.
@@ -75,13 +86,13 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // Shared memory: [Q tile | 3 K tiles | 2 V tiles | P tile | barriers | bookkeeping]; tiles are
-// D/64 swizzled blocks of [64 rows][64 elements].
+// D/64 swizzled blocks of [64 rows][64 elements] and need a 1024-byte aligned base, which the kernel
+// checks (dynamic shared memory starts at the base of the CTA's window when there is no static part).
 template <int D>
 constexpr int tile_bytes() { return kBS * D * 2; }
 template <int D>
 size_t smem_bytes(int nt, int ns) {
-    return 1024 + (size_t)(1 + kKStages + kVStages) * tile_bytes<D>() + kBlockBytes + 256 + (size_t)8 * ((nt + 63) / 64) + (size_t)4 * ns +
-           (size_t)((nt + 15) & ~15);
+    return (size_t)(1 + kKStages + kVStages) * tile_bytes<D>() + kBlockBytes + 256 + (size_t)8 * ((nt + 63) / 64) + (size_t)4 * ns;
 }
 
 template <int D, bool BF16>
@@ -93,8 +104,7 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    float* __restrict__ row_stats) {
     constexpr int kNB = D / 64;
     constexpr int kTile = tile_bytes<D>();
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t sm[];
     uint8_t* q_t = sm;
     uint8_t* k_ring = sm + kTile;
     uint8_t* v_ring = k_ring + kKStages * kTile;
@@ -105,14 +115,48 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int nch = (p.nt + 63) / 64;
     unsigned long long* sel_mask = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(bars) + 256);
     int* sel_idx = reinterpret_cast<int*>(sel_mask + nch);
-    unsigned char* sel = reinterpret_cast<unsigned char*>(sel_idx + p.ns);
 
     const int qb = blockIdx.x, bh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NI = p.ns + nch;
+    const int n_keys = NI + kNB;        // key tiles: one per iteration, then the 64-row halves of h
     const int32_t* idx = indices + ((size_t)bh * p.nt + qb) * p.ns;
+    if ((ptx::smem_u32(sm) & 1023u) != 0) {          // uniform over the CTA: the swizzled tiles need 1024-byte alignment
+        if (threadIdx.x == 0) *p.status = 799;
+        return;
+    }
+    const ptx::Abort ab{abort_flag, p.status};
+
+    // ---- loads (thread 0) ----
+    // Issue order: K(t + 1) before V(t), so that the scores of the next iteration never wait for a load
+    // that was started only when its slot fell free.  Indices are read straight from global memory.
+    auto block_of = [&](int i) {
+        const int c = __ldg(idx + i);
+        return (c < 0 || c >= p.nt) ? 0 : c;         // a bad index: fetched, then masked out entirely
+    };
+    auto load_k = [&](int i) -> bool {
+        const int s = i % kKStages;
+        uint8_t* k_t = k_ring + s * kTile;
+        if (!ptx::mbar_wait(&bars[kKEmpty + s], ((i / kKStages) & 1) ^ 1, ab, 711)) return false;
+        ptx::mbar_arrive_expect_tx(&bars[kKFull + s], kTile);
+        const CUtensorMap* m = i < p.ns ? &tm_k : (i < NI ? &tm_kc : &tm_h);
+        const int r0 = i < p.ns ? block_of(i) * kBS : (i < NI ? (i - p.ns) * 64 : (i - NI) * 64);
+        for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(k_t + cb * kBlockBytes, m, &bars[kKFull + s], cb * 64, r0, bh);
+        return true;
+    };
+    auto load_v = [&](int i) -> bool {
+        const int s = i % kVStages;
+        uint8_t* v_t = v_ring + s * kTile;
+        if (!ptx::mbar_wait(&bars[kVEmpty + s], ((i / kVStages) & 1) ^ 1, ab, 712)) return false;
+        ptx::mbar_arrive_expect_tx(&bars[kVFull + s], kTile);
+        const CUtensorMap* m = i < p.ns ? &tm_v : &tm_vc;
+        const int r0 = i < p.ns ? block_of(i) * kBS : (i - p.ns) * 64;
+        for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(v_t + cb * kBlockBytes, m, &bars[kVFull + s], cb * 64, r0, bh);
+        return true;
+    };
 
     if (threadIdx.x == 0) {
+        PISA_STAMP(0);
         ptx::mbar_init(&bars[kQFull], 1);
         for (int s = 0; s < kKStages; ++s) {
             ptx::mbar_init(&bars[kKFull + s], 1);
@@ -129,79 +173,36 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ptx::mbar_init(&bars[kRFull], 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
-        ptx::prefetch_tensormap(&tm_q);
-        ptx::prefetch_tensormap(&tm_k);
-        ptx::prefetch_tensormap(&tm_v);
+        // the first loads go out before the rest of the CTA has finished setting up
+        ptx::mbar_arrive_expect_tx(&bars[kQFull], kTile);
+        for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(q_t + cb * kBlockBytes, &tm_q, &bars[kQFull], cb * 64, qb * kBS, bh);
+        load_k(0);
+        if (n_keys > 1) load_k(1);
+        if (NI > 0) load_v(0);
     }
-    for (int i = threadIdx.x; i < p.nt; i += kThreads) sel[i] = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < p.ns; i += kThreads) {
-        const int c = idx[i];
-        sel_idx[i] = c;
-        if (c >= 0 && c < p.nt) sel[c] = 1;          // a bad index selects nothing
-    }
+    for (int i = threadIdx.x; i < nch; i += kThreads) sel_mask[i] = 0ull;
     if (warp == 1) {
         ptx::tmem_alloc(tmem_slot, kTmemCols);
         ptx::tmem_relinquish();
     }
     __syncthreads();
     // one 64-bit word per group of 64 blocks: bit j set = block 64 c + j was selected
-    for (int c = warp; c < nch; c += kThreads / 32) {
-        const int a = c * 64 + lane, b = a + 32;
-        const unsigned lo = __ballot_sync(0xffffffffu, a < p.nt && sel[a] != 0);
-        const unsigned hi = __ballot_sync(0xffffffffu, b < p.nt && sel[b] != 0);
-        if (lane == 0) sel_mask[c] = ((unsigned long long)hi << 32) | lo;
+    for (int i = threadIdx.x; i < p.ns; i += kThreads) {
+        const int c = idx[i];
+        sel_idx[i] = c;
+        if (c >= 0 && c < p.nt) atomicOr(&sel_mask[c >> 6], 1ull << (c & 63));      // a bad index selects nothing
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const ptx::Abort ab{abort_flag, p.status};
+    if (threadIdx.x == 0) PISA_STAMP(1);
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---------------- TMA producer ----------------
-            ptx::mbar_arrive_expect_tx(&bars[kQFull], kTile);
-            for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(q_t + cb * kBlockBytes, &tm_q, &bars[kQFull], cb * 64, qb * kBS, bh);
-            // Key tiles are numbered 0 .. NI - 1 (one per iteration), then the halves of h ([D][D], 64 rows
-            // each) as key tiles NI, NI + 1.  Issue order: K(t + 1) before V(t), so that the scores of the
-            // next iteration never wait for a load that was started only when its slot fell free.
-            const int n_keys = NI + kNB;
-            auto load_k = [&](int i) -> bool {
-                const int s = i % kKStages;
-                uint8_t* k_t = k_ring + s * kTile;
-                if (!ptx::mbar_wait(&bars[kKEmpty + s], ((i / kKStages) & 1) ^ 1, ab, 711)) return false;
-                ptx::mbar_arrive_expect_tx(&bars[kKFull + s], kTile);
-                if (i < p.ns) {
-                    int c = sel_idx[i];
-                    if (c < 0 || c >= p.nt) c = 0;           // fetched, then masked out entirely
-                    for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_k, &bars[kKFull + s], cb * 64, c * kBS, bh);
-                } else if (i < NI) {
-                    for (int cb = 0; cb < kNB; ++cb)
-                        ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_kc, &bars[kKFull + s], cb * 64, (i - p.ns) * 64, bh);
-                } else {
-                    for (int cb = 0; cb < kNB; ++cb)
-                        ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_h, &bars[kKFull + s], cb * 64, (i - NI) * 64, bh);
-                }
-                return true;
-            };
-            auto load_v = [&](int i) -> bool {
-                const int s = i % kVStages;
-                uint8_t* v_t = v_ring + s * kTile;
-                if (!ptx::mbar_wait(&bars[kVEmpty + s], ((i / kVStages) & 1) ^ 1, ab, 712)) return false;
-                ptx::mbar_arrive_expect_tx(&bars[kVFull + s], kTile);
-                if (i < p.ns) {
-                    int c = sel_idx[i];
-                    if (c < 0 || c >= p.nt) c = 0;
-                    for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(v_t + cb * kBlockBytes, &tm_v, &bars[kVFull + s], cb * 64, c * kBS, bh);
-                } else {
-                    for (int cb = 0; cb < kNB; ++cb)
-                        ptx::tma_load_3d(v_t + cb * kBlockBytes, &tm_vc, &bars[kVFull + s], cb * 64, (i - p.ns) * 64, bh);
-                }
-                return true;
-            };
-            bool okay = load_k(0);
-            for (int t = 0; t < n_keys && okay; ++t) {
+            // ---------------- TMA producer (continued) ----------------
+            bool okay = true;
+            for (int t = 1; t < n_keys && okay; ++t) {
                 if (t + 1 < n_keys) okay = load_k(t + 1);
                 if (okay && t < NI) okay = load_v(t);
             }
@@ -231,20 +232,23 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 return true;
             };
             bool okay = ptx::mbar_wait(&bars[kQFull], 0, ab, 720);
+            PISA_STAMP(90);
             if (okay && NI > 0) okay = scores(0);
             for (int i = 0; i < NI && okay; ++i) {
+                const int b = i & 1;
                 if (i + 1 < NI && !scores(i + 1)) { okay = false; break; }
-                if (!ptx::mbar_wait(&bars[kVFull + (i & 1)], (i >> 1) & 1, ab, 725)) { okay = false; break; }
+                if (!ptx::mbar_wait(&bars[kVFull + b], (i >> 1) & 1, ab, 725)) { okay = false; break; }
                 if (!ptx::mbar_wait(&bars[kPFull], i & 1, ab, 723)) { okay = false; break; }
+                PISA_STAMP(10 + i);
                 ptx::tc_fence_after_sync();
-                const uint32_t v_base = ptx::smem_u32(v_ring + (i & 1) * kTile);
+                const uint32_t v_base = ptx::smem_u32(v_ring + b * kTile);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint64_t da = ptx::smem_desc(p_base + kk * 32, 16, 1024, ptx::kLayoutSw128);
                     const uint64_t db = ptx::smem_desc(v_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
                     ptx::mma_ss(tmem + kColO, da, db, idesc_o, !(i == 0 && kk == 0));
                 }
-                ptx::mma_commit(&bars[kVEmpty + (i & 1)]);
+                ptx::mma_commit(&bars[kVEmpty + b]);
                 ptx::mma_commit(&bars[kPvDone]);
             }
             for (int kb = 0; kb < kNB && okay; ++kb)
@@ -264,6 +268,7 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     }
                 }
                 ptx::mma_commit(&bars[kRFull]);
+                PISA_STAMP(91);
             }
         }
     } else {
@@ -286,6 +291,7 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             const int b = i & 1;
             float s[32];
             if (!ptx::mbar_wait(&bars[kSFull + b], (i >> 1) & 1, ab, 731)) { okay = false; break; }
+            if (threadIdx.x == 64) PISA_STAMP(30 + i);
             ptx::tc_fence_after_sync();
             tmem_ld_16x256b_x8(t_lane + kColS + b * 64, s);
             ptx::tmem_ld_wait();
@@ -304,24 +310,30 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 if (last_len != kBS) jl = p.nt - 1 - c0;     // position of the shorter last block, if in this group
             }
             keep &= nvalid >= 64 ? ~0ull : ((1ull << nvalid) - 1ull);
-            const bool plain = keep == ~0ull && !approx;     // a full selected block: nothing to mask or weigh
-            const unsigned long long keep_t = keep >> c2;    // bit 8 i + (e & 1) = this thread's column of group i
-            float mx[2] = {-INFINITY, -INFINITY};
-            if (plain) {
+            if (keep != ~0ull) {
+                const unsigned long long keep_t = keep >> c2;    // bit 8 i + (e & 1) = this thread's column of group i
 #pragma unroll
-                for (int x = 0; x < 32; ++x) mx[(x >> 1) & 1] = fmaxf(mx[(x >> 1) & 1], s[x]);
-            } else {
-#pragma unroll
-                for (int x = 0; x < 32; ++x) {
+                for (int x = 0; x < 32; ++x)
                     if (!((keep_t >> ((x >> 2) * 8 + (x & 1))) & 1ull)) s[x] = -INFINITY;
-                    mx[(x >> 1) & 1] = fmaxf(mx[(x >> 1) & 1], s[x]);
-                }
             }
+            // row maxima: four independent chains per row, then the quad
+            float mx[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float m4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) m4[u] = fmaxf(s[8 * u + 2 * r], s[8 * u + 2 * r + 1]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) m4[u] = fmaxf(m4[u], fmaxf(s[8 * u + 4 + 2 * r], s[8 * u + 4 + 2 * r + 1]));
+                mx[r] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            }
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], 1));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], 1));
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], 2));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], 2));
             float alpha[2], neg_m[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r] * sm2);        // scale > 0: the order is kept
                 alpha[r] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new);
                 m_run[r] = m_new;
@@ -329,19 +341,21 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 g_part[r] *= alpha[r];
                 neg_m[r] = (m_new == -INFINITY) ? 0.f : -m_new;          // exp2(-inf * sm2 + 0) = 0 for masked entries
             }
+            if (threadIdx.x == 64) PISA_STAMP(110 + i);
             uint32_t pk[16];
-            float sum[2] = {0.f, 0.f};
+            float sum[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
             if (!approx) {
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
                     const int r = (x >> 1) & 1;
                     const float p0 = exp2f(fmaf(s[x], sm2, neg_m[r]));
                     const float p1 = exp2f(fmaf(s[x + 1], sm2, neg_m[r]));
-                    sum[r] += p0 + p1;
                     pk[x >> 1] = pack2<BF16>(p0, p1);
+                    sum[r][0] += p0;
+                    sum[r][1] += p1;
                 }
-                l_part[0] += sum[0];
-                l_part[1] += sum[1];
+                l_part[0] += sum[0][0] + sum[0][1];
+                l_part[1] += sum[1][0] + sum[1][1];
             } else {
                 const int jl_t = jl - c2;                    // this thread holds block jl iff 8 i + (e & 1) == jl_t
                 float p_last[2] = {0.f, 0.f};
@@ -350,13 +364,15 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     const int r = (x >> 1) & 1;
                     const float p0 = exp2f(fmaf(s[x], sm2, neg_m[r]));
                     const float p1 = exp2f(fmaf(s[x + 1], sm2, neg_m[r]));
-                    sum[r] += p0 + p1;
-                    p_last[r] = ((x >> 2) * 8 == jl_t) ? p0 : (((x >> 2) * 8 + 1 == jl_t) ? p1 : p_last[r]);
                     pk[x >> 1] = pack2<BF16>(p0, p1);
+                    sum[r][0] += p0;
+                    sum[r][1] += p1;
+                    p_last[r] = ((x >> 2) * 8 == jl_t) ? p0 : (((x >> 2) * 8 + 1 == jl_t) ? p1 : p_last[r]);
                 }
-                g_part[0] += sum[0] * (float)kBS - p_last[0] * (float)(kBS - last_len);
-                g_part[1] += sum[1] * (float)kBS - p_last[1] * (float)(kBS - last_len);
+                g_part[0] += (sum[0][0] + sum[0][1]) * (float)kBS - p_last[0] * (float)(kBS - last_len);
+                g_part[1] += (sum[1][0] + sum[1][1]) * (float)kBS - p_last[1] * (float)(kBS - last_len);
             }
+            if (threadIdx.x == 64) PISA_STAMP(50 + i);
             if (i > 0) {
                 // the previous P V must be complete before P is overwritten and O is touched
                 if (!ptx::mbar_wait(&bars[kPvDone], (i - 1) & 1, ab, 732)) { okay = false; break; }
@@ -374,16 +390,19 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     tmem_st_wait();
                 }
             }
+            uint8_t* pb = p_t;
 #pragma unroll
             for (int x = 0; x < 16; ++x) {
                 const int row = (x & 1) ? row_b : row_a;
-                *reinterpret_cast<uint32_t*>(p_t + row * 128 + ((((x >> 1) ^ row) & 7) << 4) + c2 * 2) = pk[x];
+                *reinterpret_cast<uint32_t*>(pb + row * 128 + ((((x >> 1) ^ row) & 7) << 4) + c2 * 2) = pk[x];
             }
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&bars[kPFull]);
+            if (threadIdx.x == 64) PISA_STAMP(70 + i);
         }
         if (okay) okay = ptx::mbar_wait(&bars[kRFull], 0, ab, 733);
+        if (threadIdx.x == 64) PISA_STAMP(92);
         if (okay) {
             ptx::tc_fence_after_sync();
             float corr[2], rden[2], l_row[2], g_row[2];
@@ -393,8 +412,8 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
                 g_row[r] = g_part[r] + __shfl_xor_sync(0xffffffffu, g_part[r], 1);
                 g_row[r] += __shfl_xor_sync(0xffffffffu, g_row[r], 2);
-                corr[r] = g_row[r] * p.scale / (float)p.T;
                 rden[r] = 1.f / (l_row[r] + g_row[r]);
+                corr[r] = g_row[r] * p.scale / (float)p.T * rden[r];
             }
 #pragma unroll
             for (int c = 0; c < D; c += 64) {
@@ -408,7 +427,7 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     const int r = (x >> 1) & 1;
                     const int row = r ? row_b : row_a;
                     *reinterpret_cast<uint32_t*>(blk + row * 128 + ((((x >> 2) ^ row) & 7) << 4) + c2 * 2) =
-                        pack2<BF16>((o[x] + rr[x] * corr[r]) * rden[r], (o[x + 1] + rr[x + 1] * corr[r]) * rden[r]);
+                        pack2<BF16>(fmaf(rr[x], corr[r], o[x] * rden[r]), fmaf(rr[x + 1], corr[r], o[x + 1] * rden[r]));
                 }
             }
             if ((lane & 3) == 0 && row_stats != nullptr) {
@@ -422,12 +441,14 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             ptx::fence_proxy_async_smem();
         }
+        if (threadIdx.x == 64) PISA_STAMP(93);
         ptx::tc_fence_before_sync();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (okay && threadIdx.x == 64) {
             for (int cb = 0; cb < kNB; ++cb) ptx::tma_store_3d(&tm_o, q_t + cb * kBlockBytes, cb * 64, qb * kBS, bh);
             ptx::tma_store_commit();
-            ptx::tma_store_wait_all<0>();
+            ptx::tma_store_wait_read<0>();      // the tile may be released once it has been read
+            PISA_STAMP(94);
         }
     }
     ptx::tc_fence_before_sync();
@@ -436,6 +457,7 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, kTmemCols);
     }
+    if (threadIdx.x == 0) PISA_STAMP(2);
 }
 
 // fp32 -> 16-bit copies of the block statistics and of h, eight elements per thread
@@ -454,6 +476,12 @@ __global__ void __launch_bounds__(256) cast16_kernel(const float* __restrict__ a
 }
 
 }  // namespace pisa_tc
+
+#ifdef FBLA_PISA_TRACE
+extern "C" int fbla_debug_pisa_trace(long long* out128) {
+    return (int)cudaMemcpyFromSymbol(out128, pisa_tc::g_pisa_trace, sizeof(long long) * 128);
+}
+#endif
 
 bool pisa_tc_supported(int dtype, int dk, int dv, int bs, int nt, int ns) {
     return (dtype == FBLA_BF16 || dtype == FBLA_F16) && dk == dv && (dk == 64 || dk == 128) && bs == 64 && nt <= 2048 &&
