@@ -999,7 +999,7 @@ size_t round64(size_t n) { return (n + 63) / 64 * 64; }
 //   dkc [BH,NT,dk] | dvc [BH,NT,dv] | dh [BH,dk,dv] | drow [BH,T]
 //   tensor-core path only: | dr [BH,T,dv] 16-bit | workspace of the state pass that forms dh
 struct BwdScratch {
-    size_t dkc, dvc, dh, drow, dr, ws, total;
+    size_t dkc, dvc, dh, drow, dr, ws, c16, total;
     int64_t ws_bytes;
     fbla_problem state_problem;
 };
@@ -1029,7 +1029,8 @@ BwdScratch bwd_scratch(const PisaArgs& a) {
         s.ws_bytes = fbla_workspace_bytes(&sp);
         if (s.ws_bytes < 0) s.ws_bytes = 0;
         s.ws = s.dr + round64(((size_t)a.bh * kp.T * kp.dv + 1) / 2);
-        s.total = s.ws + round64(((size_t)s.ws_bytes + 3) / 4);
+        s.c16 = s.ws + round64(((size_t)s.ws_bytes + 3) / 4);      // 16-bit copies of kc, vc, h for the tcgen05 kernel
+        s.total = s.c16 + round64(((size_t)pisa_tc_scratch_bytes(a.bh, kp.dk, kp.nt) + 3) / 4);
     }
     return s;
 }
@@ -1087,7 +1088,21 @@ extern "C" int fbla_pisa_bwd(const fbla_pisa_problem* p, const void* q, const vo
                 kern<<<grid, fbla::pisa_mma::kThreads, smem, st>>>(mp, q, k, v, d_o, kc, vc, indices, row_stats, drow, dkc,
                                                                   dvc, dh, dk, dv);
         };
-        if (kp.dk == 64) {
+        static const bool tc_off = [] {
+            const char* v = getenv("FBLA_PISA_TC");
+            return v != nullptr && v[0] == '0';
+        }();
+        if (!tc_off && kp.scale > 0.f && fbla::pisa_tc_supported(a.dtype, kp.dk, kp.dv, kp.bs, kp.nt, kp.ns)) {
+            // tcgen05 kernel; it reads the statistics and h as 16-bit copies
+            if (const int site = fbla::tc_device_status())
+                return fbla::api_fail(FBLA_ERR_DEVICE, "a kernel gave up a bounded wait (site %d); results are invalid", site);
+            const int64_t n_stats = (int64_t)a.bh * kp.nt * kp.dk, n_h = (int64_t)a.bh * kp.dk * kp.dk;
+            uint16_t* c16 = reinterpret_cast<uint16_t*>(scratch + lay.c16);
+            fbla::pisa_tc_cast16(a.dtype, kc, vc, h, n_stats, n_h, c16, st);
+            e = fbla::pisa_tc_bwd_q(a.dtype, a.bh, kp.dk, kp.nt, kp.ns, kp.T, kp.scale, q, k, v, o, d_o, c16, c16 + n_stats,
+                                    c16 + 2 * n_stats, indices, row_stats, dq, dr, dkc, dvc, drow, st);
+            fbla::note_launches(1);
+        } else if (kp.dk == 64) {
             const size_t smem = fbla::pisa_mma::bwd_q_smem_bytes<64>(kp.nt);
             if (bf) run_q(fbla::pisa_mma::pisa_bwd_q_mma_kernel<64, true>, smem);
             else run_q(fbla::pisa_mma::pisa_bwd_q_mma_kernel<64, false>, smem);

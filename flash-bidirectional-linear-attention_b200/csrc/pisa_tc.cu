@@ -488,6 +488,16 @@ bool pisa_tc_supported(int dtype, int dk, int dv, int bs, int nt, int ns) {
            ns <= nt;
 }
 
+void pisa_tc_cast16(int dtype, const float* kc, const float* vc, const float* h, int64_t n_stats, int64_t n_h, void* out,
+                    cudaStream_t st) {
+    const int64_t total = (2 * n_stats + n_h) / 8;
+    const int grid = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+    if (dtype == FBLA_BF16)
+        pisa_tc::cast16_kernel<true><<<grid, 256, 0, st>>>(kc, vc, h, n_stats, n_stats, n_h, static_cast<uint4*>(out));
+    else
+        pisa_tc::cast16_kernel<false><<<grid, 256, 0, st>>>(kc, vc, h, n_stats, n_stats, n_h, static_cast<uint4*>(out));
+}
+
 int64_t pisa_tc_scratch_bytes(int bh, int d, int nt) {
     return ((int64_t)2 * bh * nt * d + (int64_t)bh * d * d) * 2;
 }
@@ -501,12 +511,7 @@ cudaError_t pisa_tc_fwd(int dtype, int bh, int d, int nt, int ns, int T, float s
     uint16_t* vc16 = kc16 + n_stats;
     uint16_t* h16 = vc16 + n_stats;
     const bool bf = dtype == FBLA_BF16;
-    {
-        const int64_t total = (2 * n_stats + n_h) / 8;
-        const int grid = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
-        if (bf) cast16_kernel<true><<<grid, 256, 0, st>>>(kc, vc, h, n_stats, n_stats, n_h, static_cast<uint4*>(scratch));
-        else cast16_kernel<false><<<grid, 256, 0, st>>>(kc, vc, h, n_stats, n_stats, n_h, static_cast<uint4*>(scratch));
-    }
+    pisa_tc_cast16(dtype, kc, vc, h, n_stats, n_h, scratch, st);
     CUtensorMap mq, mk, mv, mo, mkc, mvc, mh;
     cudaError_t e;
     if ((e = tc_encode_map_rows(&mq, q, dtype, d, T, bh, 64)) != cudaSuccess) return e;

@@ -16,4 +16,13 @@ cudaError_t pisa_tc_fwd(int dtype, int bh, int d, int nt, int ns, int T, float s
                         const void* v, const float* kc, const float* vc, const float* h, const int32_t* indices, void* o,
                         float* row_stats, void* scratch, cudaStream_t st);
 
+// fp32 -> 16-bit copies [kc | vc | h] (n_stats elements each of kc, vc; n_h of h) into `out`.
+void pisa_tc_cast16(int dtype, const float* kc, const float* vc, const float* h, int64_t n_stats, int64_t n_h, void* out,
+                    cudaStream_t st);
+// Query-side backward on tcgen05 (pisa_tc_bwd.cu): dq, dr rows, dD per row, and the block's share of dkc, dvc.
+cudaError_t pisa_tc_bwd_q(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,
+                          const void* v, const void* o, const void* d_o, const void* kc16, const void* vc16, const void* h16,
+                          const int32_t* indices, const float* row_stats, void* dq, void* dr, float* dkc, float* dvc,
+                          float* drow, cudaStream_t st);
+
 }  // namespace fbla

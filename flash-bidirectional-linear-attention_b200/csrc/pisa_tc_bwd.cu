@@ -1,0 +1,592 @@
+// Query-side backward of the piecewise sparse attention stage on the 5th-generation tensor cores
+// (the reference has no backward for this operator; the formulas are stated where fbla_pisa_bwd is
+// defined).  One CTA per block of 64 queries of one (batch, head); same outputs as the mma.sync
+// kernel it replaces: dq, the per-row dD, the rows dr = dO g scale / (T den) from which the state
+// pass forms dh = q^T dr, and this block's share of dkc, dvc (fp32, red.global.add).
+//
+// Per selected key block (and per group of 64 unselected blocks, with their means / sums as keys /
+// values):
+//     S  = Q K^T,  dP = dO V^T      tcgen05.mma, M = 64, N = 64 each, accumulators in TMEM
+//     p  = exp2(S scale log2e - m)  the row maximum m and denominator come from the forward's row
+//     ds = p (dP / den + dD) scale  statistics: nothing is reduced or rescaled in the loop
+//     dQ += ds K                    tcgen05.mma, ds staged in shared memory (bf16: plus its rounding
+//                                   residual as a second product), accumulator in TMEM
+// and for the groups of unselected blocks also dkc = ds^T Q and dvc = (p / den)^T dO, formed in the
+// TMEM columns of S and dP and added to global memory by the element-wise warps.
+//
+//   warp 0      TMA producer: Q, dO, O, h once; then a two-deep ring of key tiles and one value tile
+//   warp 1      MMA issuer (one thread) and owner of the TMEM allocation
+//   warps 2-9   element-wise work: two warps per TMEM lane window, each on one half of the columns
+//               (16x256b shape: thread t holds rows t / 4 and t / 4 + 8, two adjacent columns of
+//               every group of eight)
+//
+// Before the loop: r = Q h (TMEM), od = rowsum(O dO), nr = rowsum(dO r), the per-row constants, the
+// dr tile, and dQ = dr h^T as the initial value of the accumulator.
+// Every wait is bounded and reports through the library's status word.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "pisa_tc.cuh"
+#include "tc_kernels.cuh"
+#include "tc_ptx.cuh"
+
+namespace fbla {
+namespace pisa_tc_bwd {
+
+constexpr int kThreads = 320;
+constexpr int kEwThreads = 256;
+constexpr int kBS = 64;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColDq = 0;       // dQ accumulator: D columns (r = Q h before the loop)
+constexpr uint32_t kColS = 128;      // S: 64 columns; dkc / dvc use [128, 128 + D)
+constexpr uint32_t kColDp = 192;     // dP: 64 columns
+constexpr int kBlockBytes = 64 * 128;
+
+struct Params {
+    int ns, nt, T;
+    float scale;
+    int* status;
+};
+
+enum Bar {
+    kLoad0 = 0, kRFull, kDrFull, kInitDone, kKFull /*2*/, kKEmpty = kKFull + 2 /*2*/, kVFull = kKEmpty + 2, kVEmpty,
+    kSFull, kSEmpty, kDeFull, kDeEmpty, kXFull, kXEmpty, kDone, kBars
+};
+
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if constexpr (BF16) {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&t);
+    } else {
+        const __half2 t = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&t);
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    if constexpr (BF16) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    } else {
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+}
+__device__ __forceinline__ void red_add2(float* addr, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+// 32-bit pair (row, col), col even, of a [64][D] tile made of swizzled [64][64] blocks
+__device__ __forceinline__ uint32_t* pair_at(uint8_t* tile, int row, int col) {
+    return reinterpret_cast<uint32_t*>(tile + (col >> 6) * kBlockBytes + row * 128 + (((((col & 63) >> 3) ^ row) & 7) << 4) +
+                                       (col & 7) * 2);
+}
+
+template <int D>
+constexpr int tile_bytes() { return kBS * D * 2; }
+// [Q | dO | 2 key tiles | value tile | ds | ds residual | p / den | row exchange | barriers | bookkeeping]
+template <int D>
+size_t smem_bytes(int nt, int ns) {
+    return (size_t)5 * tile_bytes<D>() + 3 * kBlockBytes + 1024 + 256 + (size_t)8 * ((nt + 63) / 64) + (size_t)4 * ns;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 2)
+pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                     const __grid_constant__ CUtensorMap tm_o, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
+                     const __grid_constant__ CUtensorMap tm_vc, const __grid_constant__ CUtensorMap tm_h,
+                     const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dr, const Params p,
+                     const int32_t* __restrict__ indices, const float* __restrict__ row_stats, float* __restrict__ dkc,
+                     float* __restrict__ dvc, float* __restrict__ drow) {
+    constexpr int kNB = D / 64;
+    constexpr int kTile = tile_bytes<D>();
+    constexpr int kHalf = D / 2;            // feature columns per warp of a lane window
+    extern __shared__ __align__(1024) uint8_t sm[];
+    uint8_t* q_t = sm;
+    uint8_t* do_t = q_t + kTile;
+    uint8_t* k_ring = do_t + kTile;         // two key tiles; before the loop: O, and rows 0-63 of h
+    uint8_t* v_t = k_ring + 2 * kTile;      // value tile; before the loop: rows 64-127 of h
+    uint8_t* de_t = v_t + kTile;            // scale * ds, 16-bit; before the loop the dr tile starts here
+    uint8_t* dl_t = de_t + kBlockBytes;     // its rounding residual (bf16)
+    uint8_t* pe_t = dl_t + kBlockBytes;     // p / den (groups of unselected blocks)
+    float* xch = reinterpret_cast<float*>(pe_t + kBlockBytes);          // [2][64][2] partial row sums
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xch) + 1024);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int nch = (p.nt + 63) / 64;
+    unsigned long long* sel_mask = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(bars) + 256);
+    int* sel_idx = reinterpret_cast<int*>(sel_mask + nch);
+
+    const int qb = blockIdx.x, bh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NI = p.ns + nch;
+    const int32_t* idx = indices + ((size_t)bh * p.nt + qb) * p.ns;
+    if ((ptx::smem_u32(sm) & 1023u) != 0) {          // uniform over the CTA
+        if (threadIdx.x == 0) *p.status = 798;
+        return;
+    }
+    const ptx::Abort ab{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bars[kLoad0], 1);
+        ptx::mbar_init(&bars[kRFull], 1);
+        ptx::mbar_init(&bars[kDrFull], kEwThreads);
+        ptx::mbar_init(&bars[kInitDone], 1);
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(&bars[kKFull + s], 1);
+            ptx::mbar_init(&bars[kKEmpty + s], 1);
+        }
+        ptx::mbar_init(&bars[kVFull], 1);
+        ptx::mbar_init(&bars[kVEmpty], 1);
+        ptx::mbar_init(&bars[kSFull], 1);
+        ptx::mbar_init(&bars[kSEmpty], kEwThreads);
+        ptx::mbar_init(&bars[kDeFull], kEwThreads);
+        ptx::mbar_init(&bars[kDeEmpty], 1);
+        ptx::mbar_init(&bars[kXFull], 1);
+        ptx::mbar_init(&bars[kXEmpty], kEwThreads);
+        ptx::mbar_init(&bars[kDone], 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        // everything the part before the loop needs, on one barrier
+        ptx::mbar_arrive_expect_tx(&bars[kLoad0], (3 + kNB) * kTile);
+        for (int cb = 0; cb < kNB; ++cb) {
+            ptx::tma_load_3d(q_t + cb * kBlockBytes, &tm_q, &bars[kLoad0], cb * 64, qb * kBS, bh);
+            ptx::tma_load_3d(do_t + cb * kBlockBytes, &tm_do, &bars[kLoad0], cb * 64, qb * kBS, bh);
+            ptx::tma_load_3d(k_ring + cb * kBlockBytes, &tm_o, &bars[kLoad0], cb * 64, qb * kBS, bh);
+        }
+        for (int hb = 0; hb < kNB; ++hb) {
+            uint8_t* dst = hb == 0 ? k_ring + kTile : v_t;
+            for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(dst + cb * kBlockBytes, &tm_h, &bars[kLoad0], cb * 64, hb * 64, bh);
+        }
+    }
+    for (int i = threadIdx.x; i < nch; i += kThreads) sel_mask[i] = 0ull;
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.ns; i += kThreads) {
+        const int c = idx[i];
+        sel_idx[i] = c;
+        if (c >= 0 && c < p.nt) atomicOr(&sel_mask[c >> 6], 1ull << (c & 63));      // a bad index selects nothing
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer: the ring, once the tiles of the first part are free ----------------
+            auto block_of = [&](int i) {
+                const int c = sel_idx[i];
+                return (c < 0 || c >= p.nt) ? 0 : c;         // a bad index: fetched, then masked out entirely
+            };
+            auto load_k = [&](int i) -> bool {
+                const int s = i & 1;
+                if (!ptx::mbar_wait(&bars[kKEmpty + s], ((i >> 1) & 1) ^ 1, ab, 811)) return false;
+                ptx::mbar_arrive_expect_tx(&bars[kKFull + s], kTile);
+                const CUtensorMap* m = i < p.ns ? &tm_k : &tm_kc;
+                const int r0 = i < p.ns ? block_of(i) * kBS : (i - p.ns) * 64;
+                for (int cb = 0; cb < kNB; ++cb)
+                    ptx::tma_load_3d(k_ring + s * kTile + cb * kBlockBytes, m, &bars[kKFull + s], cb * 64, r0, bh);
+                return true;
+            };
+            auto load_v = [&](int i) -> bool {
+                if (i > 0 && !ptx::mbar_wait(&bars[kVEmpty], (i - 1) & 1, ab, 812)) return false;
+                ptx::mbar_arrive_expect_tx(&bars[kVFull], kTile);
+                const CUtensorMap* m = i < p.ns ? &tm_v : &tm_vc;
+                const int r0 = i < p.ns ? block_of(i) * kBS : (i - p.ns) * 64;
+                for (int cb = 0; cb < kNB; ++cb) ptx::tma_load_3d(v_t + cb * kBlockBytes, m, &bars[kVFull], cb * 64, r0, bh);
+                return true;
+            };
+            bool okay = ptx::mbar_wait(&bars[kInitDone], 0, ab, 810);
+            if (okay) okay = load_k(0);
+            if (okay) okay = load_v(0);
+            for (int i = 1; i <= NI && okay; ++i) {
+                if (i < NI) okay = load_k(i);            // K(i): its slot was freed by dQ of iteration i - 2
+                if (okay && i < NI) okay = load_v(i);    // V(i): freed by dP of iteration i - 1
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            const uint32_t idesc_nn = ptx::instr_desc(64, 64, BF16, false, false);     // both operands K-major
+            const uint32_t idesc_o = ptx::instr_desc(64, D, BF16, false, true);        // B MN-major
+            const uint32_t idesc_t = ptx::instr_desc(64, D, BF16, true, true);         // A and B MN-major
+            const uint32_t q_base = ptx::smem_u32(q_t), do_base = ptx::smem_u32(do_t), de_base = ptx::smem_u32(de_t);
+            const uint32_t dl_base = ptx::smem_u32(dl_t), pe_base = ptx::smem_u32(pe_t), v_base = ptx::smem_u32(v_t);
+            const uint32_t k1_base = ptx::smem_u32(k_ring + kTile);
+            bool okay = ptx::mbar_wait(&bars[kLoad0], 0, ab, 820);
+            if (okay) {
+                // r = Q h -> columns [0, D)
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb) {
+                    const uint32_t h_base = kb == 0 ? k1_base : v_base;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(h_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + kColDq, da, db, idesc_o, !(kb == 0 && kk == 0));
+                    }
+                }
+                ptx::mma_commit(&bars[kRFull]);
+                okay = ptx::mbar_wait(&bars[kDrFull], 0, ab, 821);
+            }
+            if (okay) {
+                // dQ = dr h^T: dq[row][d] = sum_vv dr[row][vv] h[d][vv]; the rows d of h lie in two tiles
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int nb = 0; nb < kNB; ++nb) {
+                    const uint32_t h_base = nb == 0 ? k1_base : v_base;
+#pragma unroll
+                    for (int kb = 0; kb < kNB; ++kb)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint64_t da = ptx::smem_desc(de_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                            const uint64_t db = ptx::smem_desc(h_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                            ptx::mma_ss(tmem + kColDq + nb * 64, da, db, idesc_nn, !(kb == 0 && kk == 0));
+                        }
+                }
+                ptx::mma_commit(&bars[kInitDone]);
+            }
+            auto scores = [&](int i) -> bool {       // S = Q K^T and dP = dO V^T of iteration i
+                const int s = i & 1;
+                if (!ptx::mbar_wait(&bars[kKFull + s], (i >> 1) & 1, ab, 822)) return false;
+                if (!ptx::mbar_wait(&bars[kVFull], i & 1, ab, 823)) return false;
+                ptx::tc_fence_after_sync();
+                const uint32_t k_base = ptx::smem_u32(k_ring + s * kTile);
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(k_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + kColS, da, db, idesc_nn, !(kb == 0 && kk == 0));
+                    }
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t da = ptx::smem_desc(do_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(v_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + kColDp, da, db, idesc_nn, !(kb == 0 && kk == 0));
+                    }
+                ptx::mma_commit(&bars[kSFull]);
+                ptx::mma_commit(&bars[kVEmpty]);
+                return true;
+            };
+            // The dr tile occupies the ds tiles until dQ = dr h^T has run; the element-wise warps wait for
+            // that themselves.  The first scores may go out at once: S, dP do not overlap the dQ columns.
+            if (okay && NI > 0) okay = scores(0);
+            int x_events = 0;
+            for (int i = 0; i < NI && okay; ++i) {
+                const bool exact = i < p.ns;
+                if (exact && i + 1 < NI) {
+                    if (!ptx::mbar_wait(&bars[kSEmpty], i & 1, ab, 824) || !scores(i + 1)) { okay = false; break; }
+                }
+                if (!ptx::mbar_wait(&bars[kDeFull], i & 1, ab, 825)) { okay = false; break; }
+                ptx::tc_fence_after_sync();
+                const uint32_t k_base = ptx::smem_u32(k_ring + (i & 1) * kTile);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t db = ptx::smem_desc(k_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + kColDq, ptx::smem_desc(de_base + kk * 32, 16, 1024, ptx::kLayoutSw128), db, idesc_o, true);
+                    if (BF16)
+                        ptx::mma_ss(tmem + kColDq, ptx::smem_desc(dl_base + kk * 32, 16, 1024, ptx::kLayoutSw128), db, idesc_o, true);
+                }
+                ptx::mma_commit(&bars[kKEmpty + (i & 1)]);
+                if (exact) {
+                    ptx::mma_commit(&bars[kDeEmpty]);
+                } else {
+                    // dkc = ds^T Q, then dvc = (p / den)^T dO, each into the columns of S and dP (both read by now)
+                    for (int which = 0; which < 2 && okay; ++which) {
+                        const uint32_t a_base = which ? pe_base : de_base;
+                        const uint32_t b_base = which ? do_base : q_base;
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint64_t da = ptx::smem_desc(a_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                            const uint64_t db = ptx::smem_desc(b_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                            ptx::mma_ss(tmem + kColS, da, db, idesc_t, kk != 0);
+                        }
+                        ptx::mma_commit(&bars[kXFull]);
+                        if (which == 1) ptx::mma_commit(&bars[kDeEmpty]);
+                        okay = ptx::mbar_wait(&bars[kXEmpty], x_events & 1, ab, 826);
+                        ++x_events;
+                        ptx::tc_fence_after_sync();
+                    }
+                    if (okay && i + 1 < NI) okay = scores(i + 1);
+                }
+            }
+            if (okay) ptx::mma_commit(&bars[kDone]);
+        }
+    } else {
+        // ---------------- element-wise warps ----------------
+        const int ew = warp - 2;
+        const int quarter = warp & 3, half = ew >> 2;
+        const int c2 = (lane & 3) * 2;
+        const int row_a = quarter * 16 + (lane >> 2), row_b = row_a + 8;
+        const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const int t0 = qb * kBS;
+        const int nrows = min(kBS, p.T - t0);
+        const size_t base_row = (size_t)bh * p.T;
+        const float sm2 = p.scale * 1.44269504f;
+        const float w = p.scale / (float)p.T;
+        const int last_len = p.T - (p.nt - 1) * kBS;
+        float m_row[2], rD[2], dD[2], dg[2];
+        bool okay = ptx::mbar_wait(&bars[kLoad0], 0, ab, 830) && ptx::mbar_wait(&bars[kRFull], 0, ab, 831);
+        if (okay) {
+            ptx::tc_fence_after_sync();
+            // od = rowsum(O dO), nr = rowsum(dO r): this warp's half of the feature columns
+            float od[2] = {0.f, 0.f}, nr[2] = {0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < kHalf; c += 32) {
+                float r[16];
+                tmem_ld_16x256b_x4(t_lane + kColDq + half * kHalf + c, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int x = 0; x < 16; x += 2) {
+                    const int rr = (x >> 1) & 1;
+                    const int row = rr ? row_b : row_a;
+                    const int col = half * kHalf + c + (x >> 2) * 8 + c2;
+                    const float2 d2 = unpack2<BF16>(*pair_at(do_t, row, col));
+                    const float2 o2 = unpack2<BF16>(*pair_at(k_ring, row, col));
+                    od[rr] += d2.x * o2.x + d2.y * o2.y;
+                    nr[rr] += d2.x * r[x] + d2.y * r[x + 1];
+                }
+            }
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                od[rr] += __shfl_xor_sync(0xffffffffu, od[rr], 1);
+                od[rr] += __shfl_xor_sync(0xffffffffu, od[rr], 2);
+                nr[rr] += __shfl_xor_sync(0xffffffffu, nr[rr], 1);
+                nr[rr] += __shfl_xor_sync(0xffffffffu, nr[rr], 2);
+            }
+            if ((lane & 3) == 0) {
+                *reinterpret_cast<float2*>(xch + (half * 64 + row_a) * 2) = make_float2(od[0], nr[0]);
+                *reinterpret_cast<float2*>(xch + (half * 64 + row_b) * 2) = make_float2(od[1], nr[1]);
+            }
+        }
+        ptx::tc_fence_before_sync();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        float gw[2] = {0.f, 0.f};
+        if (okay) {
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = rr ? row_b : row_a;
+                const float2 a = *reinterpret_cast<const float2*>(xch + row * 2);
+                const float2 b = *reinterpret_cast<const float2*>(xch + (64 + row) * 2);
+                const float od = a.x + b.x, nr = a.y + b.y;
+                float g_row = 0.f;
+                m_row[rr] = 0.f;
+                rD[rr] = 0.f;
+                if (row < nrows) {
+                    const float4 st = *reinterpret_cast<const float4*>(row_stats + (base_row + t0 + row) * 4);
+                    m_row[rr] = st.x;
+                    rD[rr] = 1.f / st.y;
+                    g_row = st.z;
+                }
+                dD[rr] = -od * rD[rr];
+                dg[rr] = dD[rr] + nr * rD[rr] * w;
+                gw[rr] = g_row * w * rD[rr];
+                if (half == 0 && (lane & 3) == 0 && row < nrows) drow[base_row + t0 + row] = dD[rr];
+            }
+            // dr = dO g w / den: this warp's columns of the dr tile (it starts where the ds tiles will be)
+#pragma unroll
+            for (int c = 0; c < kHalf; c += 8) {
+                const int col = half * kHalf + c + c2;
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int row = rr ? row_b : row_a;
+                    const float2 d2 = unpack2<BF16>(*pair_at(do_t, row, col));
+                    *pair_at(de_t, row, col) = pack2<BF16>(d2.x * gw[rr], d2.y * gw[rr]);
+                }
+            }
+            ptx::fence_proxy_async_smem();
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&bars[kDrFull]);
+        if (threadIdx.x == 64 && okay) {
+            // the dr rows also go to global memory (the state pass forms dh = q^T dr from them)
+            if (ptx::mbar_wait(&bars[kDrFull], 0, ab, 832)) {
+                for (int cb = 0; cb < kNB; ++cb) ptx::tma_store_3d(&tm_dr, de_t + cb * kBlockBytes, cb * 64, t0, bh);
+                ptx::tma_store_commit();
+                ptx::tma_store_wait_read<0>();
+            }
+        }
+        // the ds tiles may be written once dQ = dr h^T has read the dr tile and the store above has, too
+        if (okay) okay = ptx::mbar_wait(&bars[kInitDone], 0, ab, 833);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+
+        int x_events = 0;
+        for (int i = 0; i < NI && okay; ++i) {
+            float s[16], dp[16];
+            if (!ptx::mbar_wait(&bars[kSFull], i & 1, ab, 834)) { okay = false; break; }
+            ptx::tc_fence_after_sync();
+            tmem_ld_16x256b_x4(t_lane + kColS + half * 32, s);
+            tmem_ld_16x256b_x4(t_lane + kColDp + half * 32, dp);
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&bars[kSEmpty]);
+            const bool approx = i >= p.ns;
+            int nvalid, jl = -1, c0 = 0;
+            unsigned long long keep = ~0ull;
+            if (!approx) {
+                const int cb = sel_idx[i];
+                nvalid = (cb < 0 || cb >= p.nt) ? 0 : min(kBS, p.T - cb * kBS);
+            } else {
+                c0 = (i - p.ns) * 64;
+                nvalid = min(64, p.nt - c0);
+                keep = ~sel_mask[i - p.ns];
+                if (last_len != kBS) jl = p.nt - 1 - c0;     // position of the shorter last block, if in this group
+            }
+            keep &= nvalid >= 64 ? ~0ull : ((1ull << nvalid) - 1ull);
+            const unsigned long long keep_t = keep >> (half * 32 + c2);      // bit 8 g + (x & 1): this thread's columns
+            const int jl_t = jl - half * 32 - c2;
+            uint32_t hi[8], lo[8], pe[8];
+#pragma unroll
+            for (int x = 0; x < 16; x += 2) {
+                const int rr = (x >> 1) & 1;
+                float de2[2], pe2[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int bit = (x >> 2) * 8 + u;
+                    const bool ok = (keep_t >> bit) & 1ull;
+                    const float pj = ok ? exp2f(fmaf(s[x + u], sm2, -m_row[rr])) : 0.f;
+                    float dpj;
+                    if (approx) {
+                        const float len = (bit == jl_t) ? (float)last_len : (float)kBS;
+                        dpj = fmaf(dp[x + u], rD[rr], dg[rr] * len);
+                    } else {
+                        dpj = fmaf(dp[x + u], rD[rr], dD[rr]);
+                    }
+                    de2[u] = pj * dpj * p.scale;
+                    pe2[u] = pj * rD[rr];
+                }
+                hi[x >> 1] = pack2<BF16>(de2[0], de2[1]);
+                if (BF16) {
+                    const float2 f = unpack2<BF16>(hi[x >> 1]);
+                    lo[x >> 1] = pack2<BF16>(de2[0] - f.x, de2[1] - f.y);
+                }
+                pe[x >> 1] = pack2<BF16>(pe2[0], pe2[1]);
+            }
+            if (i > 0 && !ptx::mbar_wait(&bars[kDeEmpty], (i - 1) & 1, ab, 835)) { okay = false; break; }
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                const int row = (x & 1) ? row_b : row_a;
+                const uint32_t off = row * 128 + ((((half * 4 + (x >> 1)) ^ row) & 7) << 4) + c2 * 2;
+                *reinterpret_cast<uint32_t*>(de_t + off) = hi[x];
+                if (BF16) *reinterpret_cast<uint32_t*>(dl_t + off) = lo[x];
+                if (approx) *reinterpret_cast<uint32_t*>(pe_t + off) = pe[x];
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&bars[kDeFull]);
+            if (approx) {
+                // dkc, then dvc, of the 64 blocks of this group: rows = blocks, this warp's half of the features
+                for (int which = 0; which < 2 && okay; ++which) {
+                    if (!ptx::mbar_wait(&bars[kXFull], x_events & 1, ab, 836)) { okay = false; break; }
+                    ++x_events;
+                    ptx::tc_fence_after_sync();
+                    float* outp = (which ? dvc : dkc) + ((size_t)bh * p.nt + c0) * D;
+#pragma unroll
+                    for (int c = 0; c < kHalf; c += 32) {
+                        float r[16];
+                        tmem_ld_16x256b_x4(t_lane + kColS + half * kHalf + c, r);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int x = 0; x < 16; x += 2) {
+                            const int blk = ((x >> 1) & 1) ? row_b : row_a;
+                            const int col = half * kHalf + c + (x >> 2) * 8 + c2;
+                            if (blk < nvalid) red_add2(outp + (size_t)blk * D + col, r[x], r[x + 1]);
+                        }
+                    }
+                    ptx::tc_fence_before_sync();
+                    ptx::mbar_arrive(&bars[kXEmpty]);
+                }
+            }
+        }
+        if (okay) okay = ptx::mbar_wait(&bars[kDone], 0, ab, 837);
+        if (okay) {
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < kHalf; c += 32) {
+                float r[16];
+                tmem_ld_16x256b_x4(t_lane + kColDq + half * kHalf + c, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int x = 0; x < 16; x += 2) {
+                    const int row = ((x >> 1) & 1) ? row_b : row_a;
+                    const int col = half * kHalf + c + (x >> 2) * 8 + c2;
+                    *pair_at(q_t, row, col) = pack2<BF16>(r[x], r[x + 1]);     // the query tile is free: every product is done
+                }
+            }
+            ptx::fence_proxy_async_smem();
+        }
+        ptx::tc_fence_before_sync();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (okay && threadIdx.x == 64) {
+            for (int cb = 0; cb < kNB; ++cb) ptx::tma_store_3d(&tm_dq, q_t + cb * kBlockBytes, cb * 64, t0, bh);
+            ptx::tma_store_commit();
+            ptx::tma_store_wait_read<0>();
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+}  // namespace pisa_tc_bwd
+
+cudaError_t pisa_tc_bwd_q(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,
+                          const void* v, const void* o, const void* d_o, const void* kc16, const void* vc16, const void* h16,
+                          const int32_t* indices, const float* row_stats, void* dq, void* dr, float* dkc, float* dvc,
+                          float* drow, cudaStream_t st) {
+    using namespace pisa_tc_bwd;
+    CUtensorMap mq, mdo, mo, mk, mv, mkc, mvc, mh, mdq, mdr;
+    cudaError_t e;
+    if ((e = tc_encode_map_rows(&mq, q, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mdo, d_o, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mo, o, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mk, k, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mv, v, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mkc, kc16, dtype, d, nt, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mvc, vc16, dtype, d, nt, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mh, h16, dtype, d, d, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mdq, dq, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mdr, dr, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    Params p{ns, nt, T, scale, tc_status_word()};
+    if (p.status == nullptr) return cudaErrorMemoryAllocation;
+    const dim3 grid(nt, bh);
+    const bool bf = dtype == FBLA_BF16;
+    auto run = [&](auto kern, size_t smem) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            kern<<<grid, kThreads, smem, st>>>(mq, mdo, mo, mk, mv, mkc, mvc, mh, mdq, mdr, p, indices, row_stats, dkc, dvc, drow);
+    };
+    if (d == 64) {
+        if (bf) run(pisa_bwd_q_tc_kernel<64, true>, smem_bytes<64>(nt, ns));
+        else run(pisa_bwd_q_tc_kernel<64, false>, smem_bytes<64>(nt, ns));
+    } else {
+        if (bf) run(pisa_bwd_q_tc_kernel<128, true>, smem_bytes<128>(nt, ns));
+        else run(pisa_bwd_q_tc_kernel<128, false>, smem_bytes<128>(nt, ns));
+    }
+    return e == cudaSuccess ? cudaGetLastError() : e;
+}
+
+}  // namespace fbla
