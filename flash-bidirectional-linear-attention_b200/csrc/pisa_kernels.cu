@@ -1116,7 +1116,14 @@ extern "C" int fbla_pisa_bwd(const fbla_pisa_problem* p, const void* q, const vo
         if (e != cudaSuccess) return fbla::api_fail(FBLA_ERR_CUDA, "backward query kernel: %s", cudaGetErrorString(e));
         // dh = q^T dr
         if (int rc = fbla_simple_la_fwd_state(&lay.state_problem, q, dr, dh, ws, (size_t)lay.ws_bytes, stream)) return rc;
-        if (kp.dk == 64) {
+        static const bool tc_kv_off = [] {
+            const char* v = getenv("FBLA_PISA_TC_KV");
+            return v != nullptr && v[0] == '0';
+        }();
+        if (!tc_off && !tc_kv_off && kp.scale > 0.f && fbla::pisa_tc_supported(a.dtype, kp.dk, kp.dv, kp.bs, kp.nt, kp.ns)) {
+            e = fbla::pisa_tc_bwd_kv(a.dtype, a.bh, kp.dk, kp.nt, kp.ns, kp.T, kp.scale, q, k, v, d_o, kc, vc, indices, row_stats,
+                                     drow, dkc, dvc, dh, dk, dv, st);
+        } else if (kp.dk == 64) {
             const size_t smem = fbla::pisa_mma::bwd_kv_smem_bytes<64>(kp.nt);
             if (bf) run_kv(fbla::pisa_mma::pisa_bwd_kv_mma_kernel<64, true>, smem);
             else run_kv(fbla::pisa_mma::pisa_bwd_kv_mma_kernel<64, false>, smem);

@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "pisa_tc_common.cuh"
 #include "tc_kernels.cuh"
 #include "tc_ptx.cuh"
 
@@ -36,7 +37,7 @@ constexpr int kBS = 64;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColO = 0;        // O: D columns
 constexpr uint32_t kColS = 128;      // S: two buffers of 64 columns; r = Q h reuses them at the end
-constexpr int kBlockBytes = 64 * 128;   // one [64 rows][64 x 16-bit] swizzled block
+using namespace pisa_tcx;
 
 struct Params {
     int ns, nt, T;
@@ -57,33 +58,6 @@ __device__ long long g_pisa_trace[128];
 #endif
 
 enum Bar { kQFull = 0, kKFull = 1, kKEmpty = 4, kVFull = 7, kVEmpty = 9, kSFull = 11, kSEmpty = 13, kPFull = 15, kPvDone = 16, kRFull = 17, kBars = 18 };
-
-// 16 TMEM lanes x 64 columns in the 16x256b shape (eight repetitions of eight columns): 32 registers per thread.
-__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr)
-                 : "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const float (&v)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-template <bool BF16>
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-    if constexpr (BF16) {
-        const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-        return *reinterpret_cast<const uint32_t*>(&t);
-    } else {
-        const __half2 t = __floats2half2_rn(a, b);
-        return *reinterpret_cast<const uint32_t*>(&t);
-    }
-}
 
 // Shared memory: [Q tile | 3 K tiles | 2 V tiles | P tile | barriers | bookkeeping]; tiles are
 // D/64 swizzled blocks of [64 rows][64 elements] and need a 1024-byte aligned base, which the kernel

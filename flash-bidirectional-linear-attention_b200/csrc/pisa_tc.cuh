@@ -25,4 +25,11 @@ cudaError_t pisa_tc_bwd_q(int dtype, int bh, int d, int nt, int ns, int T, float
                           const int32_t* indices, const float* row_stats, void* dq, void* dr, float* dkc, float* dvc,
                           float* drow, cudaStream_t st);
 
+// Key-side backward on tcgen05: dk, dv of every key block from the query blocks that selected it, plus the
+// statistics terms (dkc, dvc, dh read as fp32).
+cudaError_t pisa_tc_bwd_kv(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,
+                           const void* v, const void* d_o, const float* kc, const float* vc, const int32_t* indices,
+                           const float* row_stats, const float* drow, const float* dkc, const float* dvc, const float* dh,
+                           void* dk, void* dv, cudaStream_t st);
+
 }  // namespace fbla

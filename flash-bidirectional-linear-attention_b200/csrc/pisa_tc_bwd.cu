@@ -27,6 +27,7 @@
 #include <cuda_fp16.h>
 
 #include "pisa_tc.cuh"
+#include "pisa_tc_common.cuh"
 #include "tc_kernels.cuh"
 #include "tc_ptx.cuh"
 
@@ -40,7 +41,7 @@ constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColDq = 0;       // dQ accumulator: D columns (r = Q h before the loop)
 constexpr uint32_t kColS = 128;      // S: 64 columns; dkc / dvc use [128, 128 + D)
 constexpr uint32_t kColDp = 192;     // dP: 64 columns
-constexpr int kBlockBytes = 64 * 128;
+using namespace pisa_tcx;
 
 struct Params {
     int ns, nt, T;
@@ -52,45 +53,6 @@ enum Bar {
     kLoad0 = 0, kRFull, kDrFull, kInitDone, kKFull /*2*/, kKEmpty = kKFull + 2 /*2*/, kVFull = kKEmpty + 2, kVEmpty,
     kSFull, kSEmpty, kDeFull, kDeEmpty, kXFull, kXEmpty, kDone, kBars
 };
-
-__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-template <bool BF16>
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-    if constexpr (BF16) {
-        const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-        return *reinterpret_cast<const uint32_t*>(&t);
-    } else {
-        const __half2 t = __floats2half2_rn(a, b);
-        return *reinterpret_cast<const uint32_t*>(&t);
-    }
-}
-template <bool BF16>
-__device__ __forceinline__ float2 unpack2(uint32_t w) {
-    if constexpr (BF16) {
-        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-    } else {
-        return __half22float2(*reinterpret_cast<const __half2*>(&w));
-    }
-}
-__device__ __forceinline__ void red_add2(float* addr, float a, float b) {
-    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
-}
-// 32-bit pair (row, col), col even, of a [64][D] tile made of swizzled [64][64] blocks
-__device__ __forceinline__ uint32_t* pair_at(uint8_t* tile, int row, int col) {
-    return reinterpret_cast<uint32_t*>(tile + (col >> 6) * kBlockBytes + row * 128 + (((((col & 63) >> 3) ^ row) & 7) << 4) +
-                                       (col & 7) * 2);
-}
 
 template <int D>
 constexpr int tile_bytes() { return kBS * D * 2; }
@@ -552,6 +514,412 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 }
 
 }  // namespace pisa_tc_bwd
+
+// ------------------------------------------------------------------------------------------------
+// Key-side backward: one CTA per key block; it visits the query blocks that selected the block and
+// works transposed (keys are the M dimension), so that the weights feed dV += P^T dO and
+// dK += dS^T Q as K-major A operands:
+//     S^T = K Q^T,  dP^T = V dO^T    tcgen05.mma, M = N = 64, two TMEM buffers
+//     p / den, ds scale              16 element-wise warps (four per TMEM lane window, 16 columns each);
+//                                    the per-column constants (m, 1 / den, dD of a query row) are
+//                                    fetched from global memory while the scores are still in flight
+//     dV += (p / den)^T-tile dO,  dK += ds^T-tile Q     accumulators in TMEM (bf16: plus residual tiles)
+// and at the end the statistics terms dk += dkc / len + (v - vc / len) dh^T, dv += dvc + (k - kc) dh,
+// with k, v centred in place and dh converted to a 16-bit tile by the element-wise warps.
+namespace pisa_tc_kvside {
+
+constexpr int kEwThreads = 512;
+constexpr int kThreads = 64 + kEwThreads;
+constexpr int kBS = 64;
+constexpr int kQStages = 3;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColDk = 0, kColDv = 128, kColS = 256;    // S^T buffer b at kColS + 128 b, dP^T 64 columns after it
+using namespace pisa_tcx;
+using pisa_tc_bwd::Params;
+
+enum Bar { kKvFull = 0, kQFull = 1, kQEmpty = 4, kSFull = 7, kSEmpty = 9, kAFull = 11, kAEmpty = 13, kCentre = 15, kDone = 16, kBars = 17 };
+
+template <int D>
+constexpr int tile_bytes() { return kBS * D * 2; }
+// [K | V | 3 x (Q, dO) | 2 x (p/den, its residual, ds, its residual) | barriers | visit list]
+template <int D>
+size_t smem_bytes(int nt) {
+    return (size_t)(2 + 2 * kQStages) * tile_bytes<D>() + 8 * kBlockBytes + 256 + (size_t)4 * nt + (size_t)((nt + 15) & ~15);
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, const Params p,
+                      const int32_t* __restrict__ indices, const float* __restrict__ row_stats,
+                      const float* __restrict__ drow, const float* __restrict__ kc, const float* __restrict__ vc,
+                      const float* __restrict__ dkc, const float* __restrict__ dvc, const float* __restrict__ dh) {
+    constexpr int kNB = D / 64;
+    constexpr int kTile = tile_bytes<D>();
+    constexpr int kPart = D / 4;            // feature columns per warp of a lane window in the epilogue
+    extern __shared__ __align__(1024) uint8_t sm[];
+    uint8_t* k_t = sm;
+    uint8_t* v_t = k_t + kTile;
+    uint8_t* q_ring = v_t + kTile;                      // stage s: Q at + 2 s kTile, dO one tile after; at the end: dh
+    uint8_t* a_t = q_ring + 2 * kQStages * kTile;       // buffer b: + 4 b kBlockBytes: p/den, residual, ds, residual
+    uint64_t* bars = reinterpret_cast<uint64_t*>(a_t + 8 * kBlockBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* n_hit = reinterpret_cast<int*>(tmem_slot + 2);
+    int* hlist = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);
+    unsigned char* hit = reinterpret_cast<unsigned char*>(hlist + p.nt);
+
+    const int c_blk = blockIdx.x, bh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bos = c_blk * kBS;
+    const int nkeys = min(kBS, p.T - bos);
+    const size_t base_row = (size_t)bh * p.T;
+    if ((ptx::smem_u32(sm) & 1023u) != 0) {          // uniform over the CTA
+        if (threadIdx.x == 0) *p.status = 797;
+        return;
+    }
+    const ptx::Abort ab{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bars[kKvFull], 1);
+        for (int s = 0; s < kQStages; ++s) {
+            ptx::mbar_init(&bars[kQFull + s], 1);
+            ptx::mbar_init(&bars[kQEmpty + s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(&bars[kSFull + s], 1);
+            ptx::mbar_init(&bars[kSEmpty + s], kEwThreads);
+            ptx::mbar_init(&bars[kAFull + s], kEwThreads);
+            ptx::mbar_init(&bars[kAEmpty + s], 1);
+        }
+        ptx::mbar_init(&bars[kCentre], kEwThreads);
+        ptx::mbar_init(&bars[kDone], 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::mbar_arrive_expect_tx(&bars[kKvFull], 2 * kTile);
+        for (int cb = 0; cb < kNB; ++cb) {
+            ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_k, &bars[kKvFull], cb * 64, bos, bh);
+            ptx::tma_load_3d(v_t + cb * kBlockBytes, &tm_v, &bars[kKvFull], cb * 64, bos, bh);
+        }
+    }
+    // which query blocks selected this key block, in block order (the accumulation order is fixed)
+    for (int i = threadIdx.x; i < p.nt; i += kThreads) {
+        const int32_t* idx = indices + ((size_t)bh * p.nt + i) * p.ns;
+        bool any = false;
+        for (int n = 0; n < p.ns; ++n) any |= (idx[n] == c_blk);
+        hit[i] = any ? 1 : 0;
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int count = 0;
+        for (int base = 0; base < p.nt; base += 32) {
+            const int i = base + lane;
+            const bool bit = i < p.nt && hit[i] != 0;
+            const unsigned mask = __ballot_sync(0xffffffffu, bit);
+            if (bit) hlist[count + __popc(mask & ((1u << lane) - 1u))] = i;
+            count += __popc(mask);
+        }
+        if (lane == 0) *n_hit = count;
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const int nh = *n_hit;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer: (Q, dO) of the visiting query blocks ----------------
+            for (int j = 0; j < nh; ++j) {
+                const int s = j % kQStages;
+                if (!ptx::mbar_wait(&bars[kQEmpty + s], ((j / kQStages) & 1) ^ 1, ab, 851)) break;
+                ptx::mbar_arrive_expect_tx(&bars[kQFull + s], 2 * kTile);
+                const int t0 = hlist[j] * kBS;
+                for (int cb = 0; cb < kNB; ++cb) {
+                    ptx::tma_load_3d(q_ring + 2 * s * kTile + cb * kBlockBytes, &tm_q, &bars[kQFull + s], cb * 64, t0, bh);
+                    ptx::tma_load_3d(q_ring + (2 * s + 1) * kTile + cb * kBlockBytes, &tm_do, &bars[kQFull + s], cb * 64, t0, bh);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            const uint32_t idesc_nn = ptx::instr_desc(64, 64, BF16, false, false);
+            const uint32_t idesc_kk = ptx::instr_desc(64, D, BF16, false, false);
+            const uint32_t idesc_o = ptx::instr_desc(64, D, BF16, false, true);
+            const uint32_t k_base = ptx::smem_u32(k_t), v_base = ptx::smem_u32(v_t), ring_base = ptx::smem_u32(q_ring);
+            const uint32_t a_base = ptx::smem_u32(a_t);
+            auto scores = [&](int j) -> bool {
+                const int s = j % kQStages, b = j & 1;
+                if (!ptx::mbar_wait(&bars[kQFull + s], (j / kQStages) & 1, ab, 861)) return false;
+                if (!ptx::mbar_wait(&bars[kSEmpty + b], ((j >> 1) & 1) ^ 1, ab, 862)) return false;
+                ptx::tc_fence_after_sync();
+                const uint32_t qs = ring_base + 2 * s * kTile, ds = qs + kTile;
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t da = ptx::smem_desc(k_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(qs + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + kColS + b * 128, da, db, idesc_nn, !(kb == 0 && kk == 0));
+                    }
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t da = ptx::smem_desc(v_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(ds + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + kColS + b * 128 + 64, da, db, idesc_nn, !(kb == 0 && kk == 0));
+                    }
+                ptx::mma_commit(&bars[kSFull + b]);
+                return true;
+            };
+            bool okay = ptx::mbar_wait(&bars[kKvFull], 0, ab, 860);
+            if (okay && nh > 0) okay = scores(0);
+            for (int j = 0; j < nh && okay; ++j) {
+                const int s = j % kQStages, b = j & 1;
+                if (j + 1 < nh && !scores(j + 1)) { okay = false; break; }
+                if (!ptx::mbar_wait(&bars[kAFull + b], (j >> 1) & 1, ab, 863)) { okay = false; break; }
+                ptx::tc_fence_after_sync();
+                const uint32_t qs = ring_base + 2 * s * kTile, ds = qs + kTile;
+                const uint32_t pe_b = a_base + 4 * b * kBlockBytes;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t db = ptx::smem_desc(ds + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + kColDv, ptx::smem_desc(pe_b + kk * 32, 16, 1024, ptx::kLayoutSw128), db, idesc_o,
+                                !(j == 0 && kk == 0));
+                    if (BF16)
+                        ptx::mma_ss(tmem + kColDv, ptx::smem_desc(pe_b + kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128), db,
+                                    idesc_o, true);
+                }
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t db = ptx::smem_desc(qs + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
+                    ptx::mma_ss(tmem + kColDk, ptx::smem_desc(pe_b + 2 * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128), db,
+                                idesc_o, !(j == 0 && kk == 0));
+                    if (BF16)
+                        ptx::mma_ss(tmem + kColDk, ptx::smem_desc(pe_b + 3 * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128), db,
+                                    idesc_o, true);
+                }
+                ptx::mma_commit(&bars[kAEmpty + b]);
+                ptx::mma_commit(&bars[kQEmpty + s]);
+            }
+            if (okay) okay = ptx::mbar_wait(&bars[kCentre], 0, ab, 864);
+            if (okay) {
+                // statistics terms; dh lies in the first ring stage as 64-column blocks of [D rows][64]
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        // dk[key][d] += sum_vv v'[key][vv] dh[d][vv]: rows d of dh are the N dimension
+                        const uint64_t da = ptx::smem_desc(v_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(ring_base + kb * (D * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + kColDk, da, db, idesc_kk, nh > 0 || !(kb == 0 && kk == 0));
+                    }
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        // dv[key][vv] += sum_d k'[key][d] dh[d][vv]: rows d of dh are the K dimension
+                        const uint64_t da = ptx::smem_desc(k_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
+                        const uint64_t db = ptx::smem_desc(ring_base + (kb * 64 + kk * 16) * 128, D * 128, 1024, ptx::kLayoutSw128);
+                        ptx::mma_ss(tmem + kColDv, da, db, idesc_o, nh > 0 || !(kb == 0 && kk == 0));
+                    }
+                ptx::mma_commit(&bars[kDone]);
+            }
+        }
+    } else {
+        // ---------------- element-wise warps ----------------
+        const int ew = warp - 2, et = threadIdx.x - 64;
+        const int quarter = warp & 3, part = ew >> 2;
+        const int c2 = (lane & 3) * 2;
+        const int key_a = quarter * 16 + (lane >> 2), key_b = key_a + 8;
+        const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const float sm2 = p.scale * 1.44269504f;
+        bool okay = true;
+        for (int j = 0; j < nh; ++j) {
+            const int b = j & 1;
+            const int t0 = hlist[j] * kBS;
+            const int nrows = min(kBS, p.T - t0);
+            // constants of this thread's four query rows (columns part * 16 + 8 g + c2 + u)
+            float neg_m[2][2], rd[2][2], dd[2][2];
+#pragma unroll
+            for (int g = 0; g < 2; ++g)
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int r = part * 16 + g * 8 + c2 + u;
+                    neg_m[g][u] = 0.f; rd[g][u] = 0.f; dd[g][u] = 0.f;     // 1/den = 0 and dD = 0: a padded row contributes nothing
+                    if (r < nrows) {
+                        const float4 st = __ldg(reinterpret_cast<const float4*>(row_stats + (base_row + t0 + r) * 4));
+                        neg_m[g][u] = -st.x;
+                        rd[g][u] = st.w;
+                        dd[g][u] = __ldg(drow + base_row + t0 + r);
+                    }
+                }
+            float s[8], dp[8];
+            if (!ptx::mbar_wait(&bars[kSFull + b], (j >> 1) & 1, ab, 871)) { okay = false; break; }
+            ptx::tc_fence_after_sync();
+            tmem_ld_16x256b_x2(t_lane + kColS + b * 128 + part * 16, s);
+            tmem_ld_16x256b_x2(t_lane + kColS + b * 128 + 64 + part * 16, dp);
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&bars[kSEmpty + b]);
+            uint32_t pa[4], pl[4], da[4], dl[4];
+#pragma unroll
+            for (int x = 0; x < 8; x += 2) {
+                const int g = x >> 2;
+                float pe2[2], de2[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const float pj = exp2f(fmaf(s[x + u], sm2, neg_m[g][u]));
+                    pe2[u] = pj * rd[g][u];
+                    de2[u] = pj * fmaf(dp[x + u], rd[g][u], dd[g][u]) * p.scale;
+                }
+                pa[x >> 1] = pack2<BF16>(pe2[0], pe2[1]);
+                da[x >> 1] = pack2<BF16>(de2[0], de2[1]);
+                if (BF16) {
+                    const float2 f = unpack2<BF16>(pa[x >> 1]);
+                    pl[x >> 1] = pack2<BF16>(pe2[0] - f.x, pe2[1] - f.y);
+                    const float2 h2 = unpack2<BF16>(da[x >> 1]);
+                    dl[x >> 1] = pack2<BF16>(de2[0] - h2.x, de2[1] - h2.y);
+                }
+            }
+            if (!ptx::mbar_wait(&bars[kAEmpty + b], ((j >> 1) & 1) ^ 1, ab, 872)) { okay = false; break; }
+            uint8_t* ab_t = a_t + 4 * b * kBlockBytes;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int row = (x & 1) ? key_b : key_a;
+                const uint32_t off = row * 128 + ((((part * 2 + (x >> 1)) ^ row) & 7) << 4) + c2 * 2;
+                *reinterpret_cast<uint32_t*>(ab_t + off) = pa[x];
+                *reinterpret_cast<uint32_t*>(ab_t + 2 * kBlockBytes + off) = da[x];
+                if (BF16) {
+                    *reinterpret_cast<uint32_t*>(ab_t + kBlockBytes + off) = pl[x];
+                    *reinterpret_cast<uint32_t*>(ab_t + 3 * kBlockBytes + off) = dl[x];
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&bars[kAFull + b]);
+        }
+        // ---- statistics terms: centre k, v in place, dh as a 16-bit tile; all products of the loop must be done ----
+        if (okay) okay = ptx::mbar_wait(&bars[kKvFull], 0, ab, 873);
+        if (okay && nh > 0) okay = ptx::mbar_wait(&bars[kAEmpty + ((nh - 1) & 1)], ((nh - 1) >> 1) & 1, ab, 874);
+        const float inv_len = 1.f / (float)nkeys;
+        const float* kcb = kc + ((size_t)bh * p.nt + c_blk) * D;
+        const float* vcb = vc + ((size_t)bh * p.nt + c_blk) * D;
+        if (okay) {
+#pragma unroll
+            for (int c = 0; c < kPart; c += 8) {
+                const int col = part * kPart + c + c2;
+                const float2 kc2 = *reinterpret_cast<const float2*>(kcb + col);
+                const float2 vc2 = *reinterpret_cast<const float2*>(vcb + col);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int row = rr ? key_b : key_a;
+                    if (row < nkeys) {      // rows past the block's end stay zero: their results are dropped
+                        const float2 k2 = unpack2<BF16>(*pair_at(k_t, row, col));
+                        const float2 v2 = unpack2<BF16>(*pair_at(v_t, row, col));
+                        *pair_at(k_t, row, col) = pack2<BF16>(k2.x - kc2.x, k2.y - kc2.y);
+                        *pair_at(v_t, row, col) = pack2<BF16>(v2.x - vc2.x * inv_len, v2.y - vc2.y * inv_len);
+                    }
+                }
+            }
+            const float* dhb = dh + (size_t)bh * D * D;
+            for (int i = et; i < D * (D / 8); i += kEwThreads) {
+                const int d = i / (D / 8), vv0 = (i - d * (D / 8)) * 8;
+                const float4 a = *reinterpret_cast<const float4*>(dhb + (size_t)d * D + vv0);
+                const float4 c = *reinterpret_cast<const float4*>(dhb + (size_t)d * D + vv0 + 4);
+                *reinterpret_cast<uint4*>(q_ring + (vv0 >> 6) * (D * 128) + d * 128 + (((((vv0 & 63) >> 3) ^ d) & 7) << 4)) =
+                    make_uint4(pack2<BF16>(a.x, a.y), pack2<BF16>(a.z, a.w), pack2<BF16>(c.x, c.y), pack2<BF16>(c.z, c.w));
+            }
+            ptx::fence_proxy_async_smem();
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&bars[kCentre]);
+        if (okay) okay = ptx::mbar_wait(&bars[kDone], 0, ab, 875);
+        if (okay) {
+            ptx::tc_fence_after_sync();
+            const float* dkcb = dkc + ((size_t)bh * p.nt + c_blk) * D;
+            const float* dvcb = dvc + ((size_t)bh * p.nt + c_blk) * D;
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                uint8_t* tile = which ? v_t : k_t;          // the centred tiles are free: every product is done
+                const float* add = which ? dvcb : dkcb;
+                const float mul = which ? 1.f : inv_len;
+#pragma unroll
+                for (int c = 0; c < kPart; c += 16) {
+                    float r[8];
+                    tmem_ld_16x256b_x2(t_lane + (which ? kColDv : kColDk) + part * kPart + c, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int x = 0; x < 8; x += 2) {
+                        const int row = ((x >> 1) & 1) ? key_b : key_a;
+                        const int col = part * kPart + c + (x >> 2) * 8 + c2;
+                        const float2 a2 = *reinterpret_cast<const float2*>(add + col);
+                        *pair_at(tile, row, col) = pack2<BF16>(fmaf(a2.x, mul, r[x]), fmaf(a2.y, mul, r[x + 1]));
+                    }
+                }
+            }
+            ptx::fence_proxy_async_smem();
+        }
+        ptx::tc_fence_before_sync();
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        if (okay && threadIdx.x == 64) {
+            for (int cb = 0; cb < kNB; ++cb) {
+                ptx::tma_store_3d(&tm_dk, k_t + cb * kBlockBytes, cb * 64, bos, bh);
+                ptx::tma_store_3d(&tm_dv, v_t + cb * kBlockBytes, cb * 64, bos, bh);
+            }
+            ptx::tma_store_commit();
+            ptx::tma_store_wait_read<0>();
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+}  // namespace pisa_tc_kvside
+
+cudaError_t pisa_tc_bwd_kv(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,
+                           const void* v, const void* d_o, const float* kc, const float* vc, const int32_t* indices,
+                           const float* row_stats, const float* drow, const float* dkc, const float* dvc, const float* dh,
+                           void* dk, void* dv, cudaStream_t st) {
+    using namespace pisa_tc_kvside;
+    CUtensorMap mk, mv, mq, mdo, mdk, mdv;
+    cudaError_t e;
+    if ((e = tc_encode_map_rows(&mk, k, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mv, v, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mq, q, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mdo, d_o, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mdk, dk, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mdv, dv, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    Params p{ns, nt, T, scale, tc_status_word()};
+    if (p.status == nullptr) return cudaErrorMemoryAllocation;
+    const dim3 grid(nt, bh);
+    const bool bf = dtype == FBLA_BF16;
+    auto run = [&](auto kern, size_t smem) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            kern<<<grid, kThreads, smem, st>>>(mk, mv, mq, mdo, mdk, mdv, p, indices, row_stats, drow, kc, vc, dkc, dvc, dh);
+    };
+    if (d == 64) {
+        if (bf) run(pisa_bwd_kv_tc_kernel<64, true>, smem_bytes<64>(nt));
+        else run(pisa_bwd_kv_tc_kernel<64, false>, smem_bytes<64>(nt));
+    } else {
+        if (bf) run(pisa_bwd_kv_tc_kernel<128, true>, smem_bytes<128>(nt));
+        else run(pisa_bwd_kv_tc_kernel<128, false>, smem_bytes<128>(nt));
+    }
+    return e == cudaSuccess ? cudaGetLastError() : e;
+}
 
 cudaError_t pisa_tc_bwd_q(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,
                           const void* v, const void* o, const void* d_o, const void* kc16, const void* vc16, const void* h16,
