@@ -999,7 +999,7 @@ size_t round64(size_t n) { return (n + 63) / 64 * 64; }
 //   dkc [BH,NT,dk] | dvc [BH,NT,dv] | dh [BH,dk,dv] | drow [BH,T]
 //   tensor-core path only: | dr [BH,T,dv] 16-bit | workspace of the state pass that forms dh
 struct BwdScratch {
-    size_t dkc, dvc, dh, drow, dr, ws, c16, total;
+    size_t dkc, dvc, dh, drow, dr, ws, c16, dh16, total;
     int64_t ws_bytes;
     fbla_problem state_problem;
 };
@@ -1030,7 +1030,8 @@ BwdScratch bwd_scratch(const PisaArgs& a) {
         if (s.ws_bytes < 0) s.ws_bytes = 0;
         s.ws = s.dr + round64(((size_t)a.bh * kp.T * kp.dv + 1) / 2);
         s.c16 = s.ws + round64(((size_t)s.ws_bytes + 3) / 4);      // 16-bit copies of kc, vc, h for the tcgen05 kernel
-        s.total = s.c16 + round64(((size_t)pisa_tc_scratch_bytes(a.bh, kp.dk, kp.nt) + 3) / 4);
+        s.dh16 = s.c16 + round64(((size_t)pisa_tc_scratch_bytes(a.bh, kp.dk, kp.nt) + 3) / 4);   // dh as the key-side kernel reads it
+        s.total = s.dh16 + round64(((size_t)a.bh * kp.dk * kp.dv + 1) / 2);
     }
     return s;
 }
@@ -1120,9 +1121,11 @@ extern "C" int fbla_pisa_bwd(const fbla_pisa_problem* p, const void* q, const vo
             const char* v = getenv("FBLA_PISA_TC_KV");
             return v != nullptr && v[0] == '0';
         }();
-        if (!tc_off && !tc_kv_off && kp.scale > 0.f && fbla::pisa_tc_supported(a.dtype, kp.dk, kp.dv, kp.bs, kp.nt, kp.ns)) {
+        if (!tc_off && !tc_kv_off && kp.scale > 0.f && fbla::pisa_tc_supported(a.dtype, kp.dk, kp.dv, kp.bs, kp.nt, kp.ns) &&
+            fbla::pisa_tc_bwd_kv_fits(kp.dk, kp.nt)) {
             e = fbla::pisa_tc_bwd_kv(a.dtype, a.bh, kp.dk, kp.nt, kp.ns, kp.T, kp.scale, q, k, v, d_o, kc, vc, indices, row_stats,
-                                     drow, dkc, dvc, dh, dk, dv, st);
+                                     drow, dkc, dvc, dh, scratch + lay.dh16, dk, dv, st);
+            fbla::note_launches(1);
         } else if (kp.dk == 64) {
             const size_t smem = fbla::pisa_mma::bwd_kv_smem_bytes<64>(kp.nt);
             if (bf) run_kv(fbla::pisa_mma::pisa_bwd_kv_mma_kernel<64, true>, smem);

@@ -186,21 +186,22 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             // ---------------- MMA issuer ----------------
             const uint32_t idesc_s = ptx::instr_desc(64, 64, BF16, false, false);
             const uint32_t idesc_o = ptx::instr_desc(64, D, BF16, false, true);
-            const uint32_t q_base = ptx::smem_u32(q_t), p_base = ptx::smem_u32(p_t);
+            // descriptors of the first k-step of every operand tile; the rest are offsets from these
+            const uint64_t d_q = ptx::smem_desc(ptx::smem_u32(q_t), 16, 1024, ptx::kLayoutSw128);
+            const uint64_t d_p = ptx::smem_desc(ptx::smem_u32(p_t), 16, 1024, ptx::kLayoutSw128);
+            const uint64_t d_k0 = ptx::smem_desc(ptx::smem_u32(k_ring), 16, 1024, ptx::kLayoutSw128);              // K-major
+            const uint64_t d_kmn0 = ptx::smem_desc(ptx::smem_u32(k_ring), kBlockBytes, 1024, ptx::kLayoutSw128);    // MN-major (h)
+            const uint64_t d_v0 = ptx::smem_desc(ptx::smem_u32(v_ring), kBlockBytes, 1024, ptx::kLayoutSw128);
+            constexpr int kTileUnits = kTile / 16;
             auto scores = [&](int i) -> bool {
                 const int s = i & 1, ks = i % kKStages;
                 if (!ptx::mbar_wait(&bars[kKFull + ks], (i / kKStages) & 1, ab, 721)) return false;
                 if (!ptx::mbar_wait(&bars[kSEmpty + s], ((i >> 1) & 1) ^ 1, ab, 722)) return false;
                 ptx::tc_fence_after_sync();
-                const uint32_t k_base = ptx::smem_u32(k_ring + ks * kTile);
 #pragma unroll
                 for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(k_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColS + s * 64, da, db, idesc_s, !(kb == 0 && kk == 0));
-                    }
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepK>(tmem + kColS + s * 64, d_q + kb * ptx::kDescBlock,
+                                                                     d_k0 + ks * kTileUnits + kb * ptx::kDescBlock, idesc_s, kb != 0);
                 ptx::mma_commit(&bars[kSFull + s]);
                 ptx::mma_commit(&bars[kKEmpty + ks]);
                 return true;
@@ -215,13 +216,7 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 if (!ptx::mbar_wait(&bars[kPFull], i & 1, ab, 723)) { okay = false; break; }
                 PISA_STAMP(10 + i);
                 ptx::tc_fence_after_sync();
-                const uint32_t v_base = ptx::smem_u32(v_ring + b * kTile);
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t da = ptx::smem_desc(p_base + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                    const uint64_t db = ptx::smem_desc(v_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                    ptx::mma_ss(tmem + kColO, da, db, idesc_o, !(i == 0 && kk == 0));
-                }
+                ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColO, d_p, d_v0 + b * kTileUnits, idesc_o, i != 0);
                 ptx::mma_commit(&bars[kVEmpty + b]);
                 ptx::mma_commit(&bars[kPvDone]);
             }
@@ -232,15 +227,9 @@ pisa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 // weights were waited for above)
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int kb = 0; kb < kNB; ++kb) {
-                    const uint32_t h_base = ptx::smem_u32(k_ring + ((NI + kb) % kKStages) * kTile);
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(h_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColS, da, db, idesc_o, !(kb == 0 && kk == 0));
-                    }
-                }
+                for (int kb = 0; kb < kNB; ++kb)
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColS, d_q + kb * ptx::kDescBlock,
+                                                                      d_kmn0 + ((NI + kb) % kKStages) * kTileUnits, idesc_o, kb != 0);
                 ptx::mma_commit(&bars[kRFull]);
                 PISA_STAMP(91);
             }

@@ -26,10 +26,12 @@ cudaError_t pisa_tc_bwd_q(int dtype, int bh, int d, int nt, int ns, int T, float
                           float* drow, cudaStream_t st);
 
 // Key-side backward on tcgen05: dk, dv of every key block from the query blocks that selected it, plus the
-// statistics terms (dkc, dvc, dh read as fp32).
+// statistics terms.  dkc, dvc are overwritten (the per-block terms every key receives alike); dh16: 16-bit
+// scratch of bh * d * d elements.  Usable while pisa_tc_bwd_kv_fits() (shared memory grows with nt).
 cudaError_t pisa_tc_bwd_kv(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,
                            const void* v, const void* d_o, const float* kc, const float* vc, const int32_t* indices,
-                           const float* row_stats, const float* drow, const float* dkc, const float* dvc, const float* dh,
+                           const float* row_stats, const float* drow, float* dkc, float* dvc, const float* dh, void* dh16,
                            void* dk, void* dv, cudaStream_t st);
+bool pisa_tc_bwd_kv_fits(int d, int nt);
 
 }  // namespace fbla

@@ -32,6 +32,21 @@
 #include "tc_ptx.cuh"
 
 namespace fbla {
+
+// Development aid (compile with -DFBLA_PISA_TRACE): one CTA writes clock64() stamps of its phases.
+#ifdef FBLA_PISA_TRACE
+__device__ long long g_pisa_bwd_trace[128];
+#define PISA_BSTAMP(slot)                                                                     \
+    do {                                                                                      \
+        if (blockIdx.x == 36 && blockIdx.y == 20 && (slot) < 128) g_pisa_bwd_trace[(slot)] = clock64(); \
+    } while (0)
+extern "C" int fbla_debug_pisa_bwd_trace(long long* out128) {
+    return (int)cudaMemcpyFromSymbol(out128, g_pisa_bwd_trace, sizeof(long long) * 128);
+}
+#else
+#define PISA_BSTAMP(slot) do { } while (0)
+#endif
+
 namespace pisa_tc_bwd {
 
 constexpr int kThreads = 320;
@@ -99,6 +114,12 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         return;
     }
     const ptx::Abort ab{abort_flag, p.status};
+#ifdef FBLA_PISA_TRACE_Q
+#define PISA_QSTAMP(slot) PISA_BSTAMP(slot)
+#else
+#define PISA_QSTAMP(slot) do { } while (0)
+#endif
+    if (threadIdx.x == 0) PISA_QSTAMP(0);
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(&bars[kLoad0], 1);
@@ -187,23 +208,21 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const uint32_t idesc_nn = ptx::instr_desc(64, 64, BF16, false, false);     // both operands K-major
             const uint32_t idesc_o = ptx::instr_desc(64, D, BF16, false, true);        // B MN-major
             const uint32_t idesc_t = ptx::instr_desc(64, D, BF16, true, true);         // A and B MN-major
-            const uint32_t q_base = ptx::smem_u32(q_t), do_base = ptx::smem_u32(do_t), de_base = ptx::smem_u32(de_t);
-            const uint32_t dl_base = ptx::smem_u32(dl_t), pe_base = ptx::smem_u32(pe_t), v_base = ptx::smem_u32(v_t);
-            const uint32_t k1_base = ptx::smem_u32(k_ring + kTile);
+            // descriptors of the first k-step of every operand tile (K-major "k", MN-major "m"); the rest are offsets
+            constexpr int kTileUnits = kTile / 16;
+            auto dk_ = [](const void* t) { return ptx::smem_desc(ptx::smem_u32(t), 16, 1024, ptx::kLayoutSw128); };
+            auto dm_ = [](const void* t) { return ptx::smem_desc(ptx::smem_u32(t), kBlockBytes, 1024, ptx::kLayoutSw128); };
+            const uint64_t q_k = dk_(q_t), q_m = dm_(q_t), do_k = dk_(do_t), do_m = dm_(do_t);
+            const uint64_t de_k = dk_(de_t), de_m = dm_(de_t), dl_k = dk_(dl_t), pe_m = dm_(pe_t);
+            const uint64_t kr_k = dk_(k_ring), kr_m = dm_(k_ring), v_k = dk_(v_t), v_m = dm_(v_t);
             bool okay = ptx::mbar_wait(&bars[kLoad0], 0, ab, 820);
             if (okay) {
-                // r = Q h -> columns [0, D)
+                // r = Q h -> columns [0, D); rows 0-63 of h lie in the second key tile, rows 64-127 in the value tile
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int kb = 0; kb < kNB; ++kb) {
-                    const uint32_t h_base = kb == 0 ? k1_base : v_base;
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(h_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColDq, da, db, idesc_o, !(kb == 0 && kk == 0));
-                    }
-                }
+                for (int kb = 0; kb < kNB; ++kb)
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDq, q_k + kb * ptx::kDescBlock,
+                                                                      kb == 0 ? kr_m + kTileUnits : v_m, idesc_o, kb != 0);
                 ptx::mma_commit(&bars[kRFull]);
                 okay = ptx::mbar_wait(&bars[kDrFull], 0, ab, 821);
             }
@@ -211,17 +230,12 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 // dQ = dr h^T: dq[row][d] = sum_vv dr[row][vv] h[d][vv]; the rows d of h lie in two tiles
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int nb = 0; nb < kNB; ++nb) {
-                    const uint32_t h_base = nb == 0 ? k1_base : v_base;
+                for (int nb = 0; nb < kNB; ++nb)
 #pragma unroll
                     for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const uint64_t da = ptx::smem_desc(de_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                            const uint64_t db = ptx::smem_desc(h_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                            ptx::mma_ss(tmem + kColDq + nb * 64, da, db, idesc_nn, !(kb == 0 && kk == 0));
-                        }
-                }
+                        ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepK>(tmem + kColDq + nb * 64, de_k + kb * ptx::kDescBlock,
+                                                                         (nb == 0 ? kr_k + kTileUnits : v_k) + kb * ptx::kDescBlock,
+                                                                         idesc_nn, kb != 0);
                 ptx::mma_commit(&bars[kInitDone]);
             }
             auto scores = [&](int i) -> bool {       // S = Q K^T and dP = dO V^T of iteration i
@@ -229,23 +243,14 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 if (!ptx::mbar_wait(&bars[kKFull + s], (i >> 1) & 1, ab, 822)) return false;
                 if (!ptx::mbar_wait(&bars[kVFull], i & 1, ab, 823)) return false;
                 ptx::tc_fence_after_sync();
-                const uint32_t k_base = ptx::smem_u32(k_ring + s * kTile);
 #pragma unroll
                 for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t da = ptx::smem_desc(q_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(k_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColS, da, db, idesc_nn, !(kb == 0 && kk == 0));
-                    }
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepK>(tmem + kColS, q_k + kb * ptx::kDescBlock,
+                                                                     kr_k + s * kTileUnits + kb * ptx::kDescBlock, idesc_nn, kb != 0);
 #pragma unroll
                 for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t da = ptx::smem_desc(do_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(v_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColDp, da, db, idesc_nn, !(kb == 0 && kk == 0));
-                    }
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepK>(tmem + kColDp, do_k + kb * ptx::kDescBlock,
+                                                                     v_k + kb * ptx::kDescBlock, idesc_nn, kb != 0);
                 ptx::mma_commit(&bars[kSFull]);
                 ptx::mma_commit(&bars[kVEmpty]);
                 return true;
@@ -260,29 +265,19 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (!ptx::mbar_wait(&bars[kSEmpty], i & 1, ab, 824) || !scores(i + 1)) { okay = false; break; }
                 }
                 if (!ptx::mbar_wait(&bars[kDeFull], i & 1, ab, 825)) { okay = false; break; }
+                PISA_QSTAMP(10 + i);
                 ptx::tc_fence_after_sync();
-                const uint32_t k_base = ptx::smem_u32(k_ring + (i & 1) * kTile);
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t db = ptx::smem_desc(k_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                    ptx::mma_ss(tmem + kColDq, ptx::smem_desc(de_base + kk * 32, 16, 1024, ptx::kLayoutSw128), db, idesc_o, true);
-                    if (BF16)
-                        ptx::mma_ss(tmem + kColDq, ptx::smem_desc(dl_base + kk * 32, 16, 1024, ptx::kLayoutSw128), db, idesc_o, true);
-                }
+                ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDq, de_k, kr_m + (i & 1) * kTileUnits, idesc_o, true);
+                if (BF16)
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDq, dl_k, kr_m + (i & 1) * kTileUnits, idesc_o, true);
                 ptx::mma_commit(&bars[kKEmpty + (i & 1)]);
                 if (exact) {
                     ptx::mma_commit(&bars[kDeEmpty]);
                 } else {
                     // dkc = ds^T Q, then dvc = (p / den)^T dO, each into the columns of S and dP (both read by now)
                     for (int which = 0; which < 2 && okay; ++which) {
-                        const uint32_t a_base = which ? pe_base : de_base;
-                        const uint32_t b_base = which ? do_base : q_base;
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const uint64_t da = ptx::smem_desc(a_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                            const uint64_t db = ptx::smem_desc(b_base + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                            ptx::mma_ss(tmem + kColS, da, db, idesc_t, kk != 0);
-                        }
+                        ptx::mma_ss_k4<ptx::kDescStepMN, ptx::kDescStepMN>(tmem + kColS, which ? pe_m : de_m, which ? do_m : q_m, idesc_t,
+                                                                           false);
                         ptx::mma_commit(&bars[kXFull]);
                         if (which == 1) ptx::mma_commit(&bars[kDeEmpty]);
                         okay = ptx::mbar_wait(&bars[kXEmpty], x_events & 1, ab, 826);
@@ -309,6 +304,7 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int last_len = p.T - (p.nt - 1) * kBS;
         float m_row[2], rD[2], dD[2], dg[2];
         bool okay = ptx::mbar_wait(&bars[kLoad0], 0, ab, 830) && ptx::mbar_wait(&bars[kRFull], 0, ab, 831);
+        if (threadIdx.x == 64) PISA_QSTAMP(1);
         if (okay) {
             ptx::tc_fence_after_sync();
             // od = rowsum(O dO), nr = rowsum(dO r): this warp's half of the feature columns
@@ -391,11 +387,13 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // the ds tiles may be written once dQ = dr h^T has read the dr tile and the store above has, too
         if (okay) okay = ptx::mbar_wait(&bars[kInitDone], 0, ab, 833);
         asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (threadIdx.x == 64) PISA_QSTAMP(3);
 
         int x_events = 0;
         for (int i = 0; i < NI && okay; ++i) {
             float s[16], dp[16];
             if (!ptx::mbar_wait(&bars[kSFull], i & 1, ab, 834)) { okay = false; break; }
+            if (threadIdx.x == 64) PISA_QSTAMP(30 + i);
             ptx::tc_fence_after_sync();
             tmem_ld_16x256b_x4(t_lane + kColS + half * 32, s);
             tmem_ld_16x256b_x4(t_lane + kColDp + half * 32, dp);
@@ -444,6 +442,7 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
                 pe[x >> 1] = pack2<BF16>(pe2[0], pe2[1]);
             }
+            if (threadIdx.x == 64) PISA_QSTAMP(50 + i);
             if (i > 0 && !ptx::mbar_wait(&bars[kDeEmpty], (i - 1) & 1, ab, 835)) { okay = false; break; }
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
@@ -456,6 +455,7 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&bars[kDeFull]);
+            if (threadIdx.x == 64) PISA_QSTAMP(70 + i);
             if (approx) {
                 // dkc, then dvc, of the 64 blocks of this group: rows = blocks, this warp's half of the features
                 for (int which = 0; which < 2 && okay; ++which) {
@@ -481,6 +481,7 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
         }
         if (okay) okay = ptx::mbar_wait(&bars[kDone], 0, ab, 837);
+        if (threadIdx.x == 64) PISA_QSTAMP(92);
         if (okay) {
             ptx::tc_fence_after_sync();
 #pragma unroll
@@ -503,6 +504,7 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int cb = 0; cb < kNB; ++cb) ptx::tma_store_3d(&tm_dq, q_t + cb * kBlockBytes, cb * 64, t0, bh);
             ptx::tma_store_commit();
             ptx::tma_store_wait_read<0>();
+            PISA_QSTAMP(94);
         }
     }
     ptx::tc_fence_before_sync();
@@ -524,8 +526,11 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 //                                    the per-column constants (m, 1 / den, dD of a query row) are
 //                                    fetched from global memory while the scores are still in flight
 //     dV += (p / den)^T-tile dO,  dK += ds^T-tile Q     accumulators in TMEM (bf16: plus residual tiles)
-// and at the end the statistics terms dk += dkc / len + (v - vc / len) dh^T, dv += dvc + (k - kc) dh,
-// with k, v centred in place and dh converted to a 16-bit tile by the element-wise warps.
+// The statistics terms dk += dkc / len + (v - vc / len) dh^T, dv += dvc + (k - kc) dh are split: the
+// products with the uncentred tiles, dK = V dh^T and dV = K dh, are the first thing the tensor cores do
+// (they initialise the accumulators), and what is the same for every key of a block,
+// dkc / len - (vc / len) dh^T and dvc - kc dh, is formed per block by pisa_stats_terms_kernel beforehand
+// (with the same 16-bit rounding of dh, so that the two halves cancel as they would in the centred form).
 namespace pisa_tc_kvside {
 
 constexpr int kEwThreads = 512;
@@ -537,32 +542,34 @@ constexpr uint32_t kColDk = 0, kColDv = 128, kColS = 256;    // S^T buffer b at 
 using namespace pisa_tcx;
 using pisa_tc_bwd::Params;
 
-enum Bar { kKvFull = 0, kQFull = 1, kQEmpty = 4, kSFull = 7, kSEmpty = 9, kAFull = 11, kAEmpty = 13, kCentre = 15, kDone = 16, kBars = 17 };
+enum Bar { kKvFull = 0, kQFull = 1, kQEmpty = 4, kSFull = 7, kSEmpty = 9, kAFull = 11, kAEmpty = 13, kDhFull = 15, kDone = 16, kBars = 17 };
 
 template <int D>
 constexpr int tile_bytes() { return kBS * D * 2; }
-// [K | V | 3 x (Q, dO) | 2 x (p/den, its residual, ds, its residual) | barriers | visit list]
+// [K | V | 3 x (Q, dO) | dh | 2 x (p/den, its residual, ds, its residual) | barriers | visit list]
 template <int D>
 size_t smem_bytes(int nt) {
-    return (size_t)(2 + 2 * kQStages) * tile_bytes<D>() + 8 * kBlockBytes + 256 + (size_t)4 * nt + (size_t)((nt + 15) & ~15);
+    return (size_t)(2 + 2 * kQStages) * tile_bytes<D>() + (size_t)D * D * 2 + 8 * kBlockBytes + 256 + (size_t)4 * nt +
+           (size_t)((nt + 15) & ~15);
 }
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, const Params p,
-                      const int32_t* __restrict__ indices, const float* __restrict__ row_stats,
-                      const float* __restrict__ drow, const float* __restrict__ kc, const float* __restrict__ vc,
-                      const float* __restrict__ dkc, const float* __restrict__ dvc, const float* __restrict__ dh) {
+                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                      const __grid_constant__ CUtensorMap tm_dh, const Params p, const int32_t* __restrict__ indices,
+                      const float* __restrict__ row_stats, const float* __restrict__ drow, const float* __restrict__ dkc,
+                      const float* __restrict__ dvc) {
     constexpr int kNB = D / 64;
     constexpr int kTile = tile_bytes<D>();
     constexpr int kPart = D / 4;            // feature columns per warp of a lane window in the epilogue
     extern __shared__ __align__(1024) uint8_t sm[];
     uint8_t* k_t = sm;
     uint8_t* v_t = k_t + kTile;
-    uint8_t* q_ring = v_t + kTile;                      // stage s: Q at + 2 s kTile, dO one tile after; at the end: dh
-    uint8_t* a_t = q_ring + 2 * kQStages * kTile;       // buffer b: + 4 b kBlockBytes: p/den, residual, ds, residual
+    uint8_t* q_ring = v_t + kTile;                      // stage s: Q at + 2 s kTile, dO one tile after
+    uint8_t* dh_t = q_ring + 2 * kQStages * kTile;      // dh as 64-column blocks of [D rows][64]
+    uint8_t* a_t = dh_t + D * D * 2;                    // buffer b: + 4 b kBlockBytes: p/den, residual, ds, residual
     uint64_t* bars = reinterpret_cast<uint64_t*>(a_t + 8 * kBlockBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -593,7 +600,7 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             ptx::mbar_init(&bars[kAFull + s], kEwThreads);
             ptx::mbar_init(&bars[kAEmpty + s], 1);
         }
-        ptx::mbar_init(&bars[kCentre], kEwThreads);
+        ptx::mbar_init(&bars[kDhFull], 1);
         ptx::mbar_init(&bars[kDone], 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -602,7 +609,12 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             ptx::tma_load_3d(k_t + cb * kBlockBytes, &tm_k, &bars[kKvFull], cb * 64, bos, bh);
             ptx::tma_load_3d(v_t + cb * kBlockBytes, &tm_v, &bars[kKvFull], cb * 64, bos, bh);
         }
+        ptx::mbar_arrive_expect_tx(&bars[kDhFull], D * D * 2);
+        for (int vb = 0; vb < kNB; ++vb)
+            for (int db = 0; db < kNB; ++db)
+                ptx::tma_load_3d(dh_t + vb * (D * 128) + db * kBlockBytes, &tm_dh, &bars[kDhFull], vb * 64, db * 64, bh);
     }
+    if (threadIdx.x == 0) PISA_BSTAMP(0);
     // which query blocks selected this key block, in block order (the accumulation order is fixed)
     for (int i = threadIdx.x; i < p.nt; i += kThreads) {
         const int32_t* idx = indices + ((size_t)bh * p.nt + i) * p.ns;
@@ -631,6 +643,7 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     ptx::tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     const int nh = *n_hit;
+    if (threadIdx.x == 0) PISA_BSTAMP(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -652,91 +665,65 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             const uint32_t idesc_nn = ptx::instr_desc(64, 64, BF16, false, false);
             const uint32_t idesc_kk = ptx::instr_desc(64, D, BF16, false, false);
             const uint32_t idesc_o = ptx::instr_desc(64, D, BF16, false, true);
-            const uint32_t k_base = ptx::smem_u32(k_t), v_base = ptx::smem_u32(v_t), ring_base = ptx::smem_u32(q_ring);
-            const uint32_t a_base = ptx::smem_u32(a_t);
+            constexpr int kTileUnits = kTile / 16;
+            auto dk_ = [](const void* t) { return ptx::smem_desc(ptx::smem_u32(t), 16, 1024, ptx::kLayoutSw128); };
+            auto dm_ = [](const void* t) { return ptx::smem_desc(ptx::smem_u32(t), kBlockBytes, 1024, ptx::kLayoutSw128); };
+            const uint64_t k_k = dk_(k_t), v_k = dk_(v_t), ring_k = dk_(q_ring), ring_m = dm_(q_ring), a_k = dk_(a_t);
+            const uint64_t dh_k = dk_(dh_t);
+            const uint64_t dh_m = ptx::smem_desc(ptx::smem_u32(dh_t), D * 128, 1024, ptx::kLayoutSw128);
             auto scores = [&](int j) -> bool {
                 const int s = j % kQStages, b = j & 1;
                 if (!ptx::mbar_wait(&bars[kQFull + s], (j / kQStages) & 1, ab, 861)) return false;
                 if (!ptx::mbar_wait(&bars[kSEmpty + b], ((j >> 1) & 1) ^ 1, ab, 862)) return false;
                 ptx::tc_fence_after_sync();
-                const uint32_t qs = ring_base + 2 * s * kTile, ds = qs + kTile;
 #pragma unroll
                 for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t da = ptx::smem_desc(k_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(qs + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColS + b * 128, da, db, idesc_nn, !(kb == 0 && kk == 0));
-                    }
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepK>(tmem + kColS + b * 128, k_k + kb * ptx::kDescBlock,
+                                                                     ring_k + 2 * s * kTileUnits + kb * ptx::kDescBlock, idesc_nn,
+                                                                     kb != 0);
 #pragma unroll
                 for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t da = ptx::smem_desc(v_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(ds + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColS + b * 128 + 64, da, db, idesc_nn, !(kb == 0 && kk == 0));
-                    }
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepK>(tmem + kColS + b * 128 + 64, v_k + kb * ptx::kDescBlock,
+                                                                     ring_k + (2 * s + 1) * kTileUnits + kb * ptx::kDescBlock, idesc_nn,
+                                                                     kb != 0);
                 ptx::mma_commit(&bars[kSFull + b]);
                 return true;
             };
-            bool okay = ptx::mbar_wait(&bars[kKvFull], 0, ab, 860);
+            bool okay = ptx::mbar_wait(&bars[kKvFull], 0, ab, 860) && ptx::mbar_wait(&bars[kDhFull], 0, ab, 864);
+            if (okay) {
+                ptx::tc_fence_after_sync();
+                // dk[key][d] = sum_vv v[key][vv] dh[d][vv]: rows d of dh are the N dimension (blocks of 64 vv)
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepK>(tmem + kColDk, v_k + kb * ptx::kDescBlock, dh_k + kb * (D * 128 / 16),
+                                                                     idesc_kk, kb != 0);
+                // dv[key][vv] = sum_d k[key][d] dh[d][vv]: rows d of dh are the K dimension
+#pragma unroll
+                for (int kb = 0; kb < kNB; ++kb)
+                    ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDv, k_k + kb * ptx::kDescBlock, dh_m + kb * ptx::kDescBlock,
+                                                                      idesc_o, kb != 0);
+            }
             if (okay && nh > 0) okay = scores(0);
             for (int j = 0; j < nh && okay; ++j) {
                 const int s = j % kQStages, b = j & 1;
                 if (j + 1 < nh && !scores(j + 1)) { okay = false; break; }
                 if (!ptx::mbar_wait(&bars[kAFull + b], (j >> 1) & 1, ab, 863)) { okay = false; break; }
+                PISA_BSTAMP(10 + j);
                 ptx::tc_fence_after_sync();
-                const uint32_t qs = ring_base + 2 * s * kTile, ds = qs + kTile;
-                const uint32_t pe_b = a_base + 4 * b * kBlockBytes;
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t db = ptx::smem_desc(ds + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                    ptx::mma_ss(tmem + kColDv, ptx::smem_desc(pe_b + kk * 32, 16, 1024, ptx::kLayoutSw128), db, idesc_o,
-                                !(j == 0 && kk == 0));
-                    if (BF16)
-                        ptx::mma_ss(tmem + kColDv, ptx::smem_desc(pe_b + kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128), db,
-                                    idesc_o, true);
-                }
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t db = ptx::smem_desc(qs + kk * 2048, kBlockBytes, 1024, ptx::kLayoutSw128);
-                    ptx::mma_ss(tmem + kColDk, ptx::smem_desc(pe_b + 2 * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128), db,
-                                idesc_o, !(j == 0 && kk == 0));
-                    if (BF16)
-                        ptx::mma_ss(tmem + kColDk, ptx::smem_desc(pe_b + 3 * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128), db,
-                                    idesc_o, true);
-                }
+                const uint64_t q_m = ring_m + 2 * s * kTileUnits, do_m = q_m + kTileUnits;
+                const uint64_t pe_k = a_k + 4 * b * ptx::kDescBlock;
+                ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDv, pe_k, do_m, idesc_o, true);
+                if (BF16) ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDv, pe_k + ptx::kDescBlock, do_m, idesc_o, true);
+                ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDk, pe_k + 2 * ptx::kDescBlock, q_m, idesc_o, true);
+                if (BF16) ptx::mma_ss_k4<ptx::kDescStepK, ptx::kDescStepMN>(tmem + kColDk, pe_k + 3 * ptx::kDescBlock, q_m, idesc_o, true);
                 ptx::mma_commit(&bars[kAEmpty + b]);
                 ptx::mma_commit(&bars[kQEmpty + s]);
             }
-            if (okay) okay = ptx::mbar_wait(&bars[kCentre], 0, ab, 864);
-            if (okay) {
-                // statistics terms; dh lies in the first ring stage as 64-column blocks of [D rows][64]
-                ptx::tc_fence_after_sync();
-#pragma unroll
-                for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        // dk[key][d] += sum_vv v'[key][vv] dh[d][vv]: rows d of dh are the N dimension
-                        const uint64_t da = ptx::smem_desc(v_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(ring_base + kb * (D * 128) + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColDk, da, db, idesc_kk, nh > 0 || !(kb == 0 && kk == 0));
-                    }
-#pragma unroll
-                for (int kb = 0; kb < kNB; ++kb)
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        // dv[key][vv] += sum_d k'[key][d] dh[d][vv]: rows d of dh are the K dimension
-                        const uint64_t da = ptx::smem_desc(k_base + kb * kBlockBytes + kk * 32, 16, 1024, ptx::kLayoutSw128);
-                        const uint64_t db = ptx::smem_desc(ring_base + (kb * 64 + kk * 16) * 128, D * 128, 1024, ptx::kLayoutSw128);
-                        ptx::mma_ss(tmem + kColDv, da, db, idesc_o, nh > 0 || !(kb == 0 && kk == 0));
-                    }
-                ptx::mma_commit(&bars[kDone]);
-            }
+            if (okay) ptx::mma_commit(&bars[kDone]);
         }
     } else {
         // ---------------- element-wise warps ----------------
-        const int ew = warp - 2, et = threadIdx.x - 64;
+        const int ew = warp - 2;
         const int quarter = warp & 3, part = ew >> 2;
         const int c2 = (lane & 3) * 2;
         const int key_a = quarter * 16 + (lane >> 2), key_b = key_a + 8;
@@ -763,7 +750,9 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                     }
                 }
             float s[8], dp[8];
+            if (threadIdx.x == 64) PISA_BSTAMP(100 + j);
             if (!ptx::mbar_wait(&bars[kSFull + b], (j >> 1) & 1, ab, 871)) { okay = false; break; }
+            if (threadIdx.x == 64) PISA_BSTAMP(30 + j);
             ptx::tc_fence_after_sync();
             tmem_ld_16x256b_x2(t_lane + kColS + b * 128 + part * 16, s);
             tmem_ld_16x256b_x2(t_lane + kColS + b * 128 + 64 + part * 16, dp);
@@ -790,6 +779,7 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                     dl[x >> 1] = pack2<BF16>(de2[0] - h2.x, de2[1] - h2.y);
                 }
             }
+            if (threadIdx.x == 64) PISA_BSTAMP(50 + j);
             if (!ptx::mbar_wait(&bars[kAEmpty + b], ((j >> 1) & 1) ^ 1, ab, 872)) { okay = false; break; }
             uint8_t* ab_t = a_t + 4 * b * kBlockBytes;
 #pragma unroll
@@ -806,52 +796,20 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&bars[kAFull + b]);
+            if (threadIdx.x == 64) PISA_BSTAMP(70 + j);
         }
-        // ---- statistics terms: centre k, v in place, dh as a 16-bit tile; all products of the loop must be done ----
-        if (okay) okay = ptx::mbar_wait(&bars[kKvFull], 0, ab, 873);
-        if (okay && nh > 0) okay = ptx::mbar_wait(&bars[kAEmpty + ((nh - 1) & 1)], ((nh - 1) >> 1) & 1, ab, 874);
-        const float inv_len = 1.f / (float)nkeys;
-        const float* kcb = kc + ((size_t)bh * p.nt + c_blk) * D;
-        const float* vcb = vc + ((size_t)bh * p.nt + c_blk) * D;
-        if (okay) {
-#pragma unroll
-            for (int c = 0; c < kPart; c += 8) {
-                const int col = part * kPart + c + c2;
-                const float2 kc2 = *reinterpret_cast<const float2*>(kcb + col);
-                const float2 vc2 = *reinterpret_cast<const float2*>(vcb + col);
-#pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {
-                    const int row = rr ? key_b : key_a;
-                    if (row < nkeys) {      // rows past the block's end stay zero: their results are dropped
-                        const float2 k2 = unpack2<BF16>(*pair_at(k_t, row, col));
-                        const float2 v2 = unpack2<BF16>(*pair_at(v_t, row, col));
-                        *pair_at(k_t, row, col) = pack2<BF16>(k2.x - kc2.x, k2.y - kc2.y);
-                        *pair_at(v_t, row, col) = pack2<BF16>(v2.x - vc2.x * inv_len, v2.y - vc2.y * inv_len);
-                    }
-                }
-            }
-            const float* dhb = dh + (size_t)bh * D * D;
-            for (int i = et; i < D * (D / 8); i += kEwThreads) {
-                const int d = i / (D / 8), vv0 = (i - d * (D / 8)) * 8;
-                const float4 a = *reinterpret_cast<const float4*>(dhb + (size_t)d * D + vv0);
-                const float4 c = *reinterpret_cast<const float4*>(dhb + (size_t)d * D + vv0 + 4);
-                *reinterpret_cast<uint4*>(q_ring + (vv0 >> 6) * (D * 128) + d * 128 + (((((vv0 & 63) >> 3) ^ d) & 7) << 4)) =
-                    make_uint4(pack2<BF16>(a.x, a.y), pack2<BF16>(a.z, a.w), pack2<BF16>(c.x, c.y), pack2<BF16>(c.z, c.w));
-            }
-            ptx::fence_proxy_async_smem();
-        }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(&bars[kCentre]);
+        if (threadIdx.x == 64) PISA_BSTAMP(90);
         if (okay) okay = ptx::mbar_wait(&bars[kDone], 0, ab, 875);
+        if (threadIdx.x == 64) PISA_BSTAMP(92);
         if (okay) {
             ptx::tc_fence_after_sync();
+            // what every key of the block receives alike (pisa_stats_terms_kernel left it in dkc, dvc)
             const float* dkcb = dkc + ((size_t)bh * p.nt + c_blk) * D;
             const float* dvcb = dvc + ((size_t)bh * p.nt + c_blk) * D;
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
-                uint8_t* tile = which ? v_t : k_t;          // the centred tiles are free: every product is done
+                uint8_t* tile = which ? v_t : k_t;          // the key and value tiles are free: every product is done
                 const float* add = which ? dvcb : dkcb;
-                const float mul = which ? 1.f : inv_len;
 #pragma unroll
                 for (int c = 0; c < kPart; c += 16) {
                     float r[8];
@@ -862,12 +820,13 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                         const int row = ((x >> 1) & 1) ? key_b : key_a;
                         const int col = part * kPart + c + (x >> 2) * 8 + c2;
                         const float2 a2 = *reinterpret_cast<const float2*>(add + col);
-                        *pair_at(tile, row, col) = pack2<BF16>(fmaf(a2.x, mul, r[x]), fmaf(a2.y, mul, r[x + 1]));
+                        *pair_at(tile, row, col) = pack2<BF16>(a2.x + r[x], a2.y + r[x + 1]);
                     }
                 }
             }
             ptx::fence_proxy_async_smem();
         }
+        if (threadIdx.x == 64) PISA_BSTAMP(93);
         ptx::tc_fence_before_sync();
         asm volatile("bar.sync 1, 512;" ::: "memory");
         if (okay && threadIdx.x == 64) {
@@ -877,6 +836,7 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             }
             ptx::tma_store_commit();
             ptx::tma_store_wait_read<0>();
+            PISA_BSTAMP(94);
         }
     }
     ptx::tc_fence_before_sync();
@@ -885,16 +845,73 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, kTmemCols);
     }
+    if (threadIdx.x == 0) PISA_BSTAMP(2);
+}
+
+// dkc <- dkc / len - (vc / len) dh^T and dvc <- dvc - kc dh per key block (in place), with dh rounded to the
+// 16-bit type as the tensor-core products see it; the CTAs of the first block group also write that copy out.
+// Eight key blocks per CTA, one thread per feature.
+constexpr int kTermBlocks = 8;
+template <bool BF16>
+__global__ void __launch_bounds__(128)
+pisa_stats_terms_kernel(int D, int nt, int T, const float* __restrict__ kc, const float* __restrict__ vc,
+                        const float* __restrict__ dh, float* __restrict__ dkc, float* __restrict__ dvc,
+                        uint32_t* __restrict__ dh16) {
+    __shared__ uint16_t dhs[128 * 130];         // rows padded by two elements: a column walk touches every bank
+    __shared__ float kcs[128], vcs[128];
+    const int bh = blockIdx.y, t = threadIdx.x;
+    const int stride = D + 2;
+    const float* dhb = dh + (size_t)bh * D * D;
+    for (int i = t; i < D * D / 2; i += 128) {
+        const float2 f = *reinterpret_cast<const float2*>(dhb + 2 * i);
+        const uint32_t w = pack2<BF16>(f.x, f.y);
+        const int d = (2 * i) / D, vv = 2 * i - d * D;
+        *reinterpret_cast<uint32_t*>(&dhs[d * stride + vv]) = w;
+        if (blockIdx.x == 0) dh16[(size_t)bh * D * D / 2 + i] = w;
+    }
+    for (int cc = 0; cc < kTermBlocks; ++cc) {
+        const int c = blockIdx.x * kTermBlocks + cc;
+        if (c >= nt) break;                     // uniform over the CTA
+        const float inv_len = 1.f / (float)min(kBS, T - c * kBS);
+        const size_t row = ((size_t)bh * nt + c) * D;
+        __syncthreads();
+        if (t < D) {
+            kcs[t] = kc[row + t];
+            vcs[t] = vc[row + t] * inv_len;
+        }
+        __syncthreads();
+        if (t < D) {
+            float uk = 0.f, uv = 0.f;
+            for (int x = 0; x < D; x += 2) {
+                const float2 r = unpack2<BF16>(*reinterpret_cast<const uint32_t*>(&dhs[t * stride + x]));   // dh[t][x], dh[t][x+1]
+                uk = fmaf(vcs[x], r.x, uk);
+                uk = fmaf(vcs[x + 1], r.y, uk);
+            }
+            for (int d = 0; d < D; ++d) {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(&dhs[d * stride + (t & ~1)]);
+                const float2 r = unpack2<BF16>(w);
+                uv = fmaf(kcs[d], (t & 1) ? r.y : r.x, uv);
+            }
+            dkc[row + t] = dkc[row + t] * inv_len - uk;
+            dvc[row + t] = dvc[row + t] - uv;
+        }
+    }
 }
 
 }  // namespace pisa_tc_kvside
 
 cudaError_t pisa_tc_bwd_kv(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,
                            const void* v, const void* d_o, const float* kc, const float* vc, const int32_t* indices,
-                           const float* row_stats, const float* drow, const float* dkc, const float* dvc, const float* dh,
+                           const float* row_stats, const float* drow, float* dkc, float* dvc, const float* dh, void* dh16,
                            void* dk, void* dv, cudaStream_t st) {
     using namespace pisa_tc_kvside;
-    CUtensorMap mk, mv, mq, mdo, mdk, mdv;
+    const bool bf = dtype == FBLA_BF16;
+    {
+        const dim3 grid((nt + kTermBlocks - 1) / kTermBlocks, bh);
+        if (bf) pisa_stats_terms_kernel<true><<<grid, 128, 0, st>>>(d, nt, T, kc, vc, dh, dkc, dvc, static_cast<uint32_t*>(dh16));
+        else pisa_stats_terms_kernel<false><<<grid, 128, 0, st>>>(d, nt, T, kc, vc, dh, dkc, dvc, static_cast<uint32_t*>(dh16));
+    }
+    CUtensorMap mk, mv, mq, mdo, mdk, mdv, mdh;
     cudaError_t e;
     if ((e = tc_encode_map_rows(&mk, k, dtype, d, T, bh, 64)) != cudaSuccess) return e;
     if ((e = tc_encode_map_rows(&mv, v, dtype, d, T, bh, 64)) != cudaSuccess) return e;
@@ -902,14 +919,14 @@ cudaError_t pisa_tc_bwd_kv(int dtype, int bh, int d, int nt, int ns, int T, floa
     if ((e = tc_encode_map_rows(&mdo, d_o, dtype, d, T, bh, 64)) != cudaSuccess) return e;
     if ((e = tc_encode_map_rows(&mdk, dk, dtype, d, T, bh, 64)) != cudaSuccess) return e;
     if ((e = tc_encode_map_rows(&mdv, dv, dtype, d, T, bh, 64)) != cudaSuccess) return e;
+    if ((e = tc_encode_map_rows(&mdh, dh16, dtype, d, d, bh, 64)) != cudaSuccess) return e;
     Params p{ns, nt, T, scale, tc_status_word()};
     if (p.status == nullptr) return cudaErrorMemoryAllocation;
     const dim3 grid(nt, bh);
-    const bool bf = dtype == FBLA_BF16;
     auto run = [&](auto kern, size_t smem) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
-            kern<<<grid, kThreads, smem, st>>>(mk, mv, mq, mdo, mdk, mdv, p, indices, row_stats, drow, kc, vc, dkc, dvc, dh);
+            kern<<<grid, kThreads, smem, st>>>(mk, mv, mq, mdo, mdk, mdv, mdh, p, indices, row_stats, drow, dkc, dvc);
     };
     if (d == 64) {
         if (bf) run(pisa_bwd_kv_tc_kernel<64, true>, smem_bytes<64>(nt));
@@ -919,6 +936,11 @@ cudaError_t pisa_tc_bwd_kv(int dtype, int bh, int d, int nt, int ns, int T, floa
         else run(pisa_bwd_kv_tc_kernel<128, false>, smem_bytes<128>(nt));
     }
     return e == cudaSuccess ? cudaGetLastError() : e;
+}
+
+// The key-side kernel keeps one CTA per SM busy with 3 (Q, dO) stages and dh resident: it fits up to this many blocks.
+bool pisa_tc_bwd_kv_fits(int d, int nt) {
+    return (d == 64 ? pisa_tc_kvside::smem_bytes<64>(nt) : pisa_tc_kvside::smem_bytes<128>(nt)) <= 232448;
 }
 
 cudaError_t pisa_tc_bwd_q(int dtype, int bh, int d, int nt, int ns, int T, float scale, const void* q, const void* k,

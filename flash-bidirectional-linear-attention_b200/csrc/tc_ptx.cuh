@@ -213,6 +213,38 @@ __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
         : "memory");
 }
+// Four MMAs over the consecutive k-steps of one 64-element block of the contraction dimension, as one
+// statement: the descriptors advance by A_STEP / B_STEP (units of 16 bytes: 2 for a K-major operand,
+// 128 for an MN-major one) from step to step.  The first accumulates iff `accumulate`, the others always.
+// With small tiles (M = 64, N = 64 or 128) an MMA runs for 32-64 cycles, so the issuing thread must not
+// spend dozens of instructions assembling descriptors for each.
+template <int A_STEP, int B_STEP>
+__device__ __forceinline__ void mma_ss_k4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          bool accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, t;\n\t"
+        ".reg .b64 a, b;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 t, %0, %0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "add.s64 a, %1, %5;\n\t"
+        "add.s64 b, %2, %6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+        "add.s64 a, a, %5;\n\t"
+        "add.s64 b, b, %6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+        "add.s64 a, a, %5;\n\t"
+        "add.s64 b, b, %6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+        "}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate), "n"(A_STEP), "n"(B_STEP)
+        : "memory");
+}
+constexpr int kDescStepK = 2;        // K-major operand: 16 elements of 2 bytes
+constexpr int kDescStepMN = 128;     // MN-major operand: 16 rows of 128 bytes
+constexpr int kDescBlock = 512;      // next [64 rows][64 elements] block of a tile (8192 bytes)
+
 // Arrives once on `bar` when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
