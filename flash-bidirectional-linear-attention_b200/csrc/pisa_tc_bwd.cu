@@ -389,6 +389,11 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (threadIdx.x == 64) PISA_QSTAMP(3);
 
+        // scale folded into the per-row constants: scale * ds = p (dP rDs + dDs)
+        const float neg_m[2] = {-m_row[0], -m_row[1]};
+        const float rDs[2] = {rD[0] * p.scale, rD[1] * p.scale};
+        const float dDs[2] = {dD[0] * p.scale, dD[1] * p.scale};
+        const float dgs[2] = {dg[0] * p.scale, dg[1] * p.scale};
         int x_events = 0;
         for (int i = 0; i < NI && okay; ++i) {
             float s[16], dp[16];
@@ -416,31 +421,46 @@ pisa_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const unsigned long long keep_t = keep >> (half * 32 + c2);      // bit 8 g + (x & 1): this thread's columns
             const int jl_t = jl - half * 32 - c2;
             uint32_t hi[8], lo[8], pe[8];
+            if (!approx && keep == ~0ull) {
+                // a full selected block (the common case): nothing to mask, p / den is not needed
 #pragma unroll
-            for (int x = 0; x < 16; x += 2) {
-                const int rr = (x >> 1) & 1;
-                float de2[2], pe2[2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int bit = (x >> 2) * 8 + u;
-                    const bool ok = (keep_t >> bit) & 1ull;
-                    const float pj = ok ? exp2f(fmaf(s[x + u], sm2, -m_row[rr])) : 0.f;
-                    float dpj;
-                    if (approx) {
-                        const float len = (bit == jl_t) ? (float)last_len : (float)kBS;
-                        dpj = fmaf(dp[x + u], rD[rr], dg[rr] * len);
-                    } else {
-                        dpj = fmaf(dp[x + u], rD[rr], dD[rr]);
+                for (int x = 0; x < 16; x += 2) {
+                    const int rr = (x >> 1) & 1;
+                    const float d0 = exp2f(fmaf(s[x], sm2, neg_m[rr])) * fmaf(dp[x], rDs[rr], dDs[rr]);
+                    const float d1 = exp2f(fmaf(s[x + 1], sm2, neg_m[rr])) * fmaf(dp[x + 1], rDs[rr], dDs[rr]);
+                    hi[x >> 1] = pack2<BF16>(d0, d1);
+                    if (BF16) {
+                        const float2 f = unpack2<BF16>(hi[x >> 1]);
+                        lo[x >> 1] = pack2<BF16>(d0 - f.x, d1 - f.y);
                     }
-                    de2[u] = pj * dpj * p.scale;
-                    pe2[u] = pj * rD[rr];
                 }
-                hi[x >> 1] = pack2<BF16>(de2[0], de2[1]);
-                if (BF16) {
-                    const float2 f = unpack2<BF16>(hi[x >> 1]);
-                    lo[x >> 1] = pack2<BF16>(de2[0] - f.x, de2[1] - f.y);
+            } else {
+#pragma unroll
+                for (int x = 0; x < 16; x += 2) {
+                    const int rr = (x >> 1) & 1;
+                    float de2[2], pe2[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int bit = (x >> 2) * 8 + u;
+                        const bool ok = (keep_t >> bit) & 1ull;
+                        const float pj = ok ? exp2f(fmaf(s[x + u], sm2, neg_m[rr])) : 0.f;
+                        float dpj;
+                        if (approx) {
+                            const float len = (bit == jl_t) ? (float)last_len : (float)kBS;
+                            dpj = fmaf(dp[x + u], rDs[rr], dgs[rr] * len);
+                        } else {
+                            dpj = fmaf(dp[x + u], rDs[rr], dDs[rr]);
+                        }
+                        de2[u] = pj * dpj;
+                        pe2[u] = pj * rD[rr];
+                    }
+                    hi[x >> 1] = pack2<BF16>(de2[0], de2[1]);
+                    if (BF16) {
+                        const float2 f = unpack2<BF16>(hi[x >> 1]);
+                        lo[x >> 1] = pack2<BF16>(de2[0] - f.x, de2[1] - f.y);
+                    }
+                    pe[x >> 1] = pack2<BF16>(pe2[0], pe2[1]);
                 }
-                pe[x >> 1] = pack2<BF16>(pe2[0], pe2[1]);
             }
             if (threadIdx.x == 64) PISA_QSTAMP(50 + i);
             if (i > 0 && !ptx::mbar_wait(&bars[kDeEmpty], (i - 1) & 1, ab, 835)) { okay = false; break; }
@@ -730,25 +750,39 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         const float sm2 = p.scale * 1.44269504f;
         bool okay = true;
-        for (int j = 0; j < nh; ++j) {
-            const int b = j & 1;
+        // Constants of this thread's four query rows (columns part * 16 + 8 g + c2 + u) of a visit: (m, 1 / den) and dD.
+        // They are fetched one visit ahead and not touched before they are needed: the first use of a loaded
+        // register is where a thread waits for the load.
+        float4 st_next[2][2];
+        float dd_next[2][2];
+        auto fetch = [&](int j) {
             const int t0 = hlist[j] * kBS;
             const int nrows = min(kBS, p.T - t0);
-            // constants of this thread's four query rows (columns part * 16 + 8 g + c2 + u)
-            float neg_m[2][2], rd[2][2], dd[2][2];
 #pragma unroll
             for (int g = 0; g < 2; ++g)
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const int r = part * 16 + g * 8 + c2 + u;
-                    neg_m[g][u] = 0.f; rd[g][u] = 0.f; dd[g][u] = 0.f;     // 1/den = 0 and dD = 0: a padded row contributes nothing
-                    if (r < nrows) {
-                        const float4 st = __ldg(reinterpret_cast<const float4*>(row_stats + (base_row + t0 + r) * 4));
-                        neg_m[g][u] = -st.x;
-                        rd[g][u] = st.w;
-                        dd[g][u] = __ldg(drow + base_row + t0 + r);
-                    }
+                    const int r = min(part * 16 + g * 8 + c2 + u, nrows - 1);      // padded rows are masked when used
+                    st_next[g][u] = __ldg(reinterpret_cast<const float4*>(row_stats + (base_row + t0 + r) * 4));
+                    dd_next[g][u] = __ldg(drow + base_row + t0 + r);
                 }
+        };
+        if (nh > 0) fetch(0);
+        for (int j = 0; j < nh; ++j) {
+            const int b = j & 1;
+            const int nrows = min(kBS, p.T - hlist[j] * kBS);
+            float neg_m[2][2], rd[2][2], rds[2][2], dd[2][2];
+#pragma unroll
+            for (int g = 0; g < 2; ++g)
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const bool valid = part * 16 + g * 8 + c2 + u < nrows;      // 1/den = 0 and dD = 0: a padded row contributes nothing
+                    neg_m[g][u] = valid ? -st_next[g][u].x : 0.f;
+                    rd[g][u] = valid ? st_next[g][u].w : 0.f;
+                    dd[g][u] = valid ? dd_next[g][u] * p.scale : 0.f;      // scale folded in: scale * ds = p (dP rds + dds)
+                    rds[g][u] = rd[g][u] * p.scale;
+                }
+            if (j + 1 < nh) fetch(j + 1);
             float s[8], dp[8];
             if (threadIdx.x == 64) PISA_BSTAMP(100 + j);
             if (!ptx::mbar_wait(&bars[kSFull + b], (j >> 1) & 1, ab, 871)) { okay = false; break; }
@@ -768,7 +802,7 @@ pisa_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 for (int u = 0; u < 2; ++u) {
                     const float pj = exp2f(fmaf(s[x + u], sm2, neg_m[g][u]));
                     pe2[u] = pj * rd[g][u];
-                    de2[u] = pj * fmaf(dp[x + u], rd[g][u], dd[g][u]) * p.scale;
+                    de2[u] = pj * fmaf(dp[x + u], rds[g][u], dd[g][u]);
                 }
                 pa[x >> 1] = pack2<BF16>(pe2[0], pe2[1]);
                 da[x >> 1] = pack2<BF16>(de2[0], de2[1]);
