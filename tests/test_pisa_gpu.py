@@ -1,5 +1,7 @@
 """piecewise_sparse_attention on the GPU against the golden fixtures (produced by the
 reference's own Triton kernels) and the CPU oracle."""
+import os
+
 import pytest
 import torch
 
@@ -287,3 +289,42 @@ def test_reference_surface():
     assert bias.shape == (1, 2, 1, 4) and bias.dtype == q.dtype
     with pytest.raises(RuntimeError):
         piecewise_sparse_attention(q.cpu(), q.cpu(), q.cpu())
+
+
+_CHILD = r"""
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+from flash_bla.ops.piecewise_attn.kernel import piecewise_sparse_attention
+g = torch.Generator(device="cuda").manual_seed(11)
+q, k, v, do = (torch.randn(1, 2, 1000, 128, device="cuda", generator=g).bfloat16() for _ in range(4))
+xs = [x.clone().requires_grad_() for x in (q, k, v)]
+o = piecewise_sparse_attention(*xs, density=0.2, block_size=64)
+o.backward(do)
+torch.save([o.detach().cpu()] + [x.grad.cpu() for x in xs], sys.argv[2])
+"""
+
+
+def test_mma_sync_kernels_agree_with_the_tcgen05_kernels(tmp_path):
+    """The mma.sync attention kernels stay in the library (FBLA_PISA_TC=0; the key side of very long sequences):
+    the same seeded forward + backward (ragged last block, bf16, D = 128) through both kernel families, each in
+    its own process because the switch is read once."""
+    import subprocess
+    import sys
+    pkg = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "flash-bidirectional-linear-attention_b200")
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    outs = []
+    for flag in ("1", "0"):
+        out = tmp_path / f"out{flag}.pt"
+        env = dict(os.environ, FBLA_PISA_TC=flag)
+        r = subprocess.run([sys.executable, str(script), pkg, str(out)], env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(torch.load(out))
+    for name, a, b in zip(("o", "dq", "dk", "dv"), *outs):
+        # two results rounded to bf16 independently: within 2e-2 of the RMS, or neighbours on the bf16 grid
+        a, b = a.double(), b.double()
+        rms = b.square().mean().sqrt().item()
+        diff = (a - b).abs()
+        ulp = torch.exp2(torch.floor(torch.log2(torch.maximum(a.abs(), b.abs()).clamp_min(1e-30))) - 7)
+        bad = (diff > 2e-2 * rms) & (diff > ulp)
+        assert not bad.any(), f"{name}: tcgen05 vs mma.sync differ by {(diff / rms).max().item():.3e} of the RMS"
