@@ -53,12 +53,35 @@ pisa_block_stats_kernel(PisaParams p, const T* __restrict__ q, const T* __restri
     const int len = min(p.bs, p.T - t0);
     const size_t row0 = (size_t)bh * p.T + t0;
     float sq = 0.f, sk = 0.f, sv = 0.f;
-    for (int t = 0; t < len; ++t) {
-        if (d < p.dk) {
+    const bool has_k = d < p.dk, has_v = d < p.dv;
+    // eight rows in flight per thread: the loads of a group are issued before the first of them is added
+    // (a row-at-a-time loop waits out one memory latency per row); the order of the sums is unchanged
+    int t = 0;
+    for (; t + 8 <= len; t += 8) {
+        T a[8], b[8], e[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (has_k) {
+                a[u] = q[(row0 + t + u) * p.dk + d];
+                b[u] = k[(row0 + t + u) * p.dk + d];
+            }
+            if (has_v) e[u] = v[(row0 + t + u) * p.dv + d];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (has_k) {
+                sq += to_f<T>(a[u]);
+                sk += to_f<T>(b[u]);
+            }
+            if (has_v) sv += to_f<T>(e[u]);
+        }
+    }
+    for (; t < len; ++t) {
+        if (has_k) {
             sq += to_f<T>(q[(row0 + t) * p.dk + d]);
             sk += to_f<T>(k[(row0 + t) * p.dk + d]);
         }
-        if (d < p.dv) sv += to_f<T>(v[(row0 + t) * p.dv + d]);
+        if (has_v) sv += to_f<T>(v[(row0 + t) * p.dv + d]);
     }
     const size_t blk = (size_t)bh * p.nt + c;
     if (d < p.dk) {
@@ -86,13 +109,32 @@ pisa_first_order_kernel(PisaParams p, const float* __restrict__ kv, const float*
     for (int c0 = 0; c0 < p.nt; c0 += kChunkRows) {
         const int nc = min(kChunkRows, p.nt - c0);
         __syncthreads();
+#pragma unroll 4
         for (int i = threadIdx.x; i < nc * kFoRows; i += 256) {
             const int c = i / kFoRows, a = i - c * kFoRows;
             ks[c][a] = (a0 + a < p.dk) ? kcb[(size_t)(c0 + c) * p.dk + a0 + a] : 0.f;
         }
-        for (int i = threadIdx.x; i < nc * p.dv; i += 256) {
-            const int c = i / p.dv, b = i - c * p.dv;
-            vs[c][b] = vcb[(size_t)(c0 + c) * p.dv + b];
+        // rows of vc are contiguous in memory: a flat copy, eight loads in flight per thread
+        {
+            const float* src = vcb + (size_t)c0 * p.dv;
+            const int n = nc * p.dv;
+            const bool flat = p.dv == 128;
+            for (int i0 = 0; i0 < n; i0 += 256 * 8) {
+                float tmp[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * 256 + threadIdx.x;
+                    tmp[u] = i < n ? src[i] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * 256 + threadIdx.x;
+                    if (i < n) {
+                        if (flat) (&vs[0][0])[i] = tmp[u];
+                        else vs[i / p.dv][i % p.dv] = tmp[u];
+                    }
+                }
+            }
         }
         __syncthreads();
         for (int c = 0; c < nc; ++c) {
@@ -411,9 +453,20 @@ pisa_select_kernel(PisaParams p, int dtype, const float* __restrict__ qc, const 
         if (rows <= 0) continue;                    // uniform over the CTA
         __syncthreads();
         const float* src = kc + ((size_t)bh * p.nt + c0) * K;
-        for (int i = threadIdx.x; i < rows * K4; i += kSelectWarps * 32) {
-            const int r = i / K4, d = i - r * K4;
-            kcs[r * KS + d] = d < K ? round_like(src[(size_t)r * K + d] * p.scale, dtype) : 0.f;
+        for (int i0 = 0; i0 < rows * K4; i0 += kSelectWarps * 32 * 8) {      // eight loads in flight per thread
+            float tmp[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * kSelectWarps * 32 + threadIdx.x;
+                const int r = i / K4, d = i - r * K4;
+                tmp[u] = (i < rows * K4 && d < K) ? src[(size_t)r * K + d] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * kSelectWarps * 32 + threadIdx.x;
+                const int r = i / K4, d = i - r * K4;
+                if (i < rows * K4) kcs[r * KS + d] = d < K ? round_like(tmp[u] * p.scale, dtype) : 0.f;
+            }
         }
         __syncthreads();
 #pragma unroll
