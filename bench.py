@@ -54,6 +54,7 @@ UNIT = "tokens/s"
 CPU_SAMPLE_BATCH = 2          # the CPU arm runs B=2 of the 8 batch rows per step
 FALLBACK_HBM_GBS = 6650.0
 CFG3 = dict(B=4, H=32, D=128, T=262144)
+CFG5 = dict(B=2, H=24, T=4608, D=128, block=64, density=0.1)
 # DRAM bytes (read + write) of one launch of each pass at B8-H16-D64, T = 32768, from an ncu
 # capture of dram__bytes_read.sum + dram__bytes_write.sum (one launch per kernel).
 NCU_DRAM_BYTES_T32768 = {"fwd_state": 1.0789e9, "fwd_out": 1.0292e9, "bwd_state": 1.5895e9, "bwd_in": 2.1086e9}
@@ -360,6 +361,45 @@ def run_cfg3(world, rank, dev, barrier, peak):
     return out
 
 
+def run_cfg5(world, rank, dev, barrier):
+    """piecewise_sparse_attention bf16 B2-H24-T4608-D128, block 64, density 0.1: the 48 (batch, head) pairs are
+    independent, each rank takes its share (no communication); forward + backward of the whole operator
+    (block statistics, first-order state, selection, attention)."""
+    from flash_bla.ops.piecewise_attn.kernel import piecewise_sparse_attention
+    from flash_bla.ops.sharded import shard_units
+    c = CFG5
+    units = shard_units(c["B"] * c["H"], world, rank)
+    if len(units) == 0:
+        return {"skipped": f"{c['B'] * c['H']} (batch, head) pairs do not cover {world} ranks"}
+    g = torch.Generator(device=dev).manual_seed(5000 + rank)
+    # this rank's pairs as a (1, n, T, D) problem: pairs do not interact, so the split is free
+    q, k, v, do = (torch.randn(1, len(units), c["T"], c["D"], device=dev, generator=g).bfloat16() for _ in range(4))
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        o = piecewise_sparse_attention(q, k, v, density=c["density"], block_size=c["block"])
+        o.backward(do)
+
+    def fwd_only():
+        with torch.no_grad():
+            piecewise_sparse_attention(q, k, v, density=c["density"], block_size=c["block"])
+
+    for _ in range(3):
+        step()
+    blocks = timed_blocks(lambda: step(), 10, barrier, world, dev, min_blocks=5, min_total_s=0.1, max_blocks=40)
+    fblocks = timed_blocks(lambda: fwd_only(), 10, barrier, world, dev, min_blocks=5, min_total_s=0.05, max_blocks=40)
+    ms, fms = statistics.median(blocks) / 10, statistics.median(fblocks) / 10
+    out = {"workload": f"piecewise_sparse_attention fwd+bwd bf16 B{c['B']}-H{c['H']}-T{c['T']}-D{c['D']}, block {c['block']}, "
+                       f"density {c['density']}; {len(units)} (batch, head) pairs per GPU, no communication",
+           "scaling": "strong", "ms_per_step": ms, "fwd_ms": fms, "value": c["B"] * c["T"] / (ms * 1e-3), "unit": UNIT,
+           "kernels": "tcgen05 (attention forward, backward query side, backward key side)",
+           "blocks": {"n": len(blocks), "steps_each": 10, "min_ms": min(blocks) / 10, "max_ms": max(blocks) / 10}}
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -550,6 +590,7 @@ def run_ours(args):
 
     peak_now = peak
     cfg3 = None if args.no_cfg3 else run_cfg3(world, rank, dev, barrier, peak_now)
+    cfg5 = None if args.no_cfg5 else run_cfg5(world, rank, dev, barrier)
 
     cpu = None
     triton = None
@@ -575,6 +616,8 @@ def run_ours(args):
             line["parity"] = parity
         if cfg3 is not None:
             line["cfg3"] = cfg3
+        if cfg5 is not None:
+            line["cfg5"] = cfg5
         if triton is not None:
             line["triton_reference"] = triton
         print(json.dumps(line), flush=True)
@@ -591,6 +634,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the simple_la T=262144 block")
+    ap.add_argument("--no-cfg5", action="store_true", help="skip the piecewise_sparse_attention block")
     ap.add_argument("--no-triton", action="store_true", help="skip the run of the reference's Triton kernels")
     args = ap.parse_args()
     if args.impl == "reference":

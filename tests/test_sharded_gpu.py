@@ -73,6 +73,30 @@ def _worker(rank, world, port, ret):
                     o2.backward(do[:, :, sl].contiguous())
                     same = torch.equal(o2, o) and all(torch.equal(x.grad, g) for x, g in zip(xs, grads))
                     errs[f"{name}/repeat"] = max(errs.get(f"{name}/repeat", 0.0), 0.0 if same else 2.0)
+        # piecewise sparse attention: the (batch, head) pairs are split over the ranks without communication;
+        # a rank's share must equal the same pairs of the whole problem (the forward bit for bit, the gradients up
+        # to the order of the fp32 atomics that collect the block-statistics terms)
+        from flash_bla.ops.piecewise_attn.kernel import piecewise_sparse_attention
+        from flash_bla.ops.sharded import shard_units
+        g = torch.Generator(device="cuda").manual_seed(9)
+        n_units = 6
+        q, k, v, do = (torch.randn(1, n_units, 1000, 128, device="cuda", generator=g).bfloat16() for _ in range(4))
+        mine = shard_units(n_units, world, rank)
+        if len(mine) > 0:
+            lo, hi = mine[0], mine[-1] + 1
+            part = [x[:, lo:hi].contiguous().requires_grad_() for x in (q, k, v)]
+            whole = [x.clone().requires_grad_() for x in (q, k, v)]
+            o = piecewise_sparse_attention(*part, density=0.2, block_size=64)
+            o_ref = piecewise_sparse_attention(*whole, density=0.2, block_size=64)
+            o.backward(do[:, lo:hi].contiguous())
+            o_ref.backward(do)
+            errs["piecewise/forward"] = 0.0 if torch.equal(o, o_ref[:, lo:hi]) else 2.0
+            worst = 0.0
+            for a, f in zip(part, whole):
+                a, b = a.grad.float(), f.grad[:, lo:hi].float()
+                slack = 2.0 ** -7 * b.abs() + 2e-3 * b.pow(2).mean().sqrt().item()
+                worst = max(worst, ((a - b).abs() / slack).max().item())
+            errs["piecewise/backward"] = worst
         kinds = {type(e).__name__ for e in sharded._exchanges.values() if e is not None}
         errs["fused_path_used"] = 0.0 if "_FusedExchange" in kinds else 2.0
         errs["peer_path_used"] = 0.0 if "_PeerExchange" in kinds else 2.0
