@@ -47,14 +47,23 @@ int resolve(const fbla_problem* p, OpKind op, fbla::KParams* kp) {
     if ((p->normalize != 0) != want_norm)
         return fail(FBLA_ERR_INVALID, "normalize=%d does not match this operator", p->normalize);
     kp->heads = p->heads;
-    kp->dk = p->dk;
-    kp->dv = p->dv;
+    kp->dk = kp->mem_dk = p->dk;
+    kp->dv = kp->mem_dv = p->dv;
+    if (p->flags & FBLA_FLAG_NARROW) {
+        const bool wide = (p->dk == 64 || p->dk == 128) && (p->dv == 64 || p->dv == 128);
+        if (p->dtype == FBLA_F32 || (op != OP_LINEAR && op != OP_SIMPLE) || (p->dk % 16) || (p->dv % 16) || wide ||
+            (p->flags & FBLA_FLAG_GENERIC))
+            return fail(FBLA_ERR_UNSUPPORTED, "FBLA_FLAG_NARROW serves 16-bit fixed-length linear_attn / simple_la with "
+                        "feature dims that are multiples of 16 and not both 64 or 128 (dk=%d, dv=%d)", p->dk, p->dv);
+        kp->dk = p->dk <= 64 ? 64 : 128;        // the kernels' tile widths; the tensors keep theirs
+        kp->dv = p->dv <= 64 ? 64 : 128;
+    }
     kp->seq_len = p->seq_len;
     kp->scale = p->scale;
     kp->eps = p->eps;
     kp->normalize = p->normalize != 0;
     kp->inv_norm = p->norm_len > 0 ? (float)(1.0 / (double)p->norm_len) : 0.f;
-    kp->state_stride = p->dk * p->dv + (kp->normalize ? p->dk : 0);
+    kp->state_stride = kp->dk * kp->dv + (kp->normalize ? kp->dk : 0);
     kp->unreduced = 0;
     if (op == OP_VARLEN) {
         if (p->cu_seqlens == nullptr) return fail(FBLA_ERR_INVALID, "cu_seqlens is NULL");
@@ -129,6 +138,8 @@ int check_ws(const fbla_problem* p, const fbla::KParams& kp, void* ws, size_t ws
 bool is_empty(const fbla::KParams& kp) { return kp.units == 0 || kp.seq_len == 0; }
 
 const char* const kUnreducedNeedsTc = "the unreduced-state mode needs the tensor-core kernels (16-byte aligned tensors)";
+const char* const kNarrowNeedsTc = "FBLA_FLAG_NARROW needs the tensor-core kernels (16-byte aligned tensors)";
+bool narrow(const fbla::KParams& kp) { return kp.mem_dk != kp.dk || kp.mem_dv != kp.dv; }
 
 int fwd_state(const fbla_problem* p, OpKind op, const void* k, const void* k_rope, const void* v,
               float* state, void* ws, size_t ws_bytes, fbla_stream_t stream, bool unreduced = false) {
@@ -147,6 +158,7 @@ int fwd_state(const fbla_problem* p, OpKind op, const void* k, const void* k_rop
     if (int rc = check_device_status()) return rc;
     const bool tc = use_tc(p, kp) && aligned16(k, k_rope, v, ws) && (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
     if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
+    if (narrow(kp) && !tc) return fail(FBLA_ERR_UNSUPPORTED, kNarrowNeedsTc);
     cudaError_t e = tc ? fbla::tc_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st)
                        : fbla::simt_fwd_state(kp, p->dtype, k, k_rope, v, state, ws, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward state pass");
@@ -165,6 +177,7 @@ int fwd_out(const fbla_problem* p, OpKind op, const void* q, const void* q_rope,
     if (int rc = check_device_status()) return rc;
     const bool tc = use_tc(p, kp) && aligned16(q, q_rope, o) && (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
     if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
+    if (narrow(kp) && !tc) return fail(FBLA_ERR_UNSUPPORTED, kNarrowNeedsTc);
     cudaError_t e = tc ? fbla::tc_fwd_out(kp, p->dtype, q, q_rope, state, o, st)
                        : fbla::simt_fwd_out(kp, p->dtype, q, q_rope, state, o, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "forward output pass");
@@ -196,6 +209,7 @@ int bwd_state(const fbla_problem* p, OpKind op, const void* q, const void* q_rop
     const bool tc = use_tc(p, kp) && aligned16(q, q_rope, d_o, dq, dq_rope, ws) &&
                     (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
     if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
+    if (narrow(kp) && !tc) return fail(FBLA_ERR_UNSUPPORTED, kNarrowNeedsTc);
     cudaError_t e = tc ? fbla::tc_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st)
                        : fbla::simt_bwd_state(kp, p->dtype, q, q_rope, d_o, state, dq, dq_rope, dstate, ws, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward state pass");
@@ -218,6 +232,7 @@ int bwd_in(const fbla_problem* p, OpKind op, const void* k_rope, const void* v, 
     const bool tc = use_tc(p, kp) && aligned16(k_rope, v, dk, dk_rope, dv) &&
                     (op != OP_DECOUPLED || fbla::tc_supported_decoupled(kp));
     if (unreduced && !tc) return fail(FBLA_ERR_INVALID, kUnreducedNeedsTc);
+    if (narrow(kp) && !tc) return fail(FBLA_ERR_UNSUPPORTED, kNarrowNeedsTc);
     cudaError_t e = tc ? fbla::tc_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st)
                        : fbla::simt_bwd_in(kp, p->dtype, k_rope, v, dstate, dk, dk_rope, dv, st);
     return e == cudaSuccess ? FBLA_OK : cuda_fail(e, "backward input pass");

@@ -27,7 +27,9 @@ struct PeerArgs {
 struct KParams {
     int units;            // B*H or num_seqs*H
     int heads;
-    int dk, dv;
+    int dk, dv;           // feature dims the kernels compute with
+    int mem_dk, mem_dv;   // feature dims of the tensors in memory (smaller than dk, dv only on the narrow route of
+                          // the tensor-core kernels, whose TMA boxes zero-fill / clip the missing features)
     int64_t seq_len;      // fixed length: T; packed: total tokens
     int max_len;          // longest unit (fixed: T; packed: caller's max_seqlen)
     const int32_t* cu;    // packed layout only

@@ -348,8 +348,8 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     if (!staged) {
                         keep1[j] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
                         if (MODE == kDecoupled) keep2[j] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
-                        if ((j & 1) && tok_ok) {       // two 16-byte chunks = one 32-byte sector per store
-                            const size_t at = (grow * DK + c - 8) * 2;
+                        if ((j & 1) && tok_ok && c - 8 < p.mem_dk) {      // two 16-byte chunks = one 32-byte sector per store
+                            const size_t at = (grow * p.mem_dk + c - 8) * 2;      // (rows may be narrower than DK)
                             ptx::st_global_32B(static_cast<uint8_t*>(p.out_a) + at, keep1[j - 1], keep1[j]);
                             if (MODE == kDecoupled)
                                 ptx::st_global_32B(static_cast<uint8_t*>(p.out_b) + at, keep2[j - 1], keep2[j]);

@@ -189,6 +189,7 @@ Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) 
     q.plan = nullptr;
     q.num_seqs = 0;
     q.heads = p.heads;
+    q.mem_dk = p.mem_dk;
     q.scale_per_seq = 0;
     q.inv_norm_fixed = 0.f;
     return q;
@@ -448,9 +449,9 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
     q.part = static_cast<float*>(ws);
     CUtensorMap tkr, tk, tv;
     cudaError_t e;
-    if ((e = make_map(&tkr, dec ? k_rope : k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tk, k, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tkr, dec ? k_rope : k, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tk, k, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tv, v, dtype, p.mem_dv, p.seq_len, p.units)) != cudaSuccess) return e;
     auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_fwd_state, q, tkr, tk, tv, st); };
     if ((e = launch()) != cudaSuccess) return e;
     if (p.unreduced) return cudaSuccess;        // the pieces in `ws` are the result
@@ -480,9 +481,9 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
     q.out_a = o;
     CUtensorMap tqr, tq, to;
     cudaError_t e;
-    if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tq, q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&to, o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tq, q_, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&to, o, dtype, p.mem_dv, p.seq_len, p.units)) != cudaSuccess) return e;
     FBLA_TC_DISPATCH(launch_fwd_out, q, tqr, tq, to, st);
 }
 
@@ -520,11 +521,11 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
     q.out_b = dq;
     CUtensorMap tqr, tq, tdo, tdq, tdqr;
     cudaError_t e;
-    if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tq, q_, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tdo, d_o, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tdq, dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tdqr, dec ? dq_rope : dq, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tqr, dec ? q_rope : q_, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tq, q_, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdo, d_o, dtype, p.mem_dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdq, dq, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdqr, dec ? dq_rope : dq, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
     auto launch = [&]() -> cudaError_t { FBLA_TC_DISPATCH(launch_bwd_state, q, tqr, tq, tdo, tdq, tdqr, st); };
     if ((e = launch()) != cudaSuccess) return e;
     if (p.unreduced) return cudaSuccess;
@@ -558,11 +559,11 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
     q.out_b = dv;
     CUtensorMap tkr, tv, tdk, tdkr, tdv;
     cudaError_t e;
-    if ((e = make_map(&tkr, k_rope, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tv, v, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tdk, dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tdkr, dec ? dk_rope : dk, dtype, p.dk, p.seq_len, p.units)) != cudaSuccess) return e;
-    if ((e = make_map(&tdv, dv, dtype, p.dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tkr, k_rope, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tv, v, dtype, p.mem_dv, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdk, dk, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdkr, dec ? dk_rope : dk, dtype, p.mem_dk, p.seq_len, p.units)) != cudaSuccess) return e;
+    if ((e = make_map(&tdv, dv, dtype, p.mem_dv, p.seq_len, p.units)) != cudaSuccess) return e;
     FBLA_TC_DISPATCH(launch_bwd_in, q, tkr, tv, tdk, tdkr, tdv, st);
 }
 

@@ -15,6 +15,7 @@ LIB_PATH = os.environ.get("FLASH_BLA_LIB") or os.path.join(_HERE, "lib", "libfla
 F32, BF16, F16 = 0, 1, 2
 FLAG_GENERIC = 1
 FLAG_UNREDUCED = 2
+FLAG_NARROW = 4
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 

@@ -188,9 +188,32 @@ def _sizes(prob):
     return got
 
 
+def narrow_route(prob):
+    """Whether the library serves this problem on its narrow route: 16-bit fixed-length linear_attn / simple_la
+    whose feature dims are multiples of 16 but not the tensor-core kernels' own 64 / 128 (the reference's layers
+    use 32).  The 64- / 128-wide kernels then read and write the tensors at their own width through TMA boxes
+    that zero-fill / clip the missing features.  ``FBLA_NARROW_DIMS=0`` switches the route off."""
+    if prob.dtype == _C.dtype_code(torch.float32) or prob.cu_seqlens is not None or (prob.flags & _C.FLAG_GENERIC):
+        return False
+    if os.environ.get("FBLA_NARROW_DIMS", "1") == "0":
+        return False
+    K, V = prob.dk, prob.dv
+    if K % 16 or V % 16 or K > 128 or V > 128 or K < 16 or V < 16:
+        return False
+    return not (K in (64, 128) and V in (64, 128))
+
+
+def _aligned16(*tensors):
+    """The tensors as 16-byte aligned ones (a contiguous view at an odd storage offset is copied)."""
+    return [t if t.data_ptr() % 16 == 0 else t.clone() for t in tensors]
+
+
 def forward(prob, q, k, v):
     """fwd_state + fwd_out of linear_attention / simple_la / varlen; returns (o, state)."""
     _require_cuda(q, k, v)
+    if narrow_route(prob):
+        prob.flags |= _C.FLAG_NARROW
+        q, k, v = _aligned16(q, k, v)
     # the unreduced route needs the tensor-core kernels, and those need 16-byte aligned tensors (a contiguous
     # view at an odd storage offset is served by the CUDA-core kernels, as the reference serves it)
     if _want_unreduced and all(t.data_ptr() % 16 == 0 for t in (q, k, v)):
@@ -210,6 +233,9 @@ def forward(prob, q, k, v):
 def backward(prob, q, k, v, d_o, state):
     """bwd_state + bwd_in; returns (dq, dk, dv).  ``state`` is what ``forward`` returned."""
     _require_cuda(q, k, v, d_o, state)
+    if narrow_route(prob):
+        prob.flags |= _C.FLAG_NARROW
+        q, k, v, d_o = _aligned16(q, k, v, d_o)
     if state.dtype == torch.uint8:
         prob.flags |= _C.FLAG_UNREDUCED
     else:
@@ -248,6 +274,8 @@ def padded_dims(q, v):
     K, V = q.shape[-1], v.shape[-1]
     if K in (64, 128) and V in (64, 128):
         return None
+    if K % 16 == 0 and V % 16 == 0 and K <= 128 and V <= 128 and os.environ.get("FBLA_NARROW_DIMS", "1") != "0":
+        return None             # the library's narrow route reads them as they are (no copies)
     if K > 128 or V > 128 or q.shape[0] * q.shape[1] * q.shape[2] < _PAD_MIN_ROWS:
         return None
     up = lambda d: 64 if d <= 64 else 128

@@ -309,11 +309,13 @@ def test_full_size_varlen_bf16():
     assert not torch.equal(o2[lo:hi], o.detach()[lo:hi])
 
 
+@pytest.mark.parametrize("D", [64, 32])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_tensors_at_an_odd_storage_offset(dtype):
+def test_tensors_at_an_odd_storage_offset(dtype, D):
     """Contiguous views whose storage does not start on a 16-byte boundary (a slice of a larger buffer) are
-    accepted, as the reference accepts them: the CUDA-core kernels serve them."""
-    B, H, T, D = 1, 2, 300, 64
+    accepted, as the reference accepts them: the CUDA-core kernels serve them (D = 64), or the narrow route
+    works on aligned copies (D = 32, 16-bit)."""
+    B, H, T = 1, 2, 300
     q, k, v, do = make_inputs(71, (B, H, T, D), (B, H, T, D), dtype)
     ref = [O.linear_attn_fwd(q, k, v)] + list(O.linear_attn_bwd(q, k, v, do))
 
@@ -459,16 +461,27 @@ def test_linear_attention_blhd_layout(shape, dtype):
         check(got.permute(0, 2, 1, 3), ref, dtype, f"blhd{shape}.{name}")
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FBLA_PAD_SMALL_DIMS", "1") == "0",
-                    reason="the padded route is switched off (FBLA_PAD_SMALL_DIMS=0)")
-@pytest.mark.parametrize("shape", [(2, 8, 8192, 32, 32), (1, 16, 8192, 48, 24), (1, 16, 8192, 96, 32)])
-def test_small_head_dims_take_the_padded_tensor_core_route(shape):
-    """16-bit inputs of streaming size whose head dims are not 64 / 128 are zero-padded onto the tensor-core
-    kernels; outputs and gradients keep the caller's shapes and match the oracle."""
+@pytest.mark.skipif(__import__("os").environ.get("FBLA_PAD_SMALL_DIMS", "1") == "0"
+                    or __import__("os").environ.get("FBLA_NARROW_DIMS", "1") == "0",
+                    reason="the narrow / padded routes are switched off")
+@pytest.mark.parametrize("shape", [(2, 8, 8192, 32, 32), (1, 16, 8192, 48, 24), (1, 16, 8192, 96, 32), (4, 4, 196, 32, 32),
+                                   (1, 3, 3136, 16, 112), (1, 2, 700, 80, 48)])
+def test_small_head_dims_take_the_tensor_core_kernels(shape):
+    """16-bit inputs whose head dims are not 64 / 128 (the reference's layers use 32): multiples of 16 are read and
+    written at their own width by the 64- / 128-wide tensor-core kernels (TMA boxes zero-fill / clip the missing
+    features), at any size; other dims of streaming size are zero-padded first.  Outputs and gradients keep the
+    caller's shapes and match the oracle."""
     B, H, T, K, V = shape
     dtype = torch.bfloat16
     q, k, v, d_o = make_inputs(61, (B, H, T, K), (B, H, T, V), dtype)
-    assert P.padded_dims(q.cuda(), v.cuda()) is not None
+    prob = P.make_problem(q, batch=B, heads=H, seq_len=T, dk=K, dv=V, normalize=True)
+    if K % 16 == 0 and V % 16 == 0:
+        assert P.narrow_route(prob) and P.padded_dims(q.cuda(), v.cuda()) is None
+        from flash_bla import _C
+        prob.flags |= _C.FLAG_NARROW
+        assert P.kernel_path(prob) == 1
+    else:
+        assert not P.narrow_route(prob) and P.padded_dims(q.cuda(), v.cuda()) is not None
     rq, rk, rv = (x.double() for x in (q, k, v))
     refs = (O.linear_attn_fwd(rq, rk, rv, None, 1e-6),) + tuple(O.linear_attn_bwd(rq, rk, rv, d_o.double(), None, 1e-6))
     xs = [x.cuda().requires_grad_() for x in (q, k, v)]
