@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 
 from flash_bla.ops import _passes as P
+from flash_bla import _C
 from flash_bla.utils import contiguous
 
 _OP = "decoupled_la"
@@ -19,8 +20,19 @@ _OP = "decoupled_la"
 
 def _problem(q, v, scale, eps, norm_len=0):
     B, H, L, K = q.shape
-    return P.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
+    prob = P.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
                           scale=scale, eps=eps, norm_len=norm_len, flags=P.default_flags())
+    # head dims below the 64 x 64 tensor-core kernels of this operator (the reference layers use 32)
+    if K <= 64 and v.shape[-1] <= 64 and q.is_cuda and P.narrow_route(prob):
+        prob.flags |= _C.FLAG_NARROW
+    return prob
+
+
+def _aligned(prob, *tensors):
+    """The narrow route reads through TMA: contiguous views at an odd storage offset are copied."""
+    if prob.flags & _C.FLAG_NARROW:
+        return [t if t.data_ptr() % 16 == 0 else t.clone() for t in tensors]
+    return list(tensors)
 
 
 def _check(q, k, q_rope, k_rope, v):
@@ -38,6 +50,7 @@ class DecoupledLAFunction(torch.autograd.Function):
     def forward(ctx, q, k, q_rope, k_rope, v, scale, eps):
         _check(q, k, q_rope, k_rope, v)
         prob = _problem(q, v, scale, eps)
+        q, k, q_rope, k_rope, v = _aligned(prob, q, k, q_rope, k_rope, v)
         state = P.fwd_state(_OP, prob, k, v, k_rope=k_rope)
         o = P.fwd_out(_OP, prob, q, state, torch.empty_like(v), q_rope=q_rope)
         ctx.save_for_backward(q, q_rope, k_rope, v, state)
@@ -49,6 +62,7 @@ class DecoupledLAFunction(torch.autograd.Function):
     def backward(ctx, do):
         q, q_rope, k_rope, v, state = ctx.saved_tensors
         prob = _problem(q, v, ctx.scale, ctx.eps)
+        do, = _aligned(prob, do)
         dq, dq_rope = torch.empty_like(q), torch.empty_like(q_rope)
         dstate = P.bwd_state(_OP, prob, q, do, state, dq, q_rope=q_rope, dq_rope=dq_rope)
         dk, dk_rope, dv = torch.empty_like(k_rope), torch.empty_like(k_rope), torch.empty_like(v)
