@@ -229,6 +229,15 @@ def _aligned(*tensors):
     return [t if t is None or t.data_ptr() % 16 == 0 else t.clone() for t in tensors]
 
 
+def _narrow(prob, *tensors):
+    """Head dims below the tensor-core tiles (multiples of 16 that are not 64 / 128): the passes' narrow route,
+    which reads the tensors at their own width and wants them 16-byte aligned (CUDA tensors only)."""
+    if tensors[0].is_cuda and _passes.narrow_route(prob):
+        prob.flags |= _passes._C.FLAG_NARROW
+        return _aligned(*tensors)
+    return tensors
+
+
 def _summed_state(produce, prob, like, group):
     """Runs ``produce(out)`` (a state pass; ``out`` None = allocate) and returns the sum of the
     resulting states over the group."""
@@ -251,6 +260,7 @@ class _SeqSharded(torch.autograd.Function):
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1],
                                      normalize=normalize, scale=scale, eps=eps, norm_len=norm_len,
                                      flags=_backend.default_flags())
+        q, k, v = _narrow(prob, q, k, v)
         fx = _fused_exchange(group, prob, (q, k, v))
         if fx is not None:
             q, k, v = _aligned(q, k, v)
@@ -275,6 +285,7 @@ class _SeqSharded(torch.autograd.Function):
         prob = _backend.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1],
                                      normalize=normalize, scale=scale, eps=eps, norm_len=norm_len,
                                      flags=_backend.default_flags())
+        do, = _narrow(prob, do)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         fx = _fused_exchange(group, prob, (q, k, v))
         if fx is not None:

@@ -33,7 +33,8 @@ def _worker(rank, world, port, ret):
         # every case once with the peer-memory state exchange and once with NCCL's all-reduce
         cases = (("linear", 64, 64, torch.bfloat16), ("simple", 128, 128, torch.bfloat16),
                  ("linear_128x64", 128, 64, torch.float16), ("decoupled", 64, 64, torch.bfloat16),
-                 ("simple_64x128", 64, 128, torch.bfloat16), ("linear_f32", 32, 32, torch.float32))
+                 ("simple_64x128", 64, 128, torch.bfloat16), ("linear_f32", 32, 32, torch.float32),
+                 ("linear_narrow", 32, 48, torch.bfloat16))          # head dims below the tensor-core tiles
         for mode, (name, DK, DV, dtype) in [(m, c) for m in ("1", "0") for c in cases]:
             os.environ["FBLA_PEER_EXCHANGE"] = mode
             g = torch.Generator(device="cuda").manual_seed(7)
