@@ -51,9 +51,10 @@ int resolve(const fbla_problem* p, OpKind op, fbla::KParams* kp) {
     kp->dv = kp->mem_dv = p->dv;
     if (p->flags & FBLA_FLAG_NARROW) {
         const bool wide = (p->dk == 64 || p->dk == 128) && (p->dv == 64 || p->dv == 128);
-        const bool op_ok = op == OP_LINEAR || op == OP_SIMPLE || (op == OP_DECOUPLED && p->dk <= 64 && p->dv <= 64);
+        const bool op_ok = op == OP_LINEAR || op == OP_SIMPLE || op == OP_VARLEN ||
+                           (op == OP_DECOUPLED && p->dk <= 64 && p->dv <= 64);
         if (p->dtype == FBLA_F32 || !op_ok || (p->dk % 16) || (p->dv % 16) || wide || (p->flags & FBLA_FLAG_GENERIC))
-            return fail(FBLA_ERR_UNSUPPORTED, "FBLA_FLAG_NARROW serves 16-bit fixed-length linear_attn / simple_la (and "
+            return fail(FBLA_ERR_UNSUPPORTED, "FBLA_FLAG_NARROW serves 16-bit linear_attn (fixed or packed) / simple_la (and "
                         "decoupled_la up to 64) with feature dims that are multiples of 16 and not both 64 or 128 "
                         "(dk=%d, dv=%d)", p->dk, p->dv);
         kp->dk = p->dk <= 64 ? 64 : 128;        // the kernels' tile widths; the tensors keep theirs

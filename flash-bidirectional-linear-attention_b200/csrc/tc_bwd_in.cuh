@@ -292,9 +292,9 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                 }
                 if (direct) {
                     if (tok_ok) {
-                        uint8_t* dst = static_cast<uint8_t*>(p.out_a) + (grow * DK + c0) * 2;
-                        ptx::st_global_32B(dst, w4[0], w4[1]);
-                        ptx::st_global_32B(dst + 32, w4[2], w4[3]);
+                        uint8_t* dst = static_cast<uint8_t*>(p.out_a) + (grow * p.mem_dk + c0) * 2;
+                        if (c0 < p.mem_dk) ptx::st_global_32B(dst, w4[0], w4[1]);          // (rows may be narrower than DK)
+                        if (c0 + 16 < p.mem_dk) ptx::st_global_32B(dst + 32, w4[2], w4[3]);
                     }
                 } else {
 #pragma unroll
@@ -321,9 +321,9 @@ tc_bwd_in_kernel(const __grid_constant__ CUtensorMap tm_kr, const __grid_constan
                 }
                 if (direct) {
                     if (tok_ok) {
-                        uint8_t* dst = static_cast<uint8_t*>(p.out_b) + (grow * DV + c0) * 2;
-                        ptx::st_global_32B(dst, w4[0], w4[1]);
-                        ptx::st_global_32B(dst + 32, w4[2], w4[3]);
+                        uint8_t* dst = static_cast<uint8_t*>(p.out_b) + (grow * p.mem_dv + c0) * 2;
+                        if (c0 < p.mem_dv) ptx::st_global_32B(dst, w4[0], w4[1]);
+                        if (c0 + 16 < p.mem_dv) ptx::st_global_32B(dst + 32, w4[2], w4[3]);
                     }
                 } else {
 #pragma unroll

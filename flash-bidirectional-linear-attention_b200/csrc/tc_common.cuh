@@ -66,7 +66,7 @@ struct Params {
     // kernels that write an output with plain global stores (no staged tile): its base address
     void* out_a;
     void* out_b;
-    int mem_dk;           // key features per row of those outputs in memory (<= the kernel's DK)
+    int mem_dk, mem_dv;   // key / value features per row of those outputs in memory (<= the kernel's DK, DV)
     // packed variable-length layout (total_tokens, heads, D); all null / zero for fixed length
     const int32_t* cu;    // cu_seqlens, device
     const int32_t* plan;  // plan[s] = heads * (tiles of sequences before s), plan[num_seqs] = all tiles

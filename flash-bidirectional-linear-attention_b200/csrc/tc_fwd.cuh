@@ -464,7 +464,7 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
             if (!ptx::mbar_wait(&out_free[a], ph2, ab, 222)) break;
             // packed layout: a tile may end inside the next sequence; such a tile leaves in row-guarded
             // 32-byte stores, every full tile as a staged tile through the TMA store like the fixed layout
-            uint8_t* orow = static_cast<uint8_t*>(p.out_a) + (size_t)(t.row0 + (long long)row * t.row_stride) * DV * 2;
+            uint8_t* orow = static_cast<uint8_t*>(p.out_a) + (size_t)(t.row0 + (long long)row * t.row_stride) * p.mem_dv * 2;
             const bool row_ok = row < t.valid;
             const bool staged = !VARLEN || t.valid == kTileTokens;
             uint8_t* ob = outbuf + a * Cfg::kOutBytes;
@@ -495,8 +495,9 @@ tc_fwd_out_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_consta
                     keep[j] = w;
                 }
                 if (!staged && row_ok) {
-                    ptx::st_global_32B(orow + c0 * 2, keep[0], keep[1]);
-                    ptx::st_global_32B(orow + c0 * 2 + 32, keep[2], keep[3]);
+                    // (rows in memory may be narrower than DV: multiples of 16 features)
+                    if (c0 < p.mem_dv) ptx::st_global_32B(orow + c0 * 2, keep[0], keep[1]);
+                    if (c0 + 16 < p.mem_dv) ptx::st_global_32B(orow + c0 * 2 + 32, keep[2], keep[3]);
                 }
             }
             ptx::tc_fence_before_sync();

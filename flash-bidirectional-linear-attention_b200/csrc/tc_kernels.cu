@@ -190,6 +190,7 @@ Params make_params(const KParams& p, int dtype, const Schedule& s, int* status) 
     q.num_seqs = 0;
     q.heads = p.heads;
     q.mem_dk = p.mem_dk;
+    q.mem_dv = p.mem_dv;
     q.scale_per_seq = 0;
     q.inv_norm_fixed = 0.f;
     return q;
@@ -433,8 +434,8 @@ cudaError_t tc_fwd_state_status(const KParams& p, int dtype, const void* k, cons
         q.state_out = state;
         q.part = static_cast<float*>(ws);
         CUtensorMap tk, tv;
-        if ((e = make_map_packed(&tk, k, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
-        if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tk, k, dtype, p.mem_dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tv, v, dtype, p.mem_dv, p.heads, p.seq_len)) != cudaSuccess) return e;
         auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_fwd_state, q, tk, tk, tv, st); };
         if ((e = launch()) != cudaSuccess) return e;
         tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, state, q.sch.ctas);
@@ -467,8 +468,8 @@ cudaError_t tc_fwd_out(const KParams& p, int dtype, const void* q_, const void* 
         q.out_a = o;
         CUtensorMap tq, to;
         cudaError_t e;
-        if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
-        if ((e = make_map_packed(&to, o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tq, q_, dtype, p.mem_dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&to, o, dtype, p.mem_dv, p.heads, p.seq_len)) != cudaSuccess) return e;
         FBLA_TC_VARLEN_DISPATCH(launch_fwd_out, q, tq, tq, to, st);
     }
     const bool dec = q_rope != nullptr && q_rope != q_;
@@ -500,9 +501,9 @@ cudaError_t tc_bwd_state(const KParams& p, int dtype, const void* q_, const void
         q.out_a = dq;
         q.out_b = dq;
         CUtensorMap tq, tdo, tdq;
-        if ((e = make_map_packed(&tq, q_, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
-        if ((e = make_map_packed(&tdo, d_o, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        if ((e = make_map_packed(&tdq, dq, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tq, q_, dtype, p.mem_dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdo, d_o, dtype, p.mem_dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdq, dq, dtype, p.mem_dk, p.heads, p.seq_len)) != cudaSuccess) return e;
         auto launch = [&]() -> cudaError_t { FBLA_TC_VARLEN_DISPATCH(launch_bwd_state, q, tq, tq, tdo, tdq, tdq, st); };
         if ((e = launch()) != cudaSuccess) return e;
         tc_reduce_varlen_kernel<<<q.sch.ctas, 256, 0, st>>>(q, dstate, q.sch.ctas);
@@ -542,10 +543,10 @@ cudaError_t tc_bwd_in(const KParams& p, int dtype, const void* k_rope, const voi
         q.out_b = dv;
         CUtensorMap tk, tv, tdk, tdv;
         cudaError_t e;
-        if ((e = make_map_packed(&tk, k_rope, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
-        if ((e = make_map_packed(&tv, v, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
-        if ((e = make_map_packed(&tdk, dk, dtype, p.dk, p.heads, p.seq_len)) != cudaSuccess) return e;
-        if ((e = make_map_packed(&tdv, dv, dtype, p.dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tk, k_rope, dtype, p.mem_dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tv, v, dtype, p.mem_dv, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdk, dk, dtype, p.mem_dk, p.heads, p.seq_len)) != cudaSuccess) return e;
+        if ((e = make_map_packed(&tdv, dv, dtype, p.mem_dv, p.heads, p.seq_len)) != cudaSuccess) return e;
         FBLA_TC_VARLEN_DISPATCH(launch_bwd_in, q, tk, tv, tdk, tdk, tdv, st);
     }
     const bool dec = dk_rope != nullptr;

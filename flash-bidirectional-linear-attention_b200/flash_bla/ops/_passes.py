@@ -189,11 +189,11 @@ def _sizes(prob):
 
 
 def narrow_route(prob):
-    """Whether the library serves this problem on its narrow route: 16-bit fixed-length linear_attn / simple_la
-    whose feature dims are multiples of 16 but not the tensor-core kernels' own 64 / 128 (the reference's layers
+    """Whether the library serves this problem on its narrow route: 16-bit linear_attn (fixed-length or packed) /
+    simple_la whose feature dims are multiples of 16 but not the tensor-core kernels' own 64 / 128 (the reference's layers
     use 32).  The 64- / 128-wide kernels then read and write the tensors at their own width through TMA boxes
     that zero-fill / clip the missing features.  ``FBLA_NARROW_DIMS=0`` switches the route off."""
-    if prob.dtype == _C.dtype_code(torch.float32) or prob.cu_seqlens is not None or (prob.flags & _C.FLAG_GENERIC):
+    if prob.dtype == _C.dtype_code(torch.float32) or (prob.flags & _C.FLAG_GENERIC):
         return False
     if os.environ.get("FBLA_NARROW_DIMS", "1") == "0":
         return False
@@ -201,6 +201,28 @@ def narrow_route(prob):
     if K % 16 or V % 16 or K > 128 or V > 128 or K < 16 or V < 16:
         return False
     return not (K in (64, 128) and V in (64, 128))
+
+
+_narrow_cache = {}
+
+
+def use_narrow(prob):
+    """Sets FLAG_NARROW on ``prob`` if the narrow route applies and the tensor-core kernels take the problem with it
+    (the packed layout has limits of its own: number of sequences, heads); returns whether it did."""
+    if not narrow_route(prob):
+        return False
+    key = (prob.dtype, prob.batch, prob.heads, prob.dk, prob.dv, prob.seq_len, prob.num_seqs, prob.normalize,
+           prob.cu_seqlens is not None)
+    ok = _narrow_cache.get(key)
+    prob.flags |= _C.FLAG_NARROW
+    if ok is None:
+        ok = kernel_path(prob) == 1
+        if len(_narrow_cache) > 256:
+            _narrow_cache.clear()
+        _narrow_cache[key] = ok
+    if not ok:
+        prob.flags &= ~_C.FLAG_NARROW
+    return ok
 
 
 def _aligned16(*tensors):
@@ -211,8 +233,7 @@ def _aligned16(*tensors):
 def forward(prob, q, k, v):
     """fwd_state + fwd_out of linear_attention / simple_la / varlen; returns (o, state)."""
     _require_cuda(q, k, v)
-    if narrow_route(prob):
-        prob.flags |= _C.FLAG_NARROW
+    if use_narrow(prob):
         q, k, v = _aligned16(q, k, v)
     # the unreduced route needs the tensor-core kernels, and those need 16-byte aligned tensors (a contiguous
     # view at an odd storage offset is served by the CUDA-core kernels, as the reference serves it)
@@ -233,8 +254,7 @@ def forward(prob, q, k, v):
 def backward(prob, q, k, v, d_o, state):
     """bwd_state + bwd_in; returns (dq, dk, dv).  ``state`` is what ``forward`` returned."""
     _require_cuda(q, k, v, d_o, state)
-    if narrow_route(prob):
-        prob.flags |= _C.FLAG_NARROW
+    if use_narrow(prob):
         q, k, v, d_o = _aligned16(q, k, v, d_o)
     if state.dtype == torch.uint8:
         prob.flags |= _C.FLAG_UNREDUCED

@@ -23,8 +23,8 @@ def _problem(q, v, scale, eps, norm_len=0):
     prob = P.make_problem(q, batch=B, heads=H, seq_len=L, dk=K, dv=v.shape[-1], normalize=True,
                           scale=scale, eps=eps, norm_len=norm_len, flags=P.default_flags())
     # head dims below the 64 x 64 tensor-core kernels of this operator (the reference layers use 32)
-    if K <= 64 and v.shape[-1] <= 64 and q.is_cuda and P.narrow_route(prob):
-        prob.flags |= _C.FLAG_NARROW
+    if K <= 64 and v.shape[-1] <= 64 and q.is_cuda:
+        P.use_narrow(prob)
     return prob
 
 

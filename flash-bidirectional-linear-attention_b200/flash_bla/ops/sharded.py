@@ -232,8 +232,7 @@ def _aligned(*tensors):
 def _narrow(prob, *tensors):
     """Head dims below the tensor-core tiles (multiples of 16 that are not 64 / 128): the passes' narrow route,
     which reads the tensors at their own width and wants them 16-byte aligned (CUDA tensors only)."""
-    if tensors[0].is_cuda and _passes.narrow_route(prob):
-        prob.flags |= _passes._C.FLAG_NARROW
+    if tensors[0].is_cuda and _passes.use_narrow(prob):
         return _aligned(*tensors)
     return tensors
 

@@ -58,7 +58,7 @@ enum fbla_status {
 enum fbla_flags {
     FBLA_FLAG_GENERIC = 1,     /* force the CUDA-core (fp32 FMA) kernels              */
     FBLA_FLAG_UNREDUCED = 2,   /* fbla_linear_attn_fwd / _bwd: see fbla_unreduced_state() */
-    FBLA_FLAG_NARROW = 4       /* 16-bit fixed-length linear_attn / simple_la (decoupled_la up to 64) with feature dims: multiples
+    FBLA_FLAG_NARROW = 4       /* 16-bit linear_attn (fixed or packed) / simple_la (decoupled_la up to 64), feature dims: multiples
                                 * of 16, at most 128 and not both 64 or 128 (the reference's layers use 32): served
                                 * by the 64- / 128-wide tensor-core kernels, whose TMA boxes zero-fill the missing
                                 * features on loads and clip them on stores, so the tensors are read and written

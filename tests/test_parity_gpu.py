@@ -137,6 +137,7 @@ def test_simple_la(shape, dtype):
 VARLEN_CASES = [
     ([8, 17, 32], 1, 8, 8), ([8, 17, 32], 8, 17, 13), ([8, 17, 32], 8, 64, 48), ([8, 17, 32], 1, 128, 128),
     ([300, 1, 129, 640], 4, 64, 64), ([1000, 24], 2, 128, 128),
+    ([300, 1, 129, 640], 4, 32, 32), ([700, 130], 3, 16, 96),      # 16-bit: head dims below the tensor-core tiles
 ]
 
 
