@@ -57,7 +57,9 @@ struct BwdStateCfg {
     static constexpr int kSmemBytes = kFixed + kStages * kStageBytes;
 };
 
-template <int DK, int DV, int MODE, bool BF16, bool VARLEN>
+// NARROW: the rows of dq in memory may hold fewer than DK features (Params::mem_dk); otherwise the row width is
+// the compile-time DK, which keeps the guard and the address arithmetic out of the issue-bound epilogue.
+template <int DK, int DV, int MODE, bool BF16, bool VARLEN, bool NARROW = false>
 __global__ void __launch_bounds__(kBwdStateThreads, 1)
 tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_q,
                     const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
@@ -98,6 +100,7 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
         pv.plan = plan;
     }
     const Params& p = pv;
+    const int mem_dk = NARROW ? p.mem_dk : DK;      // features per row of dq in memory
     int g0, g1;
     Map::range(p, g0, g1);
     const ptx::Abort ab{cta_abort, p.status};
@@ -348,8 +351,8 @@ tc_bwd_state_kernel(const __grid_constant__ CUtensorMap tm_qr, const __grid_cons
                     if (!staged) {
                         keep1[j] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
                         if (MODE == kDecoupled) keep2[j] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
-                        if ((j & 1) && tok_ok && c - 8 < p.mem_dk) {      // two 16-byte chunks = one 32-byte sector per store
-                            const size_t at = (grow * p.mem_dk + c - 8) * 2;      // (rows may be narrower than DK)
+                        if ((j & 1) && tok_ok && c - 8 < mem_dk) {      // two 16-byte chunks = one 32-byte sector per store
+                            const size_t at = (grow * mem_dk + c - 8) * 2;
                             ptx::st_global_32B(static_cast<uint8_t*>(p.out_a) + at, keep1[j - 1], keep1[j]);
                             if (MODE == kDecoupled)
                                 ptx::st_global_32B(static_cast<uint8_t*>(p.out_b) + at, keep2[j - 1], keep2[j]);

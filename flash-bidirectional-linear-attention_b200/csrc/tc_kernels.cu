@@ -275,13 +275,16 @@ cudaError_t launch_bwd_state(const Params& q, const CUtensorMap& tqr, const CUte
     using Cfg = BwdStateCfg<DK, DV, MODE, VARLEN>;
     static_assert(Cfg::kSmemBytes <= kSmemLimit, "shared memory budget");
     static_assert(Cfg::kStages >= 2, "pipeline depth");
-    auto kernel = tc_bwd_state_kernel<DK, DV, MODE, BF16, VARLEN>;
-    static bool smem_set[64] = {false};
-    cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
-    if (e != cudaSuccess) return e;
-    e = launch_dependent(kernel, q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st, tqr, tq, tdo, tdq, tdqr, q);
-    note_launches(1);
-    return e != cudaSuccess ? e : cudaGetLastError();
+    auto go = [&](auto kernel, bool (&smem_set)[64]) -> cudaError_t {
+        cudaError_t e = set_smem(kernel, Cfg::kSmemBytes, smem_set);
+        if (e != cudaSuccess) return e;
+        e = launch_dependent(kernel, q.sch.ctas, kBwdStateThreads, Cfg::kSmemBytes, st, tqr, tq, tdo, tdq, tdqr, q);
+        note_launches(1);
+        return e != cudaSuccess ? e : cudaGetLastError();
+    };
+    static bool set_wide[64] = {false}, set_narrow[64] = {false};
+    if (q.mem_dk != DK) return go(tc_bwd_state_kernel<DK, DV, MODE, BF16, VARLEN, true>, set_narrow);
+    return go(tc_bwd_state_kernel<DK, DV, MODE, BF16, VARLEN, false>, set_wide);
 }
 
 template <int DK, int DV, int MODE, bool BF16, bool VARLEN = false>
