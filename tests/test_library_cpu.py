@@ -56,6 +56,31 @@ def test_sizes_and_validation_without_a_device():
     assert rc == 1
 
 
+def test_narrow_route_sizes_and_refusals_without_a_device():
+    """FBLA_FLAG_NARROW: the library answers with the sizes of the widened problem and refuses what the route does
+    not serve; the Python mirror asks for it exactly for 16-bit head dims that are multiples of 16 but not 64 / 128."""
+    lib = _C.lib()
+    like = torch.empty(0, dtype=torch.bfloat16)
+    p = P.make_problem(like, batch=2, heads=3, seq_len=1000, dk=32, dv=48, normalize=True, flags=_C.FLAG_NARROW)
+    assert lib.fbla_state_floats(ctypes.byref(p)) == 2 * 3 * (64 * 64 + 64)
+    p = P.make_problem(like, batch=2, heads=3, seq_len=1000, dk=96, dv=32, normalize=False, flags=_C.FLAG_NARROW)
+    assert lib.fbla_state_floats(ctypes.byref(p)) == 2 * 3 * 128 * 64
+    for kw, dtype in ((dict(dk=64, dv=128), torch.bfloat16),          # already the kernels' own widths
+                      (dict(dk=24, dv=32), torch.bfloat16),           # rows of 48 bytes: not a multiple of 16 features
+                      (dict(dk=32, dv=32), torch.float32)):           # fp32 runs on the CUDA cores
+        bad = P.make_problem(torch.empty(0, dtype=dtype), batch=1, heads=1, seq_len=64, normalize=True,
+                             flags=_C.FLAG_NARROW, **kw)
+        assert lib.fbla_state_floats(ctypes.byref(bad)) == -1 and b"FBLA_FLAG_NARROW" in lib.fbla_last_error()
+    # the mirror's own decision (pure host logic)
+    def route(dtype, dk, dv, **kw):
+        return P.narrow_route(P.make_problem(torch.empty(0, dtype=dtype), batch=1, heads=2, seq_len=300, dk=dk, dv=dv,
+                                             normalize=True, **kw))
+    assert route(torch.bfloat16, 32, 32) and route(torch.float16, 16, 112) and route(torch.bfloat16, 64, 48)
+    assert not route(torch.bfloat16, 64, 64) and not route(torch.bfloat16, 128, 64)
+    assert not route(torch.bfloat16, 24, 32) and not route(torch.float32, 32, 32) and not route(torch.bfloat16, 8, 8)
+    assert not route(torch.bfloat16, 32, 32, flags=_C.FLAG_GENERIC)
+
+
 def test_operators_refuse_cpu_tensors():
     from flash_bla.ops.linear_attn.fused import linear_attention
     from flash_bla.ops.simple_la.fused import simple_la
