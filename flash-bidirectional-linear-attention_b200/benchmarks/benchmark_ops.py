@@ -4,7 +4,7 @@
 other operators.  Timing: CUDA events around back-to-back calls of the public API, median of
 ``--reps`` repetitions after warm-up; inputs are larger than L2 from T=4096 up at B=8.
 
-    python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|fp32|blhd|simple_la|decoupled_la|varlen|pisa|all]
+    python benchmarks/benchmark_ops.py [--batch 8] [--op linear_attn|layers|fp32|blhd|simple_la|decoupled_la|varlen|pisa|all]
                                        [--long] [--impl b200|reference [--ref-path DIR]]
 
 ``--long`` adds ``simple_la`` at B4 H32 T262144 D128 (8.6 GB per tensor, about 70 GB on the device).
@@ -125,6 +125,17 @@ def main():
                 tg = timed(replay, args.reps)
                 print(f"{'':14s} {'  replayed from a CUDA graph':28s} {'':33s}   fwd+bwd {tg:8.4f} ms "
                       f"({11 * P / tg / 1e6:6.0f} GB/s, {B * T / tg * 1e3:.3e} tokens/s)", flush=True)
+    if args.op in ("all", "layers"):
+        # the reference layers' head dim (32), at their sizes (14 x 14 and 56 x 56 tokens) and at streaming size
+        for (b, h, T, d) in ((32, 4, 196, 32), (8, 8, 3136, 32), (B, H, 32768, 32)):
+            q, k, v = pos(b, h, T, d), pos(b, h, T, d), gau(b, h, T, d)
+            do = torch.randn_like(v)
+            P = b * h * T * d * 2
+            f, fb = both(lambda: linear_attention(q, k, v), (q, k, v), do)
+            row("linear_attn", f"B{b} H{h} T{T} D{d}", f, fb, b * T, 4 * P, 11 * P)
+            qr, kr = gau(b, h, T, d), gau(b, h, T, d)
+            f, fb = both(lambda: decoupled_la(q, k, qr, kr, v), (q, k, qr, kr, v), do)
+            row("decoupled_la", f"B{b} H{h} T{T} D{d}", f, fb, b * T, 6 * P, 16 * P)
     if args.op in ("all", "fp32"):
         # fp32 inputs (the 1e-5 parity case): B2 H4 T1024 D64 as the reference's CPU-runnable configuration, and a
         # streaming-size case
