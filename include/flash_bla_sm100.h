@@ -262,8 +262,12 @@ int fbla_pisa_fwd_ws(const fbla_pisa_problem *p, const void *q, const void *k, c
  * block statistics as well.  The reference has no backward for this operator (no counterpart).
  * o, d_o: forward output and its gradient; row_stats: as written by fbla_pisa_fwd.
  * scratch: fp32, 256-byte aligned, at least fbla_pisa_bwd_scratch_floats() elements (holds the
- * gradients of the block statistics, the per-row terms and, on the tensor-core path, the rows
- * from which the gradient of h is formed); contents are undefined afterwards.                */
+ * gradients of the block statistics, the per-row terms and, on the tensor-core paths, the rows
+ * from which the gradient of h is formed, the workspace of that state pass and 16-bit copies of
+ * kc, vc, h and dh for the tcgen05 kernels); contents are undefined afterwards.
+ * 16-bit inputs with block_size 64 and dk = dv in {64, 128} run on tcgen05 kernels (query side,
+ * key side), other shapes on CUDA-core kernels; FBLA_PISA_TC=0 in the environment selects the
+ * mma.sync kernels that served those shapes before.                                           */
 int64_t fbla_pisa_bwd_scratch_floats(const fbla_pisa_problem *p);
 int fbla_pisa_bwd(const fbla_pisa_problem *p, const void *q, const void *k, const void *v,
                   const void *o, const void *d_o, const float *kc, const float *vc, const float *h,
