@@ -891,7 +891,8 @@ __global__ void __launch_bounds__(128)
 pisa_stats_terms_kernel(int D, int nt, int T, const float* __restrict__ kc, const float* __restrict__ vc,
                         const float* __restrict__ dh, float* __restrict__ dkc, float* __restrict__ dvc,
                         uint32_t* __restrict__ dh16) {
-    __shared__ uint16_t dhs[128 * 130];         // rows padded by two elements: a column walk touches every bank
+    __shared__ __align__(16) uint16_t dhs[128 * 130];   // rows padded by two elements: a column walk touches every bank
+                                                        // (read and written as 32-bit pairs)
     __shared__ float kcs[128], vcs[128];
     const int bh = blockIdx.y, t = threadIdx.x;
     const int stride = D + 2;
