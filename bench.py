@@ -361,6 +361,45 @@ def run_cfg3(world, rank, dev, barrier, peak):
     return out
 
 
+def run_cfg4(world, rank, dev, barrier, peak):
+    """varlen_linear_attention bf16 H16-D64 on 32 packed sequences of 256..16384 tokens (seeded lengths): whole
+    sequences are dealt to the ranks (longest first onto the lightest rank), each rank packs its own and runs the
+    operator on them; no communication."""
+    from flash_bla.ops.linear_attn.varlen import varlen_linear_attention
+    from flash_bla.ops.sharded import partition_sequences
+    heads, d = 16, 64
+    lengths = torch.randint(256, 16385, (32,), generator=torch.Generator().manual_seed(0)).tolist()
+    mine = [lengths[i] for i in partition_sequences(lengths, world)[rank]]
+    if not mine:
+        return {"skipped": f"32 sequences do not cover {world} ranks"}
+    tot, mx = sum(mine), max(mine)
+    cu = torch.tensor([0] + list(torch.tensor(mine).cumsum(0)), dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(4000 + rank)
+    q = (F.elu(torch.randn(tot, heads, d, device=dev, generator=g)) + 1).bfloat16().requires_grad_()
+    k = (F.elu(torch.randn(tot, heads, d, device=dev, generator=g)) + 1).bfloat16().requires_grad_()
+    v = torch.randn(tot, heads, d, device=dev, generator=g).bfloat16().requires_grad_()
+    do = torch.randn(tot, heads, d, device=dev, generator=g).bfloat16()
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        varlen_linear_attention(q, k, v, cu, mx).backward(do)
+
+    for _ in range(3):
+        step()
+    blocks = timed_blocks(lambda: step(), 10, barrier, world, dev, min_blocks=5, min_total_s=0.1, max_blocks=40)
+    ms = statistics.median(blocks) / 10
+    nbytes = 11 * tot * heads * d * 2                      # this rank's share (the slowest rank sets the time)
+    out = {"workload": f"varlen_linear_attention fwd+bwd bf16 H{heads}-D{d}, 32 packed sequences of 256..16384 tokens "
+                       f"({sum(lengths)} in all), {len(mine)} sequences / {tot} tokens on rank 0"
+                       + (", whole sequences dealt to the ranks, no communication" if world > 1 else ""),
+           "scaling": "strong", "ms_per_step": ms, "value": sum(lengths) / (ms * 1e-3), "unit": UNIT,
+           "algo_gbs_rank0": nbytes / (ms * 1e-3) / 1e9, "frac_of_peak_rank0": nbytes / (ms * 1e-3) / 1e9 / peak,
+           "blocks": {"n": len(blocks), "steps_each": 10, "min_ms": min(blocks) / 10, "max_ms": max(blocks) / 10}}
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_cfg5(world, rank, dev, barrier):
     """piecewise_sparse_attention bf16 B2-H24-T4608-D128, block 64, density 0.1: the 48 (batch, head) pairs are
     independent, each rank takes its share (no communication); forward + backward of the whole operator
@@ -590,6 +629,7 @@ def run_ours(args):
 
     peak_now = peak
     cfg3 = None if args.no_cfg3 else run_cfg3(world, rank, dev, barrier, peak_now)
+    cfg4 = None if args.no_cfg4 else run_cfg4(world, rank, dev, barrier, peak_now)
     cfg5 = None if args.no_cfg5 else run_cfg5(world, rank, dev, barrier)
 
     cpu = None
@@ -616,6 +656,8 @@ def run_ours(args):
             line["parity"] = parity
         if cfg3 is not None:
             line["cfg3"] = cfg3
+        if cfg4 is not None:
+            line["cfg4"] = cfg4
         if cfg5 is not None:
             line["cfg5"] = cfg5
         if triton is not None:
@@ -634,6 +676,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the simple_la T=262144 block")
+    ap.add_argument("--no-cfg4", action="store_true", help="skip the packed variable-length block")
     ap.add_argument("--no-cfg5", action="store_true", help="skip the piecewise_sparse_attention block")
     ap.add_argument("--no-triton", action="store_true", help="skip the run of the reference's Triton kernels")
     args = ap.parse_args()
